@@ -1,0 +1,115 @@
+// Fused softmax + cross-entropy + in-place dlogits over the padded vocabulary, plus the
+// generic row softmax used by sampling.
+//
+// Reference behaviour: llmm/fused_classifier.mojo:186-279, :311-370 (per row: max, sum exp,
+// loss, dlogits = (p - 1[y])·dloss written over the logits, padded tail [V, Vp) zeroed);
+// llmm/softmax.mojo:172-304.  B200 design: one CTA per row; the whole row (Vp·2 B ≈ 100 KB
+// for GPT-2) is staged once in shared memory so HBM sees exactly one read and one write.
+#include "common.cuh"
+using namespace llmb;
+
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(1024) classifier_kernel(T* __restrict__ logits, float* __restrict__ losses,
+                                                         const int* __restrict__ targets, float dloss, int V, int Vp,
+                                                         int write_dlogits) {
+  constexpr int N = Pack<T>::N;
+  extern __shared__ __align__(16) unsigned char smraw[];
+  T* row_s = reinterpret_cast<T*>(smraw);
+  __shared__ float red[32];
+  __shared__ float bcast[2];
+  const int row = blockIdx.x;
+  T* g = logits + (size_t)row * Vp;
+  const int nvec = Vp / N;
+  const int tid = threadIdx.x, lane = tid % 32, wid = tid / 32, nw = blockDim.x / 32;
+  float mx = -INFINITY;
+  for (int v = tid; v < nvec; v += blockDim.x) {
+    uint4 raw = *reinterpret_cast<const uint4*>(g + v * N);
+    *reinterpret_cast<uint4*>(row_s + v * N) = raw;
+    Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) if (v * N + k < V) mx = fmaxf(mx, p.v[k]);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[wid] = mx;
+  __syncthreads();
+  if (wid == 0) { float m = lane < nw ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bcast[0] = m; }
+  __syncthreads();
+  mx = bcast[0];
+  const float L2E = 1.4426950408889634f;
+  float sum = 0.f;
+  for (int v = tid; v < nvec; v += blockDim.x) {
+    Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) if (v * N + k < V) sum += exp2f((p.v[k] - mx) * L2E);
+  }
+  sum = warp_sum(sum);
+  __syncthreads();
+  if (lane == 0) red[wid] = sum;
+  __syncthreads();
+  if (wid == 0) { float s = lane < nw ? red[lane] : 0.f; s = warp_sum(s); if (lane == 0) bcast[1] = s; }
+  __syncthreads();
+  sum = bcast[1];
+  const int tgt = targets[row];
+  if (tid == 0 && losses) {
+    float lt = to_f<T>(row_s[tgt]);
+    losses[row] = -(lt - mx - logf(sum));
+  }
+  if (!write_dlogits) return;
+  const float inv = 1.0f / sum;
+  for (int v = tid; v < nvec; v += blockDim.x) {
+    Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      int i = v * N + k;
+      float prob = exp2f((p.v[k] - mx) * L2E) * inv;
+      p.v[k] = i < V ? (prob - (i == tgt ? 1.f : 0.f)) * dloss : 0.f;
+    }
+    p.store(g + v * N);
+  }
+}
+
+template <typename T>
+__global__ void softmax_rows_kernel(float* __restrict__ out, const T* __restrict__ inp, int V, int ld, float inv_temp) {
+  __shared__ float red[32];
+  __shared__ float bc;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid % 32, wid = tid / 32, nw = blockDim.x / 32;
+  const T* g = inp + (size_t)row * ld;
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, to_f<T>(g[i]) * inv_temp);
+  mx = warp_max(mx); if (lane == 0) red[wid] = mx; __syncthreads();
+  if (wid == 0) { float m = lane < nw ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bc = m; } __syncthreads();
+  mx = bc; float s = 0.f;
+  for (int i = tid; i < V; i += blockDim.x) s += expf(to_f<T>(g[i]) * inv_temp - mx);
+  s = warp_sum(s); __syncthreads(); if (lane == 0) red[wid] = s; __syncthreads();
+  if (wid == 0) { float t = lane < nw ? red[lane] : 0.f; t = warp_sum(t); if (lane == 0) bc = t; } __syncthreads();
+  float inv = 1.f / bc;
+  for (int i = tid; i < V; i += blockDim.x) out[(size_t)row * V + i] = expf(to_f<T>(g[i]) * inv_temp - mx) * inv;
+}
+}  // namespace
+
+// logits [rows, Vp] are overwritten with dlogits when write_dlogits != 0.
+LLMB_API int llmb_fused_classifier(void* logits, float* losses, const int* targets, float dloss, int rows, int V,
+                                   int Vp, int write_dlogits, int dtype, cudaStream_t st) {
+  if (dtype == LLMB_BF16) {
+    if (Vp % 8) return LLMB_ERR_BAD_ARG;
+    size_t smem = (size_t)Vp * 2;
+    if (smem > 200 * 1024) return LLMB_ERR_BAD_ARG;
+    cudaFuncSetAttribute(classifier_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    classifier_kernel<__nv_bfloat16><<<rows, 1024, smem, st>>>((__nv_bfloat16*)logits, losses, targets, dloss, V, Vp, write_dlogits);
+  } else {
+    if (Vp % 4) return LLMB_ERR_BAD_ARG;
+    size_t smem = (size_t)Vp * 4;
+    if (smem > 220 * 1024) return LLMB_ERR_BAD_ARG;
+    cudaFuncSetAttribute(classifier_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    classifier_kernel<float><<<rows, 1024, smem, st>>>((float*)logits, losses, targets, dloss, V, Vp, write_dlogits);
+  }
+  return (int)cudaGetLastError();
+}
+
+LLMB_API int llmb_softmax_rows(float* out, const void* inp, int rows, int V, int ld, float inv_temp, int dtype,
+                               cudaStream_t st) {
+  if (dtype == LLMB_BF16) softmax_rows_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(out, (const __nv_bfloat16*)inp, V, ld, inv_temp);
+  else softmax_rows_kernel<float><<<rows, 256, 0, st>>>(out, (const float*)inp, V, ld, inv_temp);
+  return (int)cudaGetLastError();
+}

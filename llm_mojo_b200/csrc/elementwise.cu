@@ -1,0 +1,250 @@
+// Encoder (wte + wpe) forward / deterministic backward, tanh-GELU forward/backward,
+// bias-gradient column reduction, and small utility kernels.
+//
+// Reference behaviour: llmm/encoder.mojo:131-281 (fwd), :459-536 / :775-1029 (deterministic
+// bucketed dwte and dwpe), llmm/gelu.mojo:82-430, llmm/matmul.mojo:2353-2539 (dbias).
+// B200 design: all accesses are 16-byte vectors; dwte is made deterministic by a device-side
+// radix sort of (token, position) keys followed by one block per token run, instead of the
+// reference's host-side counting sort.
+#include "common.cuh"
+#include <cub/device/device_radix_sort.cuh>
+
+using namespace llmb;
+
+// ---------------------------------------------------------------- encoder forward
+template <typename T>
+__global__ void encoder_fwd_kernel(T* __restrict__ out, const int* __restrict__ tok, const T* __restrict__ wte,
+                                   const T* __restrict__ wpe, int BT, int Tlen, int C) {
+  constexpr int N = Pack<T>::N;
+  const int vec_per_row = C / N;
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = (long long)BT * vec_per_row;
+  if (idx >= total) return;
+  int row = (int)(idx / vec_per_row), c = (int)(idx % vec_per_row) * N;
+  int t = row % Tlen;
+  int id = tok[row];
+  Pack<T> a, b;
+  a.load(wte + (size_t)id * C + c);
+  b.load(wpe + (size_t)t * C + c);
+#pragma unroll
+  for (int i = 0; i < N; ++i) a.v[i] += b.v[i];
+  a.store(out + (size_t)row * C + c);
+}
+
+LLMB_API int llmb_encoder_fwd(void* out, const int* tok, const void* wte, const void* wpe, int B, int T, int C,
+                              int dtype, cudaStream_t st) {
+  int BT = B * T;
+  if (dtype == LLMB_BF16) {
+    if (C % 8) return LLMB_ERR_BAD_ARG;
+    long long total = (long long)BT * (C / 8);
+    encoder_fwd_kernel<__nv_bfloat16><<<(unsigned)ceil_div_ll(total, 256), 256, 0, st>>>(
+        (__nv_bfloat16*)out, tok, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, BT, T, C);
+  } else {
+    if (C % 4) return LLMB_ERR_BAD_ARG;
+    long long total = (long long)BT * (C / 4);
+    encoder_fwd_kernel<float><<<(unsigned)ceil_div_ll(total, 256), 256, 0, st>>>(
+        (float*)out, tok, (const float*)wte, (const float*)wpe, BT, T, C);
+  }
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- encoder backward
+__global__ void make_keys_kernel(unsigned long long* keys, const int* tok, int BT) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < BT) keys[i] = ((unsigned long long)(unsigned)tok[i] << 32) | (unsigned)i;
+}
+
+// One block per sorted index; only the block sitting on the first key of a token run works.
+// Threads are (position lane, channel vector); lanes stride the run, then a fixed-order
+// shared-memory reduction over lanes keeps the sum order independent of scheduling.
+template <typename T, int LANES>
+__global__ void wte_bwd_kernel(float* __restrict__ dwte, const T* __restrict__ dout,
+                               const unsigned long long* __restrict__ keys, int BT, int C) {
+  constexpr int N = Pack<T>::N;
+  int i = blockIdx.x;
+  unsigned tokv = (unsigned)(keys[i] >> 32);
+  if (i > 0 && (unsigned)(keys[i - 1] >> 32) == tokv) return;
+  extern __shared__ float sm[];  // [LANES][C]
+  const int vec_per_row = C / N;
+  const int nvec_threads = blockDim.x / LANES;
+  int lane = threadIdx.x / nvec_threads, vt = threadIdx.x % nvec_threads;
+  for (int vc = vt; vc < vec_per_row; vc += nvec_threads) {
+    float acc[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k) acc[k] = 0.f;
+    for (int j = i + lane; j < BT; j += LANES) {
+      unsigned long long key = keys[j];
+      if ((unsigned)(key >> 32) != tokv) break;
+      int pos = (int)(key & 0xffffffffu);
+      Pack<T> p; p.load(dout + (size_t)pos * C + vc * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] += p.v[k];
+    }
+#pragma unroll
+    for (int k = 0; k < N; ++k) sm[lane * C + vc * N + k] = acc[k];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int l = 0; l < LANES; ++l) s += sm[l * C + c];
+    dwte[(size_t)tokv * C + c] += s;
+  }
+}
+
+template <typename T>
+__global__ void wpe_bwd_kernel(float* __restrict__ dwpe, const T* __restrict__ dout, int B, int Tlen, int C) {
+  constexpr int N = Pack<T>::N;
+  const int vec_per_row = C / N;
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= Tlen * vec_per_row) return;
+  int t = idx / vec_per_row, c = (idx % vec_per_row) * N;
+  float acc[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) acc[k] = 0.f;
+  for (int b = 0; b < B; ++b) {
+    Pack<T> p; p.load(dout + ((size_t)b * Tlen + t) * C + c);
+#pragma unroll
+    for (int k = 0; k < N; ++k) acc[k] += p.v[k];
+  }
+#pragma unroll
+  for (int k = 0; k < N; ++k) dwpe[(size_t)t * C + c + k] += acc[k];
+}
+
+// Scratch layout: keys_in[BT] u64 | keys_out[BT] u64 | cub temp. Query the size first.
+LLMB_API long long llmb_encoder_bwd_scratch_bytes(int BT) {
+  size_t temp = 0;
+  cub::DeviceRadixSort::SortKeys(nullptr, temp, (unsigned long long*)nullptr, (unsigned long long*)nullptr, BT);
+  return (long long)(2 * (size_t)BT * sizeof(unsigned long long) + ((temp + 255) / 256) * 256 + 256);
+}
+
+LLMB_API int llmb_encoder_bwd(float* dwte, float* dwpe, const void* dout, const int* tok, void* scratch,
+                              long long scratch_bytes, int B, int T, int C, int vocab_bits, int dtype,
+                              cudaStream_t st) {
+  int BT = B * T;
+  if (scratch_bytes < llmb_encoder_bwd_scratch_bytes(BT)) return LLMB_ERR_BAD_ARG;
+  unsigned long long* kin = (unsigned long long*)scratch;
+  unsigned long long* kout = kin + BT;
+  void* temp = (void*)(kout + BT);
+  size_t temp_bytes = (size_t)scratch_bytes - 2 * (size_t)BT * sizeof(unsigned long long);
+  make_keys_kernel<<<ceil_div(BT, 256), 256, 0, st>>>(kin, tok, BT);
+  int pos_bits = 1; while ((1ll << pos_bits) < BT) ++pos_bits;
+  // position bits live in [0, 32); token bits in [32, 32 + vocab_bits). Sort only the used bits.
+  cudaError_t e = cub::DeviceRadixSort::SortKeys(temp, temp_bytes, kin, kout, BT, 0, 32 + vocab_bits, st);
+  if (e != cudaSuccess) return (int)e;
+  (void)pos_bits;
+  constexpr int LANES = 4;
+  size_t smem = (size_t)LANES * C * sizeof(float);
+  if (dtype == LLMB_BF16) {
+    wte_bwd_kernel<__nv_bfloat16, LANES><<<BT, 256, smem, st>>>(dwte, (const __nv_bfloat16*)dout, kout, BT, C);
+    wpe_bwd_kernel<__nv_bfloat16><<<ceil_div(T * (C / 8), 256), 256, 0, st>>>(dwpe, (const __nv_bfloat16*)dout, B, T, C);
+  } else {
+    wte_bwd_kernel<float, LANES><<<BT, 256, smem, st>>>(dwte, (const float*)dout, kout, BT, C);
+    wpe_bwd_kernel<float><<<ceil_div(T * (C / 4), 256), 256, 0, st>>>(dwpe, (const float*)dout, B, T, C);
+  }
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- GELU
+template <typename T>
+__global__ void gelu_fwd_kernel(T* __restrict__ out, const T* __restrict__ inp, long long nvec) {
+  constexpr int N = Pack<T>::N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    Pack<T> p; p.load(inp + i * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) p.v[k] = gelu_f(p.v[k]);
+    p.store(out + i * N);
+  }
+}
+template <typename T>
+__global__ void gelu_bwd_kernel(T* __restrict__ dinp, const T* __restrict__ inp, const T* __restrict__ dout, long long nvec) {
+  constexpr int N = Pack<T>::N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    Pack<T> x, d; x.load(inp + i * N); d.load(dout + i * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) d.v[k] *= gelu_grad_f(x.v[k]);
+    d.store(dinp + i * N);
+  }
+}
+LLMB_API int llmb_gelu_fwd(void* out, const void* inp, long long n, int dtype, cudaStream_t st) {
+  int grid = sm_count() * 8;
+  if (dtype == LLMB_BF16) { if (n % 8) return LLMB_ERR_BAD_ARG; gelu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)inp, n / 8); }
+  else { if (n % 4) return LLMB_ERR_BAD_ARG; gelu_fwd_kernel<float><<<grid, 256, 0, st>>>((float*)out, (const float*)inp, n / 4); }
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_gelu_bwd(void* dinp, const void* inp, const void* dout, long long n, int dtype, cudaStream_t st) {
+  int grid = sm_count() * 8;
+  if (dtype == LLMB_BF16) { if (n % 8) return LLMB_ERR_BAD_ARG; gelu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)dinp, (const __nv_bfloat16*)inp, (const __nv_bfloat16*)dout, n / 8); }
+  else { if (n % 4) return LLMB_ERR_BAD_ARG; gelu_bwd_kernel<float><<<grid, 256, 0, st>>>((float*)dinp, (const float*)inp, (const float*)dout, n / 4); }
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- dbias: dbias[c] += sum_rows dout[row, c]
+// Stage 1: grid (col blocks, row slabs); each block owns 32*N columns... threads (8 row lanes x 32 col vecs).
+// partial[slab][c] written to scratch; stage 2 sums slabs in order (deterministic) and accumulates.
+template <typename T>
+__global__ void dbias_partial_kernel(float* __restrict__ partial, const T* __restrict__ dout, int rows, int OC, int rows_per_slab) {
+  constexpr int N = Pack<T>::N;
+  __shared__ float sm[8][32 * N + 1];
+  int cv = threadIdx.x % 32, rl = threadIdx.x / 32;  // 256 threads: 8 row lanes
+  int c0 = (blockIdx.x * 32 + cv) * N;
+  int r0 = blockIdx.y * rows_per_slab, r1 = min(rows, r0 + rows_per_slab);
+  float acc[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) acc[k] = 0.f;
+  if (c0 < OC) {
+    for (int r = r0 + rl; r < r1; r += 8) {
+      Pack<T> p; p.load(dout + (size_t)r * OC + c0);
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] += p.v[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < N; ++k) sm[rl][cv * N + k] = acc[k];
+  __syncthreads();
+  for (int c = threadIdx.x; c < 32 * N; c += blockDim.x) {
+    int col = blockIdx.x * 32 * N + c;
+    if (col < OC) {
+      float s = 0.f;
+#pragma unroll
+      for (int l = 0; l < 8; ++l) s += sm[l][c];
+      partial[(size_t)blockIdx.y * OC + col] = s;
+    }
+  }
+}
+__global__ void dbias_final_kernel(float* __restrict__ dbias, const float* __restrict__ partial, int OC, int slabs) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= OC) return;
+  float s = 0.f;
+  for (int i = 0; i < slabs; ++i) s += partial[(size_t)i * OC + c];
+  dbias[c] += s;
+}
+LLMB_API int llmb_dbias_slabs(int rows) { int s = ceil_div(rows, 512); return s > 128 ? 128 : (s < 1 ? 1 : s); }
+LLMB_API long long llmb_dbias_scratch_bytes(int rows, int OC) { return (long long)llmb_dbias_slabs(rows) * OC * sizeof(float); }
+LLMB_API int llmb_dbias(float* dbias, const void* dout, float* scratch, long long scratch_bytes, int rows, int OC,
+                        int dtype, cudaStream_t st) {
+  int slabs = llmb_dbias_slabs(rows);
+  if (scratch_bytes < (long long)slabs * OC * (long long)sizeof(float)) return LLMB_ERR_BAD_ARG;  // regression guard: never overrun
+  int rows_per_slab = ceil_div(rows, slabs);
+  if (dtype == LLMB_BF16) {
+    if (OC % 8) return LLMB_ERR_BAD_ARG;
+    dim3 grid(ceil_div(OC, 32 * 8), slabs);
+    dbias_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(scratch, (const __nv_bfloat16*)dout, rows, OC, rows_per_slab);
+  } else {
+    if (OC % 4) return LLMB_ERR_BAD_ARG;
+    dim3 grid(ceil_div(OC, 32 * 4), slabs);
+    dbias_partial_kernel<float><<<grid, 256, 0, st>>>(scratch, (const float*)dout, rows, OC, rows_per_slab);
+  }
+  dbias_final_kernel<<<ceil_div(OC, 256), 256, 0, st>>>(dbias, scratch, OC, slabs);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- casts
+__global__ void cast_f32_to_bf16_kernel(__nv_bfloat16* out, const float* in, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(in[i]);
+}
+LLMB_API int llmb_cast_f32_to_bf16(void* out, const float* in, long long n, cudaStream_t st) {
+  cast_f32_to_bf16_kernel<<<sm_count() * 8, 256, 0, st>>>((__nv_bfloat16*)out, in, n);
+  return (int)cudaGetLastError();
+}

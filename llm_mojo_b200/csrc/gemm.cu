@@ -1,0 +1,326 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:  D[M,N] = epilogue(A[M,K] · B[N,K]^T).
+//
+// Covers every linear-layer GEMM of the trainer (reference call sites: llmm/matmul.mojo:463-696
+// forward + bias / bias+GELU epilogues, :2789-2938 dinp with the dGELU epilogue, :3231-3509 dW
+// with beta=1 accumulate, :3671-3908 LM head; all of them cuBLASLt calls in the reference).
+//
+// Design (one CTA per SM, 192 threads):
+//   warp 0   TMA producer: streams 128x(128 B) A tiles and 256x(128 B) B tiles through a
+//            4-stage shared-memory ring (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 1   MMA issuer: one elected lane issues tcgen05.mma 128x256xK_mma into one of two
+//            256-column TMEM accumulators and commits stage / accumulator mbarriers
+//   warps 2-5 epilogue: tcgen05.ld the finished accumulator (each warp its own 32-lane TMEM
+//            quarter), apply bias / GELU / dGELU / fp32 accumulate, store 16-byte vectors
+// so the epilogue of tile i overlaps the main loop of tile i+1.  Operands may be K-major or
+// MN-major (the UMMA descriptor and the TMA box change, not the data), which is how dinp
+// (B = W as stored) and dW (A = dout^T, B = inp^T as stored) run without any transposes.
+// Split-K work units reduce through fp32 red.global.add into the (fp32) gradient buffer.
+#include "tc05.cuh"
+using namespace llmb;
+using namespace tc05;
+
+namespace {
+constexpr int BM = 128, BN = 256;
+constexpr int STAGES = 4;
+constexpr int ROW_BYTES = 128;                       // one swizzled row
+constexpr int A_STAGE = BM * ROW_BYTES;              // 16 KB
+constexpr int B_STAGE = BN * ROW_BYTES;              // 32 KB
+constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int BAND = 16;                             // m-tiles per rasterisation band
+
+enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_DGELU = 3, EPI_ACC_F32 = 4, EPI_BIAS_RESID = 5, EPI_STORE_F32 = 6 };
+
+struct GemmParams {
+  void* D; const void* bias; void* aux; const float* alpha;
+  int M, N, K;                 // K in elements
+  long long ldd, ldaux;
+  int a_mn, b_mn;              // operand majorness (0 = K-major)
+  uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // bytes
+  uint32_t idesc;
+  int bke;                     // K elements per stage
+  int mma_per_stage;
+  int m_tiles, n_tiles, splits, kb_per_split, kb_total;
+  int* status;
+};
+
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;      // [2] accumulator ready
+  uint64_t* tempty_bar = tfull_bar + 2;          // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tmem_alloc<512>(tmem_slot);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_split = p.m_tiles * p.n_tiles;
+  const int total_units = tiles_per_split * p.splits;
+
+  auto unit_coords = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+    int split = unit / tiles_per_split, t = unit % tiles_per_split;
+    int band_sz = BAND * p.n_tiles;
+    int b = t / band_sz, r = t % band_sz;
+    int m_in_band = min(BAND, p.m_tiles - b * BAND);
+    m_blk = b * BAND + r % m_in_band;
+    n_blk = r / m_in_band;
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x) {
+        int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+          unsigned char* sa = smem + stage * STAGE_BYTES;
+          unsigned char* sb = sa + A_STAGE;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * p.bke;
+          if (!p.a_mn) tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          else {
+            const int chunk_elems = p.bke;   // elements per 128-byte row
+            const int nchunk = BM / chunk_elems;
+            for (int c = 0; c < nchunk; ++c) tma_load_2d(sa + c * p.bke * ROW_BYTES, &tmA, &full_bar[stage], m0 + c * chunk_elems, k0);
+          }
+          if (!p.b_mn) tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          else {
+            const int chunk_elems = p.bke;
+            const int nchunk = BN / chunk_elems;
+            for (int c = 0; c < nchunk; ++c) tma_load_2d(sb + c * p.bke * ROW_BYTES, &tmB, &full_bar[stage], n0 + c * chunk_elems, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
+        int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE;
+          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo);
+          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo);
+          for (int k = 0; k < p.mma_per_stage; ++k) {
+            umma_ss<KIND>(d_tmem, adesc + (uint64_t)((k * p.a_kstep) >> 4), bdesc + (uint64_t)((k * p.b_kstep) >> 4),
+                          p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    int it = 0;
+    for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
+      int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+      fence_after_sync();
+      const int row = m_blk * BM + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      const float alpha = p.alpha ? *p.alpha : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+          if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
+            if (p.bias) {
+              const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+              for (int j8 = 0; j8 < 4; ++j8) {
+                if (col0 + j8 * 8 < p.N) {
+                  Pack<__nv_bfloat16> b; b.load(bp + j8 * 8);
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) v[j8 * 8 + k] += b.v[k];
+                }
+              }
+            }
+          }
+          if (EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32) {
+            float* dp = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              if (col0 + j4 * 4 < p.N) {
+                if (EPI == EPI_ACC_F32)
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + j4 * 4), "f"(v[j4 * 4]), "f"(v[j4 * 4 + 1]),
+                               "f"(v[j4 * 4 + 2]), "f"(v[j4 * 4 + 3]) : "memory");
+                else
+                  *reinterpret_cast<float4*>(dp + j4 * 4) = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+              }
+            }
+          } else {
+            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
+            __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux) + (size_t)row * p.ldaux + col0;
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+              if (col0 + j8 * 8 < p.N) {
+                Pack<__nv_bfloat16> o;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o.v[k] = v[j8 * 8 + k];
+                if (EPI == EPI_BIAS_GELU) {
+                  o.store(ap + j8 * 8);                       // pre-GELU activations (bf16)
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) o.v[k] = gelu_f(__bfloat162float(__float2bfloat16_rn(o.v[k])));
+                } else if (EPI == EPI_DGELU) {
+                  Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) o.v[k] *= gelu_grad_f(x.v[k]);
+                } else if (EPI == EPI_BIAS_RESID) {
+                  Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) o.v[k] += x.v[k];
+                }
+                o.store(dp + j8 * 8);
+              }
+            }
+          }
+        }
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc<512>(tmem_base); }
+}
+
+template <int KIND> struct KindTraits;
+template <> struct KindTraits<KIND_F16> { static constexpr int ESZ = 2; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
+template <> struct KindTraits<KIND_TF32> { static constexpr int ESZ = 4; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
+template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ESZ = 1; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
+
+int g_dbg_mn_lbo = -1, g_dbg_mn_sbo = -1;   // test hooks: override the MN-major descriptor strides
+
+template <int KIND, int EPI>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  gemm_kernel<KIND, EPI><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+template <int KIND>
+int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void* aux, const float* alpha, int M, int N,
+                  int K, long long lda, long long ldb, long long ldd, long long ldaux, int a_mn, int b_mn, int a_fmt,
+                  int b_fmt, int epi, int splits, int* status, cudaStream_t st) {
+  constexpr int ESZ = KindTraits<KIND>::ESZ;
+  constexpr int ROW_ELEMS = ROW_BYTES / ESZ;          // elements per swizzled row
+  constexpr int BKE = ROW_ELEMS;                      // K elements per stage
+  constexpr int MMA_K = 32 / ESZ;
+  if (M <= 0 || N <= 0 || K <= 0) return LLMB_ERR_BAD_ARG;
+  if ((lda * ESZ) % 16 || (ldb * ESZ) % 16 || N % 8) return LLMB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return LLMB_ERR_BAD_ARG;
+
+  CUtensorMap ta, tb;
+  int rc;
+  // K-major: global [MN rows, K cols], box [tile rows, ROW_ELEMS]; MN-major: global [K rows, MN cols], box [BKE, ROW_ELEMS]
+  rc = a_mn ? make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BKE, ROW_ELEMS)
+            : make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, ROW_ELEMS);
+  if (rc) return 1000 + rc;
+  rc = b_mn ? make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BKE, ROW_ELEMS)
+            : make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, ROW_ELEMS);
+  if (rc) return 1000 + rc;
+
+  GemmParams p;
+  p.D = D; p.bias = bias; p.aux = aux; p.alpha = alpha;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldaux = ldaux;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  const uint32_t mn_lbo = g_dbg_mn_lbo >= 0 ? (uint32_t)g_dbg_mn_lbo : (uint32_t)(BKE * ROW_BYTES);
+  const uint32_t mn_sbo = g_dbg_mn_sbo >= 0 ? (uint32_t)g_dbg_mn_sbo : 1024u;
+  p.a_lbo = a_mn ? mn_lbo : 16; p.a_sbo = a_mn ? mn_sbo : 1024; p.a_kstep = a_mn ? MMA_K * ROW_BYTES : 32;
+  p.b_lbo = b_mn ? mn_lbo : 16; p.b_sbo = b_mn ? mn_sbo : 1024; p.b_kstep = b_mn ? MMA_K * ROW_BYTES : 32;
+  p.idesc = make_idesc((uint32_t)a_fmt, (uint32_t)b_fmt, (uint32_t)a_mn, (uint32_t)b_mn, BM, BN);
+  p.bke = BKE; p.mma_per_stage = BKE / MMA_K;
+  p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
+  p.kb_total = ceil_div(K, BKE);
+  if (splits < 1) splits = 1;
+  if (splits > p.kb_total) splits = p.kb_total;
+  if (epi != EPI_ACC_F32) splits = 1;
+  p.kb_per_split = ceil_div(p.kb_total, splits);
+  p.splits = ceil_div(p.kb_total, p.kb_per_split);
+  p.status = status;
+  long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
+  int grid = (int)(units < sm_count() ? units : sm_count());
+
+  switch (epi) {
+    case EPI_NONE: return launch<KIND, EPI_NONE>(ta, tb, p, grid, st);
+    case EPI_BIAS: return launch<KIND, EPI_BIAS>(ta, tb, p, grid, st);
+    case EPI_BIAS_GELU: return launch<KIND, EPI_BIAS_GELU>(ta, tb, p, grid, st);
+    case EPI_DGELU: return launch<KIND, EPI_DGELU>(ta, tb, p, grid, st);
+    case EPI_ACC_F32: return launch<KIND, EPI_ACC_F32>(ta, tb, p, grid, st);
+    case EPI_BIAS_RESID: return launch<KIND, EPI_BIAS_RESID>(ta, tb, p, grid, st);
+    case EPI_STORE_F32: return launch<KIND, EPI_STORE_F32>(ta, tb, p, grid, st);
+  }
+  return LLMB_ERR_BAD_ARG;
+}
+}  // namespace
+
+// D[M,N] = epi(alpha * A·B^T).  a_mn/b_mn = 1 when the operand is stored [K, M] / [K, N].
+// kind: 0 bf16, 1 tf32 (fp32 storage), 2 fp8 (a_fmt/b_fmt: 0 e4m3, 1 e5m2).  D is bf16 except for the
+// fp32 epilogues (4 = accumulate with red.add, split-K allowed; 6 = plain fp32 store).
+// `status` is a device int the kernel sets to LLMB_ERR_TIMEOUT if a bounded wait expires.
+LLMB_API int llmb_gemm(void* D, const void* A, const void* B, const void* bias, void* aux, const float* alpha, int M,
+                       int N, int K, long long lda, long long ldb, long long ldd, long long ldaux, int a_mn, int b_mn,
+                       int kind, int a_fmt, int b_fmt, int epi, int splits, int* status, cudaStream_t st) {
+  switch (kind) {
+    case 0: return gemm_dispatch<KIND_F16>(D, A, B, bias, aux, alpha, M, N, K, lda, ldb, ldd, ldaux, a_mn, b_mn, FMT_BF16, FMT_BF16, epi, splits, status, st);
+    case 1: return gemm_dispatch<KIND_TF32>(D, A, B, bias, aux, alpha, M, N, K, lda, ldb, ldd, ldaux, a_mn, b_mn, FMT_TF32, FMT_TF32, epi, splits, status, st);
+    case 2: return gemm_dispatch<KIND_F8F6F4>(D, A, B, bias, aux, alpha, M, N, K, lda, ldb, ldd, ldaux, a_mn, b_mn, a_fmt, b_fmt, epi, splits, status, st);
+  }
+  return LLMB_ERR_BAD_ARG;
+}
+
+LLMB_API void llmb_gemm_debug_mn_strides(int lbo_bytes, int sbo_bytes) { g_dbg_mn_lbo = lbo_bytes; g_dbg_mn_sbo = sbo_bytes; }

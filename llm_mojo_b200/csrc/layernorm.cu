@@ -1,0 +1,233 @@
+// LayerNorm forward (optionally fused with the residual add that precedes it) and backward
+// with the residual-gradient accumulate and dgamma/dbeta reduction.
+//
+// Reference behaviour: llmm/layernorm.mojo:197-331 (fwd, mean/rstd saved fp32), :651-1096 (fused
+// residual fwd), :1582-1895 (bwd with register-accumulated dgamma/dbeta partials + finalize),
+// :2426-2614 (fused residual bwd).  B200 design: one warp per row, the row lives in registers
+// (single HBM read), 16-byte accesses; backward is a persistent grid whose blocks write one
+// dgamma/dbeta partial row each into scratch, summed in block order by a finalize kernel so
+// the result does not depend on scheduling.
+#include "common.cuh"
+using namespace llmb;
+
+namespace {
+constexpr int LN_MAX_VEC = 16;  // 16-byte vectors per lane: C <= 32*16*8 = 4096 for bf16
+constexpr float LN_EPS = 1e-5f;
+
+template <typename T, bool RESID>
+__global__ void __launch_bounds__(256) ln_fwd_kernel(T* __restrict__ out, float* __restrict__ mean_o, float* __restrict__ rstd_o,
+                                                    T* __restrict__ resid_out, const T* __restrict__ inp1,
+                                                    const T* __restrict__ inp2, const T* __restrict__ w,
+                                                    const T* __restrict__ b, int rows, int C) {
+  constexpr int N = Pack<T>::N;
+  const int lane = threadIdx.x % 32, wid = threadIdx.x / 32;
+  const int nvec = C / N;                       // vectors per row
+  const int per_lane = (nvec + 31) / 32;        // <= LN_MAX_VEC
+  int row = blockIdx.x * (blockDim.x / 32) + wid;
+  if (row >= rows) return;
+  float x[LN_MAX_VEC][N];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAX_VEC; ++i) {
+    if (i < per_lane) {
+      int vc = i * 32 + lane;
+      if (vc < nvec) {
+        Pack<T> p; p.load(inp1 + (size_t)row * C + vc * N);
+        if (RESID) {
+          Pack<T> q; q.load(inp2 + (size_t)row * C + vc * N);
+#pragma unroll
+          for (int k = 0; k < N; ++k) p.v[k] = to_f<T>(from_f<T>(p.v[k] + q.v[k]));  // round like the stored residual
+          p.store(resid_out + (size_t)row * C + vc * N);
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) { x[i][k] = p.v[k]; sum += p.v[k]; }
+      } else {
+#pragma unroll
+        for (int k = 0; k < N; ++k) x[i][k] = 0.f;
+      }
+    }
+  }
+  float mean = warp_sum(sum) / C;
+  float var = 0.f;
+#pragma unroll
+  for (int i = 0; i < LN_MAX_VEC; ++i) {
+    if (i < per_lane) {
+      int vc = i * 32 + lane;
+      if (vc < nvec) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) { float d = x[i][k] - mean; var += d * d; }
+      }
+    }
+  }
+  float rstd = rsqrtf(warp_sum(var) / C + LN_EPS);
+  if (lane == 0) { if (mean_o) mean_o[row] = mean; if (rstd_o) rstd_o[row] = rstd; }
+#pragma unroll
+  for (int i = 0; i < LN_MAX_VEC; ++i) {
+    if (i < per_lane) {
+      int vc = i * 32 + lane;
+      if (vc < nvec) {
+        Pack<T> ww, bb, o; ww.load(w + vc * N); bb.load(b + vc * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) o.v[k] = (x[i][k] - mean) * rstd * ww.v[k] + bb.v[k];
+        o.store(out + (size_t)row * C + vc * N);
+      }
+    }
+  }
+}
+
+// Backward.  dres[row] (+)= LN'(dout[row]); partial dgamma/dbeta per block into scratch.
+// Each warp walks rows grid-stride and keeps dgamma/dbeta partials for its lanes' channels in
+// registers; warps of a block are then combined in fixed order through shared memory.
+template <typename T, int PER_LANE, bool ACCUM>
+__global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float* __restrict__ partial,
+                                                    const T* __restrict__ dout, const T* __restrict__ inp,
+                                                    const T* __restrict__ w, const float* __restrict__ mean_i,
+                                                    const float* __restrict__ rstd_i, int rows, int C) {
+  constexpr int N = Pack<T>::N;
+  extern __shared__ float sm[];  // [warps][2][C]
+  const int lane = threadIdx.x % 32, wid = threadIdx.x / 32, nwarps = blockDim.x / 32;
+  const int nvec = C / N;
+  float dg[PER_LANE][N], db[PER_LANE][N];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) { dg[i][k] = 0.f; db[i][k] = 0.f; }
+  }
+  for (int row = blockIdx.x * nwarps + wid; row < rows; row += gridDim.x * nwarps) {
+    float mean = mean_i[row], rstd = rstd_i[row];
+    uint4 xr[PER_LANE], dr[PER_LANE];   // raw 16-byte vectors: the row stays in registers
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      int vc = i * 32 + lane;
+      if (vc < nvec) {
+        xr[i] = *reinterpret_cast<const uint4*>(inp + (size_t)row * C + vc * N);
+        dr[i] = *reinterpret_cast<const uint4*>(dout + (size_t)row * C + vc * N);
+        Pack<T> x, d, ww; x.load(reinterpret_cast<const T*>(&xr[i])); d.load(reinterpret_cast<const T*>(&dr[i]));
+        ww.load(w + vc * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          float n_ = (x.v[k] - mean) * rstd;
+          float dn_ = d.v[k] * ww.v[k];
+          s1 += dn_; s2 += dn_ * n_;
+          dg[i][k] += d.v[k] * n_; db[i][k] += d.v[k];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / C; s2 = warp_sum(s2) / C;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      int vc = i * 32 + lane;
+      if (vc < nvec) {
+        Pack<T> x, d, ww, o; x.load(reinterpret_cast<const T*>(&xr[i])); d.load(reinterpret_cast<const T*>(&dr[i]));
+        ww.load(w + vc * N);
+        if (ACCUM) o.load(dres + (size_t)row * C + vc * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          float n_ = (x.v[k] - mean) * rstd;
+          float g = (d.v[k] * ww.v[k] - s1 - n_ * s2) * rstd;
+          o.v[k] = ACCUM ? o.v[k] + g : g;
+        }
+        o.store(dres + (size_t)row * C + vc * N);
+      }
+    }
+  }
+  // block combine (fixed warp order)
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    int vc = i * 32 + lane;
+    if (vc < nvec) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        sm[(wid * 2 + 0) * C + vc * N + k] = dg[i][k];
+        sm[(wid * 2 + 1) * C + vc * N + k] = db[i][k];
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+    int which = c / C, cc = c % C;
+    float s = 0.f;
+    for (int wdx = 0; wdx < nwarps; ++wdx) s += sm[(wdx * 2 + which) * C + cc];
+    partial[(size_t)blockIdx.x * 2 * C + c] = s;
+  }
+}
+
+__global__ void ln_bwd_final_kernel(float* __restrict__ dw, float* __restrict__ db, const float* __restrict__ partial,
+                                    int C, int nblocks) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * C) return;
+  float s = 0.f;
+  for (int i = 0; i < nblocks; ++i) s += partial[(size_t)i * 2 * C + c];
+  if (c < C) dw[c] += s; else db[c - C] += s;
+}
+
+template <typename T>
+int ln_fwd_launch(void* out, float* mean, float* rstd, void* resid_out, const void* inp1, const void* inp2,
+                  const void* w, const void* b, int rows, int C, cudaStream_t st) {
+  constexpr int N = Pack<T>::N;
+  if (C % N || C / N > 32 * LN_MAX_VEC) return LLMB_ERR_BAD_ARG;
+  int grid = ceil_div(rows, 8);
+  if (inp2)
+    ln_fwd_kernel<T, true><<<grid, 256, 0, st>>>((T*)out, mean, rstd, (T*)resid_out, (const T*)inp1, (const T*)inp2, (const T*)w, (const T*)b, rows, C);
+  else
+    ln_fwd_kernel<T, false><<<grid, 256, 0, st>>>((T*)out, mean, rstd, nullptr, (const T*)inp1, nullptr, (const T*)w, (const T*)b, rows, C);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int PER_LANE>
+int ln_bwd_launch_n(void* dres, float* partial, const void* dout, const void* inp, const void* w, const float* mean,
+                    const float* rstd, int rows, int C, int accumulate, int grid, cudaStream_t st) {
+  size_t smem = (size_t)8 * 2 * C * sizeof(float);
+  auto kern_a = ln_bwd_kernel<T, PER_LANE, true>;
+  auto kern_n = ln_bwd_kernel<T, PER_LANE, false>;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(kern_a, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(kern_n, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  if (accumulate) kern_a<<<grid, 256, smem, st>>>((T*)dres, partial, (const T*)dout, (const T*)inp, (const T*)w, mean, rstd, rows, C);
+  else kern_n<<<grid, 256, smem, st>>>((T*)dres, partial, (const T*)dout, (const T*)inp, (const T*)w, mean, rstd, rows, C);
+  return (int)cudaGetLastError();
+}
+}  // namespace
+
+LLMB_API int llmb_layernorm_fwd(void* out, float* mean, float* rstd, void* resid_out, const void* inp1,
+                                const void* inp2, const void* w, const void* b, int rows, int C, int dtype,
+                                cudaStream_t st) {
+  return dtype == LLMB_BF16 ? ln_fwd_launch<__nv_bfloat16>(out, mean, rstd, resid_out, inp1, inp2, w, b, rows, C, st)
+                            : ln_fwd_launch<float>(out, mean, rstd, resid_out, inp1, inp2, w, b, rows, C, st);
+}
+
+LLMB_API int llmb_layernorm_bwd_blocks(int rows) { int g = sm_count() * 2; int need = ceil_div(rows, 8); return need < g ? need : g; }
+LLMB_API long long llmb_layernorm_bwd_scratch_bytes(int rows, int C) {
+  return (long long)llmb_layernorm_bwd_blocks(rows) * 2 * C * sizeof(float);
+}
+
+// dres (+)= LN-backward(dout); dw += ..., db += ...  (dw/db fp32).  accumulate=1 adds into dres.
+LLMB_API int llmb_layernorm_bwd(void* dres, float* dw, float* db, float* scratch, long long scratch_bytes,
+                                const void* dout, const void* inp, const void* w, const float* mean,
+                                const float* rstd, int rows, int C, int accumulate, int dtype, cudaStream_t st) {
+  int grid = llmb_layernorm_bwd_blocks(rows);
+  if (scratch_bytes < (long long)grid * 2 * C * (long long)sizeof(float)) return LLMB_ERR_BAD_ARG;
+  int rc;
+  if (dtype == LLMB_BF16) {
+    int per = ceil_div(C / 8, 32);
+    if (C % 8) return LLMB_ERR_BAD_ARG;
+#define LN_CASE(P) rc = ln_bwd_launch_n<__nv_bfloat16, P>(dres, scratch, dout, inp, w, mean, rstd, rows, C, accumulate, grid, st)
+    if (per <= 2) LN_CASE(2); else if (per <= 3) LN_CASE(3); else if (per <= 4) LN_CASE(4); else if (per <= 5) LN_CASE(5);
+    else if (per <= 7) LN_CASE(7); else if (per <= 8) LN_CASE(8); else if (per <= 12) LN_CASE(12); else if (per <= 16) LN_CASE(16);
+    else return LLMB_ERR_BAD_ARG;
+#undef LN_CASE
+  } else {
+    int per = ceil_div(C / 4, 32);
+    if (C % 4) return LLMB_ERR_BAD_ARG;
+#define LN_CASE(P) rc = ln_bwd_launch_n<float, P>(dres, scratch, dout, inp, w, mean, rstd, rows, C, accumulate, grid, st)
+    if (per <= 2) LN_CASE(2); else if (per <= 4) LN_CASE(4); else if (per <= 6) LN_CASE(6); else if (per <= 8) LN_CASE(8);
+    else if (per <= 10) LN_CASE(10); else if (per <= 13) LN_CASE(13); else if (per <= 16) LN_CASE(16);
+    else return LLMB_ERR_BAD_ARG;
+#undef LN_CASE
+  }
+  if (rc) return rc;
+  ln_bwd_final_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(dw, db, scratch, C, grid);
+  return (int)cudaGetLastError();
+}

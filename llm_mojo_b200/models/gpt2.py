@@ -1,0 +1,368 @@
+"""GPT-2 over flat buffers with explicit forward / backward / update.
+
+Parity: ``train_gpt2.mojo:1189-1653`` (GPT2 struct and its three load paths), ``:3050-3848``
+(forward), ``:3948-5056`` (backward), ``:5058-5259`` (update), ``:5261-5383`` (grad norm),
+``:5615-5801`` (checkpoint glue), ``:5807-6011`` (memory report).
+
+B200-first differences: one process per GPU; parameters are one flat tensor in the storage
+dtype with an fp32 master copy, gradients are one flat **fp32** tensor (cast to bf16 only on
+the wire); attention never materialises ``[T,T]``; the residual adds are fused into the
+attn-proj / fc-proj GEMM epilogues; the clip factor stays on the device so an optimizer step
+needs no host round trip.  Distributed behaviour (DDP / ZeRO-1/2/3) is delegated to a
+``ZeroEngine`` (``parallel/zero.py``) through four hooks: ``before_layer``,
+``grads_ready``, ``reduce_all`` and ``optimizer_step``.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..config import (GPT2Config, INIT_RNG_SEED, INIT_WEIGHT_STD, PARAM_NAMES, Precision,
+                      is_model_descriptor, parse_model_descriptor)
+from ..utils import checkpointing as ckpt
+from ..utils.rand import MT19937, normal_
+
+LAYER_TENSORS = ("ln1w", "ln1b", "qkvw", "qkvb", "attprojw", "attprojb", "ln2w", "ln2b",
+                 "fcw", "fcb", "fcprojw", "fcprojb")
+
+
+def random_init_params(config: GPT2Config, seed: int = INIT_RNG_SEED) -> torch.Tensor:
+    """Flat fp32 parameter vector with the llm.c / PyTorch-compatible random init
+    (``train_gpt2.mojo:2060-2160``): draws are layer-outer, tensor-inner from MT19937 +
+    Box-Muller; N(0, 0.02), residual projections scaled by 1/sqrt(2L), LN gamma 1, rest 0."""
+    L, C, V = config.num_layer, config.channels, config.vocab_size
+    sizes = config.param_sizes()
+    offsets = [0]
+    for s in sizes:
+        offsets.append(offsets[-1] + s)
+    flat = torch.zeros(offsets[-1], dtype=torch.float32)
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)            # torch's CPU generator *is* MT19937; normal_ matches llmm/rand.mojo:162
+
+    def draw(n: int, std: float) -> torch.Tensor:
+        return torch.empty(n, dtype=torch.float32).normal_(0.0, std, generator=g)
+
+    residual_scale = 1.0 / math.sqrt(2.0 * L)
+    for l in range(L):
+        for i, name in enumerate(PARAM_NAMES):
+            off, n = offsets[i], sizes[i]
+            if l == 0 and name in ("ln1w", "ln2w", "lnfw"):
+                flat[off:off + n] = 1.0
+            if l == 0 and name == "wte":
+                flat[off:off + V * C] = draw(V * C, INIT_WEIGHT_STD)
+            elif l == 0 and name == "wpe":
+                flat[off:off + n] = draw(n, INIT_WEIGHT_STD)
+            elif name in ("qkvw", "attprojw", "fcw", "fcprojw"):
+                per = n // L
+                std = INIT_WEIGHT_STD * (residual_scale if name in ("attprojw", "fcprojw") else 1.0)
+                flat[off + l * per: off + (l + 1) * per] = draw(per, std)
+    return flat
+
+
+class GPT2:
+    def __init__(self, source: str | GPT2Config, precision: Precision | str = "bf16",
+                 device: str | torch.device = "cpu", zero=None, recompute: bool = False,
+                 init_seed: int = INIT_RNG_SEED, params_flat: Optional[torch.Tensor] = None):
+        self.precision = precision if isinstance(precision, Precision) else Precision(precision)
+        self.device = torch.device(device)
+        self.recompute = recompute or os.environ.get("LLMM_RECOMPUTE", "") not in ("", "0")
+        self.zero = zero
+        self.checkpoint_path = source if isinstance(source, str) else ""
+        # ---- three load paths: config/descriptor (random init), .bin, .safetensors
+        if params_flat is not None:
+            assert isinstance(source, GPT2Config)
+            self.config = source
+            flat = params_flat.float()
+        elif isinstance(source, GPT2Config):
+            self.config = source
+            flat = random_init_params(self.config, init_seed)
+        elif is_model_descriptor(source):
+            self.config = parse_model_descriptor(source)
+            flat = random_init_params(self.config, init_seed)
+        elif source.endswith(".safetensors"):
+            from ..utils.safetensors_io import load_hf_gpt2
+            self.config, flat = load_hf_gpt2(source)
+        else:
+            self.config, _, flat = ckpt.read_model_checkpoint(source, dtype=torch.float32)
+        cfg = self.config
+        if self.device.type == "cpu" and self.precision.storage != torch.float32:
+            raise ValueError("CPU training is fp32 by policy; use precision='fp32'")
+        self.dtype = self.precision.storage
+        self.param_sizes = cfg.param_sizes()
+        self.param_shapes = cfg.param_shapes()
+        self.num_parameters = sum(self.param_sizes)
+        self.param_offsets = [0]
+        for s in self.param_sizes:
+            self.param_offsets.append(self.param_offsets[-1] + s)
+
+        if self.zero is not None:
+            self.zero.attach(self, flat)           # allocates params/grads/m/v/master (possibly sharded)
+        else:
+            self.params = flat.to(self.device, self.dtype)
+            self.grads = torch.zeros(self.num_parameters, dtype=torch.float32, device=self.device)
+            self.m = torch.zeros(self.num_parameters, dtype=torch.float32, device=self.device)
+            self.v = torch.zeros(self.num_parameters, dtype=torch.float32, device=self.device)
+            self.master = flat.to(self.device, torch.float32).clone() if self.precision.use_master else None
+        del flat
+        self.p = self._views(self.params) if self.params is not None else {}
+        self.g = self._views(self.grads) if self.grads is not None and self.grads.numel() >= self.num_parameters else {}
+        self.B = self.T = 0
+        self.acts: Dict[str, torch.Tensor] = {}
+        self.mean_loss = -1.0
+        self.loss_acc = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.clip_scale = torch.ones(1, dtype=torch.float32, device=self.device)
+        self.inputs_dev: Optional[torch.Tensor] = None
+        self.targets_dev: Optional[torch.Tensor] = None
+        self.rng_seed = 1337
+        self.use_stochastic_rounding = False
+
+    # ------------------------------------------------------------------ views / layout
+    def _views(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+        return {n: flat[self.param_offsets[i]:self.param_offsets[i + 1]].view(self.param_shapes[i])
+                for i, n in enumerate(PARAM_NAMES)}
+
+    def tensor_range(self, name: str, layer: Optional[int] = None) -> Tuple[int, int]:
+        """[begin, end) of a tensor (or of one layer's slice of it) in the flat vector."""
+        i = PARAM_NAMES.index(name)
+        off, n = self.param_offsets[i], self.param_sizes[i]
+        if layer is None:
+            return off, off + n
+        per = n // self.config.num_layer
+        return off + layer * per, off + (layer + 1) * per
+
+    def layer_ranges(self, layer: int) -> List[Tuple[int, int]]:
+        """The 12 (offset, end) ranges of one transformer block (the per-layer gradient bucket
+        and ZeRO-3 window of ``train_gpt2.mojo:1856-1940`` / ``:4921-4929``)."""
+        return [self.tensor_range(n, layer) for n in LAYER_TENSORS]
+
+    # ------------------------------------------------------------------ activations
+    def allocate_activations(self, B: int, T: int) -> None:
+        cfg, dev, dt = self.config, self.device, self.dtype
+        L, C, NH, Vp = cfg.num_layer, cfg.channels, cfg.num_heads, cfg.padded_vocab_size
+        if T > cfg.max_seq_len:
+            raise ValueError(f"sequence length {T} exceeds max_seq_len {cfg.max_seq_len}")
+        f32 = torch.float32
+
+        def e(*shape, dtype=dt):
+            return torch.empty(*shape, dtype=dtype, device=dev)
+
+        a = {
+            "encoded": e(B, T, C),
+            "ln1": e(L, B, T, C), "ln1_mean": e(L, B, T, dtype=f32), "ln1_rstd": e(L, B, T, dtype=f32),
+            "qkv": e(L, B, T, 3 * C), "atty": e(L, B, T, C), "lse": e(L, B, NH, T, dtype=f32),
+            "residual2": e(L, B, T, C),
+            "ln2": e(L, B, T, C), "ln2_mean": e(L, B, T, dtype=f32), "ln2_rstd": e(L, B, T, dtype=f32),
+            "fch": e(L, B, T, 4 * C),
+            "fch_gelu": e(1 if self.recompute else L, B, T, 4 * C),
+            "residual3": e(L, B, T, C),
+            "lnf": e(B, T, C), "lnf_mean": e(B, T, dtype=f32), "lnf_rstd": e(B, T, dtype=f32),
+            "logits": e(B, T, Vp), "losses": e(B, T, dtype=f32),
+            # backward scratch
+            "dres": e(B, T, C), "dl_btc": e(B, T, C), "dl_bt4c": e(B, T, 4 * C),
+        }
+        self.acts = a
+        self.B, self.T = B, T
+        self.inputs_dev = torch.empty(B, T, dtype=torch.int32, device=dev)
+        self.targets_dev = torch.empty(B, T, dtype=torch.int32, device=dev)
+
+    def activation_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.acts.values())
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, inputs: torch.Tensor, targets: Optional[torch.Tensor] = None,
+                grad_accum_steps: int = 1, B: Optional[int] = None, T: Optional[int] = None) -> None:
+        """One micro-step forward.  ``inputs`` / ``targets`` are int32 host (ideally pinned) or
+        device tensors of B·T tokens.  With targets the classifier also leaves dlogits in
+        ``acts['logits']`` (llm.c design, ``train_gpt2.mojo:3751-3848``) and the micro-step's mean
+        loss / grad_accum_steps is added to ``loss_acc`` on the device."""
+        if B is None:
+            B, T = inputs.shape
+        if (B, T) != (self.B, self.T):
+            self.allocate_activations(B, T)
+        cfg, a = self.config, self.acts
+        L, C, NH, V = cfg.num_layer, cfg.channels, cfg.num_heads, cfg.vocab_size
+        self.inputs_dev.copy_(inputs.view(B, T), non_blocking=True)
+        if targets is not None:
+            self.targets_dev.copy_(targets.view(B, T), non_blocking=True)
+        z = self.zero
+        if z is not None:
+            z.before_embedding()
+        p = self.p
+        ops.encoder_fwd(a["encoded"], self.inputs_dev, p["wte"], p["wpe"])
+        for l in range(L):
+            if z is not None:
+                z.before_layer(l, backward=False)
+                p = self.p
+            x_in = a["encoded"] if l == 0 else a["residual3"][l - 1]
+            ops.layernorm_fwd(a["ln1"][l], a["ln1_mean"][l], a["ln1_rstd"][l], x_in, p["ln1w"][l], p["ln1b"][l])
+            ops.matmul_fwd(a["qkv"][l], a["ln1"][l], p["qkvw"][l], p["qkvb"][l])
+            ops.attention_fwd(a["atty"][l], a["lse"][l], a["qkv"][l], NH)
+            ops.matmul_fwd(a["residual2"][l], a["atty"][l], p["attprojw"][l], p["attprojb"][l], residual=x_in)
+            ops.layernorm_fwd(a["ln2"][l], a["ln2_mean"][l], a["ln2_rstd"][l], a["residual2"][l], p["ln2w"][l], p["ln2b"][l])
+            gelu_out = a["fch_gelu"][0 if self.recompute else l]
+            ops.matmul_fwd(gelu_out, a["ln2"][l], p["fcw"][l], p["fcb"][l], pre_gelu=a["fch"][l])
+            ops.matmul_fwd(a["residual3"][l], gelu_out, p["fcprojw"][l], p["fcprojb"][l], residual=a["residual2"][l])
+        if z is not None:
+            z.before_head(backward=False)
+            p = self.p
+        ops.layernorm_fwd(a["lnf"], a["lnf_mean"], a["lnf_rstd"], a["residual3"][L - 1], p["lnfw"], p["lnfb"])
+        ops.matmul_fwd(a["logits"], a["lnf"], p["wte"])
+        if targets is not None:
+            dloss = 1.0 / (B * T * grad_accum_steps)
+            ops.fused_classifier(a["logits"], a["losses"], self.targets_dev, dloss, V)
+            self.loss_acc += a["losses"].sum() * dloss
+
+    def read_loss(self) -> float:
+        """Synchronising read of the accumulated mean loss; resets the accumulator."""
+        self.mean_loss = float(self.loss_acc.item())
+        self.loss_acc.zero_()
+        return self.mean_loss
+
+    # ------------------------------------------------------------------ backward
+    def zero_gradients(self) -> None:
+        if self.zero is not None:
+            self.zero.zero_gradients()
+        else:
+            self.grads.zero_()
+
+    def backward(self, grad_accum_steps: int = 1, micro_step: int = 0, last_micro_step: Optional[bool] = None) -> None:
+        """One micro-step backward; gradients accumulate (fp32).  ``micro_step == 0`` zeroes them
+        (``train_gpt2.mojo:3948``); on the last micro-step the ZeRO engine reduces each bucket as
+        soon as it is complete."""
+        if last_micro_step is None:
+            last_micro_step = micro_step == grad_accum_steps - 1
+        if micro_step == 0:
+            self.zero_gradients()
+        cfg, a = self.config, self.acts
+        L, NH = cfg.num_layer, cfg.num_heads
+        z = self.zero
+        B, T = self.B, self.T
+        C = cfg.channels
+        dres, dl, dl4 = a["dres"], a["dl_btc"], a["dl_bt4c"]
+        dqkv = dl4.view(-1)[:B * T * 3 * C].view(B, T, 3 * C)
+        if z is not None:
+            z.before_head(backward=True)
+        p, g = self.p, self.g
+        # bucket 1: LM head (dlogits are already in acts['logits'])
+        ops.matmul_bwd(dl, g["wte"], None, a["logits"], a["lnf"], p["wte"])
+        # bucket 2: final layernorm
+        ops.layernorm_bwd(dres, g["lnfw"], g["lnfb"], dl, a["residual3"][L - 1], p["lnfw"], a["lnf_mean"], a["lnf_rstd"],
+                          accumulate=False)
+        if z is not None:
+            z.grads_ready("head", last_micro_step)
+        for l in range(L - 1, -1, -1):
+            if z is not None:
+                z.before_layer(l, backward=True)
+                p, g = self.p, self.g
+            x_in = a["encoded"] if l == 0 else a["residual3"][l - 1]
+            if self.recompute:
+                gelu_out = a["fch_gelu"][0]
+                ops.gelu_fwd(gelu_out, a["fch"][l])       # train_gpt2.mojo:4490-4502
+            else:
+                gelu_out = a["fch_gelu"][l]
+            ops.matmul_bwd(dl4, g["fcprojw"][l], g["fcprojb"][l], dres, gelu_out, p["fcprojw"][l], gelu_pre=a["fch"][l])
+            ops.matmul_bwd(dl, g["fcw"][l], g["fcb"][l], dl4, a["ln2"][l], p["fcw"][l])
+            ops.layernorm_bwd(dres, g["ln2w"][l], g["ln2b"][l], dl, a["residual2"][l], p["ln2w"][l],
+                              a["ln2_mean"][l], a["ln2_rstd"][l], accumulate=True)
+            ops.matmul_bwd(dl, g["attprojw"][l], g["attprojb"][l], dres, a["atty"][l], p["attprojw"][l])
+            ops.attention_bwd(dqkv, dl, a["qkv"][l], a["atty"][l], a["lse"][l], NH)
+            ops.matmul_bwd(dl, g["qkvw"][l], g["qkvb"][l], dqkv, a["ln1"][l], p["qkvw"][l])
+            ops.layernorm_bwd(dres, g["ln1w"][l], g["ln1b"][l], dl, x_in, p["ln1w"][l],
+                              a["ln1_mean"][l], a["ln1_rstd"][l], accumulate=True)
+            if z is not None:
+                z.grads_ready(l, last_micro_step)
+        if z is not None:
+            z.before_embedding(backward=True)
+            p, g = self.p, self.g
+        ops.encoder_bwd(g["wte"], g["wpe"], dres, self.inputs_dev)
+        if z is not None:
+            z.grads_ready("embed", last_micro_step)
+            if last_micro_step:
+                z.reduce_all()
+
+    # ------------------------------------------------------------------ optimizer
+    def calculate_grad_norm(self) -> torch.Tensor:
+        """Global L2 norm of the (reduced) gradients as a 1-element device tensor
+        (``train_gpt2.mojo:5261-5383``)."""
+        if self.zero is not None:
+            return self.zero.grad_norm()
+        ops.global_norm_squared(self.norm_sq, self.grads)
+        return self.norm_sq.sqrt()
+
+    def update(self, step: int, lr: float, weight_decay: float = 0.0, grad_scale: float = 1.0,
+               beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+               dev_scale: Optional[torch.Tensor] = None) -> None:
+        """AdamW step (``train_gpt2.mojo:5058-5259``; defaults β=(0.9, 0.999), eps 1e-8).
+        ``grad_scale`` multiplies every gradient (clip factor); ``dev_scale`` is the same thing
+        as a device scalar."""
+        kw = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, grad_scale=grad_scale,
+                  step=step, seed=self.rng_seed + step, stochastic_rounding=self.use_stochastic_rounding,
+                  dev_scale=dev_scale)
+        if self.zero is not None:
+            self.zero.optimizer_step(**kw)
+        else:
+            ops.adamw_update(self.params, self.master, self.grads, self.m, self.v, **kw)
+
+    def clip_scale_from_norm(self, norm: torch.Tensor, max_norm: float = 1.0) -> torch.Tensor:
+        """scale = max_norm / norm if norm > max_norm else 1, on the device
+        (``train_gpt2.mojo:6532-6537``)."""
+        torch.clamp(max_norm / (norm + 1e-6), max=1.0, out=self.clip_scale)
+        return self.clip_scale
+
+    # ------------------------------------------------------------------ checkpoints
+    def full_params(self) -> torch.Tensor:
+        return self.zero.gather_full_params() if self.zero is not None else self.params
+
+    def write_checkpoint(self, model_path: str, state_path: str, state: ckpt.TrainingState, rank: int = 0) -> None:
+        """Rank 0 writes the model file; every rank writes its m/v shard
+        (``train_gpt2.mojo:5615-5696``)."""
+        full = self.full_params()
+        if rank == 0:
+            ckpt.write_model_checkpoint(model_path, self.config, full, self.precision.checkpoint_version)
+        state.use_master_weights = int(self.master is not None)
+        ckpt.write_state_checkpoint(state_path, state, self.m, self.v)
+
+    def load_checkpoint(self, model_path: str, state_path: str) -> ckpt.TrainingState:
+        """Reload parameters and optimizer moments; the fp32 master copy is re-seeded from the
+        parameters (``train_gpt2.mojo:5698-5801``)."""
+        cfg, version = ckpt.read_model_header(model_path)
+        if cfg != self.config:
+            raise ValueError("Checkpoint error: model config does not match")
+        if self.zero is not None:
+            return self.zero.load_checkpoint(model_path, state_path)
+        _, _, flat = ckpt.read_model_checkpoint(model_path, dtype=torch.float32)
+        self.params.copy_(flat.to(self.device, self.dtype))
+        if self.master is not None:
+            self.master.copy_(self.params.float())
+        state, m, v = ckpt.read_state_checkpoint(state_path, self.m.numel())
+        self.m.copy_(m.to(self.device))
+        self.v.copy_(v.to(self.device))
+        return state
+
+    # ------------------------------------------------------------------ accounting
+    def memory_report(self) -> dict:
+        """Exact per-buffer accounting (``train_gpt2.mojo:5807-5999``; schema 3)."""
+        def nbytes(t):
+            return 0 if t is None else t.numel() * t.element_size()
+        rep = {
+            "schema": 3, "precision": self.precision.name, "num_parameters": self.num_parameters,
+            "zero_stage": 0 if self.zero is None else self.zero.stage,
+            "world_size": 1 if self.zero is None else self.zero.world_size,
+            "params_bytes": nbytes(self.params), "grads_bytes": nbytes(self.grads), "m_bytes": nbytes(self.m),
+            "v_bytes": nbytes(self.v), "master_bytes": nbytes(self.master),
+            "activations_bytes": self.activation_bytes(), "B": self.B, "T": self.T,
+        }
+        if self.zero is not None:
+            rep.update(self.zero.memory_report())
+        rep["total_bytes"] = sum(v for k, v in rep.items() if k.endswith("_bytes"))
+        return rep
+
+    def print_memory_report(self) -> None:
+        if os.environ.get("LLMM_MEM_REPORT", "") not in ("", "0"):
+            print("[mem-report] " + json.dumps(self.memory_report()), flush=True)

@@ -1,0 +1,390 @@
+"""Op library: every op of the GPT-2 trainer as explicit forward / backward functions.
+
+CUDA tensors run the hand-written sm_100a kernels (``csrc/*.cu`` through ctypes); CPU tensors
+run the fp32 PyTorch statement of the same math, which is both the CPU training target and the
+oracle the GPU tests compare against.  All functions write into caller-provided outputs so the
+training loop allocates nothing per step.
+
+Parity map (reference ``llmm/`` module → function here):
+encoder → ``encoder_fwd/bwd``; layernorm → ``layernorm_fwd``, ``residual_layernorm_fwd``,
+``layernorm_bwd``; matmul → ``matmul_fwd``, ``matmul_bwd``; attention (+split/merge/softmax) →
+``attention_fwd/bwd``; gelu → ``gelu_fwd/bwd``; fused_classifier → ``fused_classifier``;
+adamw → ``adamw_update``; global_norm → ``global_norm_squared``.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from ._lib import check, dtype_code, lib, ptr, status_word, stream
+
+LN_EPS = 1e-5
+GELU_K = math.sqrt(2.0 / math.pi)
+
+# Library GEMM/attention can be forced for A/B comparisons (never the default on CUDA).
+GEMM_IMPL = os.environ.get("LLMB_GEMM", "tcgen05")        # tcgen05 | cublas
+ATTN_IMPL = os.environ.get("LLMB_ATTN", "tcgen05")        # tcgen05 | sdpa
+
+_SCRATCH = {}
+LAUNCHES = 0     # number of kernel-library launches issued (bench.py reports it)
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
+    """Persistent per-(name, device) scratch buffer, grown on demand (cf. llmm/memory.mojo:81-123)."""
+    key = (name, str(device))
+    t = _SCRATCH.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _SCRATCH[key] = t
+    return t
+
+
+# ----------------------------------------------------------------------------- encoder
+def encoder_fwd(out: torch.Tensor, tokens: torch.Tensor, wte: torch.Tensor, wpe: torch.Tensor) -> None:
+    """out[b,t,:] = wte[tokens[b,t]] + wpe[t]   (llmm/encoder.mojo:214-281)."""
+    B, T = tokens.shape
+    C = wte.shape[1]
+    if out.is_cuda:
+        check(lib().llmb_encoder_fwd(ptr(out), ptr(tokens), ptr(wte), ptr(wpe), B, T, C, dtype_code(out), stream()),
+              "encoder_fwd")
+        _count()
+    else:
+        out.view(B, T, C).copy_(wte[tokens.long()] + wpe[:T].unsqueeze(0))
+
+
+def encoder_bwd(dwte: torch.Tensor, dwpe: torch.Tensor, dout: torch.Tensor, tokens: torch.Tensor) -> None:
+    """dwte[tok] += dout, dwpe[t] += Σ_b dout; deterministic (llmm/encoder.mojo:1032-1150)."""
+    B, T = tokens.shape
+    C = dwte.shape[1]
+    if dout.is_cuda:
+        L = lib()
+        nb = L.llmb_encoder_bwd_scratch_bytes(B * T)
+        s = scratch("encoder_bwd", nb, dout.device)
+        vocab_bits = max(1, int(dwte.shape[0] - 1).bit_length())
+        check(L.llmb_encoder_bwd(ptr(dwte), ptr(dwpe), ptr(dout), ptr(tokens), ptr(s), s.numel(), B, T, C,
+                                 vocab_bits, dtype_code(dout), stream()), "encoder_bwd")
+        _count(4)
+    else:
+        d = dout.reshape(B * T, C).float()
+        dwte.index_add_(0, tokens.reshape(-1).long(), d)
+        dwpe[:T] += d.view(B, T, C).sum(0)
+
+
+# ----------------------------------------------------------------------------- layernorm
+def layernorm_fwd(out, mean, rstd, inp, weight, bias) -> None:
+    """Row LayerNorm, saves mean / rstd in fp32 (llmm/layernorm.mojo:366-424)."""
+    residual_layernorm_fwd(None, out, mean, rstd, inp, None, weight, bias)
+
+
+def residual_layernorm_fwd(residual_out, out, mean, rstd, inp1, inp2, weight, bias) -> None:
+    """residual_out = inp1 + inp2; out = LN(residual_out)   (llmm/layernorm.mojo:1002-1096)."""
+    C = weight.numel()
+    rows = inp1.numel() // C
+    if out.is_cuda:
+        check(lib().llmb_layernorm_fwd(ptr(out), ptr(mean), ptr(rstd), ptr(residual_out), ptr(inp1), ptr(inp2),
+                                       ptr(weight), ptr(bias), rows, C, dtype_code(out), stream()), "layernorm_fwd")
+        _count()
+    else:
+        x = inp1.reshape(rows, C)
+        if inp2 is not None:
+            x = x + inp2.reshape(rows, C)
+            residual_out.view(rows, C).copy_(x)
+        x = x.float()
+        m = x.mean(1, keepdim=True)
+        v = ((x - m) ** 2).mean(1, keepdim=True)
+        r = torch.rsqrt(v + LN_EPS)
+        out.view(rows, C).copy_((x - m) * r * weight.float() + bias.float())
+        if mean is not None:
+            mean.view(rows).copy_(m.view(rows))
+        if rstd is not None:
+            rstd.view(rows).copy_(r.view(rows))
+
+
+def layernorm_bwd(dresidual, dweight, dbias, dout, inp, weight, mean, rstd, accumulate: bool = True) -> None:
+    """dresidual (+)= LN'(dout); dweight += Σ dout·norm; dbias += Σ dout (fp32 grads).
+
+    With ``accumulate`` the input gradient is added into ``dresidual`` — the fused
+    residual-backward of llmm/layernorm.mojo:2426-2614."""
+    C = weight.numel()
+    rows = inp.numel() // C
+    if dout.is_cuda:
+        L = lib()
+        nb = L.llmb_layernorm_bwd_scratch_bytes(rows, C)
+        s = scratch("layernorm_bwd", nb, dout.device)
+        check(L.llmb_layernorm_bwd(ptr(dresidual), ptr(dweight), ptr(dbias), ptr(s), s.numel(), ptr(dout), ptr(inp),
+                                   ptr(weight), ptr(mean), ptr(rstd), rows, C, int(accumulate), dtype_code(dout),
+                                   stream()), "layernorm_bwd")
+        _count(2)
+    else:
+        d = dout.reshape(rows, C).float()
+        x = inp.reshape(rows, C).float()
+        norm = (x - mean.view(rows, 1)) * rstd.view(rows, 1)
+        dweight += (d * norm).sum(0)
+        dbias += d.sum(0)
+        dn = d * weight.float()
+        g = (dn - dn.mean(1, keepdim=True) - norm * (dn * norm).mean(1, keepdim=True)) * rstd.view(rows, 1)
+        dr = dresidual.view(rows, C)
+        if accumulate:
+            dr += g.to(dr.dtype)
+        else:
+            dr.copy_(g)
+
+
+# ----------------------------------------------------------------------------- GELU
+def _gelu_t(x: torch.Tensor) -> torch.Tensor:
+    return 0.5 * x * (1.0 + torch.tanh(GELU_K * (x + 0.044715 * x ** 3)))
+
+
+def _gelu_grad_t(x: torch.Tensor) -> torch.Tensor:
+    u = GELU_K * (x + 0.044715 * x ** 3)
+    t = torch.tanh(u)
+    return 0.5 * (1 + t) + 0.5 * x * (1 - t * t) * GELU_K * (1 + 3 * 0.044715 * x * x)
+
+
+def gelu_fwd(out, inp) -> None:
+    """tanh-GELU (llmm/gelu.mojo:35-82)."""
+    if out.is_cuda:
+        check(lib().llmb_gelu_fwd(ptr(out), ptr(inp), inp.numel(), dtype_code(inp), stream()), "gelu_fwd")
+        _count()
+    else:
+        out.copy_(_gelu_t(inp.float()))
+
+
+def gelu_bwd(dinp, inp, dout) -> None:
+    """dinp = dout · gelu'(inp)   (llmm/gelu.mojo:337-430); dinp may alias dout."""
+    if dout.is_cuda:
+        check(lib().llmb_gelu_bwd(ptr(dinp), ptr(inp), ptr(dout), inp.numel(), dtype_code(inp), stream()), "gelu_bwd")
+        _count()
+    else:
+        dinp.copy_(dout.float() * _gelu_grad_t(inp.float()))
+
+
+# ----------------------------------------------------------------------------- matmul
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_DGELU, EPI_ACC_F32, EPI_BIAS_RESID, EPI_STORE_F32 = range(7)
+
+
+def gemm(D, A, B, *, a_mn=False, b_mn=False, epi=EPI_NONE, bias=None, aux=None, alpha=None, splits=1,
+         kind: int = 0, a_fmt: int = 0, b_fmt: int = 0) -> None:
+    """Raw tcgen05 GEMM: D[M,N] = epi(A·Bᵀ).  A is [M,K] (or [K,M] when ``a_mn``), B is [N,K]
+    (or [K,N] when ``b_mn``); all row-major with arbitrary row pitch."""
+    M, N = D.shape
+    K = A.shape[0] if a_mn else A.shape[1]
+    check(lib().llmb_gemm(ptr(D), ptr(A), ptr(B), ptr(bias), ptr(aux), ptr(alpha), M, N, K, A.stride(0), B.stride(0),
+                          D.stride(0), aux.stride(0) if aux is not None else 0, int(a_mn), int(b_mn), kind, a_fmt,
+                          b_fmt, epi, splits, ptr(status_word(D.device)), stream()), "gemm")
+    _count()
+
+
+def _splits_for(M: int, N: int, K: int) -> int:
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    kb = (K + 63) // 64
+    if tiles >= 148:
+        return 1
+    return max(1, min(kb // 8 if kb >= 8 else 1, (2 * 148 + tiles - 1) // tiles))
+
+
+def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> None:
+    """out = inp·weightᵀ (+bias) — optionally out = GELU(pre), pre_gelu = inp·Wᵀ+b, or
+    out = inp·Wᵀ + b + residual (llmm/matmul.mojo:1526-1722: BIAS / GELU_AUX_BIAS epilogues)."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    x = inp.reshape(rows, C)
+    o = out.view(rows, OC)
+    if out.is_cuda and GEMM_IMPL == "tcgen05" and out.dtype == torch.bfloat16:
+        if pre_gelu is not None:
+            gemm(o, x, weight, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC))
+        elif residual is not None:
+            gemm(o, x, weight, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC))
+        else:
+            gemm(o, x, weight, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias)
+        return
+    y = x @ weight.t()
+    if bias is not None:
+        y = y + bias
+    if pre_gelu is not None:
+        pre_gelu.view(rows, OC).copy_(y)
+        y = _gelu_t(pre_gelu.view(rows, OC).float())
+    if residual is not None:
+        y = y + residual.view(rows, OC)
+    o.copy_(y)
+
+
+def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> None:
+    """dinp = dout·W (⊙ gelu'(gelu_pre)); dweight += doutᵀ·inp; dbias += Σ_rows dout.
+
+    dweight / dbias are fp32 accumulators (llmm/matmul.mojo:3512-3563, DGELU epilogue :2789-2938)."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    d = dout.reshape(rows, OC)
+    x = inp.reshape(rows, C)
+    if dout.is_cuda and GEMM_IMPL == "tcgen05" and dout.dtype == torch.bfloat16:
+        if dinp is not None:
+            di = dinp.view(rows, C)
+            if gelu_pre is not None:
+                gemm(di, d, weight, b_mn=True, epi=EPI_DGELU, aux=gelu_pre.view(rows, C))
+            else:
+                gemm(di, d, weight, b_mn=True, epi=EPI_NONE)
+        gemm(dweight.view(OC, C), d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows))
+        if dbias is not None:
+            dbias_reduce(dbias, d)
+        return
+    if dinp is not None:
+        g = d @ weight
+        if gelu_pre is not None:
+            g = g.float() * _gelu_grad_t(gelu_pre.view(rows, C).float())
+        dinp.view(rows, C).copy_(g)
+    dweight.view(OC, C).add_((d.t() @ x).float())
+    if dbias is not None:
+        dbias += d.float().sum(0)
+
+
+def dbias_reduce(dbias, dout2d) -> None:
+    rows, OC = dout2d.shape
+    if dout2d.is_cuda:
+        L = lib()
+        nb = L.llmb_dbias_scratch_bytes(rows, OC)
+        s = scratch("dbias", nb, dout2d.device)
+        check(L.llmb_dbias(ptr(dbias), ptr(dout2d), ptr(s), s.numel(), rows, OC, dtype_code(dout2d), stream()), "dbias")
+        _count(2)
+    else:
+        dbias += dout2d.float().sum(0)
+
+
+# ----------------------------------------------------------------------------- attention
+def attention_fwd(out, lse, qkv, num_heads: int) -> None:
+    """Causal multi-head attention on packed qkv [B,T,3C] → out [B,T,C], lse [B,NH,T].
+
+    ``lse`` is log2-domain: log2 Σ_j 2^(s_ij·log2e/√d).  (llmm/attention.mojo:1748-1945.)"""
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    hs = C // num_heads
+    if qkv.is_cuda and ATTN_IMPL == "tcgen05" and hs == 64 and qkv.dtype == torch.bfloat16:
+        check(lib().llmb_attention_fwd(ptr(out), ptr(lse), ptr(qkv), B, T, num_heads, ptr(status_word(qkv.device)),
+                                       stream()), "attention_fwd")
+        _count()
+        return
+    q, k, v = (t.view(B, T, num_heads, hs).transpose(1, 2) for t in qkv.split(C, dim=2))
+    s = (q.float() @ k.float().transpose(-1, -2)) / math.sqrt(hs)
+    mask = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    l = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - l.unsqueeze(-1))
+    o = (p @ v.float()).transpose(1, 2).reshape(B, T, C)
+    out.copy_(o)
+    lse.copy_(l * math.log2(math.e))
+
+
+def attention_bwd(dqkv, dout, qkv, out, lse, num_heads: int) -> None:
+    """dqkv = ∂/∂qkv of causal attention (llmm/attention.mojo:5033-5276)."""
+    B, T, C3 = qkv.shape
+    C = C3 // 3
+    hs = C // num_heads
+    if qkv.is_cuda and ATTN_IMPL == "tcgen05" and hs == 64 and qkv.dtype == torch.bfloat16:
+        dvec = scratch("attn_dvec", B * num_heads * T * 4, qkv.device)
+        check(lib().llmb_attention_bwd(ptr(dqkv), ptr(dvec), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T, num_heads,
+                                       ptr(status_word(qkv.device)), stream()), "attention_bwd")
+        _count(3)
+        return
+    q, k, v = (t.view(B, T, num_heads, hs).transpose(1, 2).float() for t in qkv.split(C, dim=2))
+    do = dout.view(B, T, num_heads, hs).transpose(1, 2).float()
+    o = out.view(B, T, num_heads, hs).transpose(1, 2).float()
+    scale = 1.0 / math.sqrt(hs)
+    s = (q @ k.transpose(-1, -2)) * scale
+    mask = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
+    p = torch.exp(s - (lse / math.log2(math.e)).unsqueeze(-1)).masked_fill(~mask, 0.0)
+    dv = p.transpose(-1, -2) @ do
+    dp = do @ v.transpose(-1, -2)
+    dsum = (do * o).sum(-1, keepdim=True)
+    ds = p * (dp - dsum) * scale
+    dq = ds @ k
+    dk = ds.transpose(-1, -2) @ q
+    dqkv.copy_(torch.cat([t.transpose(1, 2).reshape(B, T, C) for t in (dq, dk, dv)], dim=2))
+
+
+# ----------------------------------------------------------------------------- classifier
+def fused_classifier(logits, losses, targets, dloss: float, vocab_size: int, write_dlogits: bool = True) -> None:
+    """Per-row softmax cross-entropy; ``logits`` [rows,Vp] is overwritten with
+    dlogits = (softmax − onehot)·dloss, padded tail zeroed (llmm/fused_classifier.mojo:311-370)."""
+    Vp = logits.shape[-1]
+    rows = logits.numel() // Vp
+    if logits.is_cuda:
+        check(lib().llmb_fused_classifier(ptr(logits), ptr(losses), ptr(targets), float(dloss), rows, vocab_size, Vp,
+                                          int(write_dlogits), dtype_code(logits), stream()), "fused_classifier")
+        _count()
+    else:
+        lg = logits.view(rows, Vp)
+        x = lg[:, :vocab_size].float()
+        lsm = torch.log_softmax(x, dim=-1)
+        t = targets.reshape(rows).long()
+        if losses is not None:
+            losses.view(rows).copy_(-lsm.gather(1, t.unsqueeze(1)).squeeze(1))
+        if write_dlogits:
+            p = lsm.exp()
+            p.scatter_add_(1, t.unsqueeze(1), torch.full((rows, 1), -1.0, dtype=p.dtype))
+            lg[:, :vocab_size] = (p * dloss).to(lg.dtype)
+            lg[:, vocab_size:] = 0
+
+
+def softmax_rows(logits2d: torch.Tensor, vocab_size: int, temperature: float = 1.0) -> torch.Tensor:
+    """Row softmax over the first ``vocab_size`` columns → fp32 (llmm/softmax.mojo:306)."""
+    rows = logits2d.shape[0]
+    if logits2d.is_cuda:
+        out = torch.empty(rows, vocab_size, dtype=torch.float32, device=logits2d.device)
+        check(lib().llmb_softmax_rows(ptr(out), ptr(logits2d), rows, vocab_size, logits2d.stride(0),
+                                      1.0 / temperature, dtype_code(logits2d), stream()), "softmax_rows")
+        _count()
+        return out
+    return torch.softmax(logits2d[:, :vocab_size].float() / temperature, dim=-1)
+
+
+# ----------------------------------------------------------------------------- optimizer
+def adamw_update(params, master, grads, m, v, *, lr, beta1, beta2, eps, weight_decay, grad_scale, step,
+                 seed: int = 0, stochastic_rounding: bool = False, dev_scale=None) -> None:
+    """AdamW on a flat (shard of the) parameter vector; wd applies to every element
+    (llmm/adamw.mojo:93-211).  ``master`` (fp32) may be None when params are fp32.
+    ``dev_scale`` is an optional 1-element device tensor multiplied into ``grad_scale`` so the
+    clip factor never has to visit the host."""
+    n = grads.numel()
+    if grads.is_cuda:
+        check(lib().llmb_adamw(ptr(params), ptr(master), ptr(grads), ptr(m), ptr(v), n, lr, beta1, beta2, eps,
+                               weight_decay, grad_scale, ptr(dev_scale), step, seed, int(stochastic_rounding), dtype_code(params),
+                               stream()), "adamw")
+        _count()
+    else:
+        g = grads.float() * grad_scale
+        if dev_scale is not None:
+            g = g * dev_scale.float()
+        m.mul_(beta1).add_(g, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        mh = m / (1 - beta1 ** step)
+        vh = v / (1 - beta2 ** step)
+        p = master if master is not None else params.float()
+        p = p - lr * (mh / (vh.sqrt() + eps) + weight_decay * p)
+        if master is not None:
+            master.copy_(p)
+        params.copy_(p)
+
+
+def global_norm_squared(out, x, accumulate: bool = False) -> None:
+    """out[0] (=|+=) Σ x² (fp32; llmm/global_norm.mojo:194-282)."""
+    if x.is_cuda:
+        L = lib()
+        s = scratch("norm_sq", L.llmb_norm_sq_blocks() * 4, x.device)
+        check(L.llmb_global_norm_sq(ptr(out), ptr(x), x.numel(), ptr(s), int(accumulate), stream()), "global_norm_sq")
+        _count(2)
+    else:
+        val = (x.double() ** 2).sum().float()
+        if accumulate:
+            out[0] += val
+        else:
+            out[0] = val

@@ -1,0 +1,114 @@
+"""ctypes binding of ``csrc/libllmb200.so``.
+
+The library exports plain C functions that take raw device pointers and a stream and return
+a CUDA error code.  ``lib()`` raises if the shared object is missing: on a GPU box a silent
+fallback to PyTorch ops would hide a broken build.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_LIB: Optional[ctypes.CDLL] = None
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "libllmb200.so")
+
+c_int, c_ll, c_f, c_p, c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
+
+_SIGS = {
+    "llmb_encoder_fwd": [c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
+    "llmb_encoder_bwd_scratch_bytes": [c_int],
+    "llmb_encoder_bwd": [c_p, c_p, c_p, c_p, c_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_p],
+    "llmb_gelu_fwd": [c_p, c_p, c_ll, c_int, c_p],
+    "llmb_gelu_bwd": [c_p, c_p, c_p, c_ll, c_int, c_p],
+    "llmb_dbias_scratch_bytes": [c_int, c_int],
+    "llmb_dbias": [c_p, c_p, c_p, c_ll, c_int, c_int, c_int, c_p],
+    "llmb_cast_f32_to_bf16": [c_p, c_p, c_ll, c_p],
+    "llmb_layernorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p],
+    "llmb_layernorm_bwd_scratch_bytes": [c_int, c_int],
+    "llmb_layernorm_bwd": [c_p, c_p, c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
+    "llmb_fused_classifier": [c_p, c_p, c_p, c_f, c_int, c_int, c_int, c_int, c_int, c_p],
+    "llmb_softmax_rows": [c_p, c_p, c_int, c_int, c_int, c_f, c_int, c_p],
+    "llmb_adamw": [c_p, c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_f, c_f, c_p, c_int, c_ull, c_int, c_int, c_p],
+    "llmb_norm_sq_blocks": [],
+    "llmb_global_norm_sq": [c_p, c_p, c_ll, c_p, c_int, c_p],
+    "llmb_sr_cast_bf16": [c_p, c_p, c_ll, c_ull, c_p],
+    "llmb_gemm": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_p, c_p],
+    "llmb_gemm_debug_mn_strides": [c_int, c_int],
+    "llmb_attention_fwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
+    "llmb_attention_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
+}
+_RET_LL = {"llmb_encoder_bwd_scratch_bytes", "llmb_dbias_scratch_bytes", "llmb_layernorm_bwd_scratch_bytes"}
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return os.path.exists(_LIB_PATH)
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(_LIB_PATH):
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python -m llm_mojo_b200.build` "
+                "(CUDA tensors never fall back to PyTorch ops)")
+        L = ctypes.CDLL(_LIB_PATH)
+        for name, sig in _SIGS.items():
+            if not hasattr(L, name):
+                continue
+            fn = getattr(L, name)
+            fn.argtypes = sig
+            fn.restype = c_ll if name in _RET_LL else c_int
+        _LIB = L
+    return _LIB
+
+
+def ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(rc: int, name: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+
+
+# A device-resident status word that kernels with bounded waits set on expiry.
+_STATUS = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    t = _STATUS.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _STATUS[key] = t
+    return t
+
+
+def read_status(device: Optional[torch.device] = None) -> int:
+    """Synchronising read of the status word (0 = ok, 1 = a bounded wait expired)."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    return int(status_word(device).item())
