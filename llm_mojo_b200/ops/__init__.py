@@ -186,11 +186,12 @@ def gemm(D, A, B, *, a_mn=False, b_mn=False, epi=EPI_NONE, bias=None, aux=None, 
 
 
 def _splits_for(M: int, N: int, K: int) -> int:
+    """Split-K factor for the dW GEMMs: fill one wave of 148 CTAs when the output has few tiles."""
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     kb = (K + 63) // 64
     if tiles >= 148:
         return 1
-    return max(1, min(kb // 8 if kb >= 8 else 1, (2 * 148 + tiles - 1) // tiles))
+    return max(1, min(148 // tiles, kb // 4 if kb >= 4 else 1))
 
 
 def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> None:
@@ -273,6 +274,10 @@ def attention_fwd(out, lse, qkv, num_heads: int) -> None:
                                        stream()), "attention_fwd")
         _count()
         return
+    if qkv.is_cuda:      # library comparator (LLMB_ATTN=sdpa) and head sizes other than 64
+        q, k, v = (t.view(B, T, num_heads, hs).transpose(1, 2) for t in qkv.split(C, dim=2))
+        out.copy_(F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, C))
+        return
     q, k, v = (t.view(B, T, num_heads, hs).transpose(1, 2) for t in qkv.split(C, dim=2))
     s = (q.float() @ k.float().transpose(-1, -2)) / math.sqrt(hs)
     mask = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
@@ -294,6 +299,14 @@ def attention_bwd(dqkv, dout, qkv, out, lse, num_heads: int) -> None:
         check(lib().llmb_attention_bwd(ptr(dqkv), ptr(dvec), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T, num_heads,
                                        ptr(status_word(qkv.device)), stream()), "attention_bwd")
         _count(3)
+        return
+    if qkv.is_cuda:      # library comparator: recompute through SDPA under autograd
+        with torch.enable_grad():
+            leaf = qkv.detach().clone().requires_grad_(True)
+            q, k, v = (t.view(B, T, num_heads, hs).transpose(1, 2) for t in leaf.split(C, dim=2))
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, C)
+            o.backward(dout.view(B, T, C))
+        dqkv.copy_(leaf.grad)
         return
     q, k, v = (t.view(B, T, num_heads, hs).transpose(1, 2).float() for t in qkv.split(C, dim=2))
     do = dout.view(B, T, num_heads, hs).transpose(1, 2).float()
