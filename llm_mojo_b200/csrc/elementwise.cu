@@ -248,3 +248,47 @@ LLMB_API int llmb_cast_f32_to_bf16(void* out, const float* in, long long n, cuda
   cast_f32_to_bf16_kernel<<<sm_count() * 8, 256, 0, st>>>((__nv_bfloat16*)out, in, n);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- dbias without caller scratch
+// Variant of llmb_dbias for callers that cannot allocate device memory (see llmb_noalloc.h).
+// The partial sums live in a file-scope device array.  In host code `g_dbias_noalloc_scratch`
+// only names the symbol; its device address is fetched with cudaGetSymbolAddress once per
+// device and that pointer is what the kernels receive.
+#include "llmb_noalloc.h"
+static __device__ __align__(256) float g_dbias_noalloc_scratch[LLMB_DBIAS_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}
+
+LLMB_API int llmb_dbias_noalloc(float* dbias, const void* dout, int rows, int OC, int dtype, cudaStream_t st) {
+  if (rows <= 0 || OC <= 0 || !dbias || !dout) return LLMB_ERR_BAD_ARG;
+  const int slabs = llmb_dbias_slabs(rows);
+  if ((long long)slabs * OC > (long long)LLMB_DBIAS_NOALLOC_MAX_FLOATS) return LLMB_ERR_BAD_ARG;   // beyond the built-in scratch
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return LLMB_ERR_BAD_ARG;
+  if (!g_noalloc_ptr[dev]) {   // set-up, once per device, with that device current
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_dbias_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  float* scratch = g_noalloc_ptr[dev];
+  const int rows_per_slab = ceil_div(rows, slabs);
+  if (dtype == LLMB_BF16) {
+    if (OC % 8) return LLMB_ERR_BAD_ARG;
+    dim3 grid(ceil_div(OC, 32 * 8), slabs);
+    dbias_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(scratch, (const __nv_bfloat16*)dout, rows, OC, rows_per_slab);
+  } else if (dtype == LLMB_F32) {
+    if (OC % 4) return LLMB_ERR_BAD_ARG;
+    dim3 grid(ceil_div(OC, 32 * 4), slabs);
+    dbias_partial_kernel<float><<<grid, 256, 0, st>>>(scratch, (const float*)dout, rows, OC, rows_per_slab);
+  } else {
+    return LLMB_ERR_BAD_ARG;
+  }
+  dbias_final_kernel<<<ceil_div(OC, 256), 256, 0, st>>>(dbias, scratch, OC, slabs);
+  return (int)cudaGetLastError();
+}
