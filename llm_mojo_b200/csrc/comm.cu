@@ -50,7 +50,9 @@ __device__ __forceinline__ unsigned* flag_ptr(void* flags_base, int kind, int ra
   return reinterpret_cast<unsigned*>(flags_base) + kind * MAX_RANKS + rank;
 }
 
-// Bounded wait until every rank's flag of `kind` in OUR arena reaches `seq`.  ~2 s budget.
+__device__ unsigned g_wait_budget = 1u << 24;   // polls of ~400 ns each; tests shrink it to provoke a clean expiry
+
+// Bounded wait until every rank's flag of `kind` in OUR arena reaches `seq` (budget: several seconds).
 __device__ bool wait_all(void* my_flags, int kind, unsigned seq, int W, int* status) {
   __shared__ int ok_s;
   if (threadIdx.x == 0) {
@@ -59,7 +61,7 @@ __device__ bool wait_all(void* my_flags, int kind, unsigned seq, int W, int* sta
       const unsigned* f = flag_ptr(my_flags, kind, r);
       unsigned it = 0;
       while ((int)(ld_acquire_sys(f) - seq) < 0) {
-        if (++it > (1u << 22)) { ok = 0; break; }
+        if (++it > g_wait_budget) { ok = 0; break; }
         __nanosleep(400);
       }
     }
@@ -72,7 +74,7 @@ __device__ bool wait_all(void* my_flags, int kind, unsigned seq, int W, int* sta
 
 // The last block to finish stores `seq` into flag (kind, me) of every rank's arena.
 __device__ void signal_all_last_block(unsigned* counter, PeerPtrs flags, int kind, int me, unsigned seq, int W) {
-  __threadfence();
+  __threadfence_system();                 // this block's peer stores are visible system-wide before it is counted
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned done = atomicAdd(counter, 1u);
@@ -103,20 +105,6 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&v)[8]) {
   return t;
 }
 
-__device__ void block_sum_to(float* dst, float v) {
-  __shared__ float red[32];
-  v = warp_sum(v);
-  const int lane = threadIdx.x % 32, wid = threadIdx.x / 32;
-  if (lane == 0) red[wid] = v;
-  __syncthreads();
-  if (wid == 0) {
-    float t = lane < (int)(blockDim.x / 32) ? red[lane] : 0.f;
-    t = warp_sum(t);
-    if (lane == 0) *dst = t;
-  }
-  __syncthreads();
-}
-
 // ------------------------------------------------------------------ pack
 __global__ void __launch_bounds__(512) pack_kernel(__nv_bfloat16* __restrict__ send, const float* __restrict__ src, SegList segs,
                                                   float scale, void* my_flags, PeerPtrs flags, int me, int W,
@@ -145,7 +133,6 @@ __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList own
   if (!wait_all(my_flags, FLAG_READY, seq, W, status)) return;
   if (mode == 1 && wait_done2_seq && !wait_all(my_flags, FLAG_DONE2, wait_done2_seq, W, status)) return;
   const long long total = owned.vec_prefix[owned.n];
-  float nsq = 0.f;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
     const int s = find_seg(owned, v);
     const long long e = (v - owned.vec_prefix[s]) * 8;
@@ -170,7 +157,6 @@ __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList own
       for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recvs.p[r]) + so) = packed;
     }
   }
-  (void)nsq; (void)norm_partials;
   // peers may now overwrite their send buffers; (AR) results are in everybody's receive buffer
   signal_all_last_block(counter, flags, FLAG_DONE, me, seq, W);
   if (mode == 1) signal_all_last_block(counter2, flags, FLAG_READY2, me, seq, W);
@@ -357,6 +343,9 @@ LLMB_API int llmb_comm_adamw_push(void* const* param_ptrs, long long param_off, 
   adamw_push_kernel<<<grid, 256, 0, st>>>(to_peers(param_ptrs, push_w), param_off, (__nv_bfloat16*)shard_copy, master, grads, m, v, n, lr,
                                          beta1, beta2, bc1, bc2, eps, wd, grad_scale, dev_scale, push_w, to_peers(flag_ptrs, W), me, W, seq, counter);
   return (int)cudaGetLastError();
+}
+LLMB_API int llmb_comm_set_wait_budget(unsigned polls) {
+  return (int)cudaMemcpyToSymbol(g_wait_budget, &polls, sizeof(polls));
 }
 LLMB_API int llmb_comm_wait(void* my_flags, int kind, unsigned seq, int W, int* status, cudaStream_t st) {
   wait_flags_kernel<<<1, 32, 0, st>>>(my_flags, kind, seq, W, status);

@@ -101,16 +101,18 @@ class GPT2:
             self.param_offsets.append(self.param_offsets[-1] + s)
 
         if self.zero is not None:
-            self.zero.attach(self, flat)           # allocates params/grads/m/v/master (possibly sharded)
+            self.params = self.grads = self.m = self.v = self.master = None
+            self.p, self.g = {}, {}
+            self.zero.attach(self, flat)           # allocates (possibly sharded) buffers and installs the views
         else:
             self.params = flat.to(self.device, self.dtype)
             self.grads = torch.zeros(self.num_parameters, dtype=torch.float32, device=self.device)
             self.m = torch.zeros(self.num_parameters, dtype=torch.float32, device=self.device)
             self.v = torch.zeros(self.num_parameters, dtype=torch.float32, device=self.device)
             self.master = flat.to(self.device, torch.float32).clone() if self.precision.use_master else None
+            self.p = self._views(self.params)
+            self.g = self._views(self.grads)
         del flat
-        self.p = self._views(self.params) if self.params is not None else {}
-        self.g = self._views(self.grads) if self.grads is not None and self.grads.numel() >= self.num_parameters else {}
         self.B = self.T = 0
         self.acts: Dict[str, torch.Tensor] = {}
         self.mean_loss = -1.0

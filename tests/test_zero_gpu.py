@@ -1,0 +1,118 @@
+"""Peer-memory collectives and ZeRO on real GPUs (2 ranks as child processes, NVLS off, plain
+peer loads), plus the bounded-wait expiry path on one GPU."""
+import ctypes
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+from llm_mojo_b200.ops import _lib
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_bounded_wait_expires_cleanly():
+    """A flag that nothing sets: the wait kernel gives up, records LLMB_ERR_TIMEOUT and returns;
+    the context stays usable."""
+    L = _lib.lib()
+    L.llmb_comm_wait.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    L.llmb_comm_set_wait_budget.argtypes = [ctypes.c_uint]
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = _lib.status_word(torch.device("cuda", torch.cuda.current_device()))
+    status.zero_()
+    assert L.llmb_comm_set_wait_budget(1 << 10) == 0
+    try:
+        assert L.llmb_comm_wait(flags.data_ptr(), 0, 1, 1, status.data_ptr(), _lib.stream()) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 1
+        status.zero_()
+        flags[0] = 1                                      # now the flag is there: no expiry
+        assert L.llmb_comm_wait(flags.data_ptr(), 0, 1, 1, status.data_ptr(), _lib.stream()) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0   # context still healthy
+    finally:
+        L.llmb_comm_set_wait_budget(1 << 24)
+        status.zero_()
+
+
+WORKER = textwrap.dedent('''
+    import os, sys, json, torch, torch.distributed as dist
+    sys.path.insert(0, os.environ["LLMB_ROOT"])
+    from llm_mojo_b200.config import GPT2Config
+    from llm_mojo_b200.models import GPT2
+    from llm_mojo_b200.parallel.zero import ZeroEngine
+    from llm_mojo_b200.ops import _lib
+    rank, W = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    stage, backend = int(os.environ["STAGE"]), os.environ["BACKEND"]
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    cfg = GPT2Config(max_seq_len=128, vocab_size=1000, num_layer=2, num_heads=2, channels=128, padded_vocab_size=1024)
+    eng = ZeroEngine(stage, rank, W, torch.device("cuda", rank), backend=backend)
+    model = GPT2(cfg, "bf16", f"cuda:{rank}", zero=eng)
+    losses = []
+    for step in range(1, 4):
+        for micro in range(2):
+            g = torch.Generator().manual_seed(1000 * rank + 10 * step + micro)
+            t = torch.randint(0, cfg.vocab_size, (2, 129), generator=g, dtype=torch.int32)
+            model.forward(t[:, :-1].contiguous(), t[:, 1:].contiguous(), 2)
+            model.backward(2, micro)
+        norm = model.calculate_grad_norm()
+        model.update(step, lr=1e-3, weight_decay=0.01, dev_scale=model.clip_scale_from_norm(norm, 1.0))
+        losses.append(eng.mean_scalar(model.read_loss()))
+    torch.cuda.synchronize()
+    full = model.full_params().float().cpu()
+    st = _lib.read_status()
+    if rank == 0:
+        torch.save({"params": full, "losses": losses, "status": st, "norm": float(norm)}, os.environ["OUT"])
+    dist.barrier()
+    eng.close()
+    dist.destroy_process_group()
+''')
+
+
+def _port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _run(stage, backend, W, tmp):
+    out = os.path.join(tmp, f"z{stage}_{backend}.pt")
+    script = os.path.join(tmp, "worker.py")
+    with open(script, "w") as f:
+        f.write(WORKER)
+    port = _port()
+    procs = []
+    for r in range(W):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(W), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), STAGE=str(stage), BACKEND=backend, OUT=out, LLMB_ROOT=ROOT,
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, script], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o = "TIMEOUT"
+        logs.append(o)
+    assert all(p.returncode == 0 for p in procs), "\\n".join(logs)[-4000:]
+    return torch.load(out)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("stage", [0, 1, 2, 3])
+def test_p2p_matches_nccl(stage, tmp_path):
+    """Our peer-memory kernels (bf16 wire) against the torch.distributed/NCCL backend (fp32 wire)."""
+    a = _run(stage, "p2p", 2, str(tmp_path))
+    b = _run(stage, "nccl", 2, str(tmp_path))
+    assert a["status"] == 0 and b["status"] == 0
+    for la, lb in zip(a["losses"], b["losses"]):
+        assert abs(la - lb) < 2e-2, (a["losses"], b["losses"])
+    rel = ((a["params"] - b["params"]).norm() / b["params"].norm()).item()
+    assert rel < 2e-3, rel
+    assert a["losses"][-1] < a["losses"][0]
