@@ -89,7 +89,7 @@ def run_ours(args, rank, world, local_rank):
                       total_batch_size=args.total_batch, learning_rate=6e-4, lr_scheduler_type="cosine",
                       warmup_iterations=10, final_learning_rate_frac=0.1, weight_decay=0.1, zero_stage=args.zero,
                       max_steps=10_000, precision="bf16", grad_clip=1.0, beta2=0.95, synthetic=True,
-                      val_loss_every=0, sample_every=0)
+                      val_loss_every=0, sample_every=0, comm_backend=os.environ.get("LLMB_COMM", "auto"))
     tr = Trainer(targs, rank, world, local_rank)
     model, B, T = tr.model, args.batch, args.seq
     ga = tr.grad_accum
@@ -115,6 +115,7 @@ def run_ours(args, rank, world, local_rank):
     for s in range(args.warmup):
         device_step(s)
     barrier()
+    model.read_loss()                      # reset the on-device loss accumulator
     sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
@@ -128,7 +129,7 @@ def run_ours(args, rank, world, local_rank):
     dev_ms = e0.elapsed_time(e1)
     launches = ops.LAUNCHES - launches0
     clocks = sampler.stop() if rank == 0 else None
-    final_loss = model.read_loss()
+    final_loss = model.read_loss() / args.steps      # mean over the timed steps
     status = ops._lib.read_status()
 
     # ---------------- end-to-end region through Trainer.train_step (H2D tokens + D2H loss per step)
