@@ -7,7 +7,8 @@
 // permutes), keep S/P and the running output in TMEM / shared memory, and store only the
 // output [B,T,C] plus one log-sum-exp per row.
 //
-// Forward  : CTA = 128 query rows of one (batch, head); thread t owns row t.
+// Forward  : CTA = 128 query rows of one (batch, head), 256 threads: two threads share a row, each
+//            owning one 64-column half of the score tile (warps w and w+4 read the same TMEM lanes).
 //            S = Q K^T (tcgen05, 128x128 fp32 in TMEM) -> online softmax in registers ->
 //            P (bf16, swizzled smem) -> O += P V (tcgen05, O in TMEM, rescaled in place).
 // Backward : two deterministic kernels (no atomics).
@@ -60,6 +61,10 @@ __device__ __forceinline__ void store_row32(unsigned char* tile, int row, int c0
   }
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
+}
+
 constexpr uint32_t IDESC_S_128x128 = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, 128);   // K-major x K-major
 constexpr uint32_t IDESC_128x64_KK = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, 64);
 constexpr uint32_t IDESC_128x64_KMN = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, 64);   // B stored [K rows, N]
@@ -88,7 +93,7 @@ __device__ __forceinline__ void load128(unsigned char* dst, const CUtensorMap* t
 // dynamic segment is declared 1024-byte aligned and the kernel verifies that before touching it.
 constexpr int FWD_SMEM = T128 /*Q*/ + 2 * T128 /*K*/ + 2 * T128 /*V*/ + 2 * T128 /*P*/ + 128;
 
-__global__ void __launch_bounds__(128, 2) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+__global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   extern __shared__ __align__(1024) unsigned char smem_fwd[];
   unsigned char* sm = smem_fwd;
   if (smem_u32(sm) & 1023u) { if (threadIdx.x == 0) atomicExch(p.status, LLMB_ERR_BAD_ARG); return; }
@@ -101,7 +106,9 @@ __global__ void __launch_bounds__(128, 2) attn_fwd_kernel(const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   int fail = 0, stopped = 0;
 
-  const int tid = threadIdx.x, warp = tid / 32;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int hb = warp >> 2;                // which 64-column half of S / 32-column half of O this thread owns
+  const int row = (warp & 3) * 32 + lane;  // row of the tile == TMEM lane
   const int n_qt = ceil_div(p.T, TILE);
   const int qt = n_qt - 1 - blockIdx.x;    // heavy tiles first
   const int h = blockIdx.y, b = blockIdx.z;
@@ -118,7 +125,7 @@ __global__ void __launch_bounds__(128, 2) attn_fwd_kernel(const __grid_constant_
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
   const int n_kv = qt + 1;
   const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
@@ -130,8 +137,9 @@ __global__ void __launch_bounds__(128, 2) attn_fwd_kernel(const __grid_constant_
     load128(sV, &tm, &kv_bar[0], colV, 0, b);
   }
 
-  const int qi = q0 + tid;
-  float m_run = -INFINITY, l_run = 0.f;
+  const int qi = q0 + row;
+  const float sc = p.scale_log2;
+  float m_run = -INFINITY, l_run = 0.f;    // l_run: partial row sum over this thread's column half
 
   for (int j = 0; j < n_kv; ++j) {
     const int st = j & 1;
@@ -152,54 +160,58 @@ __global__ void __launch_bounds__(128, 2) attn_fwd_kernel(const __grid_constant_
     if (!mbar_wait(s_bar, j & 1)) ATTN_FAIL();
     fence_after_sync();
 
-    // ---- pass 1: row max
+    // ---- pass 1: full-row max (both threads of a row read all 128 columns; own half stays in registers)
     const bool diag = (j == n_kv - 1);
-    float mx = m_run;
-#pragma unroll 1
+    uint32_t own[2][32];
+    float mx = -INFINITY;
+#pragma unroll
     for (int c = 0; c < 4; ++c) {
+      const bool mine = (c >> 1) == hb;
+      if (diag && c > (warp & 3)) {                       // chunk entirely above the diagonal for this warp
+        if (mine) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) own[c & 1][i] = 0xff800000u;   // -inf
+        }
+        continue;
+      }
       uint32_t r[32];
       tmem_ld32(tS + lane_addr + c * 32, r);
       tmem_wait_ld();
+      if (diag && c == (warp & 3)) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float s = __uint_as_float(r[i]) * p.scale_log2;
-        if (diag && (j * TILE + c * 32 + i > qi)) s = -INFINITY;
-        mx = fmaxf(mx, s);
+        for (int i = 0; i < 32; ++i) if (i > lane) r[i] = 0xff800000u;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+      if (mine) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) own[c & 1][i] = r[i];
       }
     }
-    const float alpha = exp2f(m_run - mx);
-    m_run = mx;
-    // ---- pass 2: p = 2^(s - m), row sum, P -> smem
+    const float m_new = fmaxf(m_run, mx * sc);
+    const float alpha = ex2_approx(m_run - m_new);
+    m_run = m_new;
+    // ---- pass 2: p = 2^(s*sc - m) over the own half, row sum, P -> smem (half hb of the P tile)
     float rs = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tS + lane_addr + c * 32, r);
-      tmem_wait_ld();
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        float s = __uint_as_float(r[i]) * p.scale_log2;
-        float e = exp2f(s - mx);
-        if (diag && (j * TILE + c * 32 + i > qi)) e = 0.f;
-        // accumulate the row sum from the bf16-rounded value that the PV product will use
-        e = __bfloat162float(__float2bfloat16_rn(e));
+        const float e = ex2_approx(fmaf(__uint_as_float(own[c][i]), sc, -m_new));
         v[i] = e; rs += e;
       }
-      store_row32(sP + (c >> 1) * T128, tid, (c & 1) * 32, v);
+      store_row32(sP + hb * T128, row, c * 32, v);
     }
     l_run = l_run * alpha + rs;
-    // ---- rescale running output
-    if (j > 0) {
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tO + lane_addr + c * 32, r);
-        tmem_wait_ld();
+    // ---- rescale the running output (this thread: 32 of the 64 columns); skipped when no row of the warp moved
+    if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+      uint32_t r[32];
+      tmem_ld32(tO + lane_addr + hb * 32, r);
+      tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-        tmem_st32(tO + lane_addr + c * 32, r);
-      }
+      for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+      tmem_st32(tO + lane_addr + hb * 32, r);
       tmem_wait_st();
     }
     fence_proxy_async();
@@ -217,28 +229,29 @@ __global__ void __launch_bounds__(128, 2) attn_fwd_kernel(const __grid_constant_
     if (__syncthreads_or(fail)) { stopped = 1; break; }
   }
 
-  // ---- epilogue: O / l -> bf16, LSE
+  // ---- epilogue: combine the two partial row sums, O / l -> bf16, LSE
   if (!stopped) {
-    const float inv = 1.0f / l_run;
-    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)b * p.T + qi) * p.C + h * HS;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tO + lane_addr + c * 32, r);
-      tmem_wait_ld();
-      if (qi < p.T) {
+    float* lsum = reinterpret_cast<float*>(sP);           // P is dead after the last PV product
+    lsum[hb * 128 + row] = l_run;
+    __syncthreads();
+    const float l_tot = lsum[row] + lsum[128 + row];
+    const float inv = 1.0f / l_tot;
+    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)b * p.T + qi) * p.C + h * HS + hb * 32;
+    uint32_t r[32];
+    tmem_ld32(tO + lane_addr + hb * 32, r);
+    tmem_wait_ld();
+    if (qi < p.T) {
 #pragma unroll
-        for (int j8 = 0; j8 < 4; ++j8) {
-          uint4 u;
-          u.x = pack_bf16x2(__uint_as_float(r[j8 * 8 + 0]) * inv, __uint_as_float(r[j8 * 8 + 1]) * inv);
-          u.y = pack_bf16x2(__uint_as_float(r[j8 * 8 + 2]) * inv, __uint_as_float(r[j8 * 8 + 3]) * inv);
-          u.z = pack_bf16x2(__uint_as_float(r[j8 * 8 + 4]) * inv, __uint_as_float(r[j8 * 8 + 5]) * inv);
-          u.w = pack_bf16x2(__uint_as_float(r[j8 * 8 + 6]) * inv, __uint_as_float(r[j8 * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(op + c * 32 + j8 * 8) = u;
-        }
+      for (int j8 = 0; j8 < 4; ++j8) {
+        uint4 u;
+        u.x = pack_bf16x2(__uint_as_float(r[j8 * 8 + 0]) * inv, __uint_as_float(r[j8 * 8 + 1]) * inv);
+        u.y = pack_bf16x2(__uint_as_float(r[j8 * 8 + 2]) * inv, __uint_as_float(r[j8 * 8 + 3]) * inv);
+        u.z = pack_bf16x2(__uint_as_float(r[j8 * 8 + 4]) * inv, __uint_as_float(r[j8 * 8 + 5]) * inv);
+        u.w = pack_bf16x2(__uint_as_float(r[j8 * 8 + 6]) * inv, __uint_as_float(r[j8 * 8 + 7]) * inv);
+        *reinterpret_cast<uint4*>(op + j8 * 8) = u;
       }
+      if (hb == 0) p.lse[((size_t)b * p.NH + h) * p.T + qi] = m_run + log2f(l_tot);
     }
-    if (qi < p.T) p.lse[((size_t)b * p.NH + h) * p.T + qi] = m_run + log2f(l_run);
   }
   fence_before_sync();
   __syncthreads();
@@ -268,7 +281,7 @@ __global__ void attn_bwd_prep_kernel(float* __restrict__ dvec, const __nv_bfloat
 // =================================================================== backward: dK, dV
 constexpr int DKV_SMEM = 2 * T128 /*K,V*/ + 4 * T64 /*Q,dO x2 stages*/ + 2 * T128 /*PT,dST*/ + 4 * 64 * 4 + 1024 + 128;
 
-__global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV,
+__global__ void __launch_bounds__(256, 2) attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQKV,
                                                              const __grid_constant__ CUtensorMap tmDO, const AttnParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -285,7 +298,9 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   int fail = 0, stopped = 0;
 
-  const int tid = threadIdx.x, warp = tid / 32;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int hb = warp >> 2;                // 32-column half of each 64-column tile this thread owns
+  const int row = (warp & 3) * 32 + lane;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kv0 = kt * TILE;
   const int n_qc = ceil_div(p.T, 64);
@@ -302,7 +317,7 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tST = tmem, tDPT = tmem + 64, tDV = tmem + 128, tDK = tmem + 192;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
   const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
   if (tid == 0) {
@@ -315,7 +330,7 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
       tma_load_3d(sDO, &tmDO, &q_bar[0], colQ, i0 * 64, b);
     }
   }
-  const int kj = kv0 + tid;
+  const int kj = kv0 + row;
   const size_t stat_base = ((size_t)b * p.NH + h) * p.T;
 
   for (int i = i0, n = 0; i < n_qc; ++i, ++n) {
@@ -324,7 +339,7 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
     {
       const int qcol = i * 64 + (tid & 63);
       if (tid < 64) sLse[st * 64 + tid] = qcol < p.T ? p.lse[stat_base + qcol] : INFINITY;
-      else sD[st * 64 + (tid & 63)] = qcol < p.T ? p.dvec[stat_base + qcol] : 0.f;
+      else if (tid < 128) sD[st * 64 + (tid & 63)] = qcol < p.T ? p.dvec[stat_base + qcol] : 0.f;
     }
     if (tid == 0) {
       if (i + 1 < n_qc) {
@@ -346,8 +361,8 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
     fence_after_sync();
 
     const bool need_mask = (i * 64 < kv0 + TILE);
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
+    {
+      const int c = hb;
       uint32_t rs[32], rp[32];
       tmem_ld32(tST + lane_addr + c * 32, rs);
       tmem_ld32(tDPT + lane_addr + c * 32, rp);
@@ -356,13 +371,13 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
 #pragma unroll
       for (int x = 0; x < 32; ++x) {
         const int col = c * 32 + x;
-        float pr = exp2f(__uint_as_float(rs[x]) * p.scale_log2 - sLse[st * 64 + col]);
+        float pr = ex2_approx(fmaf(__uint_as_float(rs[x]), p.scale_log2, -sLse[st * 64 + col]));
         if (need_mask && (kj > i * 64 + col)) pr = 0.f;
         pv[x] = pr;
         dv[x] = pr * (__uint_as_float(rp[x]) - sD[st * 64 + col]) * p.scale;
       }
-      store_row32(sPT, tid, c * 32, pv);
-      store_row32(sDST, tid, c * 32, dv);
+      store_row32(sPT, row, c * 32, pv);
+      store_row32(sDST, row, c * 32, dv);
     }
     fence_proxy_async();
     fence_before_sync();
@@ -383,25 +398,22 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
     const bool have = i0 < n_qc;
 #pragma unroll 1
     for (int which = 0; which < 2; ++which) {
-      __nv_bfloat16* dp = base + (which == 0 ? 2 * p.C : p.C);
+      __nv_bfloat16* dp = base + (which == 0 ? 2 * p.C : p.C) + hb * 32;
       const uint32_t tsrc = which == 0 ? tDV : tDK;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tsrc + lane_addr + c * 32, r);
-        tmem_wait_ld();
-        if (kj < p.T) {
+      uint32_t r[32];
+      tmem_ld32(tsrc + lane_addr + hb * 32, r);
+      tmem_wait_ld();
+      if (kj < p.T) {
 #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8) {
-            uint4 u;
-            if (have) {
-              u.x = pack_bf16x2(__uint_as_float(r[j8 * 8 + 0]), __uint_as_float(r[j8 * 8 + 1]));
-              u.y = pack_bf16x2(__uint_as_float(r[j8 * 8 + 2]), __uint_as_float(r[j8 * 8 + 3]));
-              u.z = pack_bf16x2(__uint_as_float(r[j8 * 8 + 4]), __uint_as_float(r[j8 * 8 + 5]));
-              u.w = pack_bf16x2(__uint_as_float(r[j8 * 8 + 6]), __uint_as_float(r[j8 * 8 + 7]));
-            } else { u = make_uint4(0, 0, 0, 0); }
-            *reinterpret_cast<uint4*>(dp + c * 32 + j8 * 8) = u;
-          }
+        for (int j8 = 0; j8 < 4; ++j8) {
+          uint4 u;
+          if (have) {
+            u.x = pack_bf16x2(__uint_as_float(r[j8 * 8 + 0]), __uint_as_float(r[j8 * 8 + 1]));
+            u.y = pack_bf16x2(__uint_as_float(r[j8 * 8 + 2]), __uint_as_float(r[j8 * 8 + 3]));
+            u.z = pack_bf16x2(__uint_as_float(r[j8 * 8 + 4]), __uint_as_float(r[j8 * 8 + 5]));
+            u.w = pack_bf16x2(__uint_as_float(r[j8 * 8 + 6]), __uint_as_float(r[j8 * 8 + 7]));
+          } else { u = make_uint4(0, 0, 0, 0); }
+          *reinterpret_cast<uint4*>(dp + j8 * 8) = u;
         }
       }
     }
@@ -414,7 +426,7 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dkv_kernel(const __grid_const
 // =================================================================== backward: dQ
 constexpr int DQ_SMEM = 2 * T128 /*Q,dO*/ + 4 * T64 /*K,V x2 stages*/ + T128 /*dS*/ + 1024 + 128;
 
-__global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQKV,
+__global__ void __launch_bounds__(256, 2) attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQKV,
                                                             const __grid_constant__ CUtensorMap tmDO, const AttnParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -428,7 +440,9 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   int fail = 0, stopped = 0;
 
-  const int tid = threadIdx.x, warp = tid / 32;
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int hb = warp >> 2;
+  const int row = (warp & 3) * 32 + lane;
   const int n_qt = ceil_div(p.T, TILE);
   const int qt = n_qt - 1 - blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -446,7 +460,7 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_consta
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tDP = tmem + 64, tDQ = tmem + 128;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
   const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
   if (tid == 0) {
@@ -457,7 +471,7 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_consta
     tma_load_3d(sK, &tmQKV, &kv_bar[0], colK, 0, b);
     tma_load_3d(sV, &tmQKV, &kv_bar[0], colV, 0, b);
   }
-  const int qi = q0 + tid;
+  const int qi = q0 + row;
   const size_t stat = ((size_t)b * p.NH + h) * p.T + qi;
   const float lse = qi < p.T ? p.lse[stat] : INFINITY;
   const float dsum = qi < p.T ? p.dvec[stat] : 0.f;
@@ -482,8 +496,8 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_consta
     if (!mbar_wait(b1, j & 1)) ATTN_FAIL();
     fence_after_sync();
     const bool need_mask = ((j + 1) * 64 - 1 > q0);
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
+    {
+      const int c = hb;
       uint32_t rs[32], rp[32];
       tmem_ld32(tS + lane_addr + c * 32, rs);
       tmem_ld32(tDP + lane_addr + c * 32, rp);
@@ -492,11 +506,11 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_consta
 #pragma unroll
       for (int x = 0; x < 32; ++x) {
         const int kcol = j * 64 + c * 32 + x;
-        float pr = exp2f(__uint_as_float(rs[x]) * p.scale_log2 - lse);
+        float pr = ex2_approx(fmaf(__uint_as_float(rs[x]), p.scale_log2, -lse));
         if (need_mask && kcol > qi) pr = 0.f;
         dv[x] = pr * (__uint_as_float(rp[x]) - dsum) * p.scale;
       }
-      store_row32(sDS, tid, c * 32, dv);
+      store_row32(sDS, row, c * 32, dv);
     }
     fence_proxy_async();
     fence_before_sync();
@@ -512,22 +526,19 @@ __global__ void __launch_bounds__(128, 2) attn_bwd_dq_kernel(const __grid_consta
   }
 
   if (!stopped) {
-    __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)b * p.T + qi) * (3 * (size_t)p.C) + h * HS;
-#pragma unroll 1
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tDQ + lane_addr + c * 32, r);
-      tmem_wait_ld();
-      if (qi < p.T) {
+    __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)b * p.T + qi) * (3 * (size_t)p.C) + h * HS + hb * 32;
+    uint32_t r[32];
+    tmem_ld32(tDQ + lane_addr + hb * 32, r);
+    tmem_wait_ld();
+    if (qi < p.T) {
 #pragma unroll
-        for (int j8 = 0; j8 < 4; ++j8) {
-          uint4 u;
-          u.x = pack_bf16x2(__uint_as_float(r[j8 * 8 + 0]), __uint_as_float(r[j8 * 8 + 1]));
-          u.y = pack_bf16x2(__uint_as_float(r[j8 * 8 + 2]), __uint_as_float(r[j8 * 8 + 3]));
-          u.z = pack_bf16x2(__uint_as_float(r[j8 * 8 + 4]), __uint_as_float(r[j8 * 8 + 5]));
-          u.w = pack_bf16x2(__uint_as_float(r[j8 * 8 + 6]), __uint_as_float(r[j8 * 8 + 7]));
-          *reinterpret_cast<uint4*>(dp + c * 32 + j8 * 8) = u;
-        }
+      for (int j8 = 0; j8 < 4; ++j8) {
+        uint4 u;
+        u.x = pack_bf16x2(__uint_as_float(r[j8 * 8 + 0]), __uint_as_float(r[j8 * 8 + 1]));
+        u.y = pack_bf16x2(__uint_as_float(r[j8 * 8 + 2]), __uint_as_float(r[j8 * 8 + 3]));
+        u.z = pack_bf16x2(__uint_as_float(r[j8 * 8 + 4]), __uint_as_float(r[j8 * 8 + 5]));
+        u.w = pack_bf16x2(__uint_as_float(r[j8 * 8 + 6]), __uint_as_float(r[j8 * 8 + 7]));
+        *reinterpret_cast<uint4*>(dp + j8 * 8) = u;
       }
     }
   }
@@ -554,7 +565,7 @@ LLMB_API int llmb_attention_fwd(void* out, float* lse, const void* qkv, int B, i
   static bool attr = false;
   if (!attr) { cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM); if (e) return (int)e; attr = true; }
   dim3 grid(ceil_div(T, TILE), NH, B);
-  attn_fwd_kernel<<<grid, 128, FWD_SMEM, st>>>(tm, p);
+  attn_fwd_kernel<<<grid, 256, FWD_SMEM, st>>>(tm, p);
   return (int)cudaGetLastError();
 }
 
@@ -576,7 +587,7 @@ LLMB_API int llmb_attention_bwd(void* dqkv, float* dvec, const void* dout, const
   long long total = (long long)B * T * NH;
   attn_bwd_prep_kernel<<<(unsigned)ceil_div_ll(total, 256), 256, 0, st>>>(dvec, (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, B, T, NH, C);
   dim3 grid(ceil_div(T, TILE), NH, B);
-  attn_bwd_dkv_kernel<<<grid, 128, DKV_SMEM, st>>>(tq, td, p);
-  attn_bwd_dq_kernel<<<grid, 128, DQ_SMEM, st>>>(tq, td, p);
+  attn_bwd_dkv_kernel<<<grid, 256, DKV_SMEM, st>>>(tq, td, p);
+  attn_bwd_dq_kernel<<<grid, 256, DQ_SMEM, st>>>(tq, td, p);
   return (int)cudaGetLastError();
 }
