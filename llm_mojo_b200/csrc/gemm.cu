@@ -15,6 +15,7 @@
 // MN-major (the UMMA descriptor and the TMA box change, not the data), which is how dinp
 // (B = W as stored) and dW (A = dout^T, B = inp^T as stored) run without any transposes.
 // Split-K work units reduce through fp32 red.global.add into the (fp32) gradient buffer.
+#include <stdlib.h>
 #include "tc05.cuh"
 using namespace llmb;
 using namespace tc05;
@@ -42,8 +43,68 @@ struct GemmParams {
   int bke;                     // K elements per stage
   int mma_per_stage;
   int m_tiles, n_tiles, splits, kb_per_split, kb_total;
+  int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0)
   int* status;
 };
+
+// Applies the epilogue to 32 accumulator columns of one output row and stores them.
+template <int EPI>
+__device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float alpha) {
+          float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+  if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
+    if (p.bias) {
+      const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+      for (int j8 = 0; j8 < 4; ++j8) {
+        if (col0 + j8 * 8 < p.N) {
+          Pack<__nv_bfloat16> b; b.load(bp + j8 * 8);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[j8 * 8 + k] += b.v[k];
+        }
+      }
+    }
+  }
+  if (EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32) {
+    float* dp = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      if (col0 + j4 * 4 < p.N) {
+        if (EPI == EPI_ACC_F32)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + j4 * 4), "f"(v[j4 * 4]), "f"(v[j4 * 4 + 1]),
+                       "f"(v[j4 * 4 + 2]), "f"(v[j4 * 4 + 3]) : "memory");
+        else
+          *reinterpret_cast<float4*>(dp + j4 * 4) = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+      }
+    }
+  } else {
+    __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
+    __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux) + (size_t)row * p.ldaux + col0;
+#pragma unroll
+    for (int j8 = 0; j8 < 4; ++j8) {
+      if (col0 + j8 * 8 < p.N) {
+        Pack<__nv_bfloat16> o;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o.v[k] = v[j8 * 8 + k];
+        if (EPI == EPI_BIAS_GELU) {
+          o.store(ap + j8 * 8);                       // pre-GELU activations (bf16)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o.v[k] = gelu_f(__bfloat162float(__float2bfloat16_rn(o.v[k])));
+        } else if (EPI == EPI_DGELU) {
+          Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o.v[k] *= gelu_grad_f(x.v[k]);
+        } else if (EPI == EPI_BIAS_RESID) {
+          Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o.v[k] += x.v[k];
+        }
+        o.store(dp + j8 * 8);
+      }
+    }
+  }
+}
 
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -165,62 +226,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
         tmem_wait_ld();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
-          if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
-            if (p.bias) {
-              const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
-#pragma unroll
-              for (int j8 = 0; j8 < 4; ++j8) {
-                if (col0 + j8 * 8 < p.N) {
-                  Pack<__nv_bfloat16> b; b.load(bp + j8 * 8);
-#pragma unroll
-                  for (int k = 0; k < 8; ++k) v[j8 * 8 + k] += b.v[k];
-                }
-              }
-            }
-          }
-          if (EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32) {
-            float* dp = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
-#pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
-              if (col0 + j4 * 4 < p.N) {
-                if (EPI == EPI_ACC_F32)
-                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + j4 * 4), "f"(v[j4 * 4]), "f"(v[j4 * 4 + 1]),
-                               "f"(v[j4 * 4 + 2]), "f"(v[j4 * 4 + 3]) : "memory");
-                else
-                  *reinterpret_cast<float4*>(dp + j4 * 4) = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
-              }
-            }
-          } else {
-            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
-            __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux) + (size_t)row * p.ldaux + col0;
-#pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
-              if (col0 + j8 * 8 < p.N) {
-                Pack<__nv_bfloat16> o;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) o.v[k] = v[j8 * 8 + k];
-                if (EPI == EPI_BIAS_GELU) {
-                  o.store(ap + j8 * 8);                       // pre-GELU activations (bf16)
-#pragma unroll
-                  for (int k = 0; k < 8; ++k) o.v[k] = gelu_f(__bfloat162float(__float2bfloat16_rn(o.v[k])));
-                } else if (EPI == EPI_DGELU) {
-                  Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
-#pragma unroll
-                  for (int k = 0; k < 8; ++k) o.v[k] *= gelu_grad_f(x.v[k]);
-                } else if (EPI == EPI_BIAS_RESID) {
-                  Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
-#pragma unroll
-                  for (int k = 0; k < 8; ++k) o.v[k] += x.v[k];
-                }
-                o.store(dp + j8 * 8);
-              }
-            }
-          }
-        }
+        if (row < p.M && col0 < p.N) epilogue_store32<EPI>(p, r, row, col0, alpha);
       }
       fence_before_sync();
       __syncwarp();
@@ -233,12 +239,186 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) { fence_after_sync(); tmem_dealloc<512>(tmem_base); }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs computes a 256 x 256 tile with cta_group::2 MMAs.  Each
+// CTA stages its own 128 rows of A and its own 128-row half of B (half the B traffic per SM, and
+// a 6-deep ring of 32 KB stages instead of 4 x 48 KB), the leader issues the MMAs, and both
+// CTAs drain their 128 x 256 accumulator halves.  No load is multicast: every CTA fetches only
+// the tiles it owns; the peer's TMA completions are reported to the leader's mbarrier.
+constexpr int STAGES2 = 6;
+constexpr int B2_STAGE = 128 * ROW_BYTES;             // 16 KB: this CTA's half of the B tile
+constexpr int STAGE2_BYTES = A_STAGE + B2_STAGE;      // 32 KB
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+
+template <int KIND, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES2;
+  uint64_t* tfull_bar = empty_bar + STAGES2;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const uint32_t cta = cluster_ctarank();              // 0 = leader
+  const bool leader = cta == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }   // 4 warps x 2 CTAs
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tmem_alloc_pair<512>(tmem_slot);
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                   // both CTAs' barriers exist before any remote signal
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = ceil_div(p.M, 2 * BM);            // cluster tiles of 256 rows
+  const int tiles_per_split = m_tiles * p.n_tiles;
+  const int total_units = tiles_per_split * p.splits;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  constexpr int BAND2 = 8;
+
+  auto unit_coords = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+    int split = unit / tiles_per_split, t = unit % tiles_per_split;
+    int band_sz = BAND2 * p.n_tiles;
+    int b = t / band_sz, r = t % band_sz;
+    int m_in_band = min(BAND2, m_tiles - b * BAND2);
+    m_blk = b * BAND2 + r % m_in_band;
+    n_blk = r / m_in_band;
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
+        int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+        int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
+        if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+          unsigned char* sa = smem + stage * STAGE2_BYTES;
+          unsigned char* sb = sa + A_STAGE;
+          const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE2_BYTES);     // bytes of both CTAs
+          const int k0 = (p.dbg & 2) ? 0 : kb * p.bke;
+          if (!p.a_mn) tma_load_2d_pair(sa, &tmA, lead_full, k0, m0);
+          else {
+            const int chunk_elems = p.bke, nchunk = BM / chunk_elems;
+            for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sa + c * p.bke * ROW_BYTES, &tmA, lead_full, m0 + c * chunk_elems, k0);
+          }
+          if (!p.b_mn) tma_load_2d_pair(sb, &tmB, lead_full, k0, n0);
+          else {
+            const int chunk_elems = p.bke, nchunk = 128 / chunk_elems;
+            for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sb + c * p.bke * ROW_BYTES, &tmB, lead_full, n0 + c * chunk_elems, k0);
+          }
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters, ++it) {
+        int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE2_BYTES);
+          const uint32_t sb = sa + A_STAGE;
+          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo);
+          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo);
+          for (int k = 0; k < p.mma_per_stage; ++k) {
+            umma_ss_pair<KIND>(d_tmem, adesc + (uint64_t)((k * p.a_kstep) >> 4), bdesc + (uint64_t)((k * p.b_kstep) >> 4),
+                               p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          umma_commit_pair(mapa_u32(eb, 0));              // stage free in both CTAs once these MMAs have read it
+          umma_commit_pair(mapa_u32(eb, 1));
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        const uint32_t tb = smem_u32(&tfull_bar[acc]);
+        umma_commit_pair(mapa_u32(tb, 0));
+        umma_commit_pair(mapa_u32(tb, 1));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    int it = 0;
+    for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters, ++it) {
+      int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+      fence_after_sync();
+      const int row = m_blk * 2 * BM + (int)cta * BM + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      const float alpha = p.alpha ? *p.alpha : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N && !(p.dbg & 1)) epilogue_store32<EPI>(p, r, row, col0, alpha);
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));   // the leader owns the accumulator hand-back
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                                   // the peer may still be signalling / reading this CTA's smem
+  if (warp == 1) { fence_after_sync(); tmem_dealloc_pair<512>(tmem_base); }
+}
+
 template <int KIND> struct KindTraits;
 template <> struct KindTraits<KIND_F16> { static constexpr int ESZ = 2; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; };
 template <> struct KindTraits<KIND_TF32> { static constexpr int ESZ = 4; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; };
 template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ESZ = 1; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
 
 int g_dbg_mn_lbo = -1, g_dbg_mn_sbo = -1;   // test hooks: override the MN-major descriptor strides
+int g_pair_mode = -1;                         // -1: read LLMB_GEMM_PAIR once; 0: single-CTA tiles; 1: CTA-pair tiles
+
+bool pair_mode() {
+  if (g_pair_mode < 0) { const char* e = getenv("LLMB_GEMM_PAIR"); g_pair_mode = (e && e[0] == '0') ? 0 : 1; }
+  return g_pair_mode == 1;
+}
+
+template <int KIND, int EPI>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  gemm_pair_kernel<KIND, EPI><<<grid, NUM_THREADS, SMEM2_BYTES, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
 
 template <int KIND, int EPI>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
@@ -264,14 +444,16 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   if ((lda * ESZ) % 16 || (ldb * ESZ) % 16 || N % 8) return LLMB_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D)) & 15) return LLMB_ERR_BAD_ARG;
 
+  const bool pair = pair_mode();
   CUtensorMap ta, tb;
   int rc;
   // K-major: global [MN rows, K cols], box [tile rows, ROW_ELEMS]; MN-major: global [K rows, MN cols], box [BKE, ROW_ELEMS]
+  // (in pair mode each CTA fetches a 128-row half of the B tile)
   rc = a_mn ? make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BKE, ROW_ELEMS)
             : make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, ROW_ELEMS);
   if (rc) return 1000 + rc;
   rc = b_mn ? make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BKE, ROW_ELEMS)
-            : make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN, ROW_ELEMS);
+            : make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? 128 : BN, ROW_ELEMS);
   if (rc) return 1000 + rc;
 
   GemmParams p;
@@ -282,7 +464,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   const uint32_t mn_sbo = g_dbg_mn_sbo >= 0 ? (uint32_t)g_dbg_mn_sbo : 1024u;
   p.a_lbo = a_mn ? mn_lbo : 16; p.a_sbo = a_mn ? mn_sbo : 1024; p.a_kstep = a_mn ? MMA_K * ROW_BYTES : 32;
   p.b_lbo = b_mn ? mn_lbo : 16; p.b_sbo = b_mn ? mn_sbo : 1024; p.b_kstep = b_mn ? MMA_K * ROW_BYTES : 32;
-  p.idesc = make_idesc((uint32_t)a_fmt, (uint32_t)b_fmt, (uint32_t)a_mn, (uint32_t)b_mn, BM, BN);
+  p.idesc = make_idesc((uint32_t)a_fmt, (uint32_t)b_fmt, (uint32_t)a_mn, (uint32_t)b_mn, pair ? 2 * BM : BM, BN);
   p.bke = BKE; p.mma_per_stage = BKE / MMA_K;
   p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
   p.kb_total = ceil_div(K, BKE);
@@ -292,6 +474,22 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   p.kb_per_split = ceil_div(p.kb_total, splits);
   p.splits = ceil_div(p.kb_total, p.kb_per_split);
   p.status = status;
+  { static int dbg = -1; if (dbg < 0) { const char* e = getenv("LLMB_GEMM_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
+  if (pair) {
+    const long long units2 = (long long)ceil_div(M, 2 * BM) * p.n_tiles * p.splits;
+    const int max_clusters = sm_count() / 2;
+    const int grid2 = 2 * (int)(units2 < max_clusters ? units2 : max_clusters);
+    switch (epi) {
+      case EPI_NONE: return launch_pair<KIND, EPI_NONE>(ta, tb, p, grid2, st);
+      case EPI_BIAS: return launch_pair<KIND, EPI_BIAS>(ta, tb, p, grid2, st);
+      case EPI_BIAS_GELU: return launch_pair<KIND, EPI_BIAS_GELU>(ta, tb, p, grid2, st);
+      case EPI_DGELU: return launch_pair<KIND, EPI_DGELU>(ta, tb, p, grid2, st);
+      case EPI_ACC_F32: return launch_pair<KIND, EPI_ACC_F32>(ta, tb, p, grid2, st);
+      case EPI_BIAS_RESID: return launch_pair<KIND, EPI_BIAS_RESID>(ta, tb, p, grid2, st);
+      case EPI_STORE_F32: return launch_pair<KIND, EPI_STORE_F32>(ta, tb, p, grid2, st);
+    }
+    return LLMB_ERR_BAD_ARG;
+  }
   long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
   int grid = (int)(units < sm_count() ? units : sm_count());
 
@@ -324,3 +522,5 @@ LLMB_API int llmb_gemm(void* D, const void* A, const void* B, const void* bias, 
 }
 
 LLMB_API void llmb_gemm_debug_mn_strides(int lbo_bytes, int sbo_bytes) { g_dbg_mn_lbo = lbo_bytes; g_dbg_mn_sbo = sbo_bytes; }
+// 0: single-CTA 128x256 tiles, 1: CTA-pair 256x256 tiles (default; env LLMB_GEMM_PAIR=0 selects the former)
+LLMB_API void llmb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }

@@ -1,0 +1,342 @@
+// Low-precision training support: amax, delayed scaling, FP8 quantisation, NVFP4 quantisation
+// (e2m1 values + e4m3 block scales + fp32 tensor scale, RNE or stochastic rounding, optional
+// 16-point randomised Hadamard transform), and the Squares counter RNG.
+//
+// Reference behaviour: llmm/amax.mojo:129-302 (NaN-infectious amax), :336-398 (scale from the
+// pre-push history, own amax during warm-up), llmm/lowp.mojo:539-853 (quantise with a device
+// scale), llmm/nvfp4_quant.mojo:202-282 (e2m1 encode), :528-571 (tensor scale amax/(448*6)),
+// :604-724 (block quantise), :400-410 (128x4 scale swizzle), llmm/hadamard.mojo:73-264,
+// llmm/rng_device.mojo:113-232.
+//
+// B200 design: FP8 operands feed tcgen05 kind::f8f6f4 GEMMs directly in whatever majorness the
+// trainer stores them (no transposed copies: the UMMA descriptor handles MN-major e4m3/e5m2).
+// The NVFP4 kernels emit both the packed format (bytes + scales) and the dequantised value x
+// block-scale in bf16; every e2m1 x e4m3 product is exactly representable in bf16, so a bf16
+// tensor-core GEMM over those values with the fp32 tensor scales folded into alpha reproduces
+// the NVFP4 GEMM's arithmetic.
+#include "common.cuh"
+#include <cuda_fp8.h>
+using namespace llmb;
+
+namespace {
+// ------------------------------------------------------------------ Squares RNG
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+__device__ __forceinline__ uint64_t rng_key(uint64_t seed, uint64_t stream) { return splitmix64(seed ^ splitmix64(stream)) | 1ull; }
+__device__ __forceinline__ uint32_t squares32(uint64_t ctr, uint64_t key) {
+  uint64_t x = ctr * key, y = x, z = y + key;
+  x = x * x + y; x = (x >> 32) | (x << 32);
+  x = x * x + z; x = (x >> 32) | (x << 32);
+  x = x * x + y; x = (x >> 32) | (x << 32);
+  return (uint32_t)((x * x + z) >> 32);
+}
+__device__ __forceinline__ float rng_uniform01(uint64_t seed, uint64_t ctr, uint64_t stream) {
+  return (float)(squares32(ctr, rng_key(seed, stream)) >> 8) * (1.0f / 16777216.0f);
+}
+
+// ------------------------------------------------------------------ amax
+template <typename T>
+__global__ void amax_kernel(unsigned* __restrict__ out_bits, const T* __restrict__ x, long long n) {
+  // |x| as raw bits orders like an unsigned integer and NaN patterns sort above +inf, so an
+  // integer max is a NaN-infectious float max.
+  constexpr int N = Pack<T>::N;
+  unsigned m = 0;
+  const long long nvec = n / N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    Pack<T> p; p.load(x + i * N);
+#pragma unroll
+    for (int k = 0; k < N; ++k) m = max(m, __float_as_uint(p.v[k]) & 0x7fffffffu);
+  }
+  if (blockIdx.x == 0) for (long long i = nvec * N + threadIdx.x; i < n; i += blockDim.x) m = max(m, __float_as_uint(to_f<T>(x[i])) & 0x7fffffffu);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ unsigned red[32];
+  const int lane = threadIdx.x % 32, wid = threadIdx.x / 32;
+  if (lane == 0) red[wid] = m;
+  __syncthreads();
+  if (wid == 0) {
+    m = lane < (int)(blockDim.x / 32) ? red[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) atomicMax(out_bits, m);
+  }
+}
+
+// state layout (floats): [0] scale  [1] scale_inv  [2] step counter (as float bits of int)  [3] pad  [4..4+H) history
+constexpr int AMAX_HISTORY = 16;
+__global__ void amax_update_kernel(float* state, const float* amax_cur, float fmt_max, float margin_mult) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int step = __float_as_int(state[2]);
+  float* hist = state + 4;
+  const float cur = *amax_cur;
+  float a;
+  if (step < AMAX_HISTORY) a = cur;
+  else {
+    float m = 0.f; bool bad = false;
+    for (int i = 0; i < AMAX_HISTORY; ++i) { float h = hist[i]; if (isnan(h) || isinf(h)) bad = true; else m = fmaxf(m, h); }
+    a = bad ? NAN : m;
+  }
+  float scale = (a <= 0.f || isnan(a) || isinf(a)) ? 1.0f : (fmt_max * margin_mult) / a;
+  state[0] = scale; state[1] = 1.0f / scale;
+  hist[step % AMAX_HISTORY] = cur;           // pushed after the scale was derived: a step never sees its own amax
+  state[2] = __int_as_float(step + 1);
+}
+
+// ------------------------------------------------------------------ FP8 quantise (device scale)
+template <typename T, int FMT>
+__global__ void quantize_fp8_kernel(uint8_t* __restrict__ out, const T* __restrict__ x, const float* __restrict__ scale_ptr, long long n) {
+  constexpr int N = Pack<T>::N;
+  const float s = *scale_ptr;
+  const long long nvec = n / N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    Pack<T> p; p.load(x + i * N);
+    uint8_t q[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k)
+      q[k] = (uint8_t)__nv_cvt_float_to_fp8(p.v[k] * s, __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+    if (N == 8) *reinterpret_cast<uint2*>(out + i * N) = *reinterpret_cast<uint2*>(q);
+    else *reinterpret_cast<uint32_t*>(out + i * N) = *reinterpret_cast<uint32_t*>(q);
+  }
+}
+__global__ void dequantize_fp8_kernel(float* __restrict__ out, const uint8_t* __restrict__ q, const float* __restrict__ scale_inv, long long n, int fmt) {
+  const float s = *scale_inv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(q[i], fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+    out[i] = __half2float(*reinterpret_cast<__half*>(&h)) * s;
+  }
+}
+
+// ------------------------------------------------------------------ NVFP4
+__device__ __forceinline__ float e2m1_value(int code) {   // code: 3-bit magnitude index
+  const float tab[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  return tab[code & 7];
+}
+// nearest grid point, ties away from zero (the larger magnitude); returns sign<<3 | index
+__device__ __forceinline__ int encode_e2m1_rne(float v) {
+  const float a = fabsf(v);
+  int idx;
+  if (a < 0.25f) idx = 0; else if (a < 0.75f) idx = 1; else if (a < 1.25f) idx = 2; else if (a < 1.75f) idx = 3;
+  else if (a < 2.5f) idx = 4; else if (a < 3.5f) idx = 5; else if (a < 5.0f) idx = 6; else idx = 7;
+  return (v < 0.f ? 8 : 0) | idx;
+}
+// stochastic rounding between the two bracketing grid points: P(up) = (|v| - lo) / (hi - lo)
+__device__ __forceinline__ int encode_e2m1_sr(float v, float rnd) {
+  const float a = fminf(fabsf(v), 6.0f);
+  int lo = 0;
+#pragma unroll
+  for (int i = 1; i < 8; ++i) if (a >= e2m1_value(i)) lo = i;
+  int idx = lo;
+  if (lo < 7) {
+    const float l = e2m1_value(lo), h = e2m1_value(lo + 1);
+    const float pup = (a - l) / (h - l);
+    if (rnd < pup) idx = lo + 1;
+  }
+  return (v < 0.f ? 8 : 0) | idx;
+}
+__device__ __forceinline__ uint8_t encode_e4m3(float v) { return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
+__device__ __forceinline__ float decode_e4m3(uint8_t c) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(c, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+// offset of block scale (row r, k-block kb) in the 128-row x 4-column tiled scale layout
+__device__ __host__ inline long long nvfp4_scale_swizzle_offset(long long r, long long kb, long long n_col_tiles) {
+  const long long tile_r = r / 128, tile_c = kb / 4;
+  const long long in_r = r % 128, in_c = kb % 4;
+  return (tile_r * n_col_tiles + tile_c) * 512 + (in_r % 32) * 16 + (in_r / 32) * 4 + in_c;
+}
+__device__ __forceinline__ float hadamard_sign(int i) {
+  // fixed sign vector of the randomised Hadamard transform
+  return ((0x9ACA >> i) & 1) ? 1.0f : -1.0f;   // bit i set <=> +1: [-1,1,1,-1,-1,-1,-1,1,-1,1,1,-1,1,-1,-1,1]
+}
+__device__ __forceinline__ void fwht16(float (&b)[16]) {
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 2 * h) {
+#pragma unroll
+      for (int j = i; j < i + h; ++j) { const float x = b[j], y = b[j + h]; b[j] = x + y; b[j + h] = x - y; }
+    }
+  }
+}
+
+// One thread quantises one block: BLOCK_ROWS x 16 elements along the block axis.
+//   axis 1: blocks run along the columns (K = last dim); axis 0: blocks run along the rows.
+// Outputs (each optional): packed e2m1 (logical [outer, K/2] with K the block axis), e4m3 scales
+// (swizzled 128x4 tiles, or row-major when n_col_tiles == 0), and dequantised bf16 = value x
+// block scale (WITHOUT the fp32 tensor scale) in the source layout.
+template <typename T, int BLOCK_ROWS>
+__global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ deq,
+                                      const T* __restrict__ x, const float* __restrict__ tensor_scale_ptr, int rows, int cols,
+                                      int axis, int rht, int sr, unsigned long long seed, unsigned long long stream,
+                                      long long step, long long n_col_tiles) {
+  const int outer = axis == 1 ? rows : cols;            // index across blocks' "rows"
+  const int K = axis == 1 ? cols : rows;                // length along the block axis
+  const int kblocks = K / 16;
+  const int tile_rows = ceil_div(outer, BLOCK_ROWS);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)tile_rows * kblocks) return;
+  // consecutive threads walk the contiguous memory direction
+  int br, kb;
+  if (axis == 1) { br = (int)(idx / kblocks); kb = (int)(idx % kblocks); }
+  else { kb = (int)(idx / tile_rows); br = (int)(idx % tile_rows); }
+  const float ts = *tensor_scale_ptr;
+  auto addr = [&](int o, int k) -> long long { return axis == 1 ? (long long)o * cols + k : (long long)k * cols + o; };
+
+  float v[BLOCK_ROWS][16];
+  float amax = 0.f;
+#pragma unroll
+  for (int rr = 0; rr < BLOCK_ROWS; ++rr) {
+    const int o = br * BLOCK_ROWS + rr;
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) v[rr][kk] = o < outer ? to_f<T>(x[addr(o, kb * 16 + kk)]) : 0.f;
+    if (rht) {
+#pragma unroll
+      for (int kk = 0; kk < 16; ++kk) v[rr][kk] *= hadamard_sign(kk);
+      fwht16(v[rr]);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) amax = fmaxf(amax, fabsf(v[rr][kk]));
+  }
+  const float raw = (amax <= 0.f || ts <= 0.f) ? 1.0f : (amax / 6.0f) / ts;
+  const uint8_t sc_code = encode_e4m3(raw);
+  const float sc_dec = decode_e4m3(sc_code);
+  float sc_val = sc_dec * ts;
+  if (sc_val <= 0.f) sc_val = 1.0f;
+  const float inv = 1.0f / sc_val;
+#pragma unroll
+  for (int rr = 0; rr < BLOCK_ROWS; ++rr) {
+    const int o = br * BLOCK_ROWS + rr;
+    if (o >= outer) continue;
+    if (scales) scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(o, kb, n_col_tiles) : (long long)o * kblocks + kb] = sc_code;
+    uint8_t packed[8];
+#pragma unroll
+    for (int kk = 0; kk < 16; kk += 2) {
+      int c[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const float s = v[rr][kk + t] * inv;
+        if (sr) {
+          const unsigned long long flat = (unsigned long long)o * K + kb * 16 + kk + t;
+          c[t] = encode_e2m1_sr(s, rng_uniform01(seed, ((unsigned long long)step << 32) | flat, stream));
+        } else c[t] = encode_e2m1_rne(s);
+        if (deq) deq[addr(o, kb * 16 + kk + t)] = __float2bfloat16_rn((c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec);
+      }
+      packed[kk / 2] = (uint8_t)(c[0] | (c[1] << 4));      // even index -> low nibble
+    }
+    if (q) *reinterpret_cast<uint2*>(q + ((long long)o * K + kb * 16) / 2) = *reinterpret_cast<uint2*>(packed);
+  }
+}
+
+__global__ void nvfp4_tensor_scale_kernel(float* ts, const float* amax) {
+  const float a = *amax;
+  *ts = (a > 0.f && !isnan(a) && !isinf(a)) ? a / (448.0f * 6.0f) : 1.0f;
+}
+__global__ void nvfp4_dequant_kernel(float* __restrict__ out, const uint8_t* __restrict__ q, const uint8_t* __restrict__ scales,
+                                     const float* __restrict__ ts, int rows, int K, long long n_col_tiles) {
+  const long long n = (long long)rows * K;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / K), k = (int)(i % K);
+    const uint8_t byte = q[i / 2];
+    const int code = (i & 1) ? (byte >> 4) : (byte & 15);
+    const uint8_t sc = scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(r, k / 16, n_col_tiles) : (long long)r * (K / 16) + k / 16];
+    out[i] = (code & 8 ? -1.f : 1.f) * e2m1_value(code) * decode_e4m3(sc) * (*ts);
+  }
+}
+
+template <typename T>
+__global__ void hadamard16_kernel(T* __restrict__ out, const T* __restrict__ x, long long nblocks, int inverse) {
+  for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (long long)gridDim.x * blockDim.x) {
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = to_f<T>(x[b * 16 + i]) * (inverse ? 1.0f : hadamard_sign(i));
+    fwht16(v);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[b * 16 + i] = from_f<T>(inverse ? v[i] * hadamard_sign(i) * (1.0f / 16.0f) : v[i]);
+  }
+}
+
+__global__ void rng_uniform_kernel(float* out, long long n, unsigned long long seed, unsigned long long stream, unsigned long long base) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = rng_uniform01(seed, base + i, stream);
+}
+}  // namespace
+
+// out (1 float, device) = max |x|, NaN if any element is NaN
+LLMB_API int llmb_amax(float* out, const void* x, long long n, int dtype, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(out, 0, sizeof(float), st);
+  if (e != cudaSuccess) return (int)e;
+  long long blocks = ceil_div_ll(n, 512 * 8);
+  int grid = (int)(blocks < (long long)sm_count() * 4 ? (blocks < 1 ? 1 : blocks) : (long long)sm_count() * 4);
+  if (dtype == LLMB_BF16) amax_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>((unsigned*)out, (const __nv_bfloat16*)x, n);
+  else amax_kernel<float><<<grid, 512, 0, st>>>((unsigned*)out, (const float*)x, n);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_amax_state_floats() { return 4 + AMAX_HISTORY; }
+// state: llmb_amax_state_floats() floats, initialised to {1, 1, 0, 0, 0...}; fmt_max 448 (e4m3) / 57344 (e5m2)
+LLMB_API int llmb_amax_update(float* state, const float* amax_cur, float fmt_max, float margin_mult, cudaStream_t st) {
+  amax_update_kernel<<<1, 32, 0, st>>>(state, amax_cur, fmt_max, margin_mult);
+  return (int)cudaGetLastError();
+}
+// out[i] = fp8(x[i] * *scale); fmt 0 = e4m3, 1 = e5m2
+LLMB_API int llmb_quantize_fp8(void* out, const void* x, const float* scale, long long n, int fmt, int dtype, cudaStream_t st) {
+  int grid = sm_count() * 8;
+  if (dtype == LLMB_BF16) {
+    if (n % 8) return LLMB_ERR_BAD_ARG;
+    if (fmt == 0) quantize_fp8_kernel<__nv_bfloat16, 0><<<grid, 256, 0, st>>>((uint8_t*)out, (const __nv_bfloat16*)x, scale, n);
+    else quantize_fp8_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>((uint8_t*)out, (const __nv_bfloat16*)x, scale, n);
+  } else {
+    if (n % 4) return LLMB_ERR_BAD_ARG;
+    if (fmt == 0) quantize_fp8_kernel<float, 0><<<grid, 256, 0, st>>>((uint8_t*)out, (const float*)x, scale, n);
+    else quantize_fp8_kernel<float, 1><<<grid, 256, 0, st>>>((uint8_t*)out, (const float*)x, scale, n);
+  }
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_dequantize_fp8(float* out, const void* q, const float* scale_inv, long long n, int fmt, cudaStream_t st) {
+  dequantize_fp8_kernel<<<sm_count() * 8, 256, 0, st>>>(out, (const uint8_t*)q, scale_inv, n, fmt);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_nvfp4_tensor_scale(float* ts, const float* amax, cudaStream_t st) {
+  nvfp4_tensor_scale_kernel<<<1, 1, 0, st>>>(ts, amax);
+  return (int)cudaGetLastError();
+}
+LLMB_API long long llmb_nvfp4_scale_bytes(long long outer, long long K, int swizzled) {
+  const long long kb = K / 16;
+  if (!swizzled) return outer * kb;
+  return ceil_div_ll(outer, 128) * ceil_div_ll(kb, 4) * 512;
+}
+// x [rows, cols]; blocks of (block_rows x 16) along `axis`; any of q / scales / deq may be null.
+LLMB_API int llmb_nvfp4_quantize(void* q, void* scales, void* deq, const void* x, const float* tensor_scale, int rows, int cols,
+                                 int axis, int block_rows, int rht, int sr, unsigned long long seed, unsigned long long stream,
+                                 long long step, int swizzled, int dtype, cudaStream_t st) {
+  const int outer = axis == 1 ? rows : cols, K = axis == 1 ? cols : rows;
+  if (K % 16 || (block_rows != 1 && block_rows != 16)) return LLMB_ERR_BAD_ARG;
+  const long long n_col_tiles = swizzled ? ceil_div_ll(K / 16, 4) : 0;
+  const long long total = (long long)ceil_div(outer, block_rows) * (K / 16);
+  const int threads = 128;
+  const unsigned grid = (unsigned)ceil_div_ll(total, threads);
+#define NVFP4_LAUNCH(T, BR) nvfp4_quantize_kernel<T, BR><<<grid, threads, 0, st>>>((uint8_t*)q, (uint8_t*)scales, (__nv_bfloat16*)deq, (const T*)x, tensor_scale, rows, cols, axis, rht, sr, seed, stream, step, n_col_tiles)
+  if (dtype == LLMB_BF16) { if (block_rows == 1) NVFP4_LAUNCH(__nv_bfloat16, 1); else NVFP4_LAUNCH(__nv_bfloat16, 16); }
+  else { if (block_rows == 1) NVFP4_LAUNCH(float, 1); else NVFP4_LAUNCH(float, 16); }
+#undef NVFP4_LAUNCH
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_nvfp4_dequantize(float* out, const void* q, const void* scales, const float* tensor_scale, int rows, int K,
+                                   int swizzled, cudaStream_t st) {
+  const long long n_col_tiles = swizzled ? ceil_div_ll(K / 16, 4) : 0;
+  nvfp4_dequant_kernel<<<sm_count() * 8, 256, 0, st>>>(out, (const uint8_t*)q, (const uint8_t*)scales, tensor_scale, rows, K, n_col_tiles);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_hadamard16(void* out, const void* x, long long n, int inverse, int dtype, cudaStream_t st) {
+  if (n % 16) return LLMB_ERR_BAD_ARG;
+  if (dtype == LLMB_BF16) hadamard16_kernel<__nv_bfloat16><<<sm_count() * 4, 256, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, n / 16, inverse);
+  else hadamard16_kernel<float><<<sm_count() * 4, 256, 0, st>>>((float*)out, (const float*)x, n / 16, inverse);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_rng_uniform(float* out, long long n, unsigned long long seed, unsigned long long stream, unsigned long long base, cudaStream_t st) {
+  rng_uniform_kernel<<<sm_count() * 4, 256, 0, st>>>(out, n, seed, stream, base);
+  return (int)cudaGetLastError();
+}

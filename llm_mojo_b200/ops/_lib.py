@@ -38,10 +38,24 @@ _SIGS = {
     "llmb_gemm": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_int,
                   c_int, c_int, c_int, c_int, c_int, c_p, c_p],
     "llmb_gemm_debug_mn_strides": [c_int, c_int],
+    "llmb_gemm_set_pair_mode": [c_int],
+    "llmb_amax": [c_p, c_p, c_ll, c_int, c_p],
+    "llmb_amax_state_floats": [],
+    "llmb_amax_update": [c_p, c_p, c_f, c_f, c_p],
+    "llmb_quantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_int, c_p],
+    "llmb_dequantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_p],
+    "llmb_nvfp4_tensor_scale": [c_p, c_p, c_p],
+    "llmb_nvfp4_scale_bytes": [c_ll, c_ll, c_int],
+    "llmb_nvfp4_quantize": [c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_int, c_ull, c_ull, c_ll, c_int,
+                            c_int, c_p],
+    "llmb_nvfp4_dequantize": [c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p],
+    "llmb_hadamard16": [c_p, c_p, c_ll, c_int, c_int, c_p],
+    "llmb_rng_uniform": [c_p, c_ll, c_ull, c_ull, c_ull, c_p],
     "llmb_attention_fwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
     "llmb_attention_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
 }
-_RET_LL = {"llmb_encoder_bwd_scratch_bytes", "llmb_dbias_scratch_bytes", "llmb_layernorm_bwd_scratch_bytes"}
+_RET_LL = {"llmb_encoder_bwd_scratch_bytes", "llmb_dbias_scratch_bytes", "llmb_layernorm_bwd_scratch_bytes",
+           "llmb_nvfp4_scale_bytes"}
 
 
 def lib_path() -> str:

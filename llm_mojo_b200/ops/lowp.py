@@ -1,0 +1,351 @@
+"""FP8 and NVFP4 linear layers: amax tracking, delayed scaling, quantisation, low-precision GEMMs.
+
+Parity: ``llmm/lowp.mojo:51-99`` (precision specs: e4m3 forward operands, e5m2 output gradients,
+per-tensor delayed scaling, history 16, margin 0), ``llmm/amax.mojo:230-682`` (amax + device-resident
+scale state), ``llmm/matmul.mojo:1851-2138`` / ``:4146-4711`` (forward / backward wrappers for fp8 and
+fp4), ``llmm/nvfp4_quant.mojo`` (NVFP4 format), ``llmm/hadamard.mojo`` (RHT-16),
+``train_gpt2.mojo:861-994`` (``Fp8State``: per layer {qkv, attproj, fc, fcproj} x {input, weight,
+d_output}).
+
+GPU path: FP8 operands go straight into the tcgen05 ``kind::f8f6f4`` GEMM in the layout the
+trainer already has (K-major or MN-major), so unlike the reference no transposed quantised copies
+are made.  NVFP4 operands are quantised to e2m1 + e4m3 block scales (+ fp32 tensor scale) and the
+GEMM runs on the dequantised value x block-scale in bf16 with the tensor scales folded into alpha:
+every e2m1 x e4m3 product is exact in bf16, so the arithmetic equals the NVFP4 GEMM's while the
+throughput is that of the bf16 tensor path.  CPU tensors run an emulation of the same numerics.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import (EPI_ACC_F32, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESID, EPI_DGELU, EPI_NONE, _count, _gelu_grad_t, _gelu_t,
+               _splits_for, dbias_reduce, gemm, scratch)
+from ._lib import check, dtype_code, lib, ptr, stream
+
+E4M3, E5M2 = 0, 1
+FMT_MAX = {E4M3: 448.0, E5M2: 57344.0}
+AMAX_HISTORY = 16
+E2M1_GRID = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+HADAMARD_SIGN = torch.tensor([-1., 1., 1., -1., -1., -1., -1., 1., -1., 1., 1., -1., 1., -1., -1., 1.])
+NVFP4_SR_STREAM = 16
+
+
+# ----------------------------------------------------------------------------- amax / scaling state
+def compute_amax(out: torch.Tensor, x: torch.Tensor) -> None:
+    """out[0] = max|x| (NaN if any element is NaN); ``llmm/amax.mojo:230-302``."""
+    if x.is_cuda:
+        check(lib().llmb_amax(ptr(out), ptr(x), x.numel(), dtype_code(x), stream()), "amax")
+        _count()
+    else:
+        xf = x.float()
+        out[0] = float("nan") if torch.isnan(xf).any() else xf.abs().max()
+
+
+class AmaxState:
+    """Device-resident delayed-scaling state of one GEMM operand site (``llmm/amax.mojo:425-565``)."""
+
+    def __init__(self, device, fmt: int = E4M3, margin: int = 0):
+        self.fmt, self.margin_mult = fmt, float(2 ** margin)
+        self.state = torch.zeros(4 + AMAX_HISTORY, dtype=torch.float32, device=device)
+        self.state[0] = 1.0
+        self.state[1] = 1.0
+        self.amax = torch.zeros(1, dtype=torch.float32, device=device)
+        self.host_step = 0
+
+    @property
+    def scale(self) -> torch.Tensor:
+        return self.state[0:1]
+
+    @property
+    def scale_inv(self) -> torch.Tensor:
+        return self.state[1:2]
+
+    def update_scale(self, x: torch.Tensor) -> None:
+        """amax(x) → scale for this step (pre-push history; own amax during warm-up) → push."""
+        compute_amax(self.amax, x)
+        if x.is_cuda:
+            check(lib().llmb_amax_update(ptr(self.state), ptr(self.amax), FMT_MAX[self.fmt], self.margin_mult, stream()),
+                  "amax_update")
+            _count()
+        else:
+            step, hist = self.host_step, self.state[4:]
+            cur = float(self.amax)
+            if step < AMAX_HISTORY:
+                a = cur
+            else:
+                a = float("nan") if not torch.isfinite(hist).all() else float(hist.max())
+            scale = 1.0 if (not math.isfinite(a) or a <= 0) else FMT_MAX[self.fmt] * self.margin_mult / a
+            self.state[0], self.state[1] = scale, 1.0 / scale
+            hist[step % AMAX_HISTORY] = cur
+        self.host_step += 1
+
+
+def _fp8_dtype(fmt: int):
+    return torch.float8_e4m3fn if fmt == E4M3 else torch.float8_e5m2
+
+
+def quantize_fp8(out_u8: torch.Tensor, x: torch.Tensor, scale: torch.Tensor, fmt: int) -> None:
+    """out = fp8(x·scale) with saturation (``llmm/lowp.mojo:539-585``)."""
+    if x.is_cuda:
+        check(lib().llmb_quantize_fp8(ptr(out_u8), ptr(x), ptr(scale), x.numel(), fmt, dtype_code(x), stream()), "quantize_fp8")
+        _count()
+    else:
+        y = (x.float() * scale).clamp(-FMT_MAX[fmt], FMT_MAX[fmt]).to(_fp8_dtype(fmt))
+        out_u8.view(-1).copy_(y.view(torch.uint8).view(-1))
+
+
+def dequantize_fp8(q_u8: torch.Tensor, scale_inv: torch.Tensor, fmt: int) -> torch.Tensor:
+    return q_u8.view(_fp8_dtype(fmt)).float() * scale_inv.float().to(q_u8.device)
+
+
+class LinearSite:
+    """The three scaling states of one linear layer: input (e4m3), weight (e4m3), d_output (e5m2)."""
+
+    def __init__(self, device):
+        self.inp = AmaxState(device, E4M3)
+        self.weight = AmaxState(device, E4M3)
+        self.dout = AmaxState(device, E5M2)
+        self.alpha = torch.ones(1, dtype=torch.float32, device=device)
+
+
+class LowpState:
+    """Per-layer sites {qkv, attproj, fc, fcproj} (``train_gpt2.mojo:861-994``)."""
+    SITES = ("qkv", "attproj", "fc", "fcproj")
+
+    def __init__(self, num_layer: int, device):
+        self.sites: Dict[Tuple[str, int], LinearSite] = {(s, l): LinearSite(device) for l in range(num_layer) for s in self.SITES}
+
+    def site(self, name: str, layer: int) -> LinearSite:
+        return self.sites[(name, layer)]
+
+    def min_scales(self) -> Dict[str, float]:
+        """Current scale of every state (the fp8 calibration tool tracks their running minima)."""
+        out = {}
+        for (s, l), st in self.sites.items():
+            for k in ("inp", "weight", "dout"):
+                out[f"{s}.{l}.{k}"] = float(getattr(st, k).scale)
+        return out
+
+
+def _q(name: str, x: torch.Tensor, state: AmaxState) -> torch.Tensor:
+    """Update the site's scale from ``x`` and return its fp8 quantisation (uint8 storage, same shape)."""
+    state.update_scale(x)
+    buf = scratch("fp8_" + name, x.numel(), x.device)[:x.numel()].view(x.shape)
+    quantize_fp8(buf, x, state.scale, state.fmt)
+    return buf
+
+
+def matmul_fwd_fp8(out, inp, weight, bias, site: LinearSite, *, pre_gelu=None, residual=None) -> None:
+    """out = deq(q(inp)·q(W)ᵀ) (+bias)(+GELU / +residual); ``llmm/matmul.mojo:1851-2035``."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    x = inp.reshape(rows, C)
+    qx = _q("x", x, site.inp)
+    qw = _q("w", weight, site.weight)
+    torch.mul(site.inp.scale_inv, site.weight.scale_inv, out=site.alpha)
+    o = out.view(rows, OC)
+    if out.is_cuda:
+        if pre_gelu is not None:
+            gemm(o, qx, qw, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC), alpha=site.alpha, kind=2, a_fmt=E4M3, b_fmt=E4M3)
+        elif residual is not None:
+            gemm(o, qx, qw, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC), alpha=site.alpha, kind=2, a_fmt=E4M3, b_fmt=E4M3)
+        else:
+            gemm(o, qx, qw, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias, alpha=site.alpha, kind=2, a_fmt=E4M3, b_fmt=E4M3)
+        return
+    y = dequantize_fp8(qx, site.inp.scale_inv, E4M3) @ dequantize_fp8(qw, site.weight.scale_inv, E4M3).t()
+    _finish_fwd(o, y, bias, pre_gelu, residual, rows, OC)
+
+
+def _finish_fwd(o, y, bias, pre_gelu, residual, rows, OC):
+    if bias is not None:
+        y = y + bias.float()
+    if pre_gelu is not None:
+        pre_gelu.view(rows, OC).copy_(y)
+        y = _gelu_t(pre_gelu.view(rows, OC).float())
+    if residual is not None:
+        y = y + residual.view(rows, OC).float()
+    o.copy_(y)
+
+
+def matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, site: LinearSite, *, gelu_pre=None) -> None:
+    """dinp = deq(q5(dout)·q4(W)), dW += deq(q5(dout)ᵀ·q4(inp)); ``llmm/matmul.mojo:4146-4310``."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
+    qd = _q("d", d, site.dout)
+    if dinp is not None:
+        qw = scratch("fp8_w", weight.numel(), weight.device)[:weight.numel()].view(weight.shape)
+        quantize_fp8(qw, weight, site.weight.scale, E4M3)           # same scale as the forward pass of this step
+        torch.mul(site.dout.scale_inv, site.weight.scale_inv, out=site.alpha)
+        di = dinp.view(rows, C)
+        if dout.is_cuda:
+            gemm(di, qd, qw, b_mn=True, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE,
+                 aux=gelu_pre.view(rows, C) if gelu_pre is not None else None, alpha=site.alpha, kind=2, a_fmt=E5M2, b_fmt=E4M3)
+        else:
+            g = dequantize_fp8(qd, site.dout.scale_inv, E5M2) @ dequantize_fp8(qw, site.weight.scale_inv, E4M3)
+            if gelu_pre is not None:
+                g = g * _gelu_grad_t(gelu_pre.view(rows, C).float())
+            di.copy_(g)
+    qx = scratch("fp8_x", x.numel(), x.device)[:x.numel()].view(x.shape)
+    quantize_fp8(qx, x, site.inp.scale, E4M3)
+    alpha2 = site.dout.scale_inv * site.inp.scale_inv
+    if dout.is_cuda:
+        gemm(dweight.view(OC, C), qd, qx, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), alpha=alpha2,
+             kind=2, a_fmt=E5M2, b_fmt=E4M3)
+        if dbias is not None:
+            dbias_reduce(dbias, d)
+    else:
+        dweight.view(OC, C).add_(dequantize_fp8(qd, site.dout.scale_inv, E5M2).t() @ dequantize_fp8(qx, site.inp.scale_inv, E4M3))
+        if dbias is not None:
+            dbias += d.float().sum(0)
+
+
+# ----------------------------------------------------------------------------- NVFP4
+def hadamard16(x: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """16-point randomised Hadamard transform over consecutive blocks of the last dim
+    (forward: H·(s⊙x), unnormalised; inverse: s⊙(H·y)/16); ``llmm/hadamard.mojo:229-264``."""
+    out = torch.empty_like(x)
+    if x.is_cuda:
+        check(lib().llmb_hadamard16(ptr(out), ptr(x.contiguous()), x.numel(), int(inverse), dtype_code(x), stream()), "hadamard16")
+        _count()
+        return out
+    H = torch.tensor([[(-1.0) ** bin(i & j).count("1") for j in range(16)] for i in range(16)])
+    b = x.float().reshape(-1, 16)
+    y = (b @ H.t()) * HADAMARD_SIGN / 16.0 if inverse else (b * HADAMARD_SIGN) @ H.t()
+    return y.reshape(x.shape).to(x.dtype)
+
+
+def _e2m1_round(v: torch.Tensor, rnd: Optional[torch.Tensor]) -> torch.Tensor:
+    """Round |v| onto the e2m1 grid: nearest with ties away from zero, or stochastically."""
+    a = v.abs().clamp(max=6.0)
+    grid = E2M1_GRID.to(v.device)
+    if rnd is None:
+        mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=v.device)
+        idx = torch.bucketize(a, mids, right=True)
+    else:
+        lo = (torch.bucketize(a, grid, right=True) - 1).clamp(0, 7)
+        hi = (lo + 1).clamp(max=7)
+        span = (grid[hi] - grid[lo]).clamp(min=1e-20)
+        up = (rnd < (a - grid[lo]) / span) & (hi > lo)
+        idx = torch.where(up, hi, lo)
+    return torch.sign(v) * grid[idx]
+
+
+def nvfp4_fake_quant(x: torch.Tensor, axis: int = 1, block_rows: int = 1, rht: bool = False, sr: bool = False,
+                     seed: int = 0, stream_id: int = NVFP4_SR_STREAM, step: int = 0,
+                     want_packed: bool = False):
+    """Quantise a 2-D tensor to NVFP4 along ``axis`` and return ``(deq, tensor_scale[, q, scales])``
+    where ``deq`` (bf16, same layout as ``x``) holds value × block-scale and ``tensor_scale`` is the
+    fp32 second-level scale amax/(448·6) (``llmm/nvfp4_quant.mojo:528-724``)."""
+    rows, cols = x.shape
+    dev = x.device
+    ts = torch.empty(1, dtype=torch.float32, device=dev)
+    if x.is_cuda:
+        amax = torch.empty(1, dtype=torch.float32, device=dev)
+        src = x
+        if rht:       # the tensor amax must be taken on what is quantised
+            src_for_amax = _rht_along(x, axis)
+            compute_amax(amax, src_for_amax)
+        else:
+            compute_amax(amax, src)
+        L = lib()
+        check(L.llmb_nvfp4_tensor_scale(ptr(ts), ptr(amax), stream()), "nvfp4_tensor_scale")
+        deq = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+        outer, K = (rows, cols) if axis == 1 else (cols, rows)
+        q = torch.empty(outer * K // 2, dtype=torch.uint8, device=dev) if want_packed else None
+        sc = torch.zeros(int(L.llmb_nvfp4_scale_bytes(outer, K, 1)), dtype=torch.uint8, device=dev) if want_packed else None
+        check(L.llmb_nvfp4_quantize(ptr(q), ptr(sc), ptr(deq), ptr(x), ptr(ts), rows, cols, axis, block_rows, int(rht), int(sr),
+                                    seed, stream_id, step, 1, dtype_code(x), stream()), "nvfp4_quantize")
+        _count(3)
+        return (deq, ts, q, sc) if want_packed else (deq, ts)
+    # CPU emulation of the same numerics
+    xf = x.float()
+    if axis == 0:
+        xf = xf.t()
+    outer, K = xf.shape
+    b = xf.reshape(outer, K // 16, 16)
+    if rht:
+        H = torch.tensor([[(-1.0) ** bin(i & j).count("1") for j in range(16)] for i in range(16)])
+        b = (b * HADAMARD_SIGN) @ H.t()
+    amax_t = b.abs().max()
+    ts[0] = amax_t / (448.0 * 6.0) if amax_t > 0 else 1.0
+    if block_rows == 16:
+        pad = (-outer) % 16
+        bb = torch.nn.functional.pad(b, (0, 0, 0, 0, 0, pad)).reshape(-1, 16, K // 16, 16)
+        bamax = bb.abs().amax(dim=(1, 3)).repeat_interleave(16, dim=0)[:outer].unsqueeze(-1)
+    else:
+        bamax = b.abs().amax(dim=-1, keepdim=True)
+    raw = torch.where(bamax > 0, bamax / 6.0 / ts, torch.ones_like(bamax))
+    sc_dec = raw.clamp(max=448.0).to(torch.float8_e4m3fn).float()
+    sc_val = sc_dec * ts
+    sc_val = torch.where(sc_val > 0, sc_val, torch.ones_like(sc_val))
+    rnd = torch.rand(b.shape, generator=torch.Generator().manual_seed(seed + step)) if sr else None
+    qv = _e2m1_round(b / sc_val, rnd)
+    deq = (qv * sc_dec).reshape(outer, K)
+    if axis == 0:
+        deq = deq.t()
+    return deq.contiguous().to(torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32), ts
+
+
+def _rht_along(x: torch.Tensor, axis: int) -> torch.Tensor:
+    if axis == 1:
+        return hadamard16(x)
+    return hadamard16(x.t().contiguous()).t()
+
+
+def matmul_fwd_fp4(out, inp, weight, bias, *, pre_gelu=None, residual=None) -> None:
+    """NVFP4 forward: activations 1x16 blocks, weights 16x16 blocks, RNE (``llmm/matmul.mojo:2038-2138``)."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    x = inp.reshape(rows, C)
+    dx, tsx = nvfp4_fake_quant(x, axis=1, block_rows=1)
+    dw, tsw = nvfp4_fake_quant(weight, axis=1, block_rows=16)
+    alpha = tsx * tsw
+    o = out.view(rows, OC)
+    if out.is_cuda:
+        if pre_gelu is not None:
+            gemm(o, dx, dw, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC), alpha=alpha)
+        elif residual is not None:
+            gemm(o, dx, dw, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC), alpha=alpha)
+        else:
+            gemm(o, dx, dw, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias, alpha=alpha)
+        return
+    _finish_fwd(o, (dx.float() @ dw.float().t()) * alpha, bias, pre_gelu, residual, rows, OC)
+
+
+def matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None, rht: bool = True, sr: bool = True,
+                   seed: int = 0, step: int = 0) -> None:
+    """NVFP4 backward (``llmm/matmul.mojo:4313-4711``): the gradient operand is rounded
+    stochastically; the weight-gradient product applies the 16-point randomised Hadamard
+    transform to both operands along the contraction (row) dimension and rescales by 1/16."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
+    if dinp is not None:
+        dd, tsd = nvfp4_fake_quant(d, axis=1, block_rows=1, sr=sr, seed=seed, stream_id=NVFP4_SR_STREAM + 2, step=step)
+        dw, tsw = nvfp4_fake_quant(weight, axis=0, block_rows=16)        # contraction runs over OC for dgrad
+        alpha = tsd * tsw
+        di = dinp.view(rows, C)
+        if dout.is_cuda:
+            gemm(di, dd, dw, b_mn=True, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE,
+                 aux=gelu_pre.view(rows, C) if gelu_pre is not None else None, alpha=alpha)
+        else:
+            g = (dd.float() @ dw.float()) * alpha
+            if gelu_pre is not None:
+                g = g * _gelu_grad_t(gelu_pre.view(rows, C).float())
+            di.copy_(g)
+    usable_rht = rht and rows % 16 == 0
+    dd, tsd = nvfp4_fake_quant(d, axis=0, block_rows=1, rht=usable_rht, sr=sr, seed=seed, stream_id=NVFP4_SR_STREAM + 3, step=step)
+    dx, tsx = nvfp4_fake_quant(x, axis=0, block_rows=1, rht=usable_rht)
+    alpha = tsd * tsx * ((1.0 / 16.0) if usable_rht else 1.0)
+    if dout.is_cuda:
+        gemm(dweight.view(OC, C), dd, dx, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), alpha=alpha)
+        if dbias is not None:
+            dbias_reduce(dbias, d)
+    else:
+        dweight.view(OC, C).add_((dd.float().t() @ dx.float()) * alpha)
+        if dbias is not None:
+            dbias += d.float().sum(0)

@@ -216,23 +216,32 @@ def _gemm_case(M, N, K, a_mn, b_mn, epi="none", seed=0):
     status_ok()
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 768, 768), (384, 2304, 768), (512, 50304, 768), (200, 1600, 1600)])
-def test_gemm_tn(shape):
+@pytest.fixture(params=[1, 0], ids=["cta_pair", "single_cta"])
+def gemm_mode(request):
+    """Run every GEMM test with CTA-pair (cta_group::2, 256x256) and single-CTA (128x256) tiles."""
+    _lib.lib().llmb_gemm_set_pair_mode(request.param)
+    yield request.param
+    _lib.lib().llmb_gemm_set_pair_mode(1)
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 768, 768), (384, 2304, 768), (512, 50304, 768), (200, 1600, 1600),
+                                   (1024, 768, 768)])
+def test_gemm_tn(shape, gemm_mode):
     _gemm_case(*shape, a_mn=False, b_mn=False)
 
 
 @pytest.mark.parametrize("epi", ["bias", "bias_gelu", "bias_resid"])
-def test_gemm_fwd_epilogues(epi):
+def test_gemm_fwd_epilogues(epi, gemm_mode):
     _gemm_case(384, 3072, 768, False, False, epi=epi)
 
 
 @pytest.mark.parametrize("epi", ["none", "dgelu"])
-def test_gemm_dinp_nn(epi):
+def test_gemm_dinp_nn(epi, gemm_mode):
     _gemm_case(384, 768, 3072, a_mn=False, b_mn=True, epi=epi)
 
 
 @pytest.mark.parametrize("shape", [(768, 768, 4096), (3072, 768, 2048), (768, 3072, 1024 + 64), (50304, 768, 512)])
-def test_gemm_dw_tt_splitk(shape):
+def test_gemm_dw_tt_splitk(shape, gemm_mode):
     _gemm_case(*shape, a_mn=True, b_mn=True, epi="acc_f32")
 
 
