@@ -150,7 +150,7 @@ __device__ __host__ inline long long nvfp4_scale_swizzle_offset(long long r, lon
 }
 __device__ __forceinline__ float hadamard_sign(int i) {
   // fixed sign vector of the randomised Hadamard transform
-  return ((0x9ACA >> i) & 1) ? 1.0f : -1.0f;   // bit i set <=> +1: [-1,1,1,-1,-1,-1,-1,1,-1,1,1,-1,1,-1,-1,1]
+  return ((0x9686 >> i) & 1) ? 1.0f : -1.0f;   // bit i set <=> +1: [-1,1,1,-1,-1,-1,-1,1,-1,1,1,-1,1,-1,-1,1]
 }
 __device__ __forceinline__ void fwht16(float (&b)[16]) {
 #pragma unroll

@@ -123,6 +123,11 @@ class GPT2:
         self.targets_dev: Optional[torch.Tensor] = None
         self.rng_seed = 1337
         self.use_stochastic_rounding = False
+        self.micro_steps_done = 0
+        self.lowp = None
+        if self.precision.name == "fp8":
+            from ..ops.lowp import LowpState
+            self.lowp = LowpState(cfg.num_layer, self.device)
 
     # ------------------------------------------------------------------ views / layout
     def _views(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
@@ -176,6 +181,41 @@ class GPT2:
     def activation_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.acts.values())
 
+    # ------------------------------------------------------------------ precision dispatch of the 4 linear sites
+    def _site_mode(self, site: str, layer: int) -> str:
+        """bf16 | fp8 | fp4 for one linear site (``train_gpt2.mojo:287-347``: FP8 covers the four
+        linear layers of every block; NVFP4 covers only the MLP pair of layers [first, L-offset),
+        the remaining sites of an fp4 run stay in bf16; LM head and attention are never low precision)."""
+        pr = self.precision
+        if pr.name == "fp8" and site in pr.fp8_sites:
+            return "fp8"
+        if pr.name == "fp4" and site in ("fc", "fcproj") and pr.layer_in_fp4_range(layer, self.config.num_layer):
+            return "fp4"
+        return "bf16"
+
+    def _linear_fwd(self, site, layer, out, inp, weight, bias, **kw) -> None:
+        mode = self._site_mode(site, layer)
+        if mode == "fp8":
+            from ..ops import lowp
+            lowp.matmul_fwd_fp8(out, inp, weight, bias, self.lowp.site(site, layer), **kw)
+        elif mode == "fp4":
+            from ..ops import lowp
+            lowp.matmul_fwd_fp4(out, inp, weight, bias, **kw)
+        else:
+            ops.matmul_fwd(out, inp, weight, bias, **kw)
+
+    def _linear_bwd(self, site, layer, dinp, dweight, dbias, dout, inp, weight, **kw) -> None:
+        mode = self._site_mode(site, layer)
+        if mode == "fp8":
+            from ..ops import lowp
+            lowp.matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, self.lowp.site(site, layer), **kw)
+        elif mode == "fp4":
+            from ..ops import lowp
+            lowp.matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, rht=self.precision.fp4_rht,
+                                sr=self.precision.fp4_sr, seed=self.rng_seed, step=self.micro_steps_done, **kw)
+        else:
+            ops.matmul_bwd(dinp, dweight, dbias, dout, inp, weight, **kw)
+
     # ------------------------------------------------------------------ forward
     def forward(self, inputs: torch.Tensor, targets: Optional[torch.Tensor] = None,
                 grad_accum_steps: int = 1, B: Optional[int] = None, T: Optional[int] = None) -> None:
@@ -203,13 +243,13 @@ class GPT2:
                 p = self.p
             x_in = a["encoded"] if l == 0 else a["residual3"][l - 1]
             ops.layernorm_fwd(a["ln1"][l], a["ln1_mean"][l], a["ln1_rstd"][l], x_in, p["ln1w"][l], p["ln1b"][l])
-            ops.matmul_fwd(a["qkv"][l], a["ln1"][l], p["qkvw"][l], p["qkvb"][l])
+            self._linear_fwd("qkv", l, a["qkv"][l], a["ln1"][l], p["qkvw"][l], p["qkvb"][l])
             ops.attention_fwd(a["atty"][l], a["lse"][l], a["qkv"][l], NH)
-            ops.matmul_fwd(a["residual2"][l], a["atty"][l], p["attprojw"][l], p["attprojb"][l], residual=x_in)
+            self._linear_fwd("attproj", l, a["residual2"][l], a["atty"][l], p["attprojw"][l], p["attprojb"][l], residual=x_in)
             ops.layernorm_fwd(a["ln2"][l], a["ln2_mean"][l], a["ln2_rstd"][l], a["residual2"][l], p["ln2w"][l], p["ln2b"][l])
             gelu_out = a["fch_gelu"][0 if self.recompute else l]
-            ops.matmul_fwd(gelu_out, a["ln2"][l], p["fcw"][l], p["fcb"][l], pre_gelu=a["fch"][l])
-            ops.matmul_fwd(a["residual3"][l], gelu_out, p["fcprojw"][l], p["fcprojb"][l], residual=a["residual2"][l])
+            self._linear_fwd("fc", l, gelu_out, a["ln2"][l], p["fcw"][l], p["fcb"][l], pre_gelu=a["fch"][l])
+            self._linear_fwd("fcproj", l, a["residual3"][l], gelu_out, p["fcprojw"][l], p["fcprojb"][l], residual=a["residual2"][l])
         if z is not None:
             z.before_head(backward=False)
             p = self.p
@@ -268,13 +308,13 @@ class GPT2:
                 ops.gelu_fwd(gelu_out, a["fch"][l])       # train_gpt2.mojo:4490-4502
             else:
                 gelu_out = a["fch_gelu"][l]
-            ops.matmul_bwd(dl4, g["fcprojw"][l], g["fcprojb"][l], dres, gelu_out, p["fcprojw"][l], gelu_pre=a["fch"][l])
-            ops.matmul_bwd(dl, g["fcw"][l], g["fcb"][l], dl4, a["ln2"][l], p["fcw"][l])
+            self._linear_bwd("fcproj", l, dl4, g["fcprojw"][l], g["fcprojb"][l], dres, gelu_out, p["fcprojw"][l], gelu_pre=a["fch"][l])
+            self._linear_bwd("fc", l, dl, g["fcw"][l], g["fcb"][l], dl4, a["ln2"][l], p["fcw"][l])
             ops.layernorm_bwd(dres, g["ln2w"][l], g["ln2b"][l], dl, a["residual2"][l], p["ln2w"][l],
                               a["ln2_mean"][l], a["ln2_rstd"][l], accumulate=True)
-            ops.matmul_bwd(dl, g["attprojw"][l], g["attprojb"][l], dres, a["atty"][l], p["attprojw"][l])
+            self._linear_bwd("attproj", l, dl, g["attprojw"][l], g["attprojb"][l], dres, a["atty"][l], p["attprojw"][l])
             ops.attention_bwd(dqkv, dl, a["qkv"][l], a["atty"][l], a["lse"][l], NH)
-            ops.matmul_bwd(dl, g["qkvw"][l], g["qkvb"][l], dqkv, a["ln1"][l], p["qkvw"][l])
+            self._linear_bwd("qkv", l, dl, g["qkvw"][l], g["qkvb"][l], dqkv, a["ln1"][l], p["qkvw"][l])
             ops.layernorm_bwd(dres, g["ln1w"][l], g["ln1b"][l], dl, x_in, p["ln1w"][l],
                               a["ln1_mean"][l], a["ln1_rstd"][l], accumulate=True)
             if z is not None:
@@ -283,6 +323,7 @@ class GPT2:
             z.before_embedding(backward=True)
             p, g = self.p, self.g
         ops.encoder_bwd(g["wte"], g["wpe"], dres, self.inputs_dev)
+        self.micro_steps_done += 1
         if z is not None:
             z.grads_ready("embed", last_micro_step)
             if last_micro_step:

@@ -224,9 +224,9 @@ def _e2m1_round(v: torch.Tensor, rnd: Optional[torch.Tensor]) -> torch.Tensor:
     grid = E2M1_GRID.to(v.device)
     if rnd is None:
         mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=v.device)
-        idx = torch.bucketize(a, mids, right=True)
+        idx = torch.bucketize(a.contiguous(), mids, right=True)
     else:
-        lo = (torch.bucketize(a, grid, right=True) - 1).clamp(0, 7)
+        lo = (torch.bucketize(a.contiguous(), grid, right=True) - 1).clamp(0, 7)
         hi = (lo + 1).clamp(max=7)
         span = (grid[hi] - grid[lo]).clamp(min=1e-20)
         up = (rnd < (a - grid[lo]) / span) & (hi > lo)

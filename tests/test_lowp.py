@@ -1,0 +1,228 @@
+"""Low-precision training support: amax / delayed scaling, FP8 and NVFP4 quantisation, Hadamard,
+stochastic rounding, low-precision GEMMs against a bf16 control, and the cross-precision gradient
+gate (after tests/test_amax.mojo, test_nvfp4_quant.mojo, test_hadamard.mojo, test_lowp_gemm*.mojo,
+test_lowp_bwd.mojo and tests/compare_grad_dumps.py:49-55 of the reference)."""
+import math
+
+import pytest
+import torch
+
+from llm_mojo_b200.config import GPT2Config, Precision
+from llm_mojo_b200.models import GPT2
+from llm_mojo_b200.ops import lowp
+
+CFG = GPT2Config(max_seq_len=32, vocab_size=60, num_layer=6, num_heads=2, channels=32, padded_vocab_size=64)
+
+
+class _Fp32Storage(Precision):
+    """Low-precision GEMM numerics on fp32 storage so the emulation runs on CPU."""
+    @property
+    def storage(self):
+        return torch.float32
+
+
+def _batch(B=2, T=32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    t = torch.randint(0, CFG.vocab_size, (B, T + 1), generator=g, dtype=torch.int32)
+    return t[:, :-1].contiguous(), t[:, 1:].contiguous()
+
+
+# ------------------------------------------------------------------------------ CPU
+def test_delayed_scaling_uses_prior_steps_only():
+    st = lowp.AmaxState("cpu", lowp.E4M3)
+    amaxes = [float(i + 1) for i in range(lowp.AMAX_HISTORY + 4)]
+    for step, a in enumerate(amaxes):
+        st.update_scale(torch.tensor([a, -a / 2]))
+        if step < lowp.AMAX_HISTORY:                      # warm-up: the step's own amax
+            assert abs(float(st.scale) - 448.0 / a) < 1e-4
+        else:                                             # steady state: max of the previous 16, never its own
+            prev = max(amaxes[step - lowp.AMAX_HISTORY:step])
+            assert abs(float(st.scale) - 448.0 / prev) < 1e-4
+        assert abs(float(st.scale) * float(st.scale_inv) - 1) < 1e-6
+
+
+def test_amax_is_nan_infectious_and_zero_safe():
+    out = torch.zeros(1)
+    lowp.compute_amax(out, torch.tensor([1.0, float("nan"), -3.0]))
+    assert math.isnan(float(out))
+    st = lowp.AmaxState("cpu")
+    st.update_scale(torch.zeros(8))
+    assert float(st.scale) == 1.0
+
+
+def test_hadamard_is_orthogonal_and_invertible():
+    x = torch.randn(8, 64)
+    h = lowp.hadamard16(x)
+    assert torch.allclose(lowp.hadamard16(h, inverse=True), x, atol=1e-5)
+    assert torch.allclose(h.reshape(-1, 16).norm(dim=1), 4.0 * x.reshape(-1, 16).norm(dim=1), rtol=1e-5)
+
+
+def test_nvfp4_values_lie_on_the_grid_and_error_is_bounded():
+    x = torch.randn(64, 128)
+    deq, ts = lowp.nvfp4_fake_quant(x)
+    blocks = deq.float().reshape(64, 8, 16)
+    for b in blocks.reshape(-1, 16)[:50]:
+        nz = b[b != 0].abs()
+        if nz.numel():
+            ratios = nz / nz.min()
+            assert all(any(abs(r - g) < 1e-3 for g in (1, 1.5, 2, 3, 4, 6, 8, 12)) for r in ratios.tolist())
+    rel = ((deq.float() * ts - x).norm() / x.norm()).item()
+    assert rel < 0.15
+    deq16, ts16 = lowp.nvfp4_fake_quant(x, block_rows=16)
+    assert ((deq16.float() * ts16 - x).norm() / x.norm()).item() < 0.2
+
+
+def test_nvfp4_stochastic_rounding_is_unbiased():
+    x = torch.full((256, 64), 0.7)          # between grid points after scaling
+    x[:, 0] = 6.0                           # fixes the block scale
+    acc = torch.zeros_like(x)
+    n = 64
+    for s in range(n):
+        deq, ts = lowp.nvfp4_fake_quant(x, sr=True, seed=11, step=s)
+        acc += deq.float() * ts
+    assert abs((acc / n)[:, 1:].mean().item() - 0.7) < 0.01
+    det, ts = lowp.nvfp4_fake_quant(x)
+    assert abs((det.float() * ts)[:, 1:].mean().item() - 0.7) > 0.02       # RNE alone is biased here
+
+
+@pytest.mark.parametrize("name,floor", [("fp8", 0.99), ("fp4", 0.93)])
+def test_cross_precision_gradient_gate(name, floor):
+    """Per-tensor cosine / relative-L2 of the low-precision gradients against the full-precision build."""
+    x, y = _batch()
+    ref = GPT2(CFG, "fp32", "cpu")
+    ref.forward(x, y); ref.backward()
+    m = GPT2(CFG, _Fp32Storage(name), "cpu")
+    m.forward(x, y); m.backward()
+    assert abs(m.read_loss() - ref.read_loss()) < 0.02
+    rels = []
+    for n_, g in m.g.items():
+        a, b = g.flatten(), ref.g[n_].flatten()
+        if b.norm() == 0:
+            continue
+        cos = torch.nn.functional.cosine_similarity(a, b, dim=0).item()
+        rels.append(((a - b).norm() / b.norm()).item())
+        assert cos > floor, (n_, cos)
+        assert torch.isfinite(a).all() and a.abs().sum() > 0
+    rels.sort()
+    assert rels[len(rels) // 2] < 0.20 and rels[-1] < 0.50
+
+
+def test_fp4_layer_range_matches_reference_policy():
+    pr = Precision("fp4")
+    L = 12
+    assert [l for l in range(L) if pr.layer_in_fp4_range(l, L)] == list(range(2, 10))
+    m = GPT2(CFG, _Fp32Storage("fp4"), "cpu")
+    assert m._site_mode("fc", 0) == "bf16" and m._site_mode("fc", 2) == "fp4" and m._site_mode("qkv", 2) == "bf16"
+
+
+# ------------------------------------------------------------------------------ GPU
+gpu = pytest.mark.gpu
+
+
+@gpu
+def test_amax_and_fp8_quantize_match_torch():
+    x = (torch.randn(1024, 768) * 3).bfloat16().cuda()
+    out = torch.zeros(1, device="cuda")
+    lowp.compute_amax(out, x)
+    assert float(out) == float(x.float().abs().max())
+    x2 = x.clone(); x2[5, 5] = float("nan")
+    lowp.compute_amax(out, x2)
+    assert math.isnan(float(out))
+    for fmt, dt in ((lowp.E4M3, torch.float8_e4m3fn), (lowp.E5M2, torch.float8_e5m2)):
+        st = lowp.AmaxState("cuda", fmt)
+        st.update_scale(x)
+        q = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+        lowp.quantize_fp8(q, x, st.scale, fmt)
+        want = (x.float() * st.scale).clamp(-lowp.FMT_MAX[fmt], lowp.FMT_MAX[fmt]).to(dt).view(torch.uint8)
+        assert (q != want).float().mean().item() < 1e-3
+        back = lowp.dequantize_fp8(q, st.scale_inv, fmt)
+        assert ((back - x.float()).norm() / x.float().norm()).item() < (0.04 if fmt == lowp.E4M3 else 0.08)
+
+
+@gpu
+def test_hadamard_kernel_matches_host():
+    x = torch.randn(64, 256)
+    assert torch.allclose(lowp.hadamard16(x.cuda()).cpu(), lowp.hadamard16(x), atol=1e-5)
+    assert torch.allclose(lowp.hadamard16(lowp.hadamard16(x.cuda()), inverse=True).cpu(), x, atol=1e-5)
+
+
+@gpu
+def test_delayed_scaling_state_on_device_matches_host():
+    dev, host = lowp.AmaxState("cuda"), lowp.AmaxState("cpu")
+    g = torch.Generator().manual_seed(3)
+    for _ in range(lowp.AMAX_HISTORY + 5):
+        x = torch.randn(512, generator=g) * float(torch.rand(1, generator=g) * 5 + 0.1)
+        dev.update_scale(x.cuda()); host.update_scale(x)
+        assert abs(float(dev.scale) - float(host.scale)) / float(host.scale) < 1e-5
+
+
+@gpu
+@pytest.mark.parametrize("axis,block_rows,rht", [(1, 1, False), (1, 16, False), (0, 1, False), (0, 1, True), (0, 16, False)])
+def test_nvfp4_kernel_matches_emulation(axis, block_rows, rht):
+    x = torch.randn(256, 384).bfloat16()
+    d_cpu, ts_cpu = lowp.nvfp4_fake_quant(x.float(), axis=axis, block_rows=block_rows, rht=rht)
+    d_gpu, ts_gpu, q, sc = lowp.nvfp4_fake_quant(x.cuda(), axis=axis, block_rows=block_rows, rht=rht, want_packed=True)
+    assert abs(float(ts_gpu) - float(ts_cpu)) / float(ts_cpu) < 1e-2
+    a, b = d_gpu.float().cpu() * float(ts_gpu), d_cpu.float() * float(ts_cpu)
+    assert ((a - b).abs() > 1e-3 * b.abs().max()).float().mean().item() < 0.02      # rounding ties / bf16 hadamard
+    # the packed bytes + swizzled scales decode to the same values
+    from llm_mojo_b200.ops._lib import lib, ptr, stream, check
+    outer, K = (256, 384) if axis == 1 else (384, 256)
+    out = torch.empty(outer, K, device="cuda")
+    check(lib().llmb_nvfp4_dequantize(ptr(out), ptr(q), ptr(sc), ptr(ts_gpu), outer, K, 1, stream()), "nvfp4_dequantize")
+    want = d_gpu.float() * ts_gpu
+    want = want if axis == 1 else want.t()
+    assert torch.allclose(out, want, atol=1e-6, rtol=1e-5)
+
+
+@gpu
+def test_fp8_gemm_forward_backward_against_bf16_control():
+    rows, C, OC = 512, 768, 3072
+    x, w = torch.randn(rows, C).bfloat16().cuda(), (torch.randn(OC, C) * 0.02).bfloat16().cuda()
+    b, d = torch.randn(OC).bfloat16().cuda(), torch.randn(rows, OC).bfloat16().cuda()
+    site = lowp.LinearSite("cuda")
+    out = torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda")
+    lowp.matmul_fwd_fp8(out, x, w, b, site)
+    ref = x.float() @ w.float().t() + b.float()
+    assert ((out.float() - ref).norm() / ref.norm()).item() < 0.06
+    dinp, dw, db = torch.empty(rows, C, dtype=torch.bfloat16, device="cuda"), torch.zeros(OC, C, device="cuda"), torch.zeros(OC, device="cuda")
+    lowp.matmul_bwd_fp8(dinp, dw, db, d, x, w, site)
+    rdi, rdw = d.float() @ w.float(), d.float().t() @ x.float()
+    assert ((dinp.float() - rdi).norm() / rdi.norm()).item() < 0.1
+    assert ((dw - rdw).norm() / rdw.norm()).item() < 0.1
+    assert torch.allclose(db, d.float().sum(0), atol=0.5, rtol=1e-2)
+    from llm_mojo_b200.ops import _lib
+    assert _lib.read_status() == 0
+
+
+@gpu
+def test_fp4_gemm_matches_emulation():
+    rows, C, OC = 256, 256, 512
+    x, w = torch.randn(rows, C).bfloat16(), (torch.randn(OC, C) * 0.05).bfloat16()
+    out_c = torch.empty(rows, OC)
+    lowp.matmul_fwd_fp4(out_c, x.float(), w.float(), None)
+    out_g = torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda")
+    lowp.matmul_fwd_fp4(out_g, x.cuda(), w.cuda(), None)
+    assert ((out_g.float().cpu() - out_c).norm() / out_c.norm()).item() < 0.03
+    ref = x.float() @ w.float().t()
+    assert ((out_g.float().cpu() - ref).norm() / ref.norm()).item() < 0.2
+
+
+@gpu
+@pytest.mark.parametrize("name,floor", [("fp8", 0.97), ("fp4", 0.93)])
+def test_low_precision_model_gradients_on_gpu(name, floor):
+    cfg = GPT2Config(max_seq_len=128, vocab_size=1000, num_layer=6, num_heads=2, channels=128, padded_vocab_size=1024)
+    g = torch.Generator().manual_seed(0)
+    t = torch.randint(0, cfg.vocab_size, (4, 129), generator=g, dtype=torch.int32)
+    x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
+    ref = GPT2(cfg, "bf16", "cuda")
+    lp = GPT2(cfg, name, "cuda")
+    for m in (ref, lp):
+        m.forward(x, y); m.backward()
+    assert abs(lp.read_loss() - ref.read_loss()) < 0.05
+    for n_, gv in lp.g.items():
+        a, b = gv.flatten(), ref.g[n_].flatten()
+        cos = torch.nn.functional.cosine_similarity(a, b, dim=0).item()
+        assert cos > floor, (n_, cos)
+    from llm_mojo_b200.ops import _lib
+    assert _lib.read_status() == 0
