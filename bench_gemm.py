@@ -1,0 +1,78 @@
+#!/usr/bin/env python
+"""bench_gemm — the tcgen05 GEMM on the GPT-2 training shapes against cuBLAS (torch.matmul).
+
+Parity: ``bench_gemm.mojo:1-60`` (candidate kernels vs the library GEMM on the real model shapes).
+Prints one row per (shape, variant): forward (K-major x K-major), dinp (B stored [K,N]) and dW (both
+operands stored [K,·], split-K with fp32 red.add), in CTA-pair and single-CTA tile modes, as TF/s and as
+a fraction of the measured cuBLAS bf16 peak in MEASURED_PEAKS.json when that file is present."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from llm_mojo_b200 import ops
+from llm_mojo_b200.config import parse_model_descriptor
+from llm_mojo_b200.ops import _lib
+
+
+def timed(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="d12")
+    ap.add_argument("-b", type=int, default=64)
+    ap.add_argument("-t", type=int, default=1024)
+    ap.add_argument("--modes", default="1,0", help="1 = CTA-pair tiles, 0 = single-CTA tiles")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("bench_gemm needs a GPU")
+        return 0
+    cfg = parse_model_descriptor(a.model)
+    C, rows = cfg.channels, a.b * a.t
+    peak = None
+    pk = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = json.load(open(pk)).get("bf16_tflops")
+    shapes = [("qkv", 3 * C, C), ("attproj", C, C), ("fc", 4 * C, C), ("fcproj", C, 4 * C), ("lm_head", cfg.padded_vocab_size, C)]
+    for name, N, K in shapes:
+        A = torch.randn(rows, K, device="cuda").bfloat16()
+        W = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        D = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * rows * N * K
+        lib_ms = timed(lambda: torch.matmul(A, W.t(), out=D))
+        print(f"{name:8s} {rows}x{N}x{K}  cuBLAS fwd {lib_ms:.3f} ms {fl / lib_ms / 1e9:7.0f} TF/s")
+        for mode in [int(m) for m in a.modes.split(",")]:
+            _lib.lib().llmb_gemm_set_pair_mode(mode)
+            tag = "pair  " if mode else "single"
+            ms = timed(lambda: ops.gemm(D, A, W))
+            frac = f" ({fl / ms / 1e9 / peak:.2f} of measured)" if peak else ""
+            print(f"   {tag} fwd  {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s{frac}")
+            dA = torch.empty(rows, K, device="cuda", dtype=torch.bfloat16)
+            ms = timed(lambda: ops.gemm(dA, D, W, b_mn=True))
+            print(f"   {tag} dinp {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+            dW = torch.zeros(N, K, device="cuda")
+            sp = ops._splits_for(N, K, rows)
+            ms = timed(lambda: ops.gemm(dW, D, A, a_mn=True, b_mn=True, epi=ops.EPI_ACC_F32, splits=sp))
+            print(f"   {tag} dW   {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s (split-K {sp})")
+        _lib.lib().llmb_gemm_set_pair_mode(1)
+    print("kernel status", _lib.read_status())
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

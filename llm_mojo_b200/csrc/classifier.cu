@@ -113,3 +113,73 @@ LLMB_API int llmb_softmax_rows(float* out, const void* inp, int rows, int V, int
   else softmax_rows_kernel<float><<<rows, 256, 0, st>>>(out, (const float*)inp, V, ld, inv_temp);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- chunked cross-entropy
+// Two-pass online-softmax CE over vocabulary tiles, so the full [rows, Vp] logits never exist
+// (llmm/fused_classifier.mojo:503-841).  stats[row] = {running max, running sum-exp, target logit, -}.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256) ce_pass1_kernel(float4* __restrict__ stats, const T* __restrict__ tile, const int* __restrict__ targets,
+                                                      int ld, int col0, int width, int V, int first) {
+  __shared__ float red[32];
+  __shared__ float bc;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid % 32, wid = tid / 32, nw = blockDim.x / 32;
+  const T* g = tile + (size_t)row * ld;
+  const int valid = min(width, V - col0);           // columns of this tile that are real vocabulary
+  float mx = -INFINITY;
+  for (int i = tid; i < valid; i += blockDim.x) mx = fmaxf(mx, to_f<T>(g[i]));
+  mx = warp_max(mx); if (lane == 0) red[wid] = mx; __syncthreads();
+  if (wid == 0) { float m = lane < nw ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bc = m; } __syncthreads();
+  mx = bc;
+  float s = 0.f;
+  for (int i = tid; i < valid; i += blockDim.x) s += expf(to_f<T>(g[i]) - mx);
+  s = warp_sum(s); __syncthreads(); if (lane == 0) red[wid] = s; __syncthreads();
+  if (wid == 0) { float t = lane < nw ? red[lane] : 0.f; t = warp_sum(t); if (lane == 0) bc = t; } __syncthreads();
+  if (tid == 0) {
+    float4 st = first ? make_float4(-INFINITY, 0.f, 0.f, 0.f) : stats[row];
+    if (valid > 0) {
+      const float m_new = fmaxf(st.x, mx);
+      st.y = st.y * expf(st.x - m_new) + bc * expf(mx - m_new);
+      st.x = m_new;
+    }
+    const int tgt = targets[row];
+    if (tgt >= col0 && tgt < col0 + valid) st.z = to_f<T>(g[tgt - col0]);
+    stats[row] = st;
+  }
+}
+__global__ void ce_loss_kernel(float* __restrict__ losses, const float4* __restrict__ stats, int rows) {
+  int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < rows) { float4 st = stats[r]; losses[r] = -(st.z - st.x - logf(st.y)); }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) ce_pass2_kernel(T* __restrict__ tile, const float4* __restrict__ stats, const int* __restrict__ targets,
+                                                      int ld, int col0, int width, int V, float dloss) {
+  const int row = blockIdx.x;
+  T* g = tile + (size_t)row * ld;
+  const float4 st = stats[row];
+  const float lse = st.x + logf(st.y);
+  const int tgt = targets[row] - col0;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = 0.f;
+    if (col0 + i < V) v = (expf(to_f<T>(g[i]) - lse) - (i == tgt ? 1.f : 0.f)) * dloss;
+    g[i] = from_f<T>(v);
+  }
+}
+}  // namespace
+
+LLMB_API int llmb_ce_pass1(float* stats, const void* tile, const int* targets, int rows, int ld, int col0, int width, int V,
+                           int first, int dtype, cudaStream_t st) {
+  if (dtype == LLMB_BF16) ce_pass1_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>((float4*)stats, (const __nv_bfloat16*)tile, targets, ld, col0, width, V, first);
+  else ce_pass1_kernel<float><<<rows, 256, 0, st>>>((float4*)stats, (const float*)tile, targets, ld, col0, width, V, first);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_ce_loss(float* losses, const float* stats, int rows, cudaStream_t st) {
+  ce_loss_kernel<<<ceil_div(rows, 256), 256, 0, st>>>(losses, (const float4*)stats, rows);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_ce_pass2(void* tile, const float* stats, const int* targets, int rows, int ld, int col0, int width, int V,
+                           float dloss, int dtype, cudaStream_t st) {
+  if (dtype == LLMB_BF16) ce_pass2_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>((__nv_bfloat16*)tile, (const float4*)stats, targets, ld, col0, width, V, dloss);
+  else ce_pass2_kernel<float><<<rows, 256, 0, st>>>((float*)tile, (const float4*)stats, targets, ld, col0, width, V, dloss);
+  return (int)cudaGetLastError();
+}

@@ -67,11 +67,15 @@ def random_init_params(config: GPT2Config, seed: int = INIT_RNG_SEED) -> torch.T
 class GPT2:
     def __init__(self, source: str | GPT2Config, precision: Precision | str = "bf16",
                  device: str | torch.device = "cpu", zero=None, recompute: bool = False,
-                 init_seed: int = INIT_RNG_SEED, params_flat: Optional[torch.Tensor] = None):
+                 init_seed: int = INIT_RNG_SEED, params_flat: Optional[torch.Tensor] = None,
+                 lm_head_chunks: Optional[int] = None):
         self.precision = precision if isinstance(precision, Precision) else Precision(precision)
         self.device = torch.device(device)
         self.recompute = recompute or os.environ.get("LLMM_RECOMPUTE", "") not in ("", "0")
         self.zero = zero
+        # LM-head vocabulary tiling with chunked cross-entropy: K > 1 never materialises [B,T,Vp] logits
+        # (train_gpt2.mojo:127-149 LM_HEAD_VOCAB_TILES / LM_HEAD_CHUNKED_CE; README.md:145-149)
+        self.lm_head_chunks = int(os.environ.get("LLMM_LM_HEAD_CHUNKS", 1)) if lm_head_chunks is None else lm_head_chunks
         self.checkpoint_path = source if isinstance(source, str) else ""
         # ---- three load paths: config/descriptor (random init), .bin, .safetensors
         if params_flat is not None:
@@ -169,10 +173,16 @@ class GPT2:
             "fch_gelu": e(1 if self.recompute else L, B, T, 4 * C),
             "residual3": e(L, B, T, C),
             "lnf": e(B, T, C), "lnf_mean": e(B, T, dtype=f32), "lnf_rstd": e(B, T, dtype=f32),
-            "logits": e(B, T, Vp), "losses": e(B, T, dtype=f32),
+            "losses": e(B, T, dtype=f32),
             # backward scratch
             "dres": e(B, T, C), "dl_btc": e(B, T, C), "dl_bt4c": e(B, T, 4 * C),
         }
+        if self.lm_head_chunks > 1:
+            self.tile_width = ((Vp + self.lm_head_chunks - 1) // self.lm_head_chunks + 127) // 128 * 128
+            a["logits_tile"] = e(B * T, self.tile_width)
+            a["ce_stats"] = e(B * T, 4, dtype=f32)
+        else:
+            a["logits"] = e(B, T, Vp)
         self.acts = a
         self.B, self.T = B, T
         self.inputs_dev = torch.empty(B, T, dtype=torch.int32, device=dev)
@@ -180,6 +190,11 @@ class GPT2:
 
     def activation_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.acts.values())
+
+    def _vocab_tiles(self):
+        """(first column, width) of each LM-head vocabulary tile (train_gpt2.mojo:2333-2350)."""
+        Vp, w = self.config.padded_vocab_size, self.tile_width
+        return [(c0, min(w, Vp - c0)) for c0 in range(0, Vp, w)]
 
     # ------------------------------------------------------------------ precision dispatch of the 4 linear sites
     def _site_mode(self, site: str, layer: int) -> str:
@@ -254,9 +269,21 @@ class GPT2:
             z.before_head(backward=False)
             p = self.p
         ops.layernorm_fwd(a["lnf"], a["lnf_mean"], a["lnf_rstd"], a["residual3"][L - 1], p["lnfw"], p["lnfb"])
+        dloss = 1.0 / (B * T * grad_accum_steps)
+        self._dloss = dloss
+        if self.lm_head_chunks > 1 and targets is not None:
+            # pass 1 over vocabulary tiles: running (max, sum-exp, target logit) per row
+            for k, (c0, w) in enumerate(self._vocab_tiles()):
+                tile = a["logits_tile"][:, :w]
+                ops.matmul_fwd(tile, a["lnf"], p["wte"][c0:c0 + w])
+                ops.chunked_ce_pass1(a["ce_stats"], tile, self.targets_dev, c0, w, V, k == 0)
+            ops.chunked_ce_loss(a["losses"], a["ce_stats"])
+            self.loss_acc += a["losses"].sum() * dloss
+            return
+        if "logits" not in a:
+            a["logits"] = torch.empty(B, T, cfg.padded_vocab_size, dtype=self.dtype, device=self.device)
         ops.matmul_fwd(a["logits"], a["lnf"], p["wte"])
         if targets is not None:
-            dloss = 1.0 / (B * T * grad_accum_steps)
             ops.fused_classifier(a["logits"], a["losses"], self.targets_dev, dloss, V)
             self.loss_acc += a["losses"].sum() * dloss
 
@@ -291,8 +318,17 @@ class GPT2:
         if z is not None:
             z.before_head(backward=True)
         p, g = self.p, self.g
-        # bucket 1: LM head (dlogits are already in acts['logits'])
-        ops.matmul_bwd(dl, g["wte"], None, a["logits"], a["lnf"], p["wte"])
+        # bucket 1: LM head
+        if self.lm_head_chunks > 1:
+            # pass 2: recompute each logits tile, turn it into dlogits, and consume it at once
+            V = cfg.vocab_size
+            for k, (c0, w) in enumerate(self._vocab_tiles()):
+                tile = a["logits_tile"][:, :w]
+                ops.matmul_fwd(tile, a["lnf"], p["wte"][c0:c0 + w])
+                ops.chunked_ce_pass2(tile, a["ce_stats"], self.targets_dev, c0, w, V, self._dloss)
+                ops.lm_head_bwd_tile(dl, g["wte"][c0:c0 + w], tile, a["lnf"], p["wte"][c0:c0 + w], accumulate=k > 0)
+        else:                                  # dlogits are already in acts['logits']
+            ops.matmul_bwd(dl, g["wte"], None, a["logits"], a["lnf"], p["wte"])
         # bucket 2: final layernorm
         ops.layernorm_bwd(dres, g["lnfw"], g["lnfb"], dl, a["residual3"][L - 1], p["lnfw"], a["lnf_mean"], a["lnf_rstd"],
                           accumulate=False)

@@ -200,7 +200,7 @@ def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> 
     OC, C = weight.shape
     rows = inp.numel() // C
     x = inp.reshape(rows, C)
-    o = out.view(rows, OC)
+    o = out if out.dim() == 2 else out.view(rows, OC)       # a 2-D output may be a column slice (row pitch > OC)
     if out.is_cuda and GEMM_IMPL == "tcgen05" and out.dtype == torch.bfloat16:
         if pre_gelu is not None:
             gemm(o, x, weight, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC))
@@ -247,6 +247,27 @@ def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> Non
     dweight.view(OC, C).add_((d.t() @ x).float())
     if dbias is not None:
         dbias += d.float().sum(0)
+
+
+def lm_head_bwd_tile(dinp, dweight_tile, dlogits_tile, inp, weight_tile, accumulate: bool) -> None:
+    """One vocabulary tile of the LM-head backward: dinp (+)= dlogits·W_tile, dW_tile += dlogitsᵀ·inp
+    (llmm/matmul.mojo:3757-3908; beta=1 accumulation across tiles)."""
+    w, C = weight_tile.shape
+    rows = inp.numel() // C
+    d, x, di = dlogits_tile, inp.reshape(rows, C), dinp.view(rows, C)
+    if d.is_cuda and GEMM_IMPL == "tcgen05" and d.dtype == torch.bfloat16:
+        if accumulate:      # D = acc + D: the residual epilogue reading the output tile itself
+            gemm(di, d, weight_tile, b_mn=True, epi=EPI_BIAS_RESID, aux=di)
+        else:
+            gemm(di, d, weight_tile, b_mn=True)
+        gemm(dweight_tile, d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(w, C, rows))
+        return
+    g = d.float() @ weight_tile.float()
+    if accumulate:
+        di += g.to(di.dtype)
+    else:
+        di.copy_(g)
+    dweight_tile.add_((d.t().float() @ x.float()))
 
 
 def dbias_reduce(dbias, dout2d) -> None:
@@ -346,6 +367,58 @@ def fused_classifier(logits, losses, targets, dloss: float, vocab_size: int, wri
             p.scatter_add_(1, t.unsqueeze(1), torch.full((rows, 1), -1.0, dtype=p.dtype))
             lg[:, :vocab_size] = (p * dloss).to(lg.dtype)
             lg[:, vocab_size:] = 0
+
+
+def chunked_ce_pass1(stats, tile, targets, col0: int, width: int, vocab_size: int, first: bool) -> None:
+    """Merge one vocabulary tile [rows, width] into the per-row running (max, sum-exp, target logit)
+    statistics ``stats`` [rows, 4] fp32 (llmm/fused_classifier.mojo:565-629)."""
+    rows = stats.shape[0]
+    if tile.is_cuda:
+        check(lib().llmb_ce_pass1(ptr(stats), ptr(tile), ptr(targets), rows, tile.stride(0), col0, width, vocab_size,
+                                  int(first), dtype_code(tile), stream()), "ce_pass1")
+        _count()
+        return
+    valid = max(0, min(width, vocab_size - col0))
+    if first:
+        stats[:, 0], stats[:, 1], stats[:, 2] = float("-inf"), 0.0, 0.0
+    if valid > 0:
+        x = tile[:, :valid].float()
+        mx = x.max(1).values
+        m_new = torch.maximum(stats[:, 0], mx)
+        stats[:, 1] = stats[:, 1] * torch.exp(stats[:, 0] - m_new) + torch.exp(x - mx[:, None]).sum(1) * torch.exp(mx - m_new)
+        stats[:, 0] = m_new
+        t = targets.reshape(rows).long() - col0
+        hit = (t >= 0) & (t < valid)
+        stats[hit, 2] = x[hit, t[hit]]
+
+
+def chunked_ce_loss(losses, stats) -> None:
+    """losses[row] = logsumexp − target logit from the merged statistics (llmm/fused_classifier.mojo:656)."""
+    if stats.is_cuda:
+        check(lib().llmb_ce_loss(ptr(losses), ptr(stats), stats.shape[0], stream()), "ce_loss")
+        _count()
+    else:
+        losses.view(-1).copy_(-(stats[:, 2] - stats[:, 0] - torch.log(stats[:, 1])))
+
+
+def chunked_ce_pass2(tile, stats, targets, col0: int, width: int, vocab_size: int, dloss: float) -> None:
+    """Overwrite a recomputed logits tile with dlogits = (softmax − onehot)·dloss; padded columns → 0
+    (llmm/fused_classifier.mojo:782-841)."""
+    rows = stats.shape[0]
+    if tile.is_cuda:
+        check(lib().llmb_ce_pass2(ptr(tile), ptr(stats), ptr(targets), rows, tile.stride(0), col0, width, vocab_size,
+                                  float(dloss), dtype_code(tile), stream()), "ce_pass2")
+        _count()
+        return
+    lse = stats[:, 0] + torch.log(stats[:, 1])
+    x = tile[:, :width].float()
+    p = torch.exp(x - lse[:, None])
+    t = targets.reshape(rows).long() - col0
+    hit = (t >= 0) & (t < width)
+    p[hit, t[hit]] -= 1.0
+    cols = torch.arange(width, device=tile.device) + col0
+    p[:, cols >= vocab_size] = 0.0
+    tile[:, :width] = (p * dloss).to(tile.dtype)
 
 
 def softmax_rows(logits2d: torch.Tensor, vocab_size: int, temperature: float = 1.0) -> torch.Tensor:

@@ -90,3 +90,19 @@ def test_random_init_statistics():
     assert torch.all(p["wte"][cfg.vocab_size:] == 0)            # padded rows stay zero
     assert abs(p["qkvw"].std().item() - 0.02) < 2e-3
     assert abs(p["fcprojw"].std().item() - 0.02 / (2 * 4) ** 0.5) < 1e-3
+
+
+def test_chunked_ce_and_lm_head_tiling_match_untiled(tiny_config):
+    """Vocabulary-tiled LM head with two-pass chunked cross-entropy against the single-GEMM path
+    (tests/test_chunked_cross_entropy.mojo, tests/test_lm_head_vocab_tiling.mojo)."""
+    from llm_mojo_b200.config import GPT2Config
+    cfg = GPT2Config(max_seq_len=16, vocab_size=300, num_layer=1, num_heads=2, channels=16, padded_vocab_size=384)
+    x, y = _batch(cfg, 2, 8, seed=4)
+    a = GPT2(cfg, "fp32", "cpu")
+    b = GPT2(cfg, "fp32", "cpu", lm_head_chunks=3)
+    for mdl in (a, b):
+        mdl.forward(x, y)
+        mdl.backward()
+    assert "logits" not in b.acts and b.acts["logits_tile"].shape[1] == 128
+    assert abs(a.read_loss() - b.read_loss()) < 1e-6
+    assert torch.allclose(a.grads, b.grads, atol=1e-6, rtol=1e-4)

@@ -54,3 +54,20 @@ def test_ten_step_loss_trajectory():
         lg, lc = model.read_loss(), cpu.read_loss()
         assert abs(lg - lc) < 0.05, (step, lg, lc)
     assert lg < 6.0
+
+
+def test_chunked_ce_matches_full_logits_on_gpu():
+    cfg = GPT2Config(max_seq_len=128, vocab_size=1000, num_layer=2, num_heads=2, channels=128, padded_vocab_size=1024)
+    x, y = _batch(cfg, 4, 128, seed=2)
+    a = GPT2(cfg, "bf16", "cuda")
+    b = GPT2(cfg, "bf16", "cuda", lm_head_chunks=3)          # 3 tiles of 384: the last one is narrower
+    for mdl in (a, b):
+        mdl.forward(x, y)
+        mdl.backward()
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    assert abs(a.read_loss() - b.read_loss()) < 5e-3
+    for name in a.g:
+        ga, gb = a.g[name].flatten(), b.g[name].flatten()
+        assert torch.nn.functional.cosine_similarity(ga, gb, dim=0).item() > 0.995, name
+    assert b.activation_bytes() < a.activation_bytes()
