@@ -246,8 +246,8 @@ def nvfp4_fake_quant(x: torch.Tensor, axis: int = 1, block_rows: int = 1, rht: b
     if x.is_cuda:
         amax = torch.empty(1, dtype=torch.float32, device=dev)
         src = x
-        if rht:       # the tensor amax must be taken on what is quantised
-            src_for_amax = _rht_along(x, axis)
+        if rht:       # the tensor amax must be taken on what is quantised (transform in fp32, as the kernel does)
+            src_for_amax = _rht_along(x.float(), axis)
             compute_amax(amax, src_for_amax)
         else:
             compute_amax(amax, src)
