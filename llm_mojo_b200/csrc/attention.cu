@@ -65,7 +65,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
 }
 
-constexpr uint32_t IDESC_S_128x128 = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, 128);   // K-major x K-major
 constexpr uint32_t IDESC_128x64_KK = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, 64);
 constexpr uint32_t IDESC_128x64_KMN = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, 64);   // B stored [K rows, N]
 
@@ -89,25 +88,28 @@ __device__ __forceinline__ void load128(unsigned char* dst, const CUtensorMap* t
 }
 
 // =================================================================== forward
-// No alignment slack here: 2 x (7 x 16 KB + 128 B + 1 KB reserved) must fit the SM's 228 KB, so the
-// dynamic segment is declared 1024-byte aligned and the kernel verifies that before touching it.
-constexpr int FWD_SMEM = T128 /*Q*/ + 2 * T128 /*K*/ + 2 * T128 /*V*/ + 2 * T128 /*P*/ + 128;
+// Software-pipelined: keys are visited in tiles of 64; the score tile of step j+1 is issued to the
+// tensor core as soon as every thread has pulled step j's scores into registers, so the MMA and its
+// latency run under the exponentials of step j, and P.V of step j runs under the load/max phase of
+// step j+1.  TMEM per CTA: S[2] (2 x 64 columns) + O (64 columns); two CTAs per SM.
+constexpr int FWD_KV = 64;
+constexpr int FWD_STAGES = 3;
+constexpr int FWD_SMEM = T128 /*Q*/ + FWD_STAGES * 2 * T64 /*K,V ring*/ + T128 /*P*/ + 1024 + 256;
 
 __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
-  extern __shared__ __align__(1024) unsigned char smem_fwd[];
-  unsigned char* sm = smem_fwd;
-  if (smem_u32(sm) & 1023u) { if (threadIdx.x == 0) atomicExch(p.status, LLMB_ERR_BAD_ARG); return; }
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = sm;
-  unsigned char* sK = sQ + T128;           // 2 stages
-  unsigned char* sV = sK + 2 * T128;       // 2 stages
-  unsigned char* sP = sV + 2 * T128;       // two 64-column halves of P [128 x 128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * T128);
-  uint64_t* q_bar = bars; uint64_t* kv_bar = bars + 1; uint64_t* s_bar = bars + 3; uint64_t* o_bar = bars + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  unsigned char* sK = sQ + T128;                    // FWD_STAGES x 8 KB
+  unsigned char* sV = sK + FWD_STAGES * T64;        // FWD_STAGES x 8 KB
+  unsigned char* sP = sV + FWD_STAGES * T64;        // P [128 x 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + T128);
+  uint64_t* q_bar = bars; uint64_t* kv_bar = bars + 1; uint64_t* s_bar = bars + 1 + FWD_STAGES; uint64_t* o_bar = s_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
   int fail = 0, stopped = 0;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int hb = warp >> 2;                // which 64-column half of S / 32-column half of O this thread owns
+  const int hb = warp >> 2;                // which 32-column half of the score tile / of O this thread owns
   const int row = (warp & 3) * 32 + lane;  // row of the tile == TMEM lane
   const int n_qt = ceil_div(p.T, TILE);
   const int qt = n_qt - 1 - blockIdx.x;    // heavy tiles first
@@ -115,7 +117,9 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   const int q0 = qt * TILE;
 
   if (tid == 0) {
-    mbar_init(q_bar, 1); mbar_init(&kv_bar[0], 1); mbar_init(&kv_bar[1], 1); mbar_init(s_bar, 1); mbar_init(o_bar, 1);
+    mbar_init(q_bar, 1);
+    for (int s = 0; s < FWD_STAGES; ++s) mbar_init(&kv_bar[s], 1);
+    mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_init(o_bar, 1);
     fence_barrier_init();
     prefetch_tmap(&tm);
   }
@@ -124,17 +128,30 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t tS = tmem, tO = tmem + 128;          // S buffers at columns [0,64) and [64,128)
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
-  const int n_kv = qt + 1;
+  const int n_kv = min(ceil_div(p.T, FWD_KV), ceil_div(q0 + TILE, FWD_KV));
   const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
+  auto load_kv = [&](int j) {                          // thread 0 only
+    const int s = j % FWD_STAGES;
+    mbar_expect_tx(&kv_bar[s], 2 * T64);
+    tma_load_3d(sK + s * T64, &tm, &kv_bar[s], colK, j * FWD_KV, b);
+    tma_load_3d(sV + s * T64, &tm, &kv_bar[s], colV, j * FWD_KV, b);
+  };
+  auto issue_s = [&](int j) {                          // thread 0 only: S_j = Q K_j^T into S[j & 1]
+    if (!mbar_wait(&kv_bar[j % FWD_STAGES], (j / FWD_STAGES) & 1)) ATTN_FAIL();
+    fence_after_sync();
+    mma_kk(tS + (j & 1) * 64, smem_u32(sQ), smem_u32(sK + (j % FWD_STAGES) * T64), IDESC_128x64_KK, HS / 16, false);
+    umma_commit(&s_bar[j & 1]);
+  };
   if (tid == 0) {
     mbar_expect_tx(q_bar, T128);
     load128(sQ, &tm, q_bar, colQ, q0, b);
-    mbar_expect_tx(&kv_bar[0], 2 * T128);
-    load128(sK, &tm, &kv_bar[0], colK, 0, b);
-    load128(sV, &tm, &kv_bar[0], colV, 0, b);
+    load_kv(0);
+    if (n_kv > 1) load_kv(1);
+    if (!mbar_wait(q_bar, 0)) ATTN_FAIL();
+    issue_s(0);
   }
 
   const int qi = q0 + row;
@@ -142,69 +159,57 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   float m_run = -INFINITY, l_run = 0.f;    // l_run: partial row sum over this thread's column half
 
   for (int j = 0; j < n_kv; ++j) {
-    const int st = j & 1;
-    if (tid == 0) {
-      if (j + 1 < n_kv) {
-        const int ns = (j + 1) & 1;
-        mbar_expect_tx(&kv_bar[ns], 2 * T128);
-        load128(sK + ns * T128, &tm, &kv_bar[ns], colK, (j + 1) * TILE, b);
-        load128(sV + ns * T128, &tm, &kv_bar[ns], colV, (j + 1) * TILE, b);
-      }
-      bool ok = (j > 0) || mbar_wait(q_bar, 0);
-      ok = ok && mbar_wait(&kv_bar[st], (j >> 1) & 1);
-      if (!ok) ATTN_FAIL();
-      fence_after_sync();
-      mma_kk(tS, smem_u32(sQ), smem_u32(sK + st * T128), IDESC_S_128x128, HS / 16, false);
-      umma_commit(s_bar);
-    }
-    if (!mbar_wait(s_bar, j & 1)) ATTN_FAIL();
+    if (!mbar_wait(&s_bar[j & 1], (j >> 1) & 1)) ATTN_FAIL();
     fence_after_sync();
-
-    // ---- pass 1: full-row max (both threads of a row read all 128 columns; own half stays in registers)
-    const bool diag = (j == n_kv - 1);
-    uint32_t own[2][32];
+    // ---- scores of this step into registers: row max over all 64 columns, own 32 kept
+    const int c0 = j * FWD_KV;
+    const bool need_mask = c0 + FWD_KV - 1 > q0;
+    uint32_t own[32];
     float mx = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const bool mine = (c >> 1) == hb;
-      if (diag && c > (warp & 3)) {                       // chunk entirely above the diagonal for this warp
-        if (mine) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) own[c & 1][i] = 0xff800000u;   // -inf
-        }
-        continue;
-      }
-      uint32_t r[32];
-      tmem_ld32(tS + lane_addr + c * 32, r);
+    {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tS + (j & 1) * 64 + lane_addr, r0);
+      tmem_ld32(tS + (j & 1) * 64 + lane_addr + 32, r1);
       tmem_wait_ld();
-      if (diag && c == (warp & 3)) {
+      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) if (i > lane) r[i] = 0xff800000u;
+        for (int i = 0; i < 32; ++i) { if (c0 + i > qi) r0[i] = 0xff800000u; if (c0 + 32 + i > qi) r1[i] = 0xff800000u; }
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-      if (mine) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) own[c & 1][i] = r[i];
+      for (int i = 0; i < 32; i += 2) {
+        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1])));
       }
+      mx = fmaxf(mx0, mx1);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) own[i] = hb ? r1[i] : r0[i];
     }
+    fence_before_sync();
+    __syncthreads();                                     // (A) every thread holds its scores: S[j & 1] is free
+    if (tid == 0 && j + 1 < n_kv) issue_s(j + 1);        // runs under this step's exponentials
+
     const float m_new = fmaxf(m_run, mx * sc);
     const float alpha = ex2_approx(m_run - m_new);
     m_run = m_new;
-    // ---- pass 2: p = 2^(s*sc - m) over the own half, row sum, P -> smem (half hb of the P tile)
-    float rs = 0.f;
+    float v[32];
+    float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      float v[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float e = ex2_approx(fmaf(__uint_as_float(own[c][i]), sc, -m_new));
-        v[i] = e; rs += e;
-      }
-      store_row32(sP + hb * T128, row, c * 32, v);
+    for (int i = 0; i < 32; i += 2) {
+      v[i] = ex2_approx(fmaf(__uint_as_float(own[i]), sc, -m_new));
+      v[i + 1] = ex2_approx(fmaf(__uint_as_float(own[i + 1]), sc, -m_new));
+      rs0 += v[i]; rs1 += v[i + 1];
     }
-    l_run = l_run * alpha + rs;
-    // ---- rescale the running output (this thread: 32 of the 64 columns); skipped when no row of the warp moved
+    l_run = l_run * alpha + (rs0 + rs1);
+    // ---- P.V of the previous step must be done before P is overwritten and O is rescaled
+    if (j > 0) {
+      if (!mbar_wait(o_bar, (j - 1) & 1)) ATTN_FAIL();
+      fence_after_sync();
+      if (tid == 0 && j + 2 < n_kv) load_kv(j + 2);      // its ring slot was last read by step j-1
+    } else if (tid == 0 && n_kv > 2) {
+      load_kv(2);
+    }
+    store_row32(sP, row, hb * 32, v);
     if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
       uint32_t r[32];
       tmem_ld32(tO + lane_addr + hb * 32, r);
@@ -216,17 +221,17 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
     }
     fence_proxy_async();
     fence_before_sync();
-    __syncthreads();
+    if (__syncthreads_or(fail)) { stopped = 1; break; }  // (B) P complete, O rescaled
     if (tid == 0) {
       fence_after_sync();
-      // O (+)= P V : two 64-column halves of P, V tile viewed MN-major
-      mma_kmn(tO, smem_u32(sP), smem_u32(sV + st * T128), IDESC_128x64_KMN, 4, j > 0);
-      mma_kmn(tO, smem_u32(sP + T128), smem_u32(sV + st * T128) + 64 * ROWB, IDESC_128x64_KMN, 4, true);
+      mma_kmn(tO, smem_u32(sP), smem_u32(sV + (j % FWD_STAGES) * T64), IDESC_128x64_KMN, 4, j > 0);
       umma_commit(o_bar);
     }
-    if (!mbar_wait(o_bar, j & 1)) ATTN_FAIL();
+  }
+  if (!stopped) {
+    if (!mbar_wait(o_bar, (n_kv - 1) & 1)) ATTN_FAIL();
     fence_after_sync();
-    if (__syncthreads_or(fail)) { stopped = 1; break; }
+    if (__syncthreads_or(fail)) stopped = 1;
   }
 
   // ---- epilogue: combine the two partial row sums, O / l -> bf16, LSE

@@ -28,7 +28,7 @@ constexpr int A_STAGE = BM * ROW_BYTES;              // 16 KB
 constexpr int B_STAGE = BN * ROW_BYTES;              // 32 KB
 constexpr int STAGE_BYTES = A_STAGE + B_STAGE;
 constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * 32 * 256 /*epilogue transpose*/ + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int BAND = 16;                             // m-tiles per rasterisation band
 
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_DGELU = 3, EPI_ACC_F32 = 4, EPI_BIAS_RESID = 5, EPI_STORE_F32 = 6 };
@@ -47,62 +47,102 @@ struct GemmParams {
   int* status;
 };
 
-// Applies the epilogue to 32 accumulator columns of one output row and stores them.
+// ------------------------------------------------------------------------------------------------
+// Coalesced epilogue.  tcgen05.ld hands each thread one accumulator ROW; stored directly, a warp
+// would touch 32 different rows per instruction.  Instead every 64-column slab of the warp's
+// 32 x 256 block goes through an 8 KB shared-memory transpose (XOR-swizzled 16-byte chunks, conflict
+// free in both directions) so that 8 consecutive lanes cover 64 contiguous bytes of one output row
+// and all global traffic of the epilogue (output, bias, GELU aux, residual) is sector-aligned.
+constexpr int EPI_STAGE_BYTES = 32 * 256;             // per epilogue warp: 32 rows x 64 fp32
+
 template <int EPI>
-__device__ __forceinline__ void epilogue_store32(const GemmParams& p, const uint32_t (&r)[32], int row, int col0, float alpha) {
-          float v[32];
+__device__ __forceinline__ void epi4(const GemmParams& p, float (&v)[4], int row, int col, float alpha) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+  for (int k = 0; k < 4; ++k) v[k] *= alpha;
   if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
     if (p.bias) {
-      const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
-#pragma unroll
-      for (int j8 = 0; j8 < 4; ++j8) {
-        if (col0 + j8 * 8 < p.N) {
-          Pack<__nv_bfloat16> b; b.load(bp + j8 * 8);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) v[j8 * 8 + k] += b.v[k];
-        }
-      }
+      const uint2 braw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col);
+      const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&braw);
+      const float2 b0 = __bfloat1622float2(bh[0]), b1 = __bfloat1622float2(bh[1]);
+      v[0] += b0.x; v[1] += b0.y; v[2] += b1.x; v[3] += b1.y;
     }
   }
   if (EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32) {
-    float* dp = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col0;
+    float* dp = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col;
+    if (EPI == EPI_ACC_F32)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
+    else
+      *reinterpret_cast<float4*>(dp) = make_float4(v[0], v[1], v[2], v[3]);
+    return;
+  }
+  __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col;
+  __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux) + (size_t)row * p.ldaux + col;
+  auto pack4 = [](const float (&x)[4]) {
+    uint2 u; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+    h[0] = __floats2bfloat162_rn(x[0], x[1]); h[1] = __floats2bfloat162_rn(x[2], x[3]);
+    return u;
+  };
+  auto unpack4 = [](uint2 u, float (&x)[4]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  };
+  if (EPI == EPI_BIAS_GELU) {
+    const uint2 pre = pack4(v);
+    *reinterpret_cast<uint2*>(ap) = pre;               // pre-GELU activations (bf16)
+    float x[4]; unpack4(pre, x);
 #pragma unroll
-    for (int j4 = 0; j4 < 8; ++j4) {
-      if (col0 + j4 * 4 < p.N) {
-        if (EPI == EPI_ACC_F32)
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + j4 * 4), "f"(v[j4 * 4]), "f"(v[j4 * 4 + 1]),
-                       "f"(v[j4 * 4 + 2]), "f"(v[j4 * 4 + 3]) : "memory");
-        else
-          *reinterpret_cast<float4*>(dp + j4 * 4) = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
-      }
+    for (int k = 0; k < 4; ++k) v[k] = gelu_f(x[k]);
+  } else if (EPI == EPI_DGELU) {
+    float x[4]; unpack4(*reinterpret_cast<const uint2*>(ap), x);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] *= gelu_grad_f(x[k]);
+  } else if (EPI == EPI_BIAS_RESID) {
+    float x[4]; unpack4(*reinterpret_cast<const uint2*>(ap), x);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] += x[k];
+  }
+  *reinterpret_cast<uint2*>(dp) = pack4(v);
+}
+
+// One epilogue warp drains its 32 rows x BN columns of accumulator `tacc` (TMEM address incl. lane quarter).
+template <int EPI>
+__device__ __forceinline__ void epilogue_warp(const GemmParams& p, uint32_t tacc, unsigned char* stage, int row_base, int n0,
+                                              float alpha, int lane) {
+  const int rsub = lane >> 3, cl = lane & 7;
+#pragma unroll 1
+  for (int s = 0; s < BN / 64; ++s) {
+    if (n0 + s * 64 >= p.N) break;                      // warp-uniform
+    uint32_t r0[32], r1[32];
+    tmem_ld32(tacc + s * 64, r0);
+    tmem_ld32(tacc + s * 64 + 32, r1);
+    tmem_wait_ld();
+    unsigned char* myrow = stage + lane * 256;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      *reinterpret_cast<uint4*>(myrow + ((c ^ (lane & 15)) << 4)) = make_uint4(r0[4 * c], r0[4 * c + 1], r0[4 * c + 2], r0[4 * c + 3]);
+      *reinterpret_cast<uint4*>(myrow + (((c + 8) ^ (lane & 15)) << 4)) = make_uint4(r1[4 * c], r1[4 * c + 1], r1[4 * c + 2], r1[4 * c + 3]);
     }
-  } else {
-    __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col0;
-    __nv_bfloat16* ap = reinterpret_cast<__nv_bfloat16*>(p.aux) + (size_t)row * p.ldaux + col0;
+    __syncwarp();
+    if (!(p.dbg & 1)) {
 #pragma unroll
-    for (int j8 = 0; j8 < 4; ++j8) {
-      if (col0 + j8 * 8 < p.N) {
-        Pack<__nv_bfloat16> o;
+      for (int it = 0; it < 8; ++it) {
+        const int rr = it * 4 + rsub;
+        const int row = row_base + rr;
+        const unsigned char* src = stage + rr * 256;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o.v[k] = v[j8 * 8 + k];
-        if (EPI == EPI_BIAS_GELU) {
-          o.store(ap + j8 * 8);                       // pre-GELU activations (bf16)
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o.v[k] = gelu_f(__bfloat162float(__float2bfloat16_rn(o.v[k])));
-        } else if (EPI == EPI_DGELU) {
-          Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o.v[k] *= gelu_grad_f(x.v[k]);
-        } else if (EPI == EPI_BIAS_RESID) {
-          Pack<__nv_bfloat16> x; x.load(ap + j8 * 8);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o.v[k] += x.v[k];
+        for (int half = 0; half < 2; ++half) {
+          const int chunk = cl + half * 8;
+          const float4 f = *reinterpret_cast<const float4*>(src + ((chunk ^ (rr & 15)) << 4));
+          const int col = n0 + s * 64 + chunk * 4;
+          if (row < p.M && col < p.N) {
+            float v[4] = {f.x, f.y, f.z, f.w};
+            epi4<EPI>(p, v, row, col, alpha);
+          }
         }
-        o.store(dp + j8 * 8);
       }
     }
+    __syncwarp();
   }
 }
 
@@ -111,7 +151,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  unsigned char* epi_stage = smem + STAGES * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 4 * 32 * 256);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;      // [2] accumulator ready
   uint64_t* tempty_bar = tfull_bar + 2;          // [2] accumulator drained
@@ -217,17 +258,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
       fence_after_sync();
-      const int row = m_blk * BM + q * 32 + lane;
       const int n0 = n_blk * BN;
       const float alpha = p.alpha ? *p.alpha : 1.0f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-        tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) epilogue_store32<EPI>(p, r, row, col0, alpha);
-      }
+      epilogue_warp<EPI>(p, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                         m_blk * BM + q * 32, n0, alpha, lane);
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -249,14 +283,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 constexpr int STAGES2 = 6;
 constexpr int B2_STAGE = 128 * ROW_BYTES;             // 16 KB: this CTA's half of the B tile
 constexpr int STAGE2_BYTES = A_STAGE + B2_STAGE;      // 32 KB
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 4 * 32 * 256 /*epilogue transpose*/ + 1024 + 256;
 
 template <int KIND, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE2_BYTES);
+  unsigned char* epi_stage = smem + STAGES2 * STAGE2_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 4 * 32 * 256);
   uint64_t* empty_bar = full_bar + STAGES2;
   uint64_t* tfull_bar = empty_bar + STAGES2;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -372,17 +407,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
       fence_after_sync();
-      const int row = m_blk * 2 * BM + (int)cta * BM + q * 32 + lane;
       const int n0 = n_blk * BN;
       const float alpha = p.alpha ? *p.alpha : 1.0f;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-        tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N && !(p.dbg & 1)) epilogue_store32<EPI>(p, r, row, col0, alpha);
-      }
+      epilogue_warp<EPI>(p, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                         m_blk * 2 * BM + (int)cta * BM + q * 32, n0, alpha, lane);
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));   // the leader owns the accumulator hand-back

@@ -353,3 +353,26 @@ def test_trainer_synthetic_cpu_runs_and_resumes(tmp_path):
         assert math.isfinite(r["loss"])
     finally:
         c._GPT2_LADDER.clear(); c._GPT2_LADDER.update(saved)
+
+
+def test_supervisor_restarts_on_failure_and_stall(tmp_path):
+    import sys
+    import supervise_train as sup
+    marker = tmp_path / "count"
+    script = tmp_path / "child.py"
+    script.write_text(
+        "import sys, time, pathlib\n"
+        f"p = pathlib.Path({str(marker)!r})\n"
+        "n = int(p.read_text()) if p.exists() else 0\n"
+        "p.write_text(str(n + 1))\n"
+        "print('run', n, sys.argv[1:], flush=True)\n"
+        "if n == 0: sys.exit(3)\n"            # first run crashes
+        "if n == 1: time.sleep(60)\n"          # second run hangs silently -> stall
+        "sys.exit(0)\n")
+    log = tmp_path / "log.txt"
+    rc = sup.supervise([sys.executable, str(script), "-x", "5"], str(log), stall_seconds=1.5, poll_seconds=0.3)
+    text = log.read_text()
+    assert rc == 0 and marker.read_text() == "3"
+    assert "exit code 3" in text and "stall detected" in text
+    assert "'-y', '1'" in text.split("run 2")[1]          # restarts resume from the newest checkpoint
+    assert sup.with_resume(["a", "-y", "0"]) == ["a", "-y", "1"]
