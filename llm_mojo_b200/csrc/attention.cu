@@ -88,24 +88,27 @@ __device__ __forceinline__ void load128(unsigned char* dst, const CUtensorMap* t
 }
 
 // =================================================================== forward
-// Software-pipelined: keys are visited in tiles of 64; the score tile of step j+1 is issued to the
-// tensor core as soon as every thread has pulled step j's scores into registers, so the MMA and its
-// latency run under the exponentials of step j, and P.V of step j runs under the load/max phase of
-// step j+1.  TMEM per CTA: S[2] (2 x 64 columns) + O (64 columns); two CTAs per SM.
+// Software-pipelined over 64-key steps so that no tensor-core round trip is exposed:
+//   * three score buffers in TMEM: S_{j+2} is issued while step j's exponentials run;
+//   * P is double buffered in shared memory, so step j only needs P.V of step j-2 to be finished;
+//   * the running maximum is only raised when it grows by more than 2^8 (the accumulators then hold
+//     values below 2^8 times the usual bound, harmless in fp32), which makes the in-TMEM rescale of O
+//     - the one operation that must wait for the previous P.V - rare.
+// TMEM per CTA: S[3] (3 x 64 columns) + O (64 columns) = 256; shared memory 97 KB; two CTAs per SM.
 constexpr int FWD_KV = 64;
-constexpr int FWD_STAGES = 3;
-constexpr int FWD_SMEM = T128 /*Q*/ + FWD_STAGES * 2 * T64 /*K,V ring*/ + T128 /*P*/ + 1024 + 256;
+constexpr int FWD_SMEM = T128 /*Q*/ + 3 * T64 /*K ring*/ + 3 * T64 /*V ring*/ + 2 * T128 /*P x2*/ + 1024 + 256;
+constexpr float FWD_RESCALE_THRESHOLD = 8.0f;          // log2 units
 
 __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = sm;
-  unsigned char* sK = sQ + T128;                    // FWD_STAGES x 8 KB
-  unsigned char* sV = sK + FWD_STAGES * T64;        // FWD_STAGES x 8 KB
-  unsigned char* sP = sV + FWD_STAGES * T64;        // P [128 x 64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + T128);
-  uint64_t* q_bar = bars; uint64_t* kv_bar = bars + 1; uint64_t* s_bar = bars + 1 + FWD_STAGES; uint64_t* o_bar = s_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_bar + 1);
+  unsigned char* sK = sQ + T128;                    // 3 x 8 KB
+  unsigned char* sV = sK + 3 * T64;                 // 3 x 8 KB
+  unsigned char* sP = sV + 3 * T64;                 // 2 x P [128 x 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * T128);
+  uint64_t* q_bar = bars; uint64_t* k_bar = bars + 1; uint64_t* v_bar = bars + 4; uint64_t* s_bar = bars + 7; uint64_t* o_bar = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   int fail = 0, stopped = 0;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -118,8 +121,8 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
 
   if (tid == 0) {
     mbar_init(q_bar, 1);
-    for (int s = 0; s < FWD_STAGES; ++s) mbar_init(&kv_bar[s], 1);
-    mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_init(o_bar, 1);
+    for (int s = 0; s < 3; ++s) { mbar_init(&k_bar[s], 1); mbar_init(&v_bar[s], 1); mbar_init(&s_bar[s], 1); }
+    mbar_init(&o_bar[0], 1); mbar_init(&o_bar[1], 1);
     fence_barrier_init();
     prefetch_tmap(&tm);
   }
@@ -128,30 +131,27 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;          // S buffers at columns [0,64) and [64,128)
+  const uint32_t tS = tmem, tO = tmem + 192;           // S buffers at columns 0, 64, 128
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
   const int n_kv = min(ceil_div(p.T, FWD_KV), ceil_div(q0 + TILE, FWD_KV));
   const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
-  auto load_kv = [&](int j) {                          // thread 0 only
-    const int s = j % FWD_STAGES;
-    mbar_expect_tx(&kv_bar[s], 2 * T64);
-    tma_load_3d(sK + s * T64, &tm, &kv_bar[s], colK, j * FWD_KV, b);
-    tma_load_3d(sV + s * T64, &tm, &kv_bar[s], colV, j * FWD_KV, b);
-  };
-  auto issue_s = [&](int j) {                          // thread 0 only: S_j = Q K_j^T into S[j & 1]
-    if (!mbar_wait(&kv_bar[j % FWD_STAGES], (j / FWD_STAGES) & 1)) ATTN_FAIL();
+  auto load_k = [&](int j) { const int s = j % 3; mbar_expect_tx(&k_bar[s], T64); tma_load_3d(sK + s * T64, &tm, &k_bar[s], colK, j * FWD_KV, b); };
+  auto load_v = [&](int j) { const int s = j % 3; mbar_expect_tx(&v_bar[s], T64); tma_load_3d(sV + s * T64, &tm, &v_bar[s], colV, j * FWD_KV, b); };
+  auto issue_s = [&](int j) {                          // thread 0 only: S_j = Q K_j^T into S[j % 3]
+    if (!mbar_wait(&k_bar[j % 3], (j / 3) & 1)) ATTN_FAIL();
     fence_after_sync();
-    mma_kk(tS + (j & 1) * 64, smem_u32(sQ), smem_u32(sK + (j % FWD_STAGES) * T64), IDESC_128x64_KK, HS / 16, false);
-    umma_commit(&s_bar[j & 1]);
+    mma_kk(tS + (j % 3) * 64, smem_u32(sQ), smem_u32(sK + (j % 3) * T64), IDESC_128x64_KK, HS / 16, false);
+    umma_commit(&s_bar[j % 3]);
   };
   if (tid == 0) {
     mbar_expect_tx(q_bar, T128);
     load128(sQ, &tm, q_bar, colQ, q0, b);
-    load_kv(0);
-    if (n_kv > 1) load_kv(1);
+    for (int j = 0; j < 3 && j < n_kv; ++j) load_k(j);
+    for (int j = 0; j < 2 && j < n_kv; ++j) load_v(j);
     if (!mbar_wait(q_bar, 0)) ATTN_FAIL();
     issue_s(0);
+    if (n_kv > 1) issue_s(1);
   }
 
   const int qi = q0 + row;
@@ -159,17 +159,17 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   float m_run = -INFINITY, l_run = 0.f;    // l_run: partial row sum over this thread's column half
 
   for (int j = 0; j < n_kv; ++j) {
-    if (!mbar_wait(&s_bar[j & 1], (j >> 1) & 1)) ATTN_FAIL();
+    if (!mbar_wait(&s_bar[j % 3], (j / 3) & 1)) ATTN_FAIL();
     fence_after_sync();
     // ---- scores of this step into registers: row max over all 64 columns, own 32 kept
     const int c0 = j * FWD_KV;
     const bool need_mask = c0 + FWD_KV - 1 > q0;
     uint32_t own[32];
-    float mx = -INFINITY;
+    float mx;
     {
       uint32_t r0[32], r1[32];
-      tmem_ld32(tS + (j & 1) * 64 + lane_addr, r0);
-      tmem_ld32(tS + (j & 1) * 64 + lane_addr + 32, r1);
+      tmem_ld32(tS + (j % 3) * 64 + lane_addr, r0);
+      tmem_ld32(tS + (j % 3) * 64 + lane_addr + 32, r1);
       tmem_wait_ld();
       if (need_mask) {
 #pragma unroll
@@ -186,11 +186,15 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
       for (int i = 0; i < 32; ++i) own[i] = hb ? r1[i] : r0[i];
     }
     fence_before_sync();
-    __syncthreads();                                     // (A) every thread holds its scores: S[j & 1] is free
-    if (tid == 0 && j + 1 < n_kv) issue_s(j + 1);        // runs under this step's exponentials
-
-    const float m_new = fmaxf(m_run, mx * sc);
-    const float alpha = ex2_approx(m_run - m_new);
+    __syncthreads();                                     // (A) every thread holds its scores: S[j % 3] is free
+    if (tid == 0) {
+      if (j + 3 < n_kv) load_k(j + 3);                   // K_j's slot: S_j has been computed
+      if (j + 2 < n_kv) issue_s(j + 2);                  // two steps ahead of its consumer
+    }
+    // ---- running maximum: raised only when it grows by more than the threshold
+    const float cand = mx * sc;
+    const float m_new = (cand > m_run + FWD_RESCALE_THRESHOLD) ? cand : m_run;
+    const float alpha = ex2_approx(m_run - m_new);       // exactly 1 when unchanged
     m_run = m_new;
     float v[32];
     float rs0 = 0.f, rs1 = 0.f;
@@ -201,16 +205,17 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
       rs0 += v[i]; rs1 += v[i + 1];
     }
     l_run = l_run * alpha + (rs0 + rs1);
-    // ---- P.V of the previous step must be done before P is overwritten and O is rescaled
-    if (j > 0) {
-      if (!mbar_wait(o_bar, (j - 1) & 1)) ATTN_FAIL();
+    // ---- this step's P buffer was last read by P.V of step j-2
+    if (j >= 2) {
+      if (!mbar_wait(&o_bar[j & 1], ((j - 2) >> 1) & 1)) ATTN_FAIL();
       fence_after_sync();
-      if (tid == 0 && j + 2 < n_kv) load_kv(j + 2);      // its ring slot was last read by step j-1
-    } else if (tid == 0 && n_kv > 2) {
-      load_kv(2);
     }
-    store_row32(sP, row, hb * 32, v);
-    if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+    if (tid == 0 && j >= 1 && j + 1 < n_kv) load_v(j + 1);   // slot of V_{j-2}
+    store_row32(sP + (j & 1) * T128, row, hb * 32, v);
+    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      // the accumulator may only be touched between P.V of step j-1 and P.V of step j
+      if (!mbar_wait(&o_bar[(j - 1) & 1], ((j - 1) >> 1) & 1)) ATTN_FAIL();
+      fence_after_sync();
       uint32_t r[32];
       tmem_ld32(tO + lane_addr + hb * 32, r);
       tmem_wait_ld();
@@ -221,15 +226,16 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
     }
     fence_proxy_async();
     fence_before_sync();
-    if (__syncthreads_or(fail)) { stopped = 1; break; }  // (B) P complete, O rescaled
+    if (__syncthreads_or(fail)) { stopped = 1; break; }  // (B) P complete, O rescaled where needed
     if (tid == 0) {
+      if (!mbar_wait(&v_bar[j % 3], (j / 3) & 1)) ATTN_FAIL();
       fence_after_sync();
-      mma_kmn(tO, smem_u32(sP), smem_u32(sV + (j % FWD_STAGES) * T64), IDESC_128x64_KMN, 4, j > 0);
-      umma_commit(o_bar);
+      mma_kmn(tO, smem_u32(sP + (j & 1) * T128), smem_u32(sV + (j % 3) * T64), IDESC_128x64_KMN, 4, j > 0);
+      umma_commit(&o_bar[j & 1]);
     }
   }
   if (!stopped) {
-    if (!mbar_wait(o_bar, (n_kv - 1) & 1)) ATTN_FAIL();
+    if (!mbar_wait(&o_bar[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1)) ATTN_FAIL();
     fence_after_sync();
     if (__syncthreads_or(fail)) stopped = 1;
   }
