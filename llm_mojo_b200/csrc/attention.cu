@@ -65,6 +65,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
 }
 
+constexpr uint32_t IDESC_S_128x128 = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, 128);   // K-major x K-major
 constexpr uint32_t IDESC_128x64_KK = make_idesc(FMT_BF16, FMT_BF16, 0, 0, 128, 64);
 constexpr uint32_t IDESC_128x64_KMN = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, 64);   // B stored [K rows, N]
 
@@ -88,31 +89,25 @@ __device__ __forceinline__ void load128(unsigned char* dst, const CUtensorMap* t
 }
 
 // =================================================================== forward
-// Software-pipelined over 64-key steps so that no tensor-core round trip is exposed:
-//   * three score buffers in TMEM: S_{j+2} is issued while step j's exponentials run;
-//   * P is double buffered in shared memory, so step j only needs P.V of step j-2 to be finished;
-//   * the running maximum is only raised when it grows by more than 2^8 (the accumulators then hold
-//     values below 2^8 times the usual bound, harmless in fp32), which makes the in-TMEM rescale of O
-//     - the one operation that must wait for the previous P.V - rare.
-// TMEM per CTA: S[3] (3 x 64 columns) + O (64 columns) = 256; shared memory 97 KB; two CTAs per SM.
-constexpr int FWD_KV = 64;
-constexpr int FWD_SMEM = T128 /*Q*/ + 3 * T64 /*K ring*/ + 3 * T64 /*V ring*/ + 2 * T128 /*P x2*/ + 1024 + 256;
-constexpr float FWD_RESCALE_THRESHOLD = 8.0f;          // log2 units
+// No alignment slack here: 2 x (7 x 16 KB + 128 B + 1 KB reserved) must fit the SM's 228 KB, so the
+// dynamic segment is declared 1024-byte aligned and the kernel verifies that before touching it.
+constexpr int FWD_SMEM = T128 /*Q*/ + 2 * T128 /*K*/ + 2 * T128 /*V*/ + 2 * T128 /*P*/ + 128;
 
 __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) unsigned char smem_fwd[];
+  unsigned char* sm = smem_fwd;
+  if (smem_u32(sm) & 1023u) { if (threadIdx.x == 0) atomicExch(p.status, LLMB_ERR_BAD_ARG); return; }
   unsigned char* sQ = sm;
-  unsigned char* sK = sQ + T128;                    // 3 x 8 KB
-  unsigned char* sV = sK + 3 * T64;                 // 3 x 8 KB
-  unsigned char* sP = sV + 3 * T64;                 // 2 x P [128 x 64]
+  unsigned char* sK = sQ + T128;           // 2 stages
+  unsigned char* sV = sK + 2 * T128;       // 2 stages
+  unsigned char* sP = sV + 2 * T128;       // two 64-column halves of P [128 x 128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * T128);
-  uint64_t* q_bar = bars; uint64_t* k_bar = bars + 1; uint64_t* v_bar = bars + 4; uint64_t* s_bar = bars + 7; uint64_t* o_bar = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* q_bar = bars; uint64_t* kv_bar = bars + 1; uint64_t* s_bar = bars + 3; uint64_t* o_bar = bars + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   int fail = 0, stopped = 0;
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-  const int hb = warp >> 2;                // which 32-column half of the score tile / of O this thread owns
+  const int hb = warp >> 2;                // which 64-column half of S / 32-column half of O this thread owns
   const int row = (warp & 3) * 32 + lane;  // row of the tile == TMEM lane
   const int n_qt = ceil_div(p.T, TILE);
   const int qt = n_qt - 1 - blockIdx.x;    // heavy tiles first
@@ -120,9 +115,7 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   const int q0 = qt * TILE;
 
   if (tid == 0) {
-    mbar_init(q_bar, 1);
-    for (int s = 0; s < 3; ++s) { mbar_init(&k_bar[s], 1); mbar_init(&v_bar[s], 1); mbar_init(&s_bar[s], 1); }
-    mbar_init(&o_bar[0], 1); mbar_init(&o_bar[1], 1);
+    mbar_init(q_bar, 1); mbar_init(&kv_bar[0], 1); mbar_init(&kv_bar[1], 1); mbar_init(s_bar, 1); mbar_init(o_bar, 1);
     fence_barrier_init();
     prefetch_tmap(&tm);
   }
@@ -131,27 +124,17 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 192;           // S buffers at columns 0, 64, 128
+  const uint32_t tS = tmem, tO = tmem + 128;
   const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
 
-  const int n_kv = min(ceil_div(p.T, FWD_KV), ceil_div(q0 + TILE, FWD_KV));
+  const int n_kv = qt + 1;
   const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
-  auto load_k = [&](int j) { const int s = j % 3; mbar_expect_tx(&k_bar[s], T64); tma_load_3d(sK + s * T64, &tm, &k_bar[s], colK, j * FWD_KV, b); };
-  auto load_v = [&](int j) { const int s = j % 3; mbar_expect_tx(&v_bar[s], T64); tma_load_3d(sV + s * T64, &tm, &v_bar[s], colV, j * FWD_KV, b); };
-  auto issue_s = [&](int j) {                          // thread 0 only: S_j = Q K_j^T into S[j % 3]
-    if (!mbar_wait(&k_bar[j % 3], (j / 3) & 1)) ATTN_FAIL();
-    fence_after_sync();
-    mma_kk(tS + (j % 3) * 64, smem_u32(sQ), smem_u32(sK + (j % 3) * T64), IDESC_128x64_KK, HS / 16, false);
-    umma_commit(&s_bar[j % 3]);
-  };
   if (tid == 0) {
     mbar_expect_tx(q_bar, T128);
     load128(sQ, &tm, q_bar, colQ, q0, b);
-    for (int j = 0; j < 3 && j < n_kv; ++j) load_k(j);
-    for (int j = 0; j < 2 && j < n_kv; ++j) load_v(j);
-    if (!mbar_wait(q_bar, 0)) ATTN_FAIL();
-    issue_s(0);
-    if (n_kv > 1) issue_s(1);
+    mbar_expect_tx(&kv_bar[0], 2 * T128);
+    load128(sK, &tm, &kv_bar[0], colK, 0, b);
+    load128(sV, &tm, &kv_bar[0], colV, 0, b);
   }
 
   const int qi = q0 + row;
@@ -159,63 +142,70 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
   float m_run = -INFINITY, l_run = 0.f;    // l_run: partial row sum over this thread's column half
 
   for (int j = 0; j < n_kv; ++j) {
-    if (!mbar_wait(&s_bar[j % 3], (j / 3) & 1)) ATTN_FAIL();
-    fence_after_sync();
-    // ---- scores of this step into registers: row max over all 64 columns, own 32 kept
-    const int c0 = j * FWD_KV;
-    const bool need_mask = c0 + FWD_KV - 1 > q0;
-    uint32_t own[32];
-    float mx;
-    {
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tS + (j % 3) * 64 + lane_addr, r0);
-      tmem_ld32(tS + (j % 3) * 64 + lane_addr + 32, r1);
-      tmem_wait_ld();
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { if (c0 + i > qi) r0[i] = 0xff800000u; if (c0 + 32 + i > qi) r1[i] = 0xff800000u; }
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
-        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1])));
-      }
-      mx = fmaxf(mx0, mx1);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) own[i] = hb ? r1[i] : r0[i];
-    }
-    fence_before_sync();
-    __syncthreads();                                     // (A) every thread holds its scores: S[j % 3] is free
+    const int st = j & 1;
     if (tid == 0) {
-      if (j + 3 < n_kv) load_k(j + 3);                   // K_j's slot: S_j has been computed
-      if (j + 2 < n_kv) issue_s(j + 2);                  // two steps ahead of its consumer
+      if (j + 1 < n_kv) {
+        const int ns = (j + 1) & 1;
+        mbar_expect_tx(&kv_bar[ns], 2 * T128);
+        load128(sK + ns * T128, &tm, &kv_bar[ns], colK, (j + 1) * TILE, b);
+        load128(sV + ns * T128, &tm, &kv_bar[ns], colV, (j + 1) * TILE, b);
+      }
+      bool ok = (j > 0) || mbar_wait(q_bar, 0);
+      ok = ok && mbar_wait(&kv_bar[st], (j >> 1) & 1);
+      if (!ok) ATTN_FAIL();
+      fence_after_sync();
+      mma_kk(tS, smem_u32(sQ), smem_u32(sK + st * T128), IDESC_S_128x128, HS / 16, false);
+      umma_commit(s_bar);
     }
-    // ---- running maximum: raised only when it grows by more than the threshold
-    const float cand = mx * sc;
-    const float m_new = (cand > m_run + FWD_RESCALE_THRESHOLD) ? cand : m_run;
-    const float alpha = ex2_approx(m_run - m_new);       // exactly 1 when unchanged
-    m_run = m_new;
-    float v[32];
-    float rs0 = 0.f, rs1 = 0.f;
+    if (!mbar_wait(s_bar, j & 1)) ATTN_FAIL();
+    fence_after_sync();
+
+    // ---- pass 1: full-row max (both threads of a row read all 128 columns; own half stays in registers)
+    const bool diag = (j == n_kv - 1);
+    uint32_t own[2][32];
+    float mx = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      v[i] = ex2_approx(fmaf(__uint_as_float(own[i]), sc, -m_new));
-      v[i + 1] = ex2_approx(fmaf(__uint_as_float(own[i + 1]), sc, -m_new));
-      rs0 += v[i]; rs1 += v[i + 1];
+    for (int c = 0; c < 4; ++c) {
+      const bool mine = (c >> 1) == hb;
+      if (diag && c > (warp & 3)) {                       // chunk entirely above the diagonal for this warp
+        if (mine) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) own[c & 1][i] = 0xff800000u;   // -inf
+        }
+        continue;
+      }
+      uint32_t r[32];
+      tmem_ld32(tS + lane_addr + c * 32, r);
+      tmem_wait_ld();
+      if (diag && c == (warp & 3)) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (i > lane) r[i] = 0xff800000u;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+      if (mine) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) own[c & 1][i] = r[i];
+      }
     }
-    l_run = l_run * alpha + (rs0 + rs1);
-    // ---- this step's P buffer was last read by P.V of step j-2
-    if (j >= 2) {
-      if (!mbar_wait(&o_bar[j & 1], ((j - 2) >> 1) & 1)) ATTN_FAIL();
-      fence_after_sync();
+    const float m_new = fmaxf(m_run, mx * sc);
+    const float alpha = ex2_approx(m_run - m_new);
+    m_run = m_new;
+    // ---- pass 2: p = 2^(s*sc - m) over the own half, row sum, P -> smem (half hb of the P tile)
+    float rs = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float e = ex2_approx(fmaf(__uint_as_float(own[c][i]), sc, -m_new));
+        v[i] = e; rs += e;
+      }
+      store_row32(sP + hb * T128, row, c * 32, v);
     }
-    if (tid == 0 && j >= 1 && j + 1 < n_kv) load_v(j + 1);   // slot of V_{j-2}
-    store_row32(sP + (j & 1) * T128, row, hb * 32, v);
-    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
-      // the accumulator may only be touched between P.V of step j-1 and P.V of step j
-      if (!mbar_wait(&o_bar[(j - 1) & 1], ((j - 1) >> 1) & 1)) ATTN_FAIL();
-      fence_after_sync();
+    l_run = l_run * alpha + rs;
+    // ---- rescale the running output (this thread: 32 of the 64 columns); skipped when no row of the warp moved
+    if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
       uint32_t r[32];
       tmem_ld32(tO + lane_addr + hb * 32, r);
       tmem_wait_ld();
@@ -226,18 +216,17 @@ __global__ void __launch_bounds__(256, 2) attn_fwd_kernel(const __grid_constant_
     }
     fence_proxy_async();
     fence_before_sync();
-    if (__syncthreads_or(fail)) { stopped = 1; break; }  // (B) P complete, O rescaled where needed
+    __syncthreads();
     if (tid == 0) {
-      if (!mbar_wait(&v_bar[j % 3], (j / 3) & 1)) ATTN_FAIL();
       fence_after_sync();
-      mma_kmn(tO, smem_u32(sP + (j & 1) * T128), smem_u32(sV + (j % 3) * T64), IDESC_128x64_KMN, 4, j > 0);
-      umma_commit(&o_bar[j & 1]);
+      // O (+)= P V : two 64-column halves of P, V tile viewed MN-major
+      mma_kmn(tO, smem_u32(sP), smem_u32(sV + st * T128), IDESC_128x64_KMN, 4, j > 0);
+      mma_kmn(tO, smem_u32(sP + T128), smem_u32(sV + st * T128) + 64 * ROWB, IDESC_128x64_KMN, 4, true);
+      umma_commit(o_bar);
     }
-  }
-  if (!stopped) {
-    if (!mbar_wait(&o_bar[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1)) ATTN_FAIL();
+    if (!mbar_wait(o_bar, j & 1)) ATTN_FAIL();
     fence_after_sync();
-    if (__syncthreads_or(fail)) stopped = 1;
+    if (__syncthreads_or(fail)) { stopped = 1; break; }
   }
 
   // ---- epilogue: combine the two partial row sums, O / l -> bf16, LSE

@@ -43,6 +43,7 @@ struct GemmParams {
   int bke;                     // K elements per stage
   int mma_per_stage;
   int m_tiles, n_tiles, splits, kb_per_split, kb_total;
+  int pf;                      // L2 prefetch distance of the TMA producer, in k-blocks (0 = off)
   int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0)
   int* status;
 };
@@ -102,7 +103,9 @@ __device__ __forceinline__ void epi4(const GemmParams& p, float (&v)[4], int row
 #pragma unroll
     for (int k = 0; k < 4; ++k) v[k] += x[k];
   }
-  *reinterpret_cast<uint2*>(dp) = pack4(v);
+  const uint2 o = pack4(v);
+  if (p.dbg & 4) asm volatile("st.global.cs.v2.b32 [%0], {%1, %2};" ::"l"(dp), "r"(o.x), "r"(o.y) : "memory");   // streaming store (measurement switch)
+  else *reinterpret_cast<uint2*>(dp) = o;
 }
 
 // One epilogue warp drains its 32 rows x BN columns of accumulator `tacc` (TMEM address incl. lane quarter).
@@ -337,11 +340,35 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
+      // L2 prefetch cursor: runs p.pf k-blocks ahead of the load cursor, across work units, so that the
+      // HBM latency of a tile is paid before its TMA load is issued and the 6-stage ring only has to
+      // cover the L2 -> shared-memory latency.
+      int pf_unit = cluster_id, pf_kb = 0, pf_kb1 = 0, pf_m0 = 0, pf_n0 = 0, pf_ahead = 0;
+      bool pf_valid = false;
+      auto pf_setup = [&]() {
+        pf_valid = pf_unit < total_units;
+        if (pf_valid) {
+          int m_blk, n_blk, kb0, kb1; unit_coords(pf_unit, m_blk, n_blk, kb0, kb1);
+          pf_kb = kb0; pf_kb1 = kb1;
+          pf_m0 = m_blk * 2 * BM + (int)cta * BM; pf_n0 = n_blk * BN + (int)cta * 128;
+        }
+      };
+      auto pf_step = [&]() {            // prefetch one k-block at the cursor and advance it
+        if (!pf_valid) return;
+        const int k0 = pf_kb * p.bke;
+        if (!p.a_mn) tma_prefetch_l2_2d(&tmA, k0, pf_m0);
+        else for (int c = 0; c < BM / p.bke; ++c) tma_prefetch_l2_2d(&tmA, pf_m0 + c * p.bke, k0);
+        if (!p.b_mn) tma_prefetch_l2_2d(&tmB, k0, pf_n0);
+        else for (int c = 0; c < 128 / p.bke; ++c) tma_prefetch_l2_2d(&tmB, pf_n0 + c * p.bke, k0);
+        if (++pf_kb == pf_kb1) { pf_unit += num_clusters; pf_setup(); }
+      };
+      if (p.pf > 0) { pf_setup(); for (; pf_ahead < p.pf; ++pf_ahead) pf_step(); }
       for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
         if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
         for (int kb = kb0; kb < kb1; ++kb) {
+          if (p.pf > 0) pf_step();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
           unsigned char* sa = smem + stage * STAGE2_BYTES;
           unsigned char* sb = sa + A_STAGE;
@@ -502,6 +529,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   p.kb_per_split = ceil_div(p.kb_total, splits);
   p.splits = ceil_div(p.kb_total, p.kb_per_split);
   p.status = status;
+  { static int pf = -1; if (pf < 0) { const char* e = getenv("LLMB_GEMM_PF"); pf = e ? atoi(e) : 8; } p.pf = pf; }
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("LLMB_GEMM_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
   if (pair) {
     const long long units2 = (long long)ceil_div(M, 2 * BM) * p.n_tiles * p.splits;

@@ -56,6 +56,11 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* t, uin
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(t)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+// pull a tile into L2 ahead of the load that will consume it (no shared memory, no barrier involved)
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* t, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(t)), "r"(c0), "r"(c1) : "memory");
+}
 // generic-proxy smem writes -> visible to the async proxy (TMA / tcgen05 operand reads)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
