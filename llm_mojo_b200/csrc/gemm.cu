@@ -43,6 +43,7 @@ struct GemmParams {
   int bke;                     // K elements per stage
   int mma_per_stage;
   int m_tiles, n_tiles, splits, kb_per_split, kb_total;
+  int io_f32;                  // 1: D, bias and aux are fp32 (tf32 kind); 0: bf16
   int pf;                      // L2 prefetch distance of the TMA producer, in k-blocks (0 = off)
   int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0)
   int* status;
@@ -61,7 +62,10 @@ __device__ __forceinline__ void epi4(const GemmParams& p, float (&v)[4], int row
 #pragma unroll
   for (int k = 0; k < 4; ++k) v[k] *= alpha;
   if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
-    if (p.bias) {
+    if (p.bias && p.io_f32) {
+      const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + col);
+      v[0] += b.x; v[1] += b.y; v[2] += b.z; v[3] += b.w;
+    } else if (p.bias) {
       const uint2 braw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col);
       const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&braw);
       const float2 b0 = __bfloat1622float2(bh[0]), b1 = __bfloat1622float2(bh[1]);
@@ -74,6 +78,23 @@ __device__ __forceinline__ void epi4(const GemmParams& p, float (&v)[4], int row
       asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]) : "memory");
     else
       *reinterpret_cast<float4*>(dp) = make_float4(v[0], v[1], v[2], v[3]);
+    return;
+  }
+  if (p.io_f32) {                                       // fp32 storage (tf32 tensor path)
+    float* dp = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + col;
+    float* ap = reinterpret_cast<float*>(p.aux) + (size_t)row * p.ldaux + col;
+    if (EPI == EPI_BIAS_GELU) {
+      *reinterpret_cast<float4*>(ap) = make_float4(v[0], v[1], v[2], v[3]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = gelu_f(v[k]);
+    } else if (EPI == EPI_DGELU) {
+      const float4 x = *reinterpret_cast<const float4*>(ap);
+      v[0] *= gelu_grad_f(x.x); v[1] *= gelu_grad_f(x.y); v[2] *= gelu_grad_f(x.z); v[3] *= gelu_grad_f(x.w);
+    } else if (EPI == EPI_BIAS_RESID) {
+      const float4 x = *reinterpret_cast<const float4*>(ap);
+      v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+    }
+    *reinterpret_cast<float4*>(dp) = make_float4(v[0], v[1], v[2], v[3]);
     return;
   }
   __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + col;
@@ -529,6 +550,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   p.kb_per_split = ceil_div(p.kb_total, splits);
   p.splits = ceil_div(p.kb_total, p.kb_per_split);
   p.status = status;
+  p.io_f32 = (KIND == KIND_TF32) ? 1 : 0;
   { static int pf = -1; if (pf < 0) { const char* e = getenv("LLMB_GEMM_PF"); pf = e ? atoi(e) : 8; } p.pf = pf; }
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("LLMB_GEMM_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
   if (pair) {

@@ -185,10 +185,20 @@ def gemm(D, A, B, *, a_mn=False, b_mn=False, epi=EPI_NONE, bias=None, aux=None, 
     _count()
 
 
+def _tc_kind(t: torch.Tensor):
+    """tcgen05 kind for a storage dtype: 0 (kind::f16, bf16 operands), 1 (kind::tf32, fp32 operands)."""
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32 and os.environ.get("LLMM_NO_TF32", "") in ("", "0"):
+        return 1
+    return None
+
+
 def _splits_for(M: int, N: int, K: int) -> int:
     """Split-K factor for the dW GEMMs: fill one wave of 148 CTAs when the output has few tiles."""
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     kb = (K + 63) // 64
+    tiles = max(tiles, 1)
     if tiles >= 148:
         return 1
     return max(1, min(148 // tiles, kb // 4 if kb >= 4 else 1))
@@ -201,13 +211,14 @@ def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> 
     rows = inp.numel() // C
     x = inp.reshape(rows, C)
     o = out if out.dim() == 2 else out.view(rows, OC)       # a 2-D output may be a column slice (row pitch > OC)
-    if out.is_cuda and GEMM_IMPL == "tcgen05" and out.dtype == torch.bfloat16:
+    if out.is_cuda and GEMM_IMPL == "tcgen05" and _tc_kind(out) is not None:
+        kind = _tc_kind(out)          # bf16 -> kind::f16, fp32 storage -> kind::tf32 (fp32 accumulate either way)
         if pre_gelu is not None:
-            gemm(o, x, weight, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC))
+            gemm(o, x, weight, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC), kind=kind)
         elif residual is not None:
-            gemm(o, x, weight, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC))
+            gemm(o, x, weight, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC), kind=kind)
         else:
-            gemm(o, x, weight, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias)
+            gemm(o, x, weight, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias, kind=kind)
         return
     y = x @ weight.t()
     if bias is not None:
@@ -228,14 +239,15 @@ def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> Non
     rows = inp.numel() // C
     d = dout.reshape(rows, OC)
     x = inp.reshape(rows, C)
-    if dout.is_cuda and GEMM_IMPL == "tcgen05" and dout.dtype == torch.bfloat16:
+    if dout.is_cuda and GEMM_IMPL == "tcgen05" and _tc_kind(dout) is not None:
+        kind = _tc_kind(dout)
         if dinp is not None:
             di = dinp.view(rows, C)
             if gelu_pre is not None:
-                gemm(di, d, weight, b_mn=True, epi=EPI_DGELU, aux=gelu_pre.view(rows, C))
+                gemm(di, d, weight, b_mn=True, epi=EPI_DGELU, aux=gelu_pre.view(rows, C), kind=kind)
             else:
-                gemm(di, d, weight, b_mn=True, epi=EPI_NONE)
-        gemm(dweight.view(OC, C), d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows))
+                gemm(di, d, weight, b_mn=True, epi=EPI_NONE, kind=kind)
+        gemm(dweight.view(OC, C), d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), kind=kind)
         if dbias is not None:
             dbias_reduce(dbias, d)
         return
@@ -255,12 +267,13 @@ def lm_head_bwd_tile(dinp, dweight_tile, dlogits_tile, inp, weight_tile, accumul
     w, C = weight_tile.shape
     rows = inp.numel() // C
     d, x, di = dlogits_tile, inp.reshape(rows, C), dinp.view(rows, C)
-    if d.is_cuda and GEMM_IMPL == "tcgen05" and d.dtype == torch.bfloat16:
+    if d.is_cuda and GEMM_IMPL == "tcgen05" and _tc_kind(d) is not None:
+        kind = _tc_kind(d)
         if accumulate:      # D = acc + D: the residual epilogue reading the output tile itself
-            gemm(di, d, weight_tile, b_mn=True, epi=EPI_BIAS_RESID, aux=di)
+            gemm(di, d, weight_tile, b_mn=True, epi=EPI_BIAS_RESID, aux=di, kind=kind)
         else:
-            gemm(di, d, weight_tile, b_mn=True)
-        gemm(dweight_tile, d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(w, C, rows))
+            gemm(di, d, weight_tile, b_mn=True, kind=kind)
+        gemm(dweight_tile, d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(w, C, rows), kind=kind)
         return
     g = d.float() @ weight_tile.float()
     if accumulate:

@@ -245,6 +245,27 @@ def test_gemm_dw_tt_splitk(shape, gemm_mode):
     _gemm_case(*shape, a_mn=True, b_mn=True, epi="acc_f32")
 
 
+def test_gemm_tf32_fp32_storage(gemm_mode):
+    """fp32 operands on the kind::tf32 path: forward with bias+GELU, dinp (B stored [K,N]) and dW (both [K,.])."""
+    M, N, K = 384, 768, 512
+    g = torch.Generator().manual_seed(3)
+    A, W, b = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g) * 0.05, torch.randn(N, generator=g)
+    D, aux = torch.empty(M, N, device=DEV), torch.empty(M, N, device=DEV)
+    ops.gemm(D, A.to(DEV), W.to(DEV), epi=ops.EPI_BIAS_GELU, bias=b.to(DEV), aux=aux, kind=1)
+    pre = A @ W.t() + b
+    close(aux, pre, 2e-2, 1e-2, "tf32 pre-gelu")
+    close(D, torch.nn.functional.gelu(pre, approximate="tanh"), 2e-2, 1e-2, "tf32 gelu")
+    d = torch.randn(M, N, generator=g)
+    dA = torch.empty(M, K, device=DEV)
+    ops.gemm(dA, d.to(DEV), W.to(DEV), b_mn=True, kind=1)
+    close(dA, d @ W, 5e-2, 1e-2, "tf32 dinp")
+    dW = torch.zeros(N, K, device=DEV)
+    ops.gemm(dW, d.to(DEV), A.to(DEV), a_mn=True, b_mn=True, epi=ops.EPI_ACC_F32, splits=2, kind=1)
+    close(dW, d.t() @ A, 1e-1, 1e-2, "tf32 dW")
+    torch.cuda.synchronize()
+    status_ok()
+
+
 # ------------------------------------------------------------------------------ attention
 @pytest.mark.parametrize("B,T,NH", [(2, 128, 2), (1, 256, 3), (2, 1024, 2), (2, 64, 2), (1, 200, 1)])
 def test_attention_fwd_bwd(B, T, NH):

@@ -71,3 +71,18 @@ def test_chunked_ce_matches_full_logits_on_gpu():
         ga, gb = a.g[name].flatten(), b.g[name].flatten()
         assert torch.nn.functional.cosine_similarity(ga, gb, dim=0).item() > 0.995, name
     assert b.activation_bytes() < a.activation_bytes()
+
+
+def test_fp32_storage_model_on_gpu_uses_tf32_path():
+    cfg = GPT2Config(max_seq_len=128, vocab_size=1000, num_layer=2, num_heads=2, channels=128, padded_vocab_size=1024)
+    x, y = _batch(cfg, 2, 128, seed=3)
+    model = GPT2(cfg, "tf32", "cuda")
+    model.forward(x, y)
+    loss = model.read_loss()
+    model.backward()
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    rloss, _, rgrad = ref.loss_and_grads(cfg, model.params.cpu(), x, y)
+    assert abs(loss - rloss) < 5e-3
+    cos = torch.nn.functional.cosine_similarity(model.grads.cpu(), rgrad, dim=0).item()
+    assert cos > 0.999, cos
