@@ -133,6 +133,7 @@ __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList own
   if (!wait_all(my_flags, FLAG_READY, seq, W, status)) return;
   if (mode == 1 && wait_done2_seq && !wait_all(my_flags, FLAG_DONE2, wait_done2_seq, W, status)) return;
   const long long total = owned.vec_prefix[owned.n];
+  float nsq = 0.f;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
     const int s = find_seg(owned, v);
     const long long e = (v - owned.vec_prefix[s]) * 8;
@@ -152,9 +153,21 @@ __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList own
         o0.x += c0.x; o0.y += c0.y; o0.z += c0.z; o0.w += c0.w; o1.x += c1.x; o1.y += c1.y; o1.z += c1.z; o1.w += c1.w;
       }
       *reinterpret_cast<float4*>(d) = o0; *reinterpret_cast<float4*>(d + 4) = o1;
+      nsq += o0.x * o0.x + o0.y * o0.y + o0.z * o0.z + o0.w * o0.w + o1.x * o1.x + o1.y * o1.y + o1.z * o1.z + o1.w * o1.w;
     } else {
       const uint4 packed = pack_bf16x8(acc);
       for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recvs.p[r]) + so) = packed;
+    }
+  }
+  if (mode == 0 && norm_partials) {        // sum of squares of the reduced gradients this rank owns
+    __shared__ float red[16];
+    nsq = warp_sum(nsq);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = nsq;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) atomicAdd(norm_partials, t);
     }
   }
   // peers may now overwrite their send buffers; (AR) results are in everybody's receive buffer
@@ -308,11 +321,11 @@ LLMB_API int llmb_comm_pack(void* send, const float* src, int nseg, const long l
 }
 LLMB_API int llmb_comm_reduce(void* const* send_ptrs, int nseg, const long long* src_off, const long long* dst_off,
                               const long long* len, int mode, float* dst_f32, int accumulate, void* const* recv_ptrs,
-                              void* my_flags, void* const* flag_ptrs, int me, int W, unsigned seq, unsigned wait_done2_seq,
+                              float* norm_acc, void* my_flags, void* const* flag_ptrs, int me, int W, unsigned seq, unsigned wait_done2_seq,
                               unsigned* counter, unsigned* counter2, int* status, int blocks, cudaStream_t st) {
   SegList s; if (!fill(s, nseg, nullptr, src_off, dst_off, len)) return LLMB_ERR_BAD_ARG;
   reduce_kernel<<<comm_grid(s.vec_prefix[s.n], blocks), 512, 0, st>>>(to_peers(send_ptrs, W), s, mode, dst_f32, accumulate,
-                                                                     recv_ptrs ? to_peers(recv_ptrs, W) : PeerPtrs{}, nullptr, my_flags,
+                                                                     recv_ptrs ? to_peers(recv_ptrs, W) : PeerPtrs{}, norm_acc, my_flags,
                                                                      to_peers(flag_ptrs, W), me, W, seq, wait_done2_seq, counter, counter2, status);
   return (int)cudaGetLastError();
 }

@@ -38,7 +38,9 @@ struct GemmParams {
   int M, N, K;                 // K in elements
   long long ldd, ldaux;
   int a_mn, b_mn;              // operand majorness (0 = K-major)
+  int a_3d, b_3d;              // MN-major operand fetched with ONE 3-D box (chunk, k, chunk index) per stage
   uint32_t a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep;   // bytes
+  uint32_t a_layout, b_layout; // UMMA layout type: 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte base (fp32 MN-major)
   uint32_t idesc;
   int bke;                     // K elements per stage
   int mma_per_stage;
@@ -226,12 +228,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int k0 = kb * p.bke;
           if (!p.a_mn) tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          else if (p.a_3d) tma_load_3d(sa, &tmA, &full_bar[stage], 0, k0, m0 / p.bke);
           else {
             const int chunk_elems = p.bke;   // elements per 128-byte row
             const int nchunk = BM / chunk_elems;
             for (int c = 0; c < nchunk; ++c) tma_load_2d(sa + c * p.bke * ROW_BYTES, &tmA, &full_bar[stage], m0 + c * chunk_elems, k0);
           }
           if (!p.b_mn) tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          else if (p.b_3d) tma_load_3d(sb, &tmB, &full_bar[stage], 0, k0, n0 / p.bke);
           else {
             const int chunk_elems = p.bke;
             const int nchunk = BN / chunk_elems;
@@ -259,8 +263,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE;
-          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo);
-          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo);
+          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo, p.a_layout);
+          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo, p.b_layout);
           for (int k = 0; k < p.mma_per_stage; ++k) {
             umma_ss<KIND>(d_tmem, adesc + (uint64_t)((k * p.a_kstep) >> 4), bdesc + (uint64_t)((k * p.b_kstep) >> 4),
                           p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
@@ -383,13 +387,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         else for (int c = 0; c < 128 / p.bke; ++c) tma_prefetch_l2_2d(&tmB, pf_n0 + c * p.bke, k0);
         if (++pf_kb == pf_kb1) { pf_unit += num_clusters; pf_setup(); }
       };
-      if (p.pf > 0) { pf_setup(); for (; pf_ahead < p.pf; ++pf_ahead) pf_step(); }
+      if (p.pf > 0 && !p.a_3d && !p.b_3d) { pf_setup(); for (; pf_ahead < p.pf; ++pf_ahead) pf_step(); }
       for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
         if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (p.pf > 0) pf_step();
+          if (p.pf > 0 && !p.a_3d && !p.b_3d) pf_step();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
           unsigned char* sa = smem + stage * STAGE2_BYTES;
           unsigned char* sb = sa + A_STAGE;
@@ -397,11 +401,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE2_BYTES);     // bytes of both CTAs
           const int k0 = (p.dbg & 2) ? 0 : kb * p.bke;
           if (!p.a_mn) tma_load_2d_pair(sa, &tmA, lead_full, k0, m0);
+          else if (p.a_3d) tma_load_3d_pair(sa, &tmA, lead_full, 0, k0, m0 / p.bke);
           else {
             const int chunk_elems = p.bke, nchunk = BM / chunk_elems;
             for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sa + c * p.bke * ROW_BYTES, &tmA, lead_full, m0 + c * chunk_elems, k0);
           }
           if (!p.b_mn) tma_load_2d_pair(sb, &tmB, lead_full, k0, n0);
+          else if (p.b_3d) tma_load_3d_pair(sb, &tmB, lead_full, 0, k0, n0 / p.bke);
           else {
             const int chunk_elems = p.bke, nchunk = 128 / chunk_elems;
             for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sb + c * p.bke * ROW_BYTES, &tmB, lead_full, n0 + c * chunk_elems, k0);
@@ -428,8 +434,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * STAGE2_BYTES);
           const uint32_t sb = sa + A_STAGE;
-          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo);
-          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo);
+          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo, p.a_layout);
+          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo, p.b_layout);
           for (int k = 0; k < p.mma_per_stage; ++k) {
             umma_ss_pair<KIND>(d_tmem, adesc + (uint64_t)((k * p.a_kstep) >> 4), bdesc + (uint64_t)((k * p.b_kstep) >> 4),
                                p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
@@ -525,19 +531,38 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   int rc;
   // K-major: global [MN rows, K cols], box [tile rows, ROW_ELEMS]; MN-major: global [K rows, MN cols], box [BKE, ROW_ELEMS]
   // (in pair mode each CTA fetches a 128-row half of the B tile)
-  rc = a_mn ? make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BKE, ROW_ELEMS)
+  const bool base32 = (KIND == KIND_TF32);            // fp32 operands stored MN-major need the 32-byte-base swizzle
+  const CUtensorMapSwizzle mn_swz = base32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+  rc = a_mn ? make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BKE, ROW_ELEMS, mn_swz)
             : make_tmap_2d(&ta, A, KindTraits<KIND>::DT, ESZ, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, ROW_ELEMS);
   if (rc) return 1000 + rc;
-  rc = b_mn ? make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BKE, ROW_ELEMS)
+  int a_3d = 0, b_3d = 0;
+  static int use3d = -1;
+  if (use3d < 0) { const char* e = getenv("LLMB_GEMM_3D"); use3d = (e && e[0] == '0') ? 0 : 1; }
+  // MN-major tiles as one 3-D box: (elements of one 128-byte row, k rows, row-chunks) - one TMA request per operand and stage
+  if (a_mn && use3d && M % ROW_ELEMS == 0) {
+    CUtensorMap t3;
+    if (make_tmap_3d(&t3, A, KindTraits<KIND>::DT, ESZ, ROW_ELEMS, (uint64_t)K, (uint64_t)(M / ROW_ELEMS), (uint64_t)lda, ROW_ELEMS,
+                     ROW_ELEMS, BKE, BM / ROW_ELEMS, mn_swz) == 0) { ta = t3; a_3d = 1; }
+  }
+  rc = b_mn ? make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BKE, ROW_ELEMS, mn_swz)
             : make_tmap_2d(&tb, B, KindTraits<KIND>::DT, ESZ, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, pair ? 128 : BN, ROW_ELEMS);
   if (rc) return 1000 + rc;
 
+  if (b_mn && use3d && N % ROW_ELEMS == 0) {
+    CUtensorMap t3;
+    if (make_tmap_3d(&t3, B, KindTraits<KIND>::DT, ESZ, ROW_ELEMS, (uint64_t)K, (uint64_t)(N / ROW_ELEMS), (uint64_t)ldb, ROW_ELEMS,
+                     ROW_ELEMS, BKE, (pair ? 128 : BN) / ROW_ELEMS, mn_swz) == 0) { tb = t3; b_3d = 1; }
+  }
   GemmParams p;
+  p.a_3d = a_3d; p.b_3d = b_3d;
   p.D = D; p.bias = bias; p.aux = aux; p.alpha = alpha;
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldaux = ldaux;
   p.a_mn = a_mn; p.b_mn = b_mn;
   const uint32_t mn_lbo = g_dbg_mn_lbo >= 0 ? (uint32_t)g_dbg_mn_lbo : (uint32_t)(BKE * ROW_BYTES);
-  const uint32_t mn_sbo = g_dbg_mn_sbo >= 0 ? (uint32_t)g_dbg_mn_sbo : 1024u;
+  const uint32_t mn_sbo = g_dbg_mn_sbo >= 0 ? (uint32_t)g_dbg_mn_sbo : (base32 ? 512u : 1024u);
+  p.a_layout = (a_mn && base32) ? 1u : 2u;
+  p.b_layout = (b_mn && base32) ? 1u : 2u;
   p.a_lbo = a_mn ? mn_lbo : 16; p.a_sbo = a_mn ? mn_sbo : 1024; p.a_kstep = a_mn ? MMA_K * ROW_BYTES : 32;
   p.b_lbo = b_mn ? mn_lbo : 16; p.b_sbo = b_mn ? mn_sbo : 1024; p.b_kstep = b_mn ? MMA_K * ROW_BYTES : 32;
   p.idesc = make_idesc((uint32_t)a_fmt, (uint32_t)b_fmt, (uint32_t)a_mn, (uint32_t)b_mn, pair ? 2 * BM : BM, BN);
@@ -551,7 +576,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   p.splits = ceil_div(p.kb_total, p.kb_per_split);
   p.status = status;
   p.io_f32 = (KIND == KIND_TF32) ? 1 : 0;
-  { static int pf = -1; if (pf < 0) { const char* e = getenv("LLMB_GEMM_PF"); pf = e ? atoi(e) : 8; } p.pf = pf; }
+  { static int pf = -1; if (pf < 0) { const char* e = getenv("LLMB_GEMM_PF"); pf = e ? atoi(e) : 0; } p.pf = pf; }   // measured: prefetch requests compete with the loads for the TMA unit, off by default
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("LLMB_GEMM_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
   if (pair) {
     const long long units2 = (long long)ceil_div(M, 2 * BM) * p.n_tiles * p.splits;

@@ -118,12 +118,15 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // MN-major tile (rows of 128 B along M/N = 64 elements of 16 bit, one row per k):
 //   SBO = stride between groups of 8 k-rows (1024 B), LBO = stride between 64-element
 //   M/N chunks (the size of one TMA box).
-__host__ __device__ constexpr uint64_t make_smem_desc_hi(uint32_t sbo_bytes) {
-  return (uint64_t)((sbo_bytes >> 4) & 0x3fff) | (1ull << 14) | (2ull << 29);
+// 32-bit operands stored MN-major use layout type 1 (128-byte swizzle with a 32-byte base: 32-byte
+// chunks XOR-ed with the row index modulo 4, swizzle atoms of 4 k-rows = 512 B), which TMA writes
+// with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+__host__ __device__ constexpr uint64_t make_smem_desc_hi(uint32_t sbo_bytes, uint32_t layout_type = 2) {
+  return (uint64_t)((sbo_bytes >> 4) & 0x3fff) | (1ull << 14) | ((uint64_t)layout_type << 29);
 }
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type = 2) {
   uint32_t lo = ((smem_addr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
-  return (uint64_t)lo | (make_smem_desc_hi(sbo_bytes) << 32);
+  return (uint64_t)lo | (make_smem_desc_hi(sbo_bytes, layout_type) << 32);
 }
 
 // Instruction descriptor, kind::f16 / kind::tf32 / kind::f8f6f4 (dense, fp32 accumulate).
@@ -176,6 +179,11 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* t
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(t)), "r"(leader_bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* t, uint32_t leader_bar_cluster_addr, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(t)), "r"(leader_bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 template <int NCOLS>
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst) {  // one full warp in EACH CTA of the pair
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "n"(NCOLS) : "memory");
@@ -225,7 +233,8 @@ inline EncodeTiledFn encode_fn() {
 // 2-D row-major tensor [rows, cols] with row pitch ld (elements); box = [box_rows, box_cols];
 // 128-byte swizzle (box_cols * elem_bytes must be 128).
 inline int make_tmap_2d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
-                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols,
+                        CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {cols, rows};
@@ -233,20 +242,21 @@ inline int make_tmap_2d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt,
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (int)r;
 }
 // 3-D tensor [d2, d1, d0(inner)] with pitches in elements; box = [1, box1, box0]
 inline int make_tmap_3d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t d0,
-                        uint64_t d1, uint64_t d2, uint64_t pitch1, uint64_t pitch2, uint32_t box0, uint32_t box1) {
+                        uint64_t d1, uint64_t d2, uint64_t pitch1, uint64_t pitch2, uint32_t box0, uint32_t box1,
+                        uint32_t box2 = 1, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {pitch1 * (uint64_t)elem_bytes, pitch2 * (uint64_t)elem_bytes};
-  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t box[3] = {box0, box1, box2};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (int)r;
 }
 

@@ -156,7 +156,7 @@ class P2PBackend:
         LLp = ctypes.POINTER(ctypes.c_longlong)
         Ip = ctypes.POINTER(ctypes.c_int)
         L.llmb_comm_pack.argtypes = [P, P, I, LLp, LLp, LLp, F, P, P, I, I, U, U, P, P, I, P]
-        L.llmb_comm_reduce.argtypes = [P, I, LLp, LLp, LLp, I, P, I, P, P, P, I, I, U, U, P, P, P, I, P]
+        L.llmb_comm_reduce.argtypes = [P, I, LLp, LLp, LLp, I, P, I, P, P, P, P, I, I, U, U, P, P, P, I, P]
         L.llmb_comm_unpack.argtypes = [P, P, I, LLp, LLp, LLp, P, P, I, I, U, P, P, I, P]
         L.llmb_comm_gather.argtypes = [P, P, I, Ip, LLp, LLp, LLp, P, I, U, P, I, P]
         L.llmb_comm_adamw_push.argtypes = [P, LL, P, P, P, P, P, LL, F, F, F, F, F, F, P, I, I, P, I, I, U, P, P]
@@ -167,8 +167,9 @@ class P2PBackend:
     def _arr(vals: Sequence[int], ctype=ctypes.c_longlong):
         return (ctype * max(len(vals), 1))(*vals)
 
-    def reduce_ranges(self, src, segs, shard, dst, accumulate, allreduce) -> None:
-        """Same contract as TorchDistBackend.reduce_ranges; asynchronous on the comm stream."""
+    def reduce_ranges(self, src, segs, shard, dst, accumulate, allreduce, norm_acc=None) -> None:
+        """Same contract as TorchDistBackend.reduce_ranges; asynchronous on the comm stream.  ``norm_acc``
+        (1 fp32) additionally receives the sum of squares of the reduced values this rank owns."""
         A, W, me = self.arena, self.world, self.rank
         total = sum(n for _, n, _ in segs)
         if total > self.send_cap:
@@ -206,7 +207,7 @@ class P2PBackend:
         _lib.check(self.L.llmb_comm_reduce(A.peer_ptrs(send_name), len(owned), self._arr([o[0] for o in owned]),
                                            self._arr([o[1] for o in owned]), self._arr([o[2] for o in owned]),
                                            1 if allreduce else 0, dst.data_ptr() if dst is not None else None,
-                                           int(accumulate), A.peer_ptrs(recv_name) if allreduce else None, A.flags_ptr,
+                                           int(accumulate), A.peer_ptrs(recv_name) if allreduce else None, _lib.ptr(norm_acc), A.flags_ptr,
                                            A.flags_peer_ptrs(), me, W, seq, self.recv_last[half] if allreduce else 0,
                                            A.counter_ptr(1), A.counter_ptr(2), self.status.data_ptr(), self.blocks, st),
                    "comm_reduce")
@@ -363,6 +364,8 @@ class ZeroEngine:
             model.grads = torch.zeros(self.padded, dtype=torch.float32, device=dev)
             self.grad_shard = torch.zeros(S, dtype=torch.float32, device=dev) if self.stage == 1 else None
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.norm_acc = torch.zeros(1, dtype=torch.float32, device=dev)     # fused sum of squares (stage 1, p2p)
+        self.norm_fused = False
         self._install_views()
         if dist.is_initialized():
             dist.barrier()
@@ -471,6 +474,8 @@ class ZeroEngine:
         self._view_bucket(key, pool, self.model.g)
 
     def zero_gradients(self) -> None:
+        self.norm_acc.zero_()
+        self.norm_fused = False
         if self.stage >= 2:
             self.grad_shard.zero_()
         else:
@@ -489,6 +494,10 @@ class ZeroEngine:
                 return
             if self.stage == 0:
                 self.backend.reduce_ranges(self.model.grads, segs, self.shard_range, None, False, True)
+            elif self.backend_name == "p2p":      # the reduce kernel also emits the norm partial of its ranges
+                self.backend.reduce_ranges(self.model.grads, segs, self.shard_range, self.grad_shard, False, False,
+                                           norm_acc=self.norm_acc)
+                self.norm_fused = True
             else:
                 self.backend.reduce_ranges(self.model.grads, segs, self.shard_range, self.grad_shard, False, False)
 
@@ -502,7 +511,10 @@ class ZeroEngine:
         if self.stage == 0:
             ops.global_norm_squared(self.norm_sq, self.model.grads)        # already averaged, identical on all ranks
         else:
-            ops.global_norm_squared(self.norm_sq, self.grad_shard)
+            if self.norm_fused:
+                self.norm_sq.copy_(self.norm_acc)
+            else:
+                ops.global_norm_squared(self.norm_sq, self.grad_shard)
             if self.world_size > 1:
                 self.backend.allreduce_scalar(self.norm_sq)
         return self.norm_sq.sqrt()
