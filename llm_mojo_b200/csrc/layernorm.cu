@@ -14,7 +14,7 @@ namespace {
 constexpr int LN_MAX_VEC = 16;  // 16-byte vectors per lane: C <= 32*16*8 = 4096 for bf16
 constexpr float LN_EPS = 1e-5f;
 
-template <typename T, bool RESID>
+template <typename T, bool RESID, int PER_LANE>
 __global__ void __launch_bounds__(256) ln_fwd_kernel(T* __restrict__ out, float* __restrict__ mean_o, float* __restrict__ rstd_o,
                                                     T* __restrict__ resid_out, const T* __restrict__ inp1,
                                                     const T* __restrict__ inp2, const T* __restrict__ w,
@@ -22,13 +22,13 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(T* __restrict__ out, float*
   constexpr int N = Pack<T>::N;
   const int lane = threadIdx.x % 32, wid = threadIdx.x / 32;
   const int nvec = C / N;                       // vectors per row
-  const int per_lane = (nvec + 31) / 32;        // <= LN_MAX_VEC
+  constexpr int per_lane = PER_LANE;            // 16-byte vectors per lane: the row lives in registers
   int row = blockIdx.x * (blockDim.x / 32) + wid;
   if (row >= rows) return;
-  float x[LN_MAX_VEC][N];
+  float x[PER_LANE][N];
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < LN_MAX_VEC; ++i) {
+  for (int i = 0; i < PER_LANE; ++i) {
     if (i < per_lane) {
       int vc = i * 32 + lane;
       if (vc < nvec) {
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(T* __restrict__ out, float*
   float mean = warp_sum(sum) / C;
   float var = 0.f;
 #pragma unroll
-  for (int i = 0; i < LN_MAX_VEC; ++i) {
+  for (int i = 0; i < PER_LANE; ++i) {
     if (i < per_lane) {
       int vc = i * 32 + lane;
       if (vc < nvec) {
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(T* __restrict__ out, float*
   float rstd = rsqrtf(warp_sum(var) / C + LN_EPS);
   if (lane == 0) { if (mean_o) mean_o[row] = mean; if (rstd_o) rstd_o[row] = rstd; }
 #pragma unroll
-  for (int i = 0; i < LN_MAX_VEC; ++i) {
+  for (int i = 0; i < PER_LANE; ++i) {
     if (i < per_lane) {
       int vc = i * 32 + lane;
       if (vc < nvec) {
@@ -162,17 +162,28 @@ __global__ void ln_bwd_final_kernel(float* __restrict__ dw, float* __restrict__ 
   if (c < C) dw[c] += s; else db[c - C] += s;
 }
 
+template <typename T, int PER_LANE>
+int ln_fwd_launch_n(void* out, float* mean, float* rstd, void* resid_out, const void* inp1, const void* inp2,
+                    const void* w, const void* b, int rows, int C, cudaStream_t st) {
+  int grid = ceil_div(rows, 8);
+  if (inp2)
+    ln_fwd_kernel<T, true, PER_LANE><<<grid, 256, 0, st>>>((T*)out, mean, rstd, (T*)resid_out, (const T*)inp1, (const T*)inp2, (const T*)w, (const T*)b, rows, C);
+  else
+    ln_fwd_kernel<T, false, PER_LANE><<<grid, 256, 0, st>>>((T*)out, mean, rstd, nullptr, (const T*)inp1, nullptr, (const T*)w, (const T*)b, rows, C);
+  return (int)cudaGetLastError();
+}
+
 template <typename T>
 int ln_fwd_launch(void* out, float* mean, float* rstd, void* resid_out, const void* inp1, const void* inp2,
                   const void* w, const void* b, int rows, int C, cudaStream_t st) {
   constexpr int N = Pack<T>::N;
   if (C % N || C / N > 32 * LN_MAX_VEC) return LLMB_ERR_BAD_ARG;
-  int grid = ceil_div(rows, 8);
-  if (inp2)
-    ln_fwd_kernel<T, true><<<grid, 256, 0, st>>>((T*)out, mean, rstd, (T*)resid_out, (const T*)inp1, (const T*)inp2, (const T*)w, (const T*)b, rows, C);
-  else
-    ln_fwd_kernel<T, false><<<grid, 256, 0, st>>>((T*)out, mean, rstd, nullptr, (const T*)inp1, nullptr, (const T*)w, (const T*)b, rows, C);
-  return (int)cudaGetLastError();
+  const int per = ceil_div(C / N, 32);
+#define LNF(P) return ln_fwd_launch_n<T, P>(out, mean, rstd, resid_out, inp1, inp2, w, b, rows, C, st)
+  if (per <= 1) LNF(1); if (per <= 2) LNF(2); if (per <= 3) LNF(3); if (per <= 4) LNF(4); if (per <= 5) LNF(5);
+  if (per <= 6) LNF(6); if (per <= 7) LNF(7); if (per <= 8) LNF(8); if (per <= 10) LNF(10); if (per <= 12) LNF(12);
+  if (per <= 13) LNF(13); LNF(16);
+#undef LNF
 }
 
 template <typename T, int PER_LANE>

@@ -343,6 +343,7 @@ class ZeroEngine:
             self.embed_window = torch.empty(embed_elems, dtype=dt, device=dev)
             self.embed_valid = False
             self.window_layers = {}
+            self.window_events = [None, None]
         # ---- optimizer state (sharded for stage >= 1)
         n_opt = S if self.stage >= 1 else self.padded if W > 1 else P
         self.n_opt = n_opt
@@ -406,7 +407,11 @@ class ZeroEngine:
                 k += e - b
 
     # ------------------------------------------------------------------ parameter residency (stage 3)
-    def _gather_layer(self, l: int) -> None:
+    def _gather_layer(self, l: int, prefetch: bool = False) -> None:
+        """Make layer ``l``'s parameters resident in window ``l % 2``.  With ``prefetch`` (peer-memory
+        backend) the pull kernel runs on the comm stream, after everything already queued on the main
+        stream (the previous occupant of the window may still be in use there), and the main stream
+        only waits for it when the layer is actually needed."""
         if l in self.window_layers:
             return
         slot = l % 2
@@ -415,9 +420,26 @@ class ZeroEngine:
             for n in LAYER_TENSORS:
                 self.model.p[n].t.pop(victim, None)
         win = self.windows[slot]
-        self.backend.gather_ranges(self.param_shard, self.S, self._segs(l), win)
+        if prefetch and self.backend_name == "p2p":
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream())
+            self.backend.stream.wait_event(ready)
+            self.backend.gather_ranges(self.param_shard, self.S, self._segs(l), win, stream=self.backend.stream)
+            done = torch.cuda.Event()
+            done.record(self.backend.stream)
+            self.window_events[slot] = done
+        else:
+            self.backend.gather_ranges(self.param_shard, self.S, self._segs(l), win)
+            self.window_events[slot] = None
         self.window_layers[l] = slot
         self._view_bucket(l, win, self.model.p)
+
+    def _ensure_layer(self, l: int) -> None:
+        self._gather_layer(l)
+        ev = self.window_events[l % 2]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self.window_events[l % 2] = None
 
     def _gather_embed(self) -> None:
         if self.embed_valid:
@@ -458,7 +480,11 @@ class ZeroEngine:
 
     def before_layer(self, l: int, backward: bool) -> None:
         if self.stage == 3:
-            self._gather_layer(l)
+            self._params_ready()
+            self._ensure_layer(l)
+            nxt = l - 1 if backward else l + 1
+            if 0 <= nxt < self.model.config.num_layer:
+                self._gather_layer(nxt, prefetch=True)      # overlaps with this layer's compute
         if backward and self.stage >= 2:
             self._next_pool(l)
 
@@ -543,6 +569,7 @@ class ZeroEngine:
             for n in LAYER_TENSORS:
                 m.p[n].t.clear()
             self.embed_valid = False
+            self.window_events = [None, None]
 
     # ------------------------------------------------------------------ misc
     def mean_scalar(self, value: float) -> float:
