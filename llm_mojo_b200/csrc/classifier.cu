@@ -37,33 +37,37 @@ __global__ void __launch_bounds__(1024) classifier_kernel(T* __restrict__ logits
   __syncthreads();
   mx = bcast[0];
   const float L2E = 1.4426950408889634f;
+  // second pass: e = 2^((x - max)·log2e) once per element; the row buffer is overwritten with e (in the
+  // storage dtype) so that the third pass is a multiply, not another exponential
+  const int tgt = targets[row];
+  const float x_tgt = to_f<T>(row_s[tgt]);            // read before the buffer is overwritten
+  __syncthreads();
   float sum = 0.f;
   for (int v = tid; v < nvec; v += blockDim.x) {
     Pack<T> p; p.load(row_s + v * N);
 #pragma unroll
-    for (int k = 0; k < N; ++k) if (v * N + k < V) sum += exp2f((p.v[k] - mx) * L2E);
+    for (int k = 0; k < N; ++k) {
+      const float e = (v * N + k < V) ? exp2f((p.v[k] - mx) * L2E) : 0.f;
+      sum += e;
+      p.v[k] = e;
+    }
+    if (write_dlogits) p.store(row_s + v * N);
   }
   sum = warp_sum(sum);
-  __syncthreads();
   if (lane == 0) red[wid] = sum;
   __syncthreads();
   if (wid == 0) { float s = lane < nw ? red[lane] : 0.f; s = warp_sum(s); if (lane == 0) bcast[1] = s; }
   __syncthreads();
   sum = bcast[1];
-  const int tgt = targets[row];
-  if (tid == 0 && losses) {
-    float lt = to_f<T>(row_s[tgt]);
-    losses[row] = -(lt - mx - logf(sum));
-  }
+  if (tid == 0 && losses) losses[row] = -(x_tgt - mx - logf(sum));
   if (!write_dlogits) return;
-  const float inv = 1.0f / sum;
+  const float inv = dloss / sum;
   for (int v = tid; v < nvec; v += blockDim.x) {
     Pack<T> p; p.load(row_s + v * N);
 #pragma unroll
     for (int k = 0; k < N; ++k) {
-      int i = v * N + k;
-      float prob = exp2f((p.v[k] - mx) * L2E) * inv;
-      p.v[k] = i < V ? (prob - (i == tgt ? 1.f : 0.f)) * dloss : 0.f;
+      const int i = v * N + k;
+      p.v[k] = p.v[k] * inv - (i == tgt ? dloss : 0.f);      // padded columns hold e = 0
     }
     p.store(g + v * N);
   }

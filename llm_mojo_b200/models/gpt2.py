@@ -68,7 +68,7 @@ class GPT2:
     def __init__(self, source: str | GPT2Config, precision: Precision | str = "bf16",
                  device: str | torch.device = "cpu", zero=None, recompute: bool = False,
                  init_seed: int = INIT_RNG_SEED, params_flat: Optional[torch.Tensor] = None,
-                 lm_head_chunks: Optional[int] = None):
+                 lm_head_chunks: Optional[int] = None, vocab_parallel: Optional[bool] = None):
         self.precision = precision if isinstance(precision, Precision) else Precision(precision)
         self.device = torch.device(device)
         self.recompute = recompute or os.environ.get("LLMM_RECOMPUTE", "") not in ("", "0")
@@ -76,6 +76,12 @@ class GPT2:
         # LM-head vocabulary tiling with chunked cross-entropy: K > 1 never materialises [B,T,Vp] logits
         # (train_gpt2.mojo:127-149 LM_HEAD_VOCAB_TILES / LM_HEAD_CHUNKED_CE; README.md:145-149)
         self.lm_head_chunks = int(os.environ.get("LLMM_LM_HEAD_CHUNKS", 1)) if lm_head_chunks is None else lm_head_chunks
+        # Vocabulary-parallel LM head: every rank holds the logits of ALL ranks' rows for its 1/W slice of the
+        # vocabulary (activation all-gather -> slice GEMM -> cross-entropy with the log-sum-exp merged across
+        # ranks -> reduce-scatter of the hidden-state gradient).  The reference evaluated and rejected this on
+        # PCIe (README.md:153); it needs a ZeRO engine with world_size > 1 and stage < 3.
+        vp = os.environ.get("LLMM_VOCAB_PARALLEL", "") not in ("", "0") if vocab_parallel is None else vocab_parallel
+        self.vocab_parallel = bool(vp and zero is not None and zero.world_size > 1 and zero.stage < 3)
         self.checkpoint_path = source if isinstance(source, str) else ""
         # ---- three load paths: config/descriptor (random init), .bin, .safetensors
         if params_flat is not None:
@@ -177,7 +183,12 @@ class GPT2:
             # backward scratch
             "dres": e(B, T, C), "dl_btc": e(B, T, C), "dl_bt4c": e(B, T, 4 * C),
         }
-        if self.lm_head_chunks > 1:
+        if self.vocab_parallel:
+            W = self.zero.world_size
+            self.vslice = ((Vp + W - 1) // W + 7) // 8 * 8
+            a["logits_slice"] = e(W * B * T, self.vslice)
+            a["ce_stats"] = e(W * B * T, 4, dtype=f32)
+        elif self.lm_head_chunks > 1:
             self.tile_width = ((Vp + self.lm_head_chunks - 1) // self.lm_head_chunks + 127) // 128 * 128
             a["logits_tile"] = e(B * T, self.tile_width)
             a["ce_stats"] = e(B * T, 4, dtype=f32)
@@ -190,6 +201,49 @@ class GPT2:
 
     def activation_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.acts.values())
+
+    def _vocab_slice(self):
+        z, Vp = self.zero, self.config.padded_vocab_size
+        v0 = min(z.rank * self.vslice, Vp)
+        return v0, min(self.vslice, Vp - v0)
+
+    def _vocab_parallel_forward(self, p, dloss) -> None:
+        a, z, V = self.acts, self.zero, self.config.vocab_size
+        B, T, C = self.B, self.T, self.config.channels
+        rows = B * T
+        self._lnf_all = z.all_gather_rows(a["lnf"].view(rows, C))
+        self._tgt_all = z.all_gather_rows(self.targets_dev.view(rows))
+        v0, w = self._vocab_slice()
+        tile = a["logits_slice"][:, :max(w, 8)]
+        stats = a["ce_stats"]
+        if w > 0:
+            ops.matmul_fwd(tile, self._lnf_all, p["wte"][v0:v0 + w])
+        ops.chunked_ce_pass1(stats, tile, self._tgt_all, v0, w, V, True)
+        # merge (max, sum-exp, target logit) over the vocabulary slices of all ranks
+        allst = z.all_gather_rows(stats.unsqueeze(0))                      # [W, W·rows, 4]
+        m = allst[:, :, 0].max(dim=0).values
+        ssum = (allst[:, :, 1] * torch.exp(allst[:, :, 0] - m)).nan_to_num(0.0).sum(dim=0)
+        stats[:, 0], stats[:, 1], stats[:, 2] = m, ssum, allst[:, :, 2].sum(dim=0)
+        losses_all = torch.empty(stats.shape[0], dtype=torch.float32, device=stats.device)
+        ops.chunked_ce_loss(losses_all, stats)
+        a["losses"].view(-1).copy_(losses_all[z.rank * rows:(z.rank + 1) * rows])
+        self.loss_acc += a["losses"].sum() * dloss
+
+    def _vocab_parallel_backward(self, p, g, dl) -> None:
+        a, z, V = self.acts, self.zero, self.config.vocab_size
+        C = self.config.channels
+        v0, w = self._vocab_slice()
+        tile = a["logits_slice"][:, :max(w, 8)]
+        n_all = tile.shape[0]
+        partial = ops.scratch("vp_dlnf", n_all * C * a["lnf"].element_size(), tile.device).view(a["lnf"].dtype)[:n_all * C].view(n_all, C)
+        if w > 0:
+            # dloss keeps the per-rank convention 1/(rows·accum): the slice's weight gradient then already
+            # carries the factor W that the later mean over ranks removes
+            ops.chunked_ce_pass2(tile, a["ce_stats"], self._tgt_all, v0, w, V, self._dloss)
+            ops.lm_head_bwd_tile(partial, g["wte"][v0:v0 + w], tile, self._lnf_all, p["wte"][v0:v0 + w], accumulate=False)
+        else:
+            partial.zero_()
+        dl.view(-1, C).copy_(z.reduce_scatter_rows(partial))
 
     def _vocab_tiles(self):
         """(first column, width) of each LM-head vocabulary tile (train_gpt2.mojo:2333-2350)."""
@@ -271,6 +325,9 @@ class GPT2:
         ops.layernorm_fwd(a["lnf"], a["lnf_mean"], a["lnf_rstd"], a["residual3"][L - 1], p["lnfw"], p["lnfb"])
         dloss = 1.0 / (B * T * grad_accum_steps)
         self._dloss = dloss
+        if self.vocab_parallel and targets is not None:
+            self._vocab_parallel_forward(p, dloss)
+            return
         if self.lm_head_chunks > 1 and targets is not None:
             # pass 1 over vocabulary tiles: running (max, sum-exp, target logit) per row
             for k, (c0, w) in enumerate(self._vocab_tiles()):
@@ -319,7 +376,9 @@ class GPT2:
             z.before_head(backward=True)
         p, g = self.p, self.g
         # bucket 1: LM head
-        if self.lm_head_chunks > 1:
+        if self.vocab_parallel:
+            self._vocab_parallel_backward(p, g, dl)
+        elif self.lm_head_chunks > 1:
             # pass 2: recompute each logits tile, turn it into dlogits, and consume it at once
             V = cfg.vocab_size
             for k, (c0, w) in enumerate(self._vocab_tiles()):

@@ -579,6 +579,29 @@ class ZeroEngine:
         dist.all_reduce(t)
         return float(t.item()) / self.world_size
 
+    # ------------------------------------------------------------------ row collectives (vocab-parallel LM head)
+    def all_gather_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """[n, ...] on every rank → [W·n, ...] in rank order."""
+        if self.world_size == 1:
+            return t
+        out = torch.empty((self.world_size * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous())
+        return out
+
+    def reduce_scatter_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of [W·n, ...] over ranks; rank r keeps rows [r·n, (r+1)·n)."""
+        W = self.world_size
+        if W == 1:
+            return t
+        n = t.shape[0] // W
+        if dist.get_backend() == "gloo":                 # Gloo has no reduce-scatter
+            tmp = t.float().contiguous()
+            dist.all_reduce(tmp)
+            return tmp[self.rank * n:(self.rank + 1) * n].to(t.dtype)
+        out = torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.reduce_scatter_tensor(out, t.contiguous())
+        return out
+
     def gather_full_params(self) -> torch.Tensor:
         """Full flat parameter vector on this rank (checkpoint write, sampling; ``_z3_gather_full``)."""
         if self.stage < 3:

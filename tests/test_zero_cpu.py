@@ -60,13 +60,14 @@ def _baseline(W, steps, accum, Bp=2, T=8):
     return model.params.clone(), losses
 
 
-def _worker(rank, W, port, stage, steps, accum, q):
+def _worker(rank, W, port, stage, steps, accum, q, vocab_parallel=False):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
         dist.init_process_group("gloo", rank=rank, world_size=W)
         from llm_mojo_b200.parallel.zero import ZeroEngine
         eng = ZeroEngine(stage, rank, W, torch.device("cpu"), backend="gloo")
-        model = GPT2(CFG, "fp32", "cpu", zero=eng)
+        model = GPT2(CFG, "fp32", "cpu", zero=eng, vocab_parallel=vocab_parallel)
+        assert model.vocab_parallel == vocab_parallel
         xs, ys = zip(*[_batch(2, 8, seed=100 * rank + i) for i in range(steps * accum)])
         losses = _train(model, list(xs), list(ys), steps, accum)
         losses = [eng.mean_scalar(l) for l in losses]
@@ -80,11 +81,11 @@ def _worker(rank, W, port, stage, steps, accum, q):
         raise
 
 
-def _run(W, stage, steps=2, accum=2):
+def _run(W, stage, steps=2, accum=2, vocab_parallel=False):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, W, port, stage, steps, accum, q)) for r in range(W)]
+    procs = [ctx.Process(target=_worker, args=(r, W, port, stage, steps, accum, q, vocab_parallel)) for r in range(W)]
     for p in procs:
         p.start()
     tag, full, losses, rep = q.get(timeout=180)
@@ -109,6 +110,18 @@ def test_zero_stage_matches_single_process(stage):
         assert rep["grads_bytes"] == 0 and rep["grad_pool_bytes"] > 0
     if stage == 3:
         assert rep["params_bytes"] == 0 and rep["param_shard_bytes"] > 0
+
+
+@pytest.mark.parametrize("W,stage", [(2, 0), (4, 1), (3, 2)])
+def test_vocab_parallel_lm_head_matches_replicated_head(W, stage):
+    """LM head sharded over the vocabulary (activation all-gather, cross-rank log-sum-exp, reduce-scatter of
+    the hidden gradient) must give the single-process parameters; W=3 leaves a ragged last slice."""
+    ref_params, ref_losses = _baseline(W, 2, 1)
+    full, losses, _ = _run(W, stage, steps=2, accum=1, vocab_parallel=True)
+    assert torch.allclose(full[:ref_params.numel()], ref_params, atol=5e-5, rtol=1e-4), \
+        (full[:ref_params.numel()] - ref_params).abs().max()
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 1e-5
 
 
 def test_zero3_world4():
