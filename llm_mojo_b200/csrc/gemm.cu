@@ -46,7 +46,8 @@ struct GemmParams {
   int mma_per_stage;
   int m_tiles, n_tiles, splits, kb_per_split, kb_total;
   int io_f32;                  // 1: D, bias and aux are fp32 (tf32 kind); 0: bf16
-  int pf;                      // L2 prefetch distance of the TMA producer, in k-blocks (0 = off)
+  int tma_epi;                 // 1: bf16 outputs leave (and auxiliary inputs arrive) by TMA; 0: register/shared-memory epilogue
+  int bias_vec;                // bias pointer is 16-byte aligned (vector loads)
   int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0)
   int* status;
 };
@@ -303,27 +304,112 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 
 // ------------------------------------------------------------------------------------------------
+// Epilogue through TMA (bf16 outputs of the CTA-pair kernel).  Each epilogue warp owns a band of
+// 32 rows x 256 columns of the accumulator and moves it in slabs of 64 columns = one 128-byte-swizzled
+// box of 32 rows x 128 B (4 KB):
+//   * tcgen05.ld gives each lane one row of the slab; bias, GELU, dGELU and the residual add happen in
+//     registers in that layout;
+//   * the auxiliary INPUT (residual stream, pre-GELU activations) arrives by TMA loads that are issued a
+//     whole tile ahead - while the tensor core is still busy with that tile - into the buffer the
+//     result is then written to in place;
+//   * results leave by TMA stores (bulk groups), so no lane ever waits on global memory and every
+//     global access of the epilogue is a full 128-byte row segment; out-of-range rows and columns are
+//     clipped by the tensor maps.
+// Epilogues with an auxiliary input or a second output (BIAS_GELU stores the pre-activation too) get
+// four 4 KB buffers per warp and a 5-deep operand ring; the others two buffers and a 6-deep ring.
+template <int EPI> struct EpiCfg {
+  static constexpr bool AUX_IN = EPI == EPI_DGELU || EPI == EPI_BIAS_RESID;
+  static constexpr bool TWO_OUT = EPI == EPI_BIAS_GELU;
+  static constexpr bool F32_OUT = EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32;
+  static constexpr int STAGES = (!F32_OUT && (AUX_IN || TWO_OUT)) ? 5 : 6;
+  static constexpr int WARP_STAGE = STAGES == 5 ? 16384 : 8192;     // epilogue staging bytes per warp
+};
+constexpr int SLAB_BYTES = 32 * 128;
+
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+  uint4 u; __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+  return u;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&x)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+}
+
+// One slab (this lane's row, 64 columns) from registers to the swizzled staging buffer.  With an
+// auxiliary input the buffer holds it on entry and the result replaces it; BIAS_GELU writes the
+// pre-activation to `buf` and the activation to `buf + SLAB_BYTES`.
+template <int EPI>
+__device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
+                                              unsigned char* buf, int col0, float alpha, int lane) {
+  unsigned char* myrow = buf + lane * 128;
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(c < 4 ? r0[(c & 3) * 8 + j] : r1[(c & 3) * 8 + j]) * alpha;
+    const int col = col0 + c * 8;
+    if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
+      if (bias && col < p.N) {
+        float b[8];
+        if (p.bias_vec) unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) b[j] = __bfloat162float(bias[col + j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] += b[j];
+      }
+    }
+    unsigned char* slot = myrow + ((c ^ (lane & 7)) << 4);
+    if (EPI == EPI_BIAS_GELU) {
+      const uint4 pre = pack8(v);
+      *reinterpret_cast<uint4*>(slot) = pre;
+      float x[8]; unpack8(pre, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = gelu_fast_f(x[j]);
+      *reinterpret_cast<uint4*>(slot + SLAB_BYTES) = pack8(v);
+    } else {
+      if (EPI == EPI_DGELU || EPI == EPI_BIAS_RESID) {
+        float x[8]; unpack8(*reinterpret_cast<const uint4*>(slot), x);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (EPI == EPI_DGELU) ? v[j] * gelu_grad_fast_f(x[j]) : v[j] + x[j];
+      }
+      *reinterpret_cast<uint4*>(slot) = pack8(v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // CTA-pair variant: a cluster of two CTAs computes a 256 x 256 tile with cta_group::2 MMAs.  Each
 // CTA stages its own 128 rows of A and its own 128-row half of B (half the B traffic per SM, and
-// a 6-deep ring of 32 KB stages instead of 4 x 48 KB), the leader issues the MMAs, and both
+// a ring of 32 KB stages instead of 48 KB ones), the leader issues the MMAs, and both
 // CTAs drain their 128 x 256 accumulator halves.  No load is multicast: every CTA fetches only
 // the tiles it owns; the peer's TMA completions are reported to the leader's mbarrier.
-constexpr int STAGES2 = 6;
 constexpr int B2_STAGE = 128 * ROW_BYTES;             // 16 KB: this CTA's half of the B tile
 constexpr int STAGE2_BYTES = A_STAGE + B2_STAGE;      // 32 KB
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 4 * 32 * 256 /*epilogue transpose*/ + 1024 + 256;
+constexpr int SMEM2_TAIL = 512;                        // barriers, TMEM slot, abort flag
+template <int EPI> constexpr int smem2_bytes() { return EpiCfg<EPI>::STAGES * STAGE2_BYTES + 4 * EpiCfg<EPI>::WARP_STAGE + 1024 + SMEM2_TAIL; }
 
 template <int KIND, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
+  using Cfg = EpiCfg<EPI>;
+  constexpr int NST = Cfg::STAGES;
+  constexpr int WSB = Cfg::WARP_STAGE;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* epi_stage = smem + STAGES2 * STAGE2_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 4 * 32 * 256);
-  uint64_t* empty_bar = full_bar + STAGES2;
-  uint64_t* tfull_bar = empty_bar + STAGES2;
+  unsigned char* epi_stage = smem + NST * STAGE2_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 4 * WSB);
+  uint64_t* empty_bar = full_bar + NST;
+  uint64_t* tfull_bar = empty_bar + NST;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* aux_bar = tempty_bar + 2;                   // [4 warps][4 slabs] auxiliary-input tiles landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -331,11 +417,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const bool leader = cta == 0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES2; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < NST; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }   // 4 warps x 2 CTAs
+    for (int a = 0; a < 16; ++a) mbar_init(&aux_bar[a], 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+    if (p.tma_epi) { prefetch_tmap(&tmD); prefetch_tmap(&tmAux); }
   }
   if (warp == 1) tmem_alloc_pair<512>(tmem_slot);
   fence_before_sync();
@@ -365,35 +453,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
-      // L2 prefetch cursor: runs p.pf k-blocks ahead of the load cursor, across work units, so that the
-      // HBM latency of a tile is paid before its TMA load is issued and the 6-stage ring only has to
-      // cover the L2 -> shared-memory latency.
-      int pf_unit = cluster_id, pf_kb = 0, pf_kb1 = 0, pf_m0 = 0, pf_n0 = 0, pf_ahead = 0;
-      bool pf_valid = false;
-      auto pf_setup = [&]() {
-        pf_valid = pf_unit < total_units;
-        if (pf_valid) {
-          int m_blk, n_blk, kb0, kb1; unit_coords(pf_unit, m_blk, n_blk, kb0, kb1);
-          pf_kb = kb0; pf_kb1 = kb1;
-          pf_m0 = m_blk * 2 * BM + (int)cta * BM; pf_n0 = n_blk * BN + (int)cta * 128;
-        }
-      };
-      auto pf_step = [&]() {            // prefetch one k-block at the cursor and advance it
-        if (!pf_valid) return;
-        const int k0 = pf_kb * p.bke;
-        if (!p.a_mn) tma_prefetch_l2_2d(&tmA, k0, pf_m0);
-        else for (int c = 0; c < BM / p.bke; ++c) tma_prefetch_l2_2d(&tmA, pf_m0 + c * p.bke, k0);
-        if (!p.b_mn) tma_prefetch_l2_2d(&tmB, k0, pf_n0);
-        else for (int c = 0; c < 128 / p.bke; ++c) tma_prefetch_l2_2d(&tmB, pf_n0 + c * p.bke, k0);
-        if (++pf_kb == pf_kb1) { pf_unit += num_clusters; pf_setup(); }
-      };
-      if (p.pf > 0 && !p.a_3d && !p.b_3d) { pf_setup(); for (; pf_ahead < p.pf; ++pf_ahead) pf_step(); }
       for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
         if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (p.pf > 0 && !p.a_3d && !p.b_3d) pf_step();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
           unsigned char* sa = smem + stage * STAGE2_BYTES;
           unsigned char* sb = sa + A_STAGE;
@@ -412,7 +476,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int chunk_elems = p.bke, nchunk = 128 / chunk_elems;
             for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sb + c * p.bke * ROW_BYTES, &tmB, lead_full, n0 + c * chunk_elems, k0);
           }
-          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+          if (++stage == NST) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -443,7 +507,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t eb = smem_u32(&empty_bar[stage]);
           umma_commit_pair(mapa_u32(eb, 0));              // stage free in both CTAs once these MMAs have read it
           umma_commit_pair(mapa_u32(eb, 1));
-          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+          if (++stage == NST) { stage = 0; phase ^= 1; }
         }
         if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
         const uint32_t tb = smem_u32(&tfull_bar[acc]);
@@ -454,6 +518,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int q = warp & 3;
+    unsigned char* wstage = epi_stage + (warp - 2) * WSB;
+    uint64_t* abar = aux_bar + (warp - 2) * 4;
+    const bool tma_epi = !Cfg::F32_OUT && p.tma_epi;      // warp-uniform
+    const int band_off = (int)cta * BM + q * 32;
+    uint32_t aux_phase = 0, aux_pending = 0;              // per-slab-buffer phase bits / loads in flight (warp-uniform)
+    uint32_t nslab = 0;                                   // slabs stored so far (buffer rotation without an aux input)
+    // auxiliary-input tiles of a work unit: one box per 64-column slab that lies inside the matrix
+    auto aux_valid = [&](int row0, int n0, int s) { return row0 < p.M && n0 + s * 64 < p.N; };
+    auto aux_issue = [&](int row0, int n0, int s) {       // all lanes keep the books, lane 0 issues
+      if (!aux_valid(row0, n0, s)) return;
+      aux_pending |= 1u << s;
+      if (lane == 0) {
+        mbar_expect_tx(&abar[s], SLAB_BYTES);
+        tma_load_2d(wstage + s * SLAB_BYTES, &tmAux, &abar[s], n0 + s * 64, row0);
+      }
+    };
+    if (Cfg::AUX_IN && tma_epi && cluster_id < total_units) {
+      int m_blk, n_blk, kb0, kb1; unit_coords(cluster_id, m_blk, n_blk, kb0, kb1);
+      for (int s = 0; s < 4; ++s) aux_issue(m_blk * 2 * BM + band_off, n_blk * BN, s);
+    }
     int it = 0;
     for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters, ++it) {
       int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
@@ -462,12 +546,71 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
       fence_after_sync();
       const int n0 = n_blk * BN;
+      const int row0 = m_blk * 2 * BM + band_off;
       const float alpha = p.alpha ? *p.alpha : 1.0f;
-      epilogue_warp<EPI>(p, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
-                         m_blk * 2 * BM + (int)cta * BM + q * 32, n0, alpha, lane);
+      const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if (!tma_epi) {
+        epilogue_warp<EPI>(p, tacc, wstage, row0, n0, alpha, lane);
+      } else {
+        const int nunit = unit + num_clusters;
+        const bool has_next = Cfg::AUX_IN && nunit < total_units;
+        int nrow0 = 0, nn0 = 0;
+        if (has_next) { int mb, nb, k0, k1; unit_coords(nunit, mb, nb, k0, k1); nrow0 = mb * 2 * BM + band_off; nn0 = nb * BN; }
+        int issued = 0;                                   // slab buffers already refilled for the next unit
+        bool ok = true;
+#pragma unroll 1
+        for (int s = 0; s < BN / 64; ++s) {
+          if (!aux_valid(row0, n0, s)) break;              // warp-uniform
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tacc + s * 64, r0);
+          tmem_ld32(tacc + s * 64 + 32, r1);
+          tmem_wait_ld();
+          unsigned char* buf;
+          if (Cfg::AUX_IN) {
+            buf = wstage + s * SLAB_BYTES;
+            if (!mbar_wait(&abar[s], (aux_phase >> s) & 1)) { ok = false; break; }
+            aux_phase ^= 1u << s; aux_pending &= ~(1u << s);
+          } else {
+            buf = wstage + (nslab & 1) * (Cfg::TWO_OUT ? 2 * SLAB_BYTES : SLAB_BYTES);
+            if (lane == 0) bulk_wait_read<1>();           // the store that used this buffer two slabs ago has read it
+            __syncwarp();
+          }
+          epi_slab_bf16<EPI>(p, r0, r1, buf, n0 + s * 64, alpha, lane);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            if (Cfg::TWO_OUT) {
+              tma_store_2d(&tmAux, buf, n0 + s * 64, row0);
+              tma_store_2d(&tmD, buf + SLAB_BYTES, n0 + s * 64, row0);
+            } else {
+              tma_store_2d(&tmD, buf, n0 + s * 64, row0);
+            }
+            bulk_commit();
+          }
+          ++nslab;
+          if (Cfg::AUX_IN && has_next) {                  // refill the buffers whose stores have been read
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+            for (; issued < s; ++issued) aux_issue(nrow0, nn0, issued);
+          }
+        }
+        if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        if (Cfg::AUX_IN && has_next) {
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+          for (; issued < 4; ++issued) aux_issue(nrow0, nn0, issued);
+        }
+      }
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));   // the leader owns the accumulator hand-back
+    }
+    if (tma_epi) {
+      // nothing of this CTA's shared memory may still be a source or a destination of a copy at exit
+      for (int s = 0; s < 4; ++s)
+        if (aux_pending & (1u << s)) (void)mbar_wait(&abar[s], (aux_phase >> s) & 1);
+      if (lane == 0) bulk_wait<0>();
+      __syncwarp();
     }
   }
 
@@ -491,14 +634,16 @@ bool pair_mode() {
 }
 
 template <int KIND, int EPI>
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& taux,
+                const GemmParams& p, int grid, cudaStream_t st) {
   static bool attr_done = false;
+  constexpr int SMEM = smem2_bytes<EPI>();
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  gemm_pair_kernel<KIND, EPI><<<grid, NUM_THREADS, SMEM2_BYTES, st>>>(ta, tb, p);
+  gemm_pair_kernel<KIND, EPI><<<grid, NUM_THREADS, SMEM, st>>>(ta, tb, td, taux, p);
   return (int)cudaGetLastError();
 }
 
@@ -576,20 +721,33 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   p.splits = ceil_div(p.kb_total, p.kb_per_split);
   p.status = status;
   p.io_f32 = (KIND == KIND_TF32) ? 1 : 0;
-  { static int pf = -1; if (pf < 0) { const char* e = getenv("LLMB_GEMM_PF"); pf = e ? atoi(e) : 0; } p.pf = pf; }   // measured: prefetch requests compete with the loads for the TMA unit, off by default
+  p.bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
+  p.tma_epi = 0;
   { static int dbg = -1; if (dbg < 0) { const char* e = getenv("LLMB_GEMM_DBG"); dbg = e ? atoi(e) : 0; } p.dbg = dbg; }
   if (pair) {
     const long long units2 = (long long)ceil_div(M, 2 * BM) * p.n_tiles * p.splits;
     const int max_clusters = sm_count() / 2;
     const int grid2 = 2 * (int)(units2 < max_clusters ? units2 : max_clusters);
+    // bf16 outputs (and bf16 auxiliary tensors) travel by TMA when their layout allows a tensor map
+    CUtensorMap td = ta, taux = ta;                       // placeholders when the register epilogue runs
+    static int tma_epi_on = -1;
+    if (tma_epi_on < 0) { const char* e = getenv("LLMB_GEMM_TMA_EPI"); tma_epi_on = (e && e[0] == '0') ? 0 : 1; }
+    const bool needs_aux = epi == EPI_BIAS_GELU || epi == EPI_DGELU || epi == EPI_BIAS_RESID;
+    if (tma_epi_on && !p.io_f32 && epi != EPI_ACC_F32 && epi != EPI_STORE_F32 && (ldd * 2) % 16 == 0 &&
+        (!needs_aux || (aux && (reinterpret_cast<uintptr_t>(aux) & 15) == 0 && (ldaux * 2) % 16 == 0))) {
+      int ok = make_tmap_2d(&td, D, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldd, 32, 64) == 0;
+      if (ok && needs_aux)
+        ok = make_tmap_2d(&taux, aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldaux, 32, 64) == 0;
+      p.tma_epi = ok;
+    }
     switch (epi) {
-      case EPI_NONE: return launch_pair<KIND, EPI_NONE>(ta, tb, p, grid2, st);
-      case EPI_BIAS: return launch_pair<KIND, EPI_BIAS>(ta, tb, p, grid2, st);
-      case EPI_BIAS_GELU: return launch_pair<KIND, EPI_BIAS_GELU>(ta, tb, p, grid2, st);
-      case EPI_DGELU: return launch_pair<KIND, EPI_DGELU>(ta, tb, p, grid2, st);
-      case EPI_ACC_F32: return launch_pair<KIND, EPI_ACC_F32>(ta, tb, p, grid2, st);
-      case EPI_BIAS_RESID: return launch_pair<KIND, EPI_BIAS_RESID>(ta, tb, p, grid2, st);
-      case EPI_STORE_F32: return launch_pair<KIND, EPI_STORE_F32>(ta, tb, p, grid2, st);
+      case EPI_NONE: return launch_pair<KIND, EPI_NONE>(ta, tb, td, taux, p, grid2, st);
+      case EPI_BIAS: return launch_pair<KIND, EPI_BIAS>(ta, tb, td, taux, p, grid2, st);
+      case EPI_BIAS_GELU: return launch_pair<KIND, EPI_BIAS_GELU>(ta, tb, td, taux, p, grid2, st);
+      case EPI_DGELU: return launch_pair<KIND, EPI_DGELU>(ta, tb, td, taux, p, grid2, st);
+      case EPI_ACC_F32: return launch_pair<KIND, EPI_ACC_F32>(ta, tb, td, taux, p, grid2, st);
+      case EPI_BIAS_RESID: return launch_pair<KIND, EPI_BIAS_RESID>(ta, tb, td, taux, p, grid2, st);
+      case EPI_STORE_F32: return launch_pair<KIND, EPI_STORE_F32>(ta, tb, td, taux, p, grid2, st);
     }
     return LLMB_ERR_BAD_ARG;
   }
