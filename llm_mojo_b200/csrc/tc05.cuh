@@ -33,6 +33,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+// non-blocking probe (never suspends): for a thread that polls several barriers in turn
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
 // Bounded wait: ~2^22 polls (each poll may suspend for the hardware time slice) is on the
 // order of a second; returns false on expiry.
 constexpr uint32_t kWaitBudget = 1u << 22;
@@ -55,6 +65,16 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* t, uin
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(t)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes)
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// pull a box into L2 ahead of the load that will consume it (no shared memory, no barrier involved)
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* t, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(t)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 // TMA store of a shared-memory box to global memory (bulk async-group completion, tracked per issuing thread)
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* t, const void* src, int c0, int c1) {
@@ -144,6 +164,14 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
 }
 
 enum { KIND_F16 = 0, KIND_TF32 = 1, KIND_F8F6F4 = 2 };
+// One lane of a converged warp (the same lane on every call).  Keeping the surrounding control flow
+// warp-uniform and predicating only the tcgen05 instruction lets the compiler hold descriptors and
+// addresses in uniform registers instead of rebuilding them inside a single-lane branch.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread
 template <int KIND>
 __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {

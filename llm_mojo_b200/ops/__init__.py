@@ -329,7 +329,7 @@ def attention_bwd(dqkv, dout, qkv, out, lse, num_heads: int) -> None:
     C = C3 // 3
     hs = C // num_heads
     if qkv.is_cuda and ATTN_IMPL == "tcgen05" and hs == 64 and qkv.dtype == torch.bfloat16:
-        dvec = scratch("attn_dvec", B * num_heads * T * 4, qkv.device)
+        dvec = scratch("attn_dvec", B * num_heads * (T + 128 * ((T + 63) // 64)) * 4 + 16, qkv.device)
         check(lib().llmb_attention_bwd(ptr(dqkv), ptr(dvec), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T, num_heads,
                                        ptr(status_word(qkv.device)), stream()), "attention_bwd")
         _count(3)

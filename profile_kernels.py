@@ -1,0 +1,91 @@
+#!/usr/bin/env python
+"""Run ONE hot kernel family on a small, L2-exceeding case so that a profiler capture ends in seconds.
+
+    python profile_kernels.py attn        # flash attention forward + backward, B=32 T=1024 NH=12
+    python profile_kernels.py gemm        # fc GEMM with the fused bias+GELU epilogue, its dinp (dGELU) and dW GEMMs
+    python profile_kernels.py lmhead      # LM-head GEMM on 8192 rows + fused softmax/cross-entropy
+    python profile_kernels.py layernorm   # LayerNorm forward + backward on 65536 x 768
+
+Each case launches its kernels `--reps` times (default 2) and prints the device status word.  Meant to be run
+plain first and then under `ncu -k regex:<kernel> -c <n>` with the same command line; the per-step counterpart
+that times the whole model is profile_gpt2.py (reference: profile_gpt2.mojo / profile_gpt2cu.py).
+"""
+import argparse
+
+import torch
+
+from llm_mojo_b200 import ops
+
+
+def case_attn(reps):
+    B, T, NH, C = 32, 1024, 12, 768
+    qkv = torch.randn(B, T, 3 * C, device="cuda").bfloat16()
+    out = torch.empty(B, T, C, device="cuda", dtype=torch.bfloat16)
+    lse = torch.empty(B, NH, T, device="cuda")
+    dqkv = torch.empty_like(qkv)
+    dout = torch.randn(B, T, C, device="cuda").bfloat16()
+    for _ in range(reps):
+        ops.attention_fwd(out, lse, qkv, NH)
+        ops.attention_bwd(dqkv, dout, qkv, out, lse, NH)
+
+
+def case_gemm(reps):
+    rows, C = 32768, 768
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w = (torch.randn(4 * C, C, device="cuda") * 0.02).bfloat16()
+    b = torch.zeros(4 * C, device="cuda", dtype=torch.bfloat16)
+    pre = torch.empty(rows, 4 * C, device="cuda", dtype=torch.bfloat16)
+    act = torch.empty_like(pre)
+    dx = torch.empty_like(x)
+    dw = torch.zeros(4 * C, C, device="cuda")
+    db = torch.zeros(4 * C, device="cuda")
+    w2 = (torch.randn(C, 4 * C, device="cuda") * 0.02).bfloat16()
+    dw2 = torch.zeros(C, 4 * C, device="cuda")
+    dact = torch.empty_like(pre)
+    dy = torch.randn(rows, C, device="cuda").bfloat16()
+    for _ in range(reps):
+        ops.matmul_fwd(act, x, w, b, pre_gelu=pre)                       # bias + GELU epilogue, two outputs
+        ops.matmul_bwd(dact, dw2, None, dy, act, w2, gelu_pre=pre)       # fcproj backward: dGELU epilogue on dinp
+        ops.matmul_bwd(dx, dw, db, dact, x, w)                           # fc backward: dinp (B MN-major), split-K dW
+
+
+def case_lmhead(reps):
+    rows, C, V, Vp = 8192, 768, 50257, 50304
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w = (torch.randn(Vp, C, device="cuda") * 0.02).bfloat16()
+    logits = torch.empty(rows, Vp, device="cuda", dtype=torch.bfloat16)
+    losses = torch.empty(rows, device="cuda")
+    tgt = torch.randint(0, V, (rows,), device="cuda", dtype=torch.int32)
+    for _ in range(reps):
+        ops.matmul_fwd(logits, x, w)
+        ops.fused_classifier(logits, losses, tgt, 1.0 / rows, V)
+
+
+def case_layernorm(reps):
+    rows, C = 65536, 768
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w = torch.ones(C, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(C, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty_like(x)
+    mean = torch.empty(rows, device="cuda")
+    rstd = torch.empty(rows, device="cuda")
+    dx = torch.zeros_like(x)
+    dw = torch.zeros(C, device="cuda")
+    db = torch.zeros(C, device="cuda")
+    dout = torch.randn(rows, C, device="cuda").bfloat16()
+    for _ in range(reps):
+        ops.layernorm_fwd(o, mean, rstd, x, w, b)
+        ops.layernorm_bwd(dx, dw, db, dout, x, w, mean, rstd)
+
+
+CASES = {"attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("case", choices=sorted(CASES))
+    ap.add_argument("--reps", type=int, default=2)
+    a = ap.parse_args()
+    torch.manual_seed(0)
+    CASES[a.case](a.reps)
+    torch.cuda.synchronize()
+    print("ok, kernel status", ops._lib.read_status())
