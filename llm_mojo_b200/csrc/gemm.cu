@@ -451,69 +451,89 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane issues (same reasoning as for the MMA issuer below)
+    {
       int stage = 0; uint32_t phase = 0;
+      const uint32_t lead_full0 = mapa_u32(smem_u32(&full_bar[0]), 0);
+      bool ok = true;
       for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
         if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           unsigned char* sa = smem + stage * STAGE2_BYTES;
           unsigned char* sb = sa + A_STAGE;
-          const uint32_t lead_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE2_BYTES);     // bytes of both CTAs
+          const uint32_t lead_full = lead_full0 + stage * 8;
           const int k0 = (p.dbg & 2) ? 0 : kb * p.bke;
-          if (!p.a_mn) tma_load_2d_pair(sa, &tmA, lead_full, k0, m0);
-          else if (p.a_3d) tma_load_3d_pair(sa, &tmA, lead_full, 0, k0, m0 / p.bke);
-          else {
-            const int chunk_elems = p.bke, nchunk = BM / chunk_elems;
-            for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sa + c * p.bke * ROW_BYTES, &tmA, lead_full, m0 + c * chunk_elems, k0);
+          if (elect_one()) {
+            if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE2_BYTES);     // bytes of both CTAs
+            if (!p.a_mn) tma_load_2d_pair(sa, &tmA, lead_full, k0, m0);
+            else if (p.a_3d) tma_load_3d_pair(sa, &tmA, lead_full, 0, k0, m0 / p.bke);
+            else {
+              const int chunk_elems = p.bke, nchunk = BM / chunk_elems;
+              for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sa + c * p.bke * ROW_BYTES, &tmA, lead_full, m0 + c * chunk_elems, k0);
+            }
+            if (!p.b_mn) tma_load_2d_pair(sb, &tmB, lead_full, k0, n0);
+            else if (p.b_3d) tma_load_3d_pair(sb, &tmB, lead_full, 0, k0, n0 / p.bke);
+            else {
+              const int chunk_elems = p.bke, nchunk = 128 / chunk_elems;
+              for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sb + c * p.bke * ROW_BYTES, &tmB, lead_full, n0 + c * chunk_elems, k0);
+            }
           }
-          if (!p.b_mn) tma_load_2d_pair(sb, &tmB, lead_full, k0, n0);
-          else if (p.b_3d) tma_load_3d_pair(sb, &tmB, lead_full, 0, k0, n0 / p.bke);
-          else {
-            const int chunk_elems = p.bke, nchunk = 128 / chunk_elems;
-            for (int c = 0; c < nchunk; ++c) tma_load_2d_pair(sb + c * p.bke * ROW_BYTES, &tmB, lead_full, n0 + c * chunk_elems, k0);
-          }
+          __syncwarp();
           if (++stage == NST) { stage = 0; phase ^= 1; }
         }
+        if (!ok) break;
       }
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (lane == 0 && leader) {
+    // The whole warp walks the loop (uniform control flow, so descriptors and barrier addresses stay in
+    // uniform registers) and one elected lane issues.  Everything that does not change per k-block is
+    // computed once: the descriptors of stage 0 (a later stage only adds its byte offset >> 4 to the
+    // address field), the per-MMA descriptor increments and the cluster addresses of the barriers.
+    if (leader) {
       int stage = 0; uint32_t phase = 0;
       int it = 0;
+      const uint64_t adesc0 = make_smem_desc(smem_u32(smem), p.a_lbo, p.a_sbo, p.a_layout);
+      const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + A_STAGE, p.b_lbo, p.b_sbo, p.b_layout);
+      const uint64_t a_inc = (uint64_t)(p.a_kstep >> 4), b_inc = (uint64_t)(p.b_kstep >> 4);
+      const uint32_t idesc = p.idesc;
+      const uint32_t eb0 = mapa_u32(smem_u32(&empty_bar[0]), 0), eb1 = mapa_u32(smem_u32(&empty_bar[0]), 1);
+      const uint32_t tb0 = mapa_u32(smem_u32(&tfull_bar[0]), 0), tb1 = mapa_u32(smem_u32(&tfull_bar[0]), 1);
+      bool ok = true;
       for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters, ++it) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * STAGE2_BYTES);
-          const uint32_t sb = sa + A_STAGE;
-          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo, p.a_layout);
-          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo, p.b_layout);
-          for (int k = 0; k < p.mma_per_stage; ++k) {
-            umma_ss_pair<KIND>(d_tmem, adesc + (uint64_t)((k * p.a_kstep) >> 4), bdesc + (uint64_t)((k * p.b_kstep) >> 4),
-                               p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          const uint64_t adesc = adesc0 + (uint64_t)(stage * (STAGE2_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(stage * (STAGE2_BYTES >> 4));
+          if (elect_one()) {
+            umma_ss_pair<KIND>(d_tmem, adesc, bdesc, idesc, kb > kb0 ? 1u : 0u);
+#pragma unroll
+            for (int k = 1; k < 4; ++k) umma_ss_pair<KIND>(d_tmem, adesc + k * a_inc, bdesc + k * b_inc, idesc, 1u);
+            umma_commit_pair(eb0 + stage * 8);            // stage free in both CTAs once these MMAs have read it
+            umma_commit_pair(eb1 + stage * 8);
           }
-          const uint32_t eb = smem_u32(&empty_bar[stage]);
-          umma_commit_pair(mapa_u32(eb, 0));              // stage free in both CTAs once these MMAs have read it
-          umma_commit_pair(mapa_u32(eb, 1));
+          __syncwarp();
           if (++stage == NST) { stage = 0; phase ^= 1; }
         }
-        if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
-        const uint32_t tb = smem_u32(&tfull_bar[acc]);
-        umma_commit_pair(mapa_u32(tb, 0));
-        umma_commit_pair(mapa_u32(tb, 1));
+        if (!ok) break;
+        if (elect_one()) {
+          umma_commit_pair(tb0 + acc * 8);
+          umma_commit_pair(tb1 + acc * 8);
+        }
+        __syncwarp();
       }
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
