@@ -4,7 +4,11 @@
 Parity: ``bench_gemm.mojo:1-60`` (candidate kernels vs the library GEMM on the real model shapes).
 Prints one row per (shape, variant): forward (K-major x K-major), dinp (B stored [K,N]) and dW (both
 operands stored [K,·], split-K with fp32 red.add), in CTA-pair and single-CTA tile modes, as TF/s and as
-a fraction of the measured cuBLAS bf16 peak in MEASURED_PEAKS.json when that file is present."""
+a fraction of the measured cuBLAS bf16 peak in MEASURED_PEAKS.json when that file is present.
+
+``--layer`` times the calls a transformer block actually makes (``ops.matmul_fwd`` / ``ops.matmul_bwd`` with their
+fused bias, GELU, dGELU and residual epilogues, dinp + dW + dbias for the backward) with a 256 MB L2 flush between
+timed launches; ``LLMB_GEMM_TMA_EPI=0`` selects the register/shared-memory epilogue for comparison."""
 from __future__ import annotations
 
 import argparse
@@ -32,18 +36,72 @@ def timed(fn, iters=10, warmup=3):
     return a.elapsed_time(b) / iters
 
 
+def timed_flushed(fn, iters=10, warmup=3):
+    """Per-launch CUDA-event time with an L2 flush (a 256 MB memset) between launches."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    total = 0.0
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def layer_calls(C: int, rows: int, Vp: int) -> None:
+    bf = torch.bfloat16
+
+    def rnd(*shape):
+        return (torch.randn(*shape, device="cuda") * 0.05).to(bf)
+
+    for name, OC, K, mode in [("qkv", 3 * C, C, "bias"), ("attproj", C, C, "resid"), ("fc", 4 * C, C, "gelu"),
+                              ("fcproj", C, 4 * C, "resid"), ("lm_head", Vp, C, "none")]:
+        x, w, b = rnd(rows, K), rnd(OC, K), rnd(OC)
+        out = torch.empty(rows, OC, device="cuda", dtype=bf)
+        aux = torch.empty(rows, OC, device="cuda", dtype=bf)
+        if mode == "bias":
+            fn = lambda: ops.matmul_fwd(out, x, w, b)
+        elif mode == "resid":
+            fn = lambda: ops.matmul_fwd(out, x, w, b, residual=aux)
+        elif mode == "gelu":
+            fn = lambda: ops.matmul_fwd(out, x, w, b, pre_gelu=aux)
+        else:
+            fn = lambda: ops.matmul_fwd(out, x, w, None)
+        ms = timed_flushed(fn)
+        print(f"fwd {name:8s} ({mode:5s}) {ms:.3f} ms {2.0 * rows * OC * K / ms / 1e9:6.0f} TF/s")
+        if name == "lm_head":
+            continue
+        dinp = torch.empty(rows, K, device="cuda", dtype=bf)
+        dw = torch.zeros(OC, K, device="cuda")
+        db = torch.zeros(OC, device="cuda")
+        gelu_pre = rnd(rows, K) if name == "fcproj" else None      # fcproj's input gradient passes through dGELU
+        ms = timed_flushed(lambda: ops.matmul_bwd(dinp, dw, db, out, x, w, gelu_pre=gelu_pre))
+        print(f"bwd {name:8s} (dinp{'+dGELU' if gelu_pre is not None else ''}, dW, dbias) {ms:.3f} ms {4.0 * rows * OC * K / ms / 1e9:6.0f} TF/s")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="d12")
     ap.add_argument("-b", type=int, default=64)
     ap.add_argument("-t", type=int, default=1024)
     ap.add_argument("--modes", default="1,0", help="1 = CTA-pair tiles, 0 = single-CTA tiles")
+    ap.add_argument("--layer", action="store_true", help="time the fused per-layer calls with an L2 flush between launches")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("bench_gemm needs a GPU")
         return 0
     cfg = parse_model_descriptor(a.model)
     C, rows = cfg.channels, a.b * a.t
+    if a.layer:
+        layer_calls(C, rows, cfg.padded_vocab_size)
+        print("kernel status", _lib.read_status())
+        return 0
     peak = None
     pk = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(pk):

@@ -592,8 +592,9 @@ struct TileCursor {
   bool done;
 };
 // n_t tiles along T, n_items = ceil(n_t / 2) * B * NH work items; `heavy_low`: tile 0 is the heaviest
-__device__ __forceinline__ void cursor_seek(TileCursor& c, int n_t, int n_items, bool heavy_low) {
+__device__ __forceinline__ void cursor_seek(TileCursor& c, int n_t, int n_items, bool heavy_low, int stride = 0) {
   const int n_pairs = (n_t + 1) / 2;
+  if (stride == 0) stride = gridDim.x;
   for (;;) {
     if (c.w >= n_items) { c.done = true; return; }
     const int x = c.w % n_pairs;
@@ -601,7 +602,7 @@ __device__ __forceinline__ void cursor_seek(TileCursor& c, int n_t, int n_items,
     const int lo = x, hi = n_t - 1 - x;
     if (c.sub == 0) { c.tile = heavy_low ? lo : hi; return; }
     if (lo != hi) { c.tile = heavy_low ? hi : lo; return; }
-    c.w += gridDim.x; c.sub = 0;
+    c.w += stride; c.sub = 0;
   }
 }
 __device__ __forceinline__ TileCursor cursor_begin(int n_t, int n_items, bool heavy_low) {
@@ -609,10 +610,240 @@ __device__ __forceinline__ TileCursor cursor_begin(int n_t, int n_items, bool he
   cursor_seek(c, n_t, n_items, heavy_low);
   return c;
 }
-__device__ __forceinline__ void cursor_next(TileCursor& c, int chunks, int n_t, int n_items, bool heavy_low) {
+__device__ __forceinline__ void cursor_next(TileCursor& c, int chunks, int n_t, int n_items, bool heavy_low, int stride = 0) {
+  if (stride == 0) stride = gridDim.x;
   c.t += 1; c.g += chunks;
-  if (c.sub == 0) c.sub = 1; else { c.sub = 0; c.w += gridDim.x; }
-  cursor_seek(c, n_t, n_items, heavy_low);
+  if (c.sub == 0) c.sub = 1; else { c.sub = 0; c.w += stride; }
+  cursor_seek(c, n_t, n_items, heavy_low, stride);
+}
+// a CTA may run several independent tile streams: stream `vid` of `vgrid`
+__device__ __forceinline__ TileCursor cursor_begin_v(int vid, int vgrid, int n_t, int n_items, bool heavy_low) {
+  TileCursor c{vid, 0, 0, 0, 0, 0, false};
+  cursor_seek(c, n_t, n_items, heavy_low, vgrid);
+  return c;
+}
+
+// ------------------------------------------------------------------- forward, persistent
+// One CTA per SM runs TWO independent tile streams (groups): each group has its own TMA producer warp, its
+// own issuing warp and four softmax warps (one thread per query row), its own Q / K,V ring / P buffers and
+// its own TMEM columns, so the online-softmax chain of one group's tile never waits on the other's, and the
+// tensor core, both groups' MUFU work and the loads overlap.  Keys are taken in chunks of 64:
+//   S(j) = Q K_j^T (TMEM, double-buffered) -> softmax warps: row max, p = 2^(s - m), row sum, P(j) as bf16
+//   into shared memory (the running output in TMEM is rescaled only when a row's maximum grew by more than
+//   2^8) -> O += P(j) V_j.  The issuing warp keeps S two chunks ahead of the softmax warps.
+// warps: 0 producer A, 1 issuer A, 2 issuer B, 3 producer B, 4..7 softmax A, 8..11 softmax B.
+constexpr int FW_NS = 4;                                 // K/V chunk ring depth per group
+constexpr int FW_THREADS = 384;
+constexpr int FW_GROUP_SMEM = 2 * T128 /*Q x2*/ + FW_NS * 2 * T64 /*K,V ring*/ + T128 /*P*/;
+constexpr int FWD2_SMEM = 2 * FW_GROUP_SMEM + 1024 + 512;
+
+__global__ void __launch_bounds__(FW_THREADS, 1) attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+  const int grp = (warp == 0 || warp == 1 || (warp >= 4 && warp < 8)) ? 0 : 1;
+  unsigned char* gs = sm + grp * FW_GROUP_SMEM;
+  unsigned char* sQ = gs;                        // two buffers
+  unsigned char* sKV = sQ + 2 * T128;            // ring: stage s holds the K chunk at +0, the V chunk at +T64
+  unsigned char* sP = sKV + FW_NS * 2 * T64;     // [128 q x 64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 2 * FW_GROUP_SMEM) + grp * 24;
+  uint64_t* q_full = bars;                       // [2]
+  uint64_t* q_empty = q_full + 2;                // [2] the tile's last score product is complete
+  uint64_t* kv_full = q_empty + 2;               // [NS]
+  uint64_t* kv_empty = kv_full + FW_NS;          // [NS] O += P V of the chunk is complete (stage, P buffer and O are free)
+  uint64_t* s_full = kv_empty + FW_NS;           // [2]
+  uint64_t* p_full = s_full + 2;                 // P(j) written (and S(j) read)
+  uint64_t* o_free = p_full + 1;                 // the tile's output has been read out of TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + 2 * FW_GROUP_SMEM + 2 * 24 * 8);
+
+  const int n_t = ceil_div(p.T, TILE);
+  const int n_items = ((n_t + 1) / 2) * p.B * p.NH;
+  const int vid = 2 * blockIdx.x + grp, vgrid = 2 * gridDim.x;
+  auto chunks_of = [&](int qt) { return ceil_div(min(p.T, (qt + 1) * TILE), 64); };
+
+  if (tid == 0) {
+    uint64_t* b0 = reinterpret_cast<uint64_t*>(sm + 2 * FW_GROUP_SMEM);
+    for (int g = 0; g < 2; ++g) {
+      uint64_t* b = b0 + g * 24;
+      for (int i = 0; i < 2; ++i) { mbar_init(&b[i], 1); mbar_init(&b[2 + i], 1); mbar_init(&b[4 + 2 * FW_NS + i], 1); }
+      for (int i = 0; i < FW_NS; ++i) { mbar_init(&b[4 + i], 1); mbar_init(&b[4 + FW_NS + i], 1); }
+      mbar_init(&b[4 + 2 * FW_NS + 2], 4);       // p_full: four softmax warps
+      mbar_init(&b[4 + 2 * FW_NS + 3], 4);       // o_free
+    }
+    fence_barrier_init();
+    prefetch_tmap(&tm);
+  }
+  if (warp == 1) tmem_alloc<512>(tmem_slot);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot + grp * 256;
+  const uint32_t tS = tmem, tO = tmem + 128;             // S: two 64-column buffers; O: 64 columns
+  bool failed = false;
+
+  if (warp == 0 || warp == 3) {
+    // ------------------------------------------------------------ TMA producer of this group
+    for (TileCursor c = cursor_begin_v(vid, vgrid, n_t, n_items, false); !c.done && !failed;) {
+      const int b = c.bh / p.NH, h = c.bh % p.NH, qb = c.t & 1, n_kc = chunks_of(c.tile);
+      const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
+      if (c.t >= 2 && !mbar_wait(&q_empty[qb], ((c.t >> 1) + 1) & 1)) { BW_FAIL(); break; }
+      if (elect_one()) {
+        mbar_expect_tx(&q_full[qb], T128);
+        load128(sQ + qb * T128, &tm, &q_full[qb], colQ, c.tile * TILE, b);
+      }
+      __syncwarp();
+      for (int j = 0; j < n_kc; ++j) {
+        const int g = c.g + j, st = g % FW_NS;
+        if (g >= FW_NS && !mbar_wait(&kv_empty[st], ((g / FW_NS) + 1) & 1)) { BW_FAIL(); break; }
+        if (elect_one()) {
+          mbar_expect_tx(&kv_full[st], 2 * T64);
+          tma_load_3d(sKV + st * 2 * T64, &tm, &kv_full[st], colK, j * 64, b);
+          tma_load_3d(sKV + st * 2 * T64 + T64, &tm, &kv_full[st], colV, j * 64, b);
+        }
+        __syncwarp();
+      }
+      cursor_next(c, n_kc, n_t, n_items, false, vgrid);
+    }
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------ MMA issuer of this group
+    // fixed pipeline per tile: S(0), S(1); then for every chunk: wait P(j) -> O += P(j) V_j -> S(j + 2)
+    for (TileCursor c = cursor_begin_v(vid, vgrid, n_t, n_items, false); !c.done && !failed;) {
+      const int qb = c.t & 1, n_kc = chunks_of(c.tile);
+      const uint32_t q_addr = smem_u32(sQ + qb * T128);
+      if (!mbar_wait(&q_full[qb], (c.t >> 1) & 1)) { BW_FAIL(); break; }
+      auto issue_s = [&](int j) {
+        const int g = c.g + j, st = g % FW_NS;
+        if (!mbar_wait(&kv_full[st], (g / FW_NS) & 1)) { BW_FAIL(); return; }
+        fence_after_sync();
+        if (elect_one()) {
+          mma_kk(tS + (g & 1) * 64, q_addr, smem_u32(sKV + st * 2 * T64), IDESC_128x64_KK, HS / 16, false);   // S = Q K^T
+          umma_commit(&s_full[g & 1]);
+          if (j == n_kc - 1) umma_commit(&q_empty[qb]);
+        }
+        __syncwarp();
+      };
+      issue_s(0);
+      if (n_kc > 1 && !failed) issue_s(1);
+      // the previous tile's output must have left TMEM before this tile's first product overwrites it
+      if (c.t >= 1 && !failed && !mbar_wait(o_free, (c.t + 1) & 1)) BW_FAIL();
+      for (int j = 0; j < n_kc && !failed; ++j) {
+        const int g = c.g + j, st = g % FW_NS;
+        if (!mbar_wait(p_full, g & 1)) { BW_FAIL(); break; }
+        fence_after_sync();
+        if (elect_one()) {
+          mma_kmn(tO, smem_u32(sP), smem_u32(sKV + st * 2 * T64 + T64), IDESC_128x64_KMN, 4, j > 0);   // O (+)= P V
+          umma_commit(&kv_empty[st]);
+        }
+        __syncwarp();
+        if (j + 2 < n_kc) issue_s(j + 2);
+      }
+      cursor_next(c, n_kc, n_t, n_items, false, vgrid);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps: one thread per query row
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const float sc = p.scale_log2;
+    for (TileCursor c = cursor_begin_v(vid, vgrid, n_t, n_items, false); !c.done && !failed;) {
+      const int b = c.bh / p.NH, h = c.bh % p.NH, q0 = c.tile * TILE, qi = q0 + row, n_kc = chunks_of(c.tile);
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n_kc; ++j) {
+        const int g = c.g + j;
+        if (!mbar_wait(&s_full[g & 1], (g >> 1) & 1)) { BW_FAIL(); break; }
+        fence_after_sync();
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tS + (g & 1) * 64 + lane_addr, r0);
+        tmem_ld32(tS + (g & 1) * 64 + lane_addr + 32, r1);
+        tmem_wait_ld();
+        fence_before_sync();
+        if ((j + 1) * 64 - 1 > q0) {                    // chunk touches the diagonal: mask keys after the query
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            if (j * 64 + x > qi) r0[x] = 0xff800000u;
+            if (j * 64 + 32 + x > qi) r1[x] = 0xff800000u;
+          }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int x = 0; x < 32; ++x) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[x]), __uint_as_float(r1[x])));
+        // the running maximum only moves when it grew by more than 8 (a factor 256 in p): rescales of O become rare
+        float m_new = fmaxf(m_run, mx * sc);
+        if (m_new - m_run <= 8.0f) m_new = m_run;
+        const float alpha = ex2_approx(m_run - m_new);   // m_run = -inf on the first chunk gives 0
+        m_run = m_new;
+        float rs = 0.f;
+        uint32_t pk[32];                                 // 64 probabilities as bf16 pairs
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const float e0 = ex2_approx(fmaf(__uint_as_float(r0[2 * x]), sc, -m_new));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(r0[2 * x + 1]), sc, -m_new));
+          const float e2 = ex2_approx(fmaf(__uint_as_float(r1[2 * x]), sc, -m_new));
+          const float e3 = ex2_approx(fmaf(__uint_as_float(r1[2 * x + 1]), sc, -m_new));
+          rs += (e0 + e1) + (e2 + e3);
+          pk[x] = pack_bf16x2(e0, e1);
+          pk[16 + x] = pack_bf16x2(e2, e3);
+        }
+        l_run = l_run * alpha + rs;
+        // O += P(j-1) V must be complete before O is rescaled and before P is overwritten
+        if (g >= 1 && !mbar_wait(&kv_empty[(g - 1) % FW_NS], ((g - 1) / FW_NS) & 1)) { BW_FAIL(); break; }
+        if (j > 0 && !__all_sync(0xffffffffu, alpha == 1.0f)) {
+          fence_after_sync();
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            uint32_t o[32];
+            tmem_ld32(tO + lane_addr + half * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+            tmem_st32(tO + lane_addr + half * 32, o);
+          }
+          tmem_wait_st();
+          fence_before_sync();
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8)
+          *reinterpret_cast<uint4*>(sP + sw128(row, c8)) = make_uint4(pk[c8 * 4], pk[c8 * 4 + 1], pk[c8 * 4 + 2], pk[c8 * 4 + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+      }
+      if (failed) break;
+      // tile epilogue: O / l -> bf16, log-sum-exp
+      const int gl = c.g + n_kc - 1;
+      if (!mbar_wait(&kv_empty[gl % FW_NS], (gl / FW_NS) & 1)) { BW_FAIL(); break; }
+      fence_after_sync();
+      uint32_t o0[32], o1[32];
+      tmem_ld32(tO + lane_addr, o0);
+      tmem_ld32(tO + lane_addr + 32, o1);
+      tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
+      if (qi < p.T) {
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)b * p.T + qi) * p.C + h * HS;
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(o0[j8 * 8 + 0]) * inv, __uint_as_float(o0[j8 * 8 + 1]) * inv);
+          u.y = pack_bf16x2(__uint_as_float(o0[j8 * 8 + 2]) * inv, __uint_as_float(o0[j8 * 8 + 3]) * inv);
+          u.z = pack_bf16x2(__uint_as_float(o0[j8 * 8 + 4]) * inv, __uint_as_float(o0[j8 * 8 + 5]) * inv);
+          u.w = pack_bf16x2(__uint_as_float(o0[j8 * 8 + 6]) * inv, __uint_as_float(o0[j8 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(op + j8 * 8) = u;
+          u.x = pack_bf16x2(__uint_as_float(o1[j8 * 8 + 0]) * inv, __uint_as_float(o1[j8 * 8 + 1]) * inv);
+          u.y = pack_bf16x2(__uint_as_float(o1[j8 * 8 + 2]) * inv, __uint_as_float(o1[j8 * 8 + 3]) * inv);
+          u.z = pack_bf16x2(__uint_as_float(o1[j8 * 8 + 4]) * inv, __uint_as_float(o1[j8 * 8 + 5]) * inv);
+          u.w = pack_bf16x2(__uint_as_float(o1[j8 * 8 + 6]) * inv, __uint_as_float(o1[j8 * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(op + 32 + j8 * 8) = u;
+        }
+        p.lse[(size_t)c.bh * p.T + qi] = m_run + log2f(l_run);
+      }
+      cursor_next(c, n_kc, n_t, n_items, false, vgrid);
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc<512>(*tmem_slot); }
 }
 
 // ------------------------------------------------------------------- dQ
@@ -1067,6 +1298,18 @@ LLMB_API int llmb_attention_fwd(void* out, float* lse, const void* qkv, int B, i
   p.scale = 0.125f; p.scale_log2 = 0.125f * 1.4426950408889634f; p.status = status;
   static bool attr = false;
   if (!attr) { cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM); if (e) return (int)e; attr = true; }
+  static int ver = -1;
+  if (ver < 0) { const char* e = getenv("LLMB_ATTN_FWD"); ver = e ? atoi(e) : 2; }
+  if (ver == 2) {
+    static bool attr2 = false;
+    if (!attr2) { cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD2_SMEM); if (e) return (int)e; attr2 = true; }
+    const int n_t = ceil_div(T, TILE);
+    const long long n_items = (long long)((n_t + 1) / 2) * B * NH;
+    const long long want = (n_items + 1) / 2;            // two tile streams per CTA
+    const int pgrid = (int)(want < sm_count() ? want : sm_count());
+    attn_fwd2_kernel<<<pgrid, FW_THREADS, FWD2_SMEM, st>>>(tm, p);
+    return (int)cudaGetLastError();
+  }
   dim3 grid(ceil_div(T, TILE), NH, B);
   attn_fwd_kernel<<<grid, 256, FWD_SMEM, st>>>(tm, p);
   return (int)cudaGetLastError();

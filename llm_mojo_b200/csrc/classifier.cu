@@ -3,10 +3,13 @@
 //
 // Reference behaviour: llmm/fused_classifier.mojo:186-279, :311-370 (per row: max, sum exp,
 // loss, dlogits = (p - 1[y])·dloss written over the logits, padded tail [V, Vp) zeroed);
-// llmm/softmax.mojo:172-304.  B200 design: one CTA per row; the whole row (Vp·2 B ≈ 100 KB
-// for GPT-2) is staged once in shared memory so HBM sees exactly one read and one write.
-#include "common.cuh"
+// llmm/softmax.mojo:172-304.  B200 design: the whole row (Vp·2 B ≈ 100 KB for GPT-2) is staged once
+// in shared memory so HBM sees exactly one read and one write.  bf16 rows stream through a persistent
+// CTA per SM: the bulk-copy engine loads row r+1 into one buffer and stores row r-1 out of it while the
+// 1024 threads make their three passes (max, exponentials + sum, scale) over row r in the other.
+#include "tc05.cuh"
 using namespace llmb;
+using namespace tc05;
 
 namespace {
 template <typename T>
@@ -73,6 +76,103 @@ __global__ void __launch_bounds__(1024) classifier_kernel(T* __restrict__ logits
   }
 }
 
+// Persistent streaming variant for bf16 rows (two row buffers fit in shared memory).
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(ssrc)), "r"(bytes) : "memory");
+}
+
+__global__ void __launch_bounds__(1024, 1) classifier_stream_kernel(__nv_bfloat16* __restrict__ logits, float* __restrict__ losses,
+                                                                   const int* __restrict__ targets, float dloss, int rows, int V,
+                                                                   int Vp, int write_dlogits, int buf_bytes, int* status) {
+  using T = __nv_bfloat16;
+  constexpr int N = 8;
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ uint64_t full[2];
+  __shared__ float red[32];
+  __shared__ float bcast[2];
+  __shared__ int fail_s;
+  const int tid = threadIdx.x, lane = tid % 32, wid = tid / 32, nw = blockDim.x / 32;
+  const uint32_t row_bytes = (uint32_t)Vp * 2;
+  const int nvec = Vp / N;
+  if (tid == 0) { mbar_init(&full[0], 1); mbar_init(&full[1], 1); fail_s = 0; fence_barrier_init(); }
+  __syncthreads();
+  int r = blockIdx.x;
+  if (tid == 0 && r < rows) {
+    mbar_expect_tx(&full[0], row_bytes);
+    bulk_load_1d(smraw, logits + (size_t)r * Vp, row_bytes, &full[0]);
+  }
+  const float L2E = 1.4426950408889634f;
+  for (int it = 0; r < rows; r += gridDim.x, ++it) {
+    const int b = it & 1;
+    T* row_s = reinterpret_cast<T*>(smraw + (size_t)b * buf_bytes);
+    const int rn = r + gridDim.x;
+    if (tid == 0 && rn < rows) {
+      bulk_wait_read<0>();                  // the store of the previous row has finished reading the other buffer
+      mbar_expect_tx(&full[b ^ 1], row_bytes);
+      bulk_load_1d(smraw + (size_t)(b ^ 1) * buf_bytes, logits + (size_t)rn * Vp, row_bytes, &full[b ^ 1]);
+    }
+    if (!mbar_wait(&full[b], (it >> 1) & 1)) { atomicExch(status, LLMB_ERR_TIMEOUT); fail_s = 1; }
+    __syncthreads();
+    if (fail_s) break;
+    // pass 1: row maximum over the real vocabulary
+    float mx = -INFINITY;
+    for (int v = tid; v < nvec; v += blockDim.x) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) if (v * N + k < V) mx = fmaxf(mx, p.v[k]);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    if (wid == 0) { float m = lane < nw ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bcast[0] = m; }
+    __syncthreads();
+    mx = bcast[0];
+    const int tgt = targets[r];
+    const float x_tgt = __bfloat162float(row_s[tgt]);     // read before the buffer is overwritten
+    __syncthreads();
+    // pass 2: e = 2^((x - max) log2 e), once per element, written back over the row
+    float sum = 0.f;
+    const float mb = mx * L2E;
+    for (int v = tid; v < nvec; v += blockDim.x) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) {
+        const float e = (v * N + k < V) ? exp2f(fmaf(p.v[k], L2E, -mb)) : 0.f;
+        sum += e;
+        p.v[k] = e;
+      }
+      if (write_dlogits) p.store(row_s + v * N);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[wid] = sum;
+    __syncthreads();
+    if (wid == 0) { float s = lane < nw ? red[lane] : 0.f; s = warp_sum(s); if (lane == 0) bcast[1] = s; }
+    __syncthreads();
+    sum = bcast[1];
+    if (tid == 0 && losses) losses[r] = -(x_tgt - mx - logf(sum));
+    if (write_dlogits) {
+      // pass 3: dlogits = (e / sum - 1[target]) dloss in place, then one bulk store of the row
+      const float inv = dloss / sum;
+      for (int v = tid; v < nvec; v += blockDim.x) {
+        Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+          const int i = v * N + k;
+          p.v[k] = p.v[k] * inv - (i == tgt ? dloss : 0.f);      // padded columns hold e = 0
+        }
+        p.store(row_s + v * N);
+      }
+      fence_proxy_async();
+      __syncthreads();
+      if (tid == 0) { bulk_store_1d(logits + (size_t)r * Vp, row_s, row_bytes); bulk_commit(); }
+    } else {
+      __syncthreads();                      // everyone is done with the buffer before it is reloaded
+    }
+  }
+  if (tid == 0) bulk_wait<0>();             // shared memory must outlive the last store
+}
+
 template <typename T>
 __global__ void softmax_rows_kernel(float* __restrict__ out, const T* __restrict__ inp, int V, int ld, float inv_temp) {
   __shared__ float red[32];
@@ -94,9 +194,19 @@ __global__ void softmax_rows_kernel(float* __restrict__ out, const T* __restrict
 
 // logits [rows, Vp] are overwritten with dlogits when write_dlogits != 0.
 LLMB_API int llmb_fused_classifier(void* logits, float* losses, const int* targets, float dloss, int rows, int V,
-                                   int Vp, int write_dlogits, int dtype, cudaStream_t st) {
+                                   int Vp, int write_dlogits, int dtype, int* status, cudaStream_t st) {
   if (dtype == LLMB_BF16) {
     if (Vp % 8) return LLMB_ERR_BAD_ARG;
+    static int stream_on = -1;
+    if (stream_on < 0) { const char* e = getenv("LLMB_CLASSIFIER_STREAM"); stream_on = (e && e[0] == '0') ? 0 : 1; }
+    const int buf_bytes = (Vp * 2 + 127) & ~127;
+    if (stream_on && status && 2 * buf_bytes <= 224 * 1024 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+      cudaFuncSetAttribute(classifier_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * buf_bytes);
+      const int grid = rows < sm_count() ? rows : sm_count();
+      classifier_stream_kernel<<<grid, 1024, 2 * buf_bytes, st>>>((__nv_bfloat16*)logits, losses, targets, dloss, rows, V, Vp,
+                                                                 write_dlogits, buf_bytes, status);
+      return (int)cudaGetLastError();
+    }
     size_t smem = (size_t)Vp * 2;
     if (smem > 200 * 1024) return LLMB_ERR_BAD_ARG;
     cudaFuncSetAttribute(classifier_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

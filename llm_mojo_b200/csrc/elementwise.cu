@@ -244,6 +244,33 @@ __global__ void cast_f32_to_bf16_kernel(__nv_bfloat16* out, const float* in, lon
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = __float2bfloat16_rn(in[i]);
 }
+// ----------------------------------------------------------------------------- non-finite census
+// counts[0] += number of NaN, counts[1] += number of +-Inf in x[0..n) (debug scan of a named tensor;
+// reference: _debug_grad_nanscan, train_gpt2.mojo:5385-5577)
+template <typename T>
+__global__ void nan_census_kernel(const T* __restrict__ x, long long n, int* __restrict__ counts) {
+  int nan = 0, inf = 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float v = (float)x[i];
+    nan += isnan(v) ? 1 : 0;
+    inf += isinf(v) ? 1 : 0;
+  }
+  for (int o = 16; o > 0; o >>= 1) { nan += __shfl_xor_sync(0xffffffffu, nan, o); inf += __shfl_xor_sync(0xffffffffu, inf, o); }
+  if ((threadIdx.x & 31) == 0) {
+    if (nan) atomicAdd(&counts[0], nan);
+    if (inf) atomicAdd(&counts[1], inf);
+  }
+}
+LLMB_API int llmb_nan_census(int* counts, const void* x, long long n, int dtype, cudaStream_t st) {
+  if (n <= 0) return 0;
+  const int block = 256;
+  long long want = (n + block - 1) / block;
+  const int grid = (int)(want < 4LL * sm_count() ? want : 4LL * sm_count());
+  if (dtype == 1) nan_census_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, n, counts);
+  else nan_census_kernel<float><<<grid, block, 0, st>>>((const float*)x, n, counts);
+  return (int)cudaGetLastError();
+}
+
 LLMB_API int llmb_cast_f32_to_bf16(void* out, const float* in, long long n, cudaStream_t st) {
   cast_f32_to_bf16_kernel<<<sm_count() * 8, 256, 0, st>>>((__nv_bfloat16*)out, in, n);
   return (int)cudaGetLastError();

@@ -304,9 +304,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
 
 // ------------------------------------------------------------------------------------------------
-// Epilogue through TMA (bf16 outputs of the CTA-pair kernel).  Each epilogue warp owns a band of
-// 32 rows x 256 columns of the accumulator and moves it in slabs of 64 columns = one 128-byte-swizzled
-// box of 32 rows x 128 B (4 KB):
+// Epilogue through TMA (bf16 outputs of the CTA-pair kernel).  Each of the eight epilogue warps owns
+// 32 rows x 128 columns of the accumulator and moves them as two slabs of 64 columns = one
+// 128-byte-swizzled box of 32 rows x 128 B (4 KB) each:
 //   * tcgen05.ld gives each lane one row of the slab; bias, GELU, dGELU and the residual add happen in
 //     registers in that layout;
 //   * the auxiliary INPUT (residual stream, pre-GELU activations) arrives by TMA loads that are issued a
@@ -316,13 +316,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 //     global access of the epilogue is a full 128-byte row segment; out-of-range rows and columns are
 //     clipped by the tensor maps.
 // Epilogues with an auxiliary input or a second output (BIAS_GELU stores the pre-activation too) get
-// four 4 KB buffers per warp and a 5-deep operand ring; the others two buffers and a 6-deep ring.
+// two 4 KB buffers per warp and a 5-deep operand ring; the others one buffer and a 6-deep ring.
 template <int EPI> struct EpiCfg {
   static constexpr bool AUX_IN = EPI == EPI_DGELU || EPI == EPI_BIAS_RESID;
   static constexpr bool TWO_OUT = EPI == EPI_BIAS_GELU;
   static constexpr bool F32_OUT = EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32;
   static constexpr int STAGES = (!F32_OUT && (AUX_IN || TWO_OUT)) ? 5 : 6;
-  static constexpr int WARP_STAGE = STAGES == 5 ? 16384 : 8192;     // epilogue staging bytes per warp
+  static constexpr int WARP_STAGE = STAGES == 5 ? 16384 : 8192;     // staging bytes per warp of the 4-warp register epilogue (half that per warp of the 8-warp TMA epilogue)
 };
 constexpr int SLAB_BYTES = 32 * 128;
 
@@ -391,11 +391,12 @@ __device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_
 // the tiles it owns; the peer's TMA completions are reported to the leader's mbarrier.
 constexpr int B2_STAGE = 128 * ROW_BYTES;             // 16 KB: this CTA's half of the B tile
 constexpr int STAGE2_BYTES = A_STAGE + B2_STAGE;      // 32 KB
+constexpr int PAIR_THREADS = 320;                      // TMA producer, MMA issuer, 8 epilogue warps
 constexpr int SMEM2_TAIL = 512;                        // barriers, TMEM slot, abort flag
 template <int EPI> constexpr int smem2_bytes() { return EpiCfg<EPI>::STAGES * STAGE2_BYTES + 4 * EpiCfg<EPI>::WARP_STAGE + 1024 + SMEM2_TAIL; }
 
 template <int KIND, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using Cfg = EpiCfg<EPI>;
@@ -408,7 +409,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty_bar = full_bar + NST;
   uint64_t* tfull_bar = empty_bar + NST;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint64_t* aux_bar = tempty_bar + 2;                   // [4 warps][4 slabs] auxiliary-input tiles landed
+  uint64_t* aux_bar = tempty_bar + 2;                   // [8 warps][2 slabs] auxiliary-input tiles landed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -418,7 +419,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }   // 4 warps x 2 CTAs
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 16); }   // 8 warps x 2 CTAs
     for (int a = 0; a < 16; ++a) mbar_init(&aux_bar[a], 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -536,27 +537,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
-    const int q = warp & 3;
-    unsigned char* wstage = epi_stage + (warp - 2) * WSB;
-    uint64_t* abar = aux_bar + (warp - 2) * 4;
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    // Eight warps: warp % 4 selects the 32-row band (the TMEM lane quarter a warp may read), (warp - 2) / 4 the
+    // 128-column half of the tile, i.e. two 64-column slabs per warp and tile.  The register epilogue (fp32
+    // outputs, layouts without a tensor map) keeps four working warps with all four slabs of a band each.
+    const int q = warp & 3, e = warp - 2, hcol = e >> 2;
     const bool tma_epi = !Cfg::F32_OUT && p.tma_epi;      // warp-uniform
+    unsigned char* wstage = epi_stage + e * (tma_epi ? WSB / 2 : WSB);
+    uint64_t* abar = aux_bar + e * 2;
     const int band_off = (int)cta * BM + q * 32;
     uint32_t aux_phase = 0, aux_pending = 0;              // per-slab-buffer phase bits / loads in flight (warp-uniform)
-    uint32_t nslab = 0;                                   // slabs stored so far (buffer rotation without an aux input)
-    // auxiliary-input tiles of a work unit: one box per 64-column slab that lies inside the matrix
-    auto aux_valid = [&](int row0, int n0, int s) { return row0 < p.M && n0 + s * 64 < p.N; };
-    auto aux_issue = [&](int row0, int n0, int s) {       // all lanes keep the books, lane 0 issues
-      if (!aux_valid(row0, n0, s)) return;
-      aux_pending |= 1u << s;
+    // auxiliary-input tiles of a work unit: one box per 64-column slab that lies inside the matrix (ls = 0, 1)
+    auto slab_valid = [&](int row0, int n0, int ls) { return row0 < p.M && n0 + (hcol * 2 + ls) * 64 < p.N; };
+    auto aux_issue = [&](int row0, int n0, int ls) {      // all lanes keep the books, lane 0 issues
+      if (!slab_valid(row0, n0, ls)) return;
+      aux_pending |= 1u << ls;
       if (lane == 0) {
-        mbar_expect_tx(&abar[s], SLAB_BYTES);
-        tma_load_2d(wstage + s * SLAB_BYTES, &tmAux, &abar[s], n0 + s * 64, row0);
+        mbar_expect_tx(&abar[ls], SLAB_BYTES);
+        tma_load_2d(wstage + ls * SLAB_BYTES, &tmAux, &abar[ls], n0 + (hcol * 2 + ls) * 64, row0);
       }
     };
     if (Cfg::AUX_IN && tma_epi && cluster_id < total_units) {
       int m_blk, n_blk, kb0, kb1; unit_coords(cluster_id, m_blk, n_blk, kb0, kb1);
-      for (int s = 0; s < 4; ++s) aux_issue(m_blk * 2 * BM + band_off, n_blk * BN, s);
+      for (int ls = 0; ls < 2; ++ls) aux_issue(m_blk * 2 * BM + band_off, n_blk * BN, ls);
     }
     int it = 0;
     for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters, ++it) {
@@ -570,55 +573,52 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const float alpha = p.alpha ? *p.alpha : 1.0f;
       const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       if (!tma_epi) {
-        epilogue_warp<EPI>(p, tacc, wstage, row0, n0, alpha, lane);
+        if (e < 4) epilogue_warp<EPI>(p, tacc, wstage, row0, n0, alpha, lane);
       } else {
         const int nunit = unit + num_clusters;
         const bool has_next = Cfg::AUX_IN && nunit < total_units;
         int nrow0 = 0, nn0 = 0;
         if (has_next) { int mb, nb, k0, k1; unit_coords(nunit, mb, nb, k0, k1); nrow0 = mb * 2 * BM + band_off; nn0 = nb * BN; }
-        int issued = 0;                                   // slab buffers already refilled for the next unit
         bool ok = true;
 #pragma unroll 1
-        for (int s = 0; s < BN / 64; ++s) {
-          if (!aux_valid(row0, n0, s)) break;              // warp-uniform
+        for (int ls = 0; ls < 2; ++ls) {
+          if (!slab_valid(row0, n0, ls)) break;            // warp-uniform
+          const int col0 = n0 + (hcol * 2 + ls) * 64;
           uint32_t r0[32], r1[32];
-          tmem_ld32(tacc + s * 64, r0);
-          tmem_ld32(tacc + s * 64 + 32, r1);
+          tmem_ld32(tacc + (hcol * 2 + ls) * 64, r0);
+          tmem_ld32(tacc + (hcol * 2 + ls) * 64 + 32, r1);
           tmem_wait_ld();
           unsigned char* buf;
           if (Cfg::AUX_IN) {
-            buf = wstage + s * SLAB_BYTES;
-            if (!mbar_wait(&abar[s], (aux_phase >> s) & 1)) { ok = false; break; }
-            aux_phase ^= 1u << s; aux_pending &= ~(1u << s);
+            buf = wstage + ls * SLAB_BYTES;
+            if (!mbar_wait(&abar[ls], (aux_phase >> ls) & 1)) { ok = false; break; }
+            aux_phase ^= 1u << ls; aux_pending &= ~(1u << ls);
           } else {
-            buf = wstage + (nslab & 1) * (Cfg::TWO_OUT ? 2 * SLAB_BYTES : SLAB_BYTES);
-            if (lane == 0) bulk_wait_read<1>();           // the store that used this buffer two slabs ago has read it
+            buf = wstage;
+            if (lane == 0) bulk_wait_read<0>();           // the previous slab's stores have read the buffer
             __syncwarp();
           }
-          epi_slab_bf16<EPI>(p, r0, r1, buf, n0 + s * 64, alpha, lane);
+          epi_slab_bf16<EPI>(p, r0, r1, buf, col0, alpha, lane);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
             if (Cfg::TWO_OUT) {
-              tma_store_2d(&tmAux, buf, n0 + s * 64, row0);
-              tma_store_2d(&tmD, buf + SLAB_BYTES, n0 + s * 64, row0);
+              tma_store_2d(&tmAux, buf, col0, row0);
+              tma_store_2d(&tmD, buf + SLAB_BYTES, col0, row0);
             } else {
-              tma_store_2d(&tmD, buf, n0 + s * 64, row0);
+              tma_store_2d(&tmD, buf, col0, row0);
             }
             bulk_commit();
           }
-          ++nslab;
-          if (Cfg::AUX_IN && has_next) {                  // refill the buffers whose stores have been read
-            if (lane == 0) bulk_wait_read<1>();
-            __syncwarp();
-            for (; issued < s; ++issued) aux_issue(nrow0, nn0, issued);
-          }
         }
         if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
-        if (Cfg::AUX_IN && has_next) {
+        if (Cfg::AUX_IN && has_next) {                    // refill each buffer once its store has been read
+          if (lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+          aux_issue(nrow0, nn0, 0);
           if (lane == 0) bulk_wait_read<0>();
           __syncwarp();
-          for (; issued < 4; ++issued) aux_issue(nrow0, nn0, issued);
+          aux_issue(nrow0, nn0, 1);
         }
       }
       fence_before_sync();
@@ -627,8 +627,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (tma_epi) {
       // nothing of this CTA's shared memory may still be a source or a destination of a copy at exit
-      for (int s = 0; s < 4; ++s)
-        if (aux_pending & (1u << s)) (void)mbar_wait(&abar[s], (aux_phase >> s) & 1);
+      for (int ls = 0; ls < 2; ++ls)
+        if (aux_pending & (1u << ls)) (void)mbar_wait(&abar[ls], (aux_phase >> ls) & 1);
       if (lane == 0) bulk_wait<0>();
       __syncwarp();
     }
@@ -663,7 +663,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  gemm_pair_kernel<KIND, EPI><<<grid, NUM_THREADS, SMEM, st>>>(ta, tb, td, taux, p);
+  gemm_pair_kernel<KIND, EPI><<<grid, PAIR_THREADS, SMEM, st>>>(ta, tb, td, taux, p);
   return (int)cudaGetLastError();
 }
 

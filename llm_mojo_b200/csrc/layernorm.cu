@@ -95,14 +95,23 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float
   }
   for (int row = blockIdx.x * nwarps + wid; row < rows; row += gridDim.x * nwarps) {
     float mean = mean_i[row], rstd = rstd_i[row];
-    uint4 xr[PER_LANE], dr[PER_LANE];   // raw 16-byte vectors: the row stays in registers
+    uint4 xr[PER_LANE], dr[PER_LANE], ar[PER_LANE];   // raw 16-byte vectors: the row stays in registers
     float s1 = 0.f, s2 = 0.f;
+    // all global loads of the row (input, upstream gradient and the gradient accumulated so far) are issued
+    // before the first use, so the row costs one memory round trip instead of two
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
       int vc = i * 32 + lane;
       if (vc < nvec) {
         xr[i] = *reinterpret_cast<const uint4*>(inp + (size_t)row * C + vc * N);
         dr[i] = *reinterpret_cast<const uint4*>(dout + (size_t)row * C + vc * N);
+        if (ACCUM) ar[i] = *reinterpret_cast<const uint4*>(dres + (size_t)row * C + vc * N);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      int vc = i * 32 + lane;
+      if (vc < nvec) {
         Pack<T> x, d, ww; x.load(reinterpret_cast<const T*>(&xr[i])); d.load(reinterpret_cast<const T*>(&dr[i]));
         ww.load(w + vc * N);
 #pragma unroll
@@ -121,7 +130,7 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float
       if (vc < nvec) {
         Pack<T> x, d, ww, o; x.load(reinterpret_cast<const T*>(&xr[i])); d.load(reinterpret_cast<const T*>(&dr[i]));
         ww.load(w + vc * N);
-        if (ACCUM) o.load(dres + (size_t)row * C + vc * N);
+        if (ACCUM) o.load(reinterpret_cast<const T*>(&ar[i]));
 #pragma unroll
         for (int k = 0; k < N; ++k) {
           float n_ = (x.v[k] - mean) * rstd;

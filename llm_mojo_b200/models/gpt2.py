@@ -483,6 +483,19 @@ class GPT2:
         self.v.copy_(v.to(self.device))
         return state
 
+    def debug_nan_scan(self, which: str = "grads") -> dict:
+        """Per-tensor census of non-finite values over the named parameter, gradient or activation views
+        (``_debug_grad_nanscan``, ``train_gpt2.mojo:5385-5577``).  Returns {name: (nan, inf)} for tensors that have any."""
+        views = {"grads": self.g, "params": self.p, "acts": self.acts}[which]
+        bad = {}
+        for name, t in views.items():
+            if t is None or not torch.is_floating_point(t):
+                continue
+            nan, inf = ops.nan_census(t)
+            if nan or inf:
+                bad[name] = (nan, inf)
+        return bad
+
     # ------------------------------------------------------------------ accounting
     def memory_report(self) -> dict:
         """Exact per-buffer accounting (``train_gpt2.mojo:5807-5999``; schema 3)."""

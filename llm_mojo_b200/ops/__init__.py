@@ -366,7 +366,8 @@ def fused_classifier(logits, losses, targets, dloss: float, vocab_size: int, wri
     rows = logits.numel() // Vp
     if logits.is_cuda:
         check(lib().llmb_fused_classifier(ptr(logits), ptr(losses), ptr(targets), float(dloss), rows, vocab_size, Vp,
-                                          int(write_dlogits), dtype_code(logits), stream()), "fused_classifier")
+                                          int(write_dlogits), dtype_code(logits), ptr(status_word(logits.device)), stream()),
+              "fused_classifier")
         _count()
     else:
         lg = logits.view(rows, Vp)
@@ -472,6 +473,19 @@ def adamw_update(params, master, grads, m, v, *, lr, beta1, beta2, eps, weight_d
         if master is not None:
             master.copy_(p)
         params.copy_(p)
+
+
+def nan_census(x: torch.Tensor) -> tuple:
+    """(number of NaN, number of ±Inf) in ``x`` — the per-tensor debug scan of ``train_gpt2.mojo:5385-5577``."""
+    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16):
+        counts = torch.zeros(2, dtype=torch.int32, device=x.device)
+        flat = x.reshape(-1)
+        check(lib().llmb_nan_census(ptr(counts), ptr(flat), flat.numel(), dtype_code(flat), stream()), "nan_census")
+        _count()
+        c = counts.tolist()
+        return int(c[0]), int(c[1])
+    xf = x.float()
+    return int(torch.isnan(xf).sum().item()), int(torch.isinf(xf).sum().item())
 
 
 def global_norm_squared(out, x, accumulate: bool = False) -> None:

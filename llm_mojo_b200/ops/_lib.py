@@ -26,10 +26,11 @@ _SIGS = {
     "llmb_dbias_scratch_bytes": [c_int, c_int],
     "llmb_dbias": [c_p, c_p, c_p, c_ll, c_int, c_int, c_int, c_p],
     "llmb_cast_f32_to_bf16": [c_p, c_p, c_ll, c_p],
+    "llmb_nan_census": [c_p, c_p, c_ll, c_int, c_p],
     "llmb_layernorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p],
     "llmb_layernorm_bwd_scratch_bytes": [c_int, c_int],
     "llmb_layernorm_bwd": [c_p, c_p, c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
-    "llmb_fused_classifier": [c_p, c_p, c_p, c_f, c_int, c_int, c_int, c_int, c_int, c_p],
+    "llmb_fused_classifier": [c_p, c_p, c_p, c_f, c_int, c_int, c_int, c_int, c_int, c_p, c_p],
     "llmb_ce_pass1": [c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_p],
     "llmb_ce_loss": [c_p, c_p, c_int, c_p],
     "llmb_ce_pass2": [c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_f, c_int, c_p],

@@ -152,6 +152,7 @@ class Trainer:
         self.tracer = TraceProfiler(pid=rank)
         self.step = 0
         self.last_norm = 0.0
+        self._nanscan = os.environ.get("LLMM_DEBUG_TENSOR_NANSCAN", "") not in ("", "0")
         self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) \
             if self.device.type == "cuda" else None
         if args.resume and args.output_log_dir:
@@ -179,6 +180,10 @@ class Trainer:
                 m.forward(x, y, self.grad_accum, B=a.batch_size, T=a.seq_len)
             with self.tracer.cuda_span("backward"):
                 m.backward(self.grad_accum, micro)
+        if self._nanscan:                               # LLMM_DEBUG_TENSOR_NANSCAN=1: census of the accumulated gradients
+            bad = m.debug_nan_scan("grads")
+            if bad:
+                print(f"step {self.step}: non-finite gradients (nan, inf): {bad}", flush=True)
         lr = self.scheduler.get_learning_rate(self.step)
         with self.tracer.cuda_span("grad_norm"):
             norm = m.calculate_grad_norm()

@@ -289,3 +289,12 @@ def test_attention_fwd_bwd(B, T, NH):
     status_ok()
     for i, nm in enumerate(("dq", "dk", "dv")):
         close(dqkv[..., i * C:(i + 1) * C], r_dqkv[..., i * C:(i + 1) * C], 2e-2, 3e-2, nm)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_nan_census(dtype):
+    x = torch.randn(1_000_003, device="cuda").to(dtype)
+    assert ops.nan_census(x) == (0, 0)
+    x[5] = float("nan"); x[77777] = float("nan"); x[999_999] = float("inf"); x[123] = float("-inf"); x[124] = float("inf")
+    assert ops.nan_census(x) == (2, 3)

@@ -106,3 +106,18 @@ def test_chunked_ce_and_lm_head_tiling_match_untiled(tiny_config):
     assert "logits" not in b.acts and b.acts["logits_tile"].shape[1] == 128
     assert abs(a.read_loss() - b.read_loss()) < 1e-6
     assert torch.allclose(a.grads, b.grads, atol=1e-6, rtol=1e-4)
+
+
+def test_debug_nan_scan_cpu():
+    """The per-tensor census reports exactly the tensors that hold non-finite values."""
+    from llm_mojo_b200 import ops
+    from llm_mojo_b200.config import GPT2Config
+    from llm_mojo_b200.models import GPT2
+    cfg = GPT2Config(max_seq_len=16, vocab_size=64, padded_vocab_size=128, num_layer=1, num_heads=2, channels=16)
+    m = GPT2(cfg, "fp32", "cpu")
+    assert m.debug_nan_scan("params") == {}
+    m.g["wpe"].view(-1)[3] = float("nan")
+    m.g["lnfw"].view(-1)[0] = float("inf")
+    m.g["lnfw"].view(-1)[1] = float("-inf")
+    assert m.debug_nan_scan("grads") == {"wpe": (1, 0), "lnfw": (0, 2)}
+    assert ops.nan_census(torch.tensor([1.0, float("nan"), float("inf")])) == (1, 1)
