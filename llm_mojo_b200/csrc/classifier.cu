@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(1024) classifier_kernel(T* __restrict__ logits
 }
 
 // Persistent streaming variant for bf16 rows (two row buffers fit in shared memory).
+__device__ __forceinline__ float ex2_fast(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ void bulk_store_1d(void* gdst, const void* ssrc, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
                ::"l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(ssrc)), "r"(bytes) : "memory");
@@ -115,9 +116,17 @@ __global__ void __launch_bounds__(1024, 1) classifier_stream_kernel(__nv_bfloat1
     if (!mbar_wait(&full[b], (it >> 1) & 1)) { atomicExch(status, LLMB_ERR_TIMEOUT); fail_s = 1; }
     __syncthreads();
     if (fail_s) break;
+    // Vectors that lie wholly inside the real vocabulary [0, V) need no per-element bound checks; the one
+    // vector that straddles V and the padded ones after it are handled by a second, checked loop.
+    const int nfull = V / N;                 // vectors entirely below V
     // pass 1: row maximum over the real vocabulary
     float mx = -INFINITY;
-    for (int v = tid; v < nvec; v += blockDim.x) {
+    for (int v = tid; v < nfull; v += blockDim.x) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) mx = fmaxf(mx, p.v[k]);
+    }
+    for (int v = nfull + tid; v < nvec; v += blockDim.x) {
       Pack<T> p; p.load(row_s + v * N);
 #pragma unroll
       for (int k = 0; k < N; ++k) if (v * N + k < V) mx = fmaxf(mx, p.v[k]);
@@ -134,14 +143,16 @@ __global__ void __launch_bounds__(1024, 1) classifier_stream_kernel(__nv_bfloat1
     // pass 2: e = 2^((x - max) log2 e), once per element, written back over the row
     float sum = 0.f;
     const float mb = mx * L2E;
-    for (int v = tid; v < nvec; v += blockDim.x) {
+    for (int v = tid; v < nfull; v += blockDim.x) {
       Pack<T> p; p.load(row_s + v * N);
 #pragma unroll
-      for (int k = 0; k < N; ++k) {
-        const float e = (v * N + k < V) ? exp2f(fmaf(p.v[k], L2E, -mb)) : 0.f;
-        sum += e;
-        p.v[k] = e;
-      }
+      for (int k = 0; k < N; ++k) { p.v[k] = ex2_fast(fmaf(p.v[k], L2E, -mb)); sum += p.v[k]; }
+      if (write_dlogits) p.store(row_s + v * N);
+    }
+    for (int v = nfull + tid; v < nvec; v += blockDim.x) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) { p.v[k] = (v * N + k < V) ? ex2_fast(fmaf(p.v[k], L2E, -mb)) : 0.f; sum += p.v[k]; }
       if (write_dlogits) p.store(row_s + v * N);
     }
     sum = warp_sum(sum);
@@ -152,16 +163,19 @@ __global__ void __launch_bounds__(1024, 1) classifier_stream_kernel(__nv_bfloat1
     sum = bcast[1];
     if (tid == 0 && losses) losses[r] = -(x_tgt - mx - logf(sum));
     if (write_dlogits) {
-      // pass 3: dlogits = (e / sum - 1[target]) dloss in place, then one bulk store of the row
+      // pass 3: dlogits = (e / sum - 1[target]) dloss in place (padded columns hold e = 0); the target column is
+      // corrected afterwards by the one thread that owns it; then one bulk store of the row
       const float inv = dloss / sum;
       for (int v = tid; v < nvec; v += blockDim.x) {
         Pack<T> p; p.load(row_s + v * N);
 #pragma unroll
-        for (int k = 0; k < N; ++k) {
-          const int i = v * N + k;
-          p.v[k] = p.v[k] * inv - (i == tgt ? dloss : 0.f);      // padded columns hold e = 0
-        }
+        for (int k = 0; k < N; ++k) p.v[k] *= inv;
         p.store(row_s + v * N);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        const float e_t = ex2_fast(fmaf(x_tgt, L2E, -mb));
+        row_s[tgt] = __float2bfloat16(__bfloat162float(__float2bfloat16(e_t)) * inv - dloss);
       }
       fence_proxy_async();
       __syncthreads();
