@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(512) pack_kernel(__nv_bfloat16* __restrict__ s
 // ------------------------------------------------------------------ reduce
 // mode 0 (reduce-scatter): dst_f32[dst_off + e] (+)= sum_p send_p[src_off + e]; norm partials.
 // mode 1 (all-reduce, two-shot): recv_p[src_off + e] = bf16(sum) for every rank p.
+template <int WT>   // WT > 0: world size known at compile time (peer loads unrolled and all in flight together); 0: runtime W
 __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList owned, int mode, float* __restrict__ dst_f32,
                                                     int accumulate, PeerPtrs recvs, float* __restrict__ norm_partials,
                                                     void* my_flags, PeerPtrs flags, int me, int W, unsigned seq,
@@ -139,11 +140,23 @@ __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList own
     const long long e = (v - owned.vec_prefix[s]) * 8;
     const long long so = owned.src_off[s] + e;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < W; ++r) {          // fixed rank order: identical bits on every rank
-      float x[8];
-      load_bf16x8(reinterpret_cast<const __nv_bfloat16*>(sends.p[r]) + so, x);
+    if (WT > 0) {
+      uint4 raw[WT > 0 ? WT : 1];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += x[k];
+      for (int r = 0; r < WT; ++r) raw[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(sends.p[r]) + so);
+#pragma unroll
+      for (int r = 0; r < WT; ++r) {       // fixed rank order: identical bits on every rank
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); acc[2 * i] += f.x; acc[2 * i + 1] += f.y; }
+      }
+    } else {
+      for (int r = 0; r < W; ++r) {
+        float x[8];
+        load_bf16x8(reinterpret_cast<const __nv_bfloat16*>(sends.p[r]) + so, x);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += x[k];
+      }
     }
     if (mode == 0) {
       float* d = dst_f32 + owned.dst_off[s] + e;
@@ -156,7 +169,12 @@ __global__ void __launch_bounds__(512) reduce_kernel(PeerPtrs sends, SegList own
       nsq += o0.x * o0.x + o0.y * o0.y + o0.z * o0.z + o0.w * o0.w + o1.x * o1.x + o1.y * o1.y + o1.z * o1.z + o1.w * o1.w;
     } else {
       const uint4 packed = pack_bf16x8(acc);
-      for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recvs.p[r]) + so) = packed;
+      if (WT > 0) {
+#pragma unroll
+        for (int r = 0; r < WT; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recvs.p[r]) + so) = packed;
+      } else {
+        for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recvs.p[r]) + so) = packed;
+      }
     }
   }
   if (mode == 0 && norm_partials) {        // sum of squares of the reduced gradients this rank owns
@@ -324,9 +342,17 @@ LLMB_API int llmb_comm_reduce(void* const* send_ptrs, int nseg, const long long*
                               float* norm_acc, void* my_flags, void* const* flag_ptrs, int me, int W, unsigned seq, unsigned wait_done2_seq,
                               unsigned* counter, unsigned* counter2, int* status, int blocks, cudaStream_t st) {
   SegList s; if (!fill(s, nseg, nullptr, src_off, dst_off, len)) return LLMB_ERR_BAD_ARG;
-  reduce_kernel<<<comm_grid(s.vec_prefix[s.n], blocks), 512, 0, st>>>(to_peers(send_ptrs, W), s, mode, dst_f32, accumulate,
-                                                                     recv_ptrs ? to_peers(recv_ptrs, W) : PeerPtrs{}, norm_acc, my_flags,
-                                                                     to_peers(flag_ptrs, W), me, W, seq, wait_done2_seq, counter, counter2, status);
+  const int grid = comm_grid(s.vec_prefix[s.n], blocks);
+#define LLMB_REDUCE(WT) reduce_kernel<WT><<<grid, 512, 0, st>>>(to_peers(send_ptrs, W), s, mode, dst_f32, accumulate, \
+                          recv_ptrs ? to_peers(recv_ptrs, W) : PeerPtrs{}, norm_acc, my_flags, to_peers(flag_ptrs, W), me, W, seq, \
+                          wait_done2_seq, counter, counter2, status)
+  switch (W) {
+    case 2: LLMB_REDUCE(2); break;
+    case 4: LLMB_REDUCE(4); break;
+    case 8: LLMB_REDUCE(8); break;
+    default: LLMB_REDUCE(0); break;
+  }
+#undef LLMB_REDUCE
   return (int)cudaGetLastError();
 }
 LLMB_API int llmb_comm_unpack(float* dst, const void* recv, int nseg, const long long* src_off, const long long* dst_off,

@@ -43,7 +43,6 @@ struct GemmParams {
   uint32_t a_layout, b_layout; // UMMA layout type: 2 = SWIZZLE_128B, 1 = SWIZZLE_128B with 32-byte base (fp32 MN-major)
   uint32_t idesc;
   int bke;                     // K elements per stage
-  int mma_per_stage;
   int m_tiles, n_tiles, splits, kb_per_split, kb_total;
   int io_f32;                  // 1: D, bias and aux are fp32 (tf32 kind); 0: bf16
   int tma_epi;                 // 1: bf16 outputs leave (and auxiliary inputs arrive) by TMA; 0: register/shared-memory epilogue
@@ -248,34 +247,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane issues; descriptors of stage 0 and the per-MMA increments are hoisted
+    {
       int stage = 0; uint32_t phase = 0;
       int it = 0;
+      const uint64_t adesc0 = make_smem_desc(smem_u32(smem), p.a_lbo, p.a_sbo, p.a_layout);
+      const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + A_STAGE, p.b_lbo, p.b_sbo, p.b_layout);
+      const uint64_t a_inc = (uint64_t)(p.a_kstep >> 4), b_inc = (uint64_t)(p.b_kstep >> 4);
+      const uint32_t idesc = p.idesc;
+      bool ok = true;
       for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { ok = false; break; }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        bool ok = true;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
           fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_STAGE;
-          const uint64_t adesc = make_smem_desc(sa, p.a_lbo, p.a_sbo, p.a_layout);
-          const uint64_t bdesc = make_smem_desc(sb, p.b_lbo, p.b_sbo, p.b_layout);
-          for (int k = 0; k < p.mma_per_stage; ++k) {
-            umma_ss<KIND>(d_tmem, adesc + (uint64_t)((k * p.a_kstep) >> 4), bdesc + (uint64_t)((k * p.b_kstep) >> 4),
-                          p.idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          const uint64_t adesc = adesc0 + (uint64_t)(stage * (STAGE_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + (uint64_t)(stage * (STAGE_BYTES >> 4));
+          if (elect_one()) {
+            umma_ss<KIND>(d_tmem, adesc, bdesc, idesc, kb > kb0 ? 1u : 0u);
+#pragma unroll
+            for (int k = 1; k < 4; ++k) umma_ss<KIND>(d_tmem, adesc + k * a_inc, bdesc + k * b_inc, idesc, 1u);
+            umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
           }
-          umma_commit(&empty_bar[stage]);   // stage reusable once these MMAs have read it
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
-        umma_commit(&tfull_bar[acc]);
+        if (!ok) break;
+        if (elect_one()) umma_commit(&tfull_bar[acc]);
+        __syncwarp();
       }
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -731,7 +737,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   p.a_lbo = a_mn ? mn_lbo : 16; p.a_sbo = a_mn ? mn_sbo : 1024; p.a_kstep = a_mn ? MMA_K * ROW_BYTES : 32;
   p.b_lbo = b_mn ? mn_lbo : 16; p.b_sbo = b_mn ? mn_sbo : 1024; p.b_kstep = b_mn ? MMA_K * ROW_BYTES : 32;
   p.idesc = make_idesc((uint32_t)a_fmt, (uint32_t)b_fmt, (uint32_t)a_mn, (uint32_t)b_mn, pair ? 2 * BM : BM, BN);
-  p.bke = BKE; p.mma_per_stage = BKE / MMA_K;
+  p.bke = BKE;                                          // a 128-byte stage row holds BKE / MMA_K = 4 MMA k-steps for every kind
   p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, BN);
   p.kb_total = ceil_div(K, BKE);
   if (splits < 1) splits = 1;

@@ -162,13 +162,25 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float
   }
 }
 
-__global__ void ln_bwd_final_kernel(float* __restrict__ dw, float* __restrict__ db, const float* __restrict__ partial,
-                                    int C, int nblocks) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * C) return;
+// dw[c] += sum_i partial[i][c], db[c] += sum_i partial[i][C + c] over the per-block partial rows.  A block of
+// 32 x 8 threads owns 32 adjacent columns of the 2C-wide partial matrix: 8 row groups walk the rows in parallel
+// (coalesced 128-byte reads) and are combined in fixed order through shared memory.
+__global__ void __launch_bounds__(256) ln_bwd_final_kernel(float* __restrict__ dw, float* __restrict__ db,
+                                                          const float* __restrict__ partial, int C, int nblocks) {
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int i = 0; i < nblocks; ++i) s += partial[(size_t)i * 2 * C + c];
-  if (c < C) dw[c] += s; else db[c - C] += s;
+  if (c < 2 * C)
+    for (int i = ty; i < nblocks; i += 8) s += partial[(size_t)i * 2 * C + c];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < 2 * C) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][tx];
+    if (c < C) dw[c] += t; else db[c - C] += t;
+  }
 }
 
 template <typename T, int PER_LANE>
@@ -248,6 +260,6 @@ LLMB_API int llmb_layernorm_bwd(void* dres, float* dw, float* db, float* scratch
 #undef LN_CASE
   }
   if (rc) return rc;
-  ln_bwd_final_kernel<<<ceil_div(2 * C, 256), 256, 0, st>>>(dw, db, scratch, C, grid);
+  ln_bwd_final_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(dw, db, scratch, C, grid);
   return (int)cudaGetLastError();
 }

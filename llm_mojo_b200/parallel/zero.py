@@ -130,7 +130,7 @@ class P2PBackend:
     wire_dtype = torch.bfloat16
 
     def __init__(self, rank: int, world: int, device: torch.device, send_cap: int, param_elems: int,
-                 blocks: int = 32):
+                 blocks: int = 296):
         from .symm import SymmetricArena
         self.rank, self.world, self.device = rank, world, device
         self.send_cap = (send_cap + 1023) // 1024 * 1024
