@@ -35,7 +35,8 @@ def run_infer(model: GPT2, tokenizer: Tokenizer, prompt, gen_tokens: int, seed: 
     cfg = model.config
     T = min(cfg.max_seq_len, max(64, len(prompt) + gen_tokens))
     T = (T + 7) // 8 * 8
-    toks = torch.full((1, T), tokenizer.eot_token if tokenizer.has_initialized else 50256, dtype=torch.int32)
+    pad = tokenizer.eot_token if tokenizer.has_initialized else 50256
+    toks = torch.full((1, T), min(pad, cfg.vocab_size - 1), dtype=torch.int32)      # filler beyond the prompt (never attended to)
     toks[0, :len(prompt)] = torch.tensor(prompt, dtype=torch.int32)
     rng = SamplerRNG(seed)
     model.forward(toks, None, B=1, T=T)                    # warm-up: allocates activations for this shape

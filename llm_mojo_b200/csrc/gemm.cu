@@ -47,7 +47,7 @@ struct GemmParams {
   int io_f32;                  // 1: D, bias and aux are fp32 (tf32 kind); 0: bf16
   int tma_epi;                 // 1: bf16 outputs leave (and auxiliary inputs arrive) by TMA; 0: register/shared-memory epilogue
   int bias_vec;                // bias pointer is 16-byte aligned (vector loads)
-  int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0)
+  int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0), 8 = skip the GELU math
   int* status;
 };
 
@@ -376,7 +376,7 @@ __device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_
       *reinterpret_cast<uint4*>(slot) = pre;
       float x[8]; unpack8(pre, x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = gelu_fast_f(x[j]);
+      for (int j = 0; j < 8; ++j) v[j] = (p.dbg & 8) ? x[j] : gelu_fast_f(x[j]);
       *reinterpret_cast<uint4*>(slot + SLAB_BYTES) = pack8(v);
     } else {
       if (EPI == EPI_DGELU || EPI == EPI_BIAS_RESID) {
@@ -607,7 +607,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           epi_slab_bf16<EPI>(p, r0, r1, buf, col0, alpha, lane);
           fence_proxy_async();
           __syncwarp();
-          if (lane == 0) {
+          if (lane == 0 && !(p.dbg & 1)) {
             if (Cfg::TWO_OUT) {
               tma_store_2d(&tmAux, buf, col0, row0);
               tma_store_2d(&tmD, buf + SLAB_BYTES, col0, row0);

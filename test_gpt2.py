@@ -46,7 +46,7 @@ def write_debug_state(path, config, flat, x, y, steps=NUM_STEPS):
         _, l = ref.forward(config, ref.unflatten(config, leaf), x, y)
         l.backward()
         opt.step()
-        losses.append(float(l))
+        losses.append(float(l.detach()))
     header[8] = steps
     with open(path, "wb") as f:
         f.write(header.tobytes())

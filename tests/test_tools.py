@@ -1,0 +1,90 @@
+"""Smoke tests of the command-line tools on CPU with tiny models (after the reference's generation smoke test,
+`make verify-cpu` debug-state gate, `make verify-fp8-grads` gradient gate and per-precision `make smoke` runs)."""
+import io
+import json
+import os
+import sys
+from contextlib import redirect_stdout
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def _run(mod_name, argv):
+    import importlib
+    mod = importlib.import_module(mod_name)
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        rc = mod.main(argv)
+    return rc, buf.getvalue()
+
+
+def test_infer_generation_smoke(tmp_path):
+    """infer_gpt2 samples the requested number of tokens from a checkpoint and is reproducible for a fixed seed."""
+    from llm_mojo_b200.config import GPT2Config
+    from llm_mojo_b200.models import GPT2
+    m = GPT2(GPT2Config(max_seq_len=32, vocab_size=300, num_layer=2, num_heads=2, channels=32, padded_vocab_size=384), "fp32", "cpu")
+    from llm_mojo_b200.utils import checkpointing as ckpt
+    ck = str(tmp_path / "tiny.bin")
+    ckpt.write_model_checkpoint(ck, m.config, m.full_params(), m.precision.checkpoint_version)
+    import subprocess
+    cmd = [sys.executable, os.path.join(ROOT, "infer_gpt2.py"), ck, "--tokens", "8", "--device", "cpu", "--seed", "7", "-t", "32",
+           "--prompt-tokens", "5,6,7"]
+    outs = [subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(tmp_path)) for _ in range(2)]
+    assert all(o.returncode == 0 for o in outs), outs[0].stderr
+    gen1, gen2 = (o.stdout.split("---")[-2] for o in outs)      # the text between the tokenizer notice and the timing line
+    assert gen1 == gen2 and len(gen1.split()) == 8 and all(0 <= int(t) < 300 for t in gen1.split())
+
+
+def test_debug_state_gate_roundtrip(tmp_path):
+    """test_gpt2 --write produces model + debug state from the autograd oracle; the checker passes on our model."""
+    mf, sf = str(tmp_path / "m.bin"), str(tmp_path / "s.bin")
+    rc, _ = _run("test_gpt2", ["--write", "--model", "d6", "--model-file", mf, "--state", sf, "-b", "2", "-t", "16", "--device", "cpu"])
+    assert rc == 0 and os.path.getsize(mf) > 0 and os.path.getsize(sf) > 0
+    rc, out = _run("test_gpt2", ["--model-file", mf, "--state", sf, "--device", "cpu", "--precision", "fp32"])
+    assert rc == 0, out
+    assert "overall okay: 1" in out or "OK" in out.upper()
+
+
+def test_gradient_dump_gate_fp32_vs_itself(tmp_path):
+    """dump_grads_gpt2 writes one file per gradient tensor; compare_grad_dumps accepts identical dumps and rejects noise."""
+    import compare_grad_dumps
+    a, b = str(tmp_path / "a"), str(tmp_path / "b")
+    for d in (a, b):
+        rc, _ = _run("dump_grads_gpt2", ["--model", "d6", "--precision", "fp32", "--out", d, "-b", "2", "-t", "16", "--device", "cpu"])
+        assert rc == 0
+    assert len(os.listdir(a)) >= 16
+    assert compare_grad_dumps.compare(a, b, verbose=False)
+    victim = sorted(f for f in os.listdir(b) if os.path.isfile(os.path.join(b, f)) and not f.endswith(".json"))[0]
+    path = os.path.join(b, victim)
+    raw = bytearray(open(path, "rb").read())
+    t = torch.frombuffer(raw, dtype=torch.float32, offset=len(raw) % 4)
+    t.copy_(torch.randn(t.numel()))
+    open(path, "wb").write(bytes(raw))
+    assert not compare_grad_dumps.compare(a, b, verbose=False)
+
+
+def test_bench_reference_arm_reports_unavailable():
+    """--impl reference never runs our code: it prints the `unavailable` JSON line and exits 0."""
+    import subprocess
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
+
+
+@pytest.mark.parametrize("precision", ["fp32", "fp8", "fp4"])
+def test_short_training_run_per_precision(precision, tmp_path):
+    """Five optimizer steps of a tiny model on CPU for every precision the trainer accepts there (fp8 / fp4 run their
+    quantise-dequantise emulation on fp32 storage); the loss must fall and stay finite."""
+    from llm_mojo_b200.trainer import TrainArgs, Trainer
+    args = TrainArgs(load_filename="d6", batch_size=2, seq_len=32, total_batch_size=64, max_steps=5, learning_rate=1e-3,
+                     synthetic=True, device="cpu", precision=precision, val_loss_every=0, sample_every=0, overfit_single_batch=1,
+                     output_log_dir=str(tmp_path))
+    tr = Trainer(args)
+    losses = [tr.train_step()["loss"] for _ in range(5)]
+    assert all(torch.isfinite(torch.tensor(l)) for l in losses)
+    assert losses[-1] < losses[0]
