@@ -28,7 +28,8 @@ using namespace llmb;
 namespace {
 constexpr int MAX_RANKS = 8;
 constexpr int MAX_SEGS = 40;
-enum { FLAG_READY = 0, FLAG_DONE = 1, FLAG_READY2 = 2, FLAG_PARAM = 3, FLAG_SCALAR = 4, FLAG_DONE2 = 5, NUM_FLAG_KINDS = 8 };
+enum { FLAG_READY = 0, FLAG_DONE = 1, FLAG_READY2 = 2, FLAG_PARAM = 3, FLAG_SCALAR = 4, FLAG_DONE2 = 5, FLAG_ROWS_READY = 6,
+       FLAG_ROWS_DONE = 7, NUM_FLAG_KINDS = 8 };
 
 struct PeerPtrs { void* p[MAX_RANKS]; };
 struct SegList {
@@ -265,6 +266,12 @@ __global__ void __launch_bounds__(256) adamw_push_kernel(PeerPtrs params, long l
   signal_all_last_block(counter, flags, FLAG_PARAM, me, seq, W);
 }
 
+// everything this stream wrote so far is visible system-wide before the flag: announces (kind, me) = seq to every rank
+__global__ void signal_flags_kernel(PeerPtrs flags, int kind, int me, int W, unsigned seq) {
+  __threadfence_system();
+  for (int r = 0; r < W; ++r) st_release_sys(flag_ptr(flags.p[r], kind, me), seq);
+}
+
 __global__ void wait_flags_kernel(void* my_flags, int kind, unsigned seq, int W, int* status) {
   wait_all(my_flags, kind, seq, W, status);
 }
@@ -385,6 +392,10 @@ LLMB_API int llmb_comm_adamw_push(void* const* param_ptrs, long long param_off, 
 }
 LLMB_API int llmb_comm_set_wait_budget(unsigned polls) {
   return (int)cudaMemcpyToSymbol(g_wait_budget, &polls, sizeof(polls));
+}
+LLMB_API int llmb_comm_signal(void* const* flag_ptrs, int kind, int me, int W, unsigned seq, cudaStream_t st) {
+  signal_flags_kernel<<<1, 1, 0, st>>>(to_peers(flag_ptrs, W), kind, me, W, seq);
+  return (int)cudaGetLastError();
 }
 LLMB_API int llmb_comm_wait(void* my_flags, int kind, unsigned seq, int W, int* status, cudaStream_t st) {
   wait_flags_kernel<<<1, 32, 0, st>>>(my_flags, kind, seq, W, status);

@@ -21,6 +21,16 @@ using namespace llmb;
 using namespace tc05;
 
 namespace {
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const uint4* p) {     // streaming 16-byte load (peer memory: read once)
+  uint4 v; asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory"); return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 constexpr int BM = 128, BN = 256;
 constexpr int STAGES = 4;
 constexpr int ROW_BYTES = 128;                       // one swizzled row
@@ -33,7 +43,24 @@ constexpr int BAND = 16;                             // m-tiles per rasterisatio
 
 enum { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_DGELU = 3, EPI_ACC_F32 = 4, EPI_BIAS_RESID = 5, EPI_STORE_F32 = 6 };
 
+// All-gather fused into the GEMM: the A matrix [W*n, K] is the concatenation of W row chunks, chunk r produced by
+// rank r.  Every rank holds a full-size local buffer whose own chunk is already in place; two copier warps per
+// CTA pull the other chunks out of the peers' buffers (plain 16-byte peer loads over NVLink, each byte crosses
+// once) into the local buffer WHILE the tile loop runs, starting with the tiles of the local chunk and taking the
+// remote chunks in ring order.  A chunk's tiles are fetched (TMA, local memory) once every CTA's copiers have
+// counted it complete.
+struct GatherArgs {
+  const void* peer_src[8];     // [r]: start of chunk r inside rank r's buffer
+  void* local;                 // start of this rank's [W*n, K] buffer
+  const void* flags;           // this rank's flag words: peers announce "my chunk is written" (kind ROWS_READY)
+  unsigned* counts;            // [16] local counters, zeroed before the launch: [r] = slices of chunk r copied, [8 + r] = slice tickets
+  long long chunk_vecs;        // 16-byte vectors per chunk
+  unsigned seq, target;        // announce sequence number to wait for; slices per chunk (counts[r] == target: chunk landed)
+  int W, me, tiles_per_chunk;  // W = 0: no gather
+};
+
 struct GemmParams {
+  GatherArgs g;
   void* D; const void* bias; void* aux; const float* alpha;
   int M, N, K;                 // K in elements
   long long ldd, ldaux;
@@ -397,7 +424,8 @@ __device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_
 // the tiles it owns; the peer's TMA completions are reported to the leader's mbarrier.
 constexpr int B2_STAGE = 128 * ROW_BYTES;             // 16 KB: this CTA's half of the B tile
 constexpr int STAGE2_BYTES = A_STAGE + B2_STAGE;      // 32 KB
-constexpr int PAIR_THREADS = 320;                      // TMA producer, MMA issuer, 8 epilogue warps
+constexpr int PAIR_THREADS = 384;                      // TMA producer, MMA issuer, 8 epilogue warps, 2 gather copier warps
+constexpr int FLAG_ROWS_READY = 6;                     // flag kind (layout of comm.cu: flags[kind][8 ranks])
 constexpr int SMEM2_TAIL = 512;                        // barriers, TMEM slot, abort flag
 template <int EPI> constexpr int smem2_bytes() { return EpiCfg<EPI>::STAGES * STAGE2_BYTES + 4 * EpiCfg<EPI>::WARP_STAGE + 1024 + SMEM2_TAIL; }
 
@@ -452,6 +480,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int m_in_band = min(BAND2, m_tiles - b * BAND2);
     m_blk = b * BAND2 + r % m_in_band;
     n_blk = r / m_in_band;
+    if (p.g.W > 1) m_blk = (m_blk + p.g.me * p.g.tiles_per_chunk) % m_tiles;   // the local chunk's tiles come first
     kb0 = split * p.kb_per_split;
     kb1 = min(p.kb_total, kb0 + p.kb_per_split);
   };
@@ -463,10 +492,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0; uint32_t phase = 0;
       const uint32_t lead_full0 = mapa_u32(smem_u32(&full_bar[0]), 0);
       bool ok = true;
+      int landed = -1;
       for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
         if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
+        if (p.g.W > 1) {                                 // gathered A: this tile's chunk must have landed in local memory
+          const int chunk = m_blk / p.g.tiles_per_chunk;
+          if (chunk != p.g.me && chunk != landed) {
+            unsigned spins = 0;
+            while ((int)(ld_acquire_gpu(&p.g.counts[chunk]) - p.g.target) < 0) {
+              if (++spins > (1u << 24)) { ok = false; break; }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            fence_proxy_async_all();                      // the copiers' generic-proxy stores before this warp's TMA reads
+            landed = chunk;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { ok = false; break; }
           unsigned char* sa = smem + stage * STAGE2_BYTES;
@@ -539,6 +582,50 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           umma_commit_pair(tb1 + acc * 8);
         }
         __syncwarp();
+      }
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------ gather copiers (warps 10, 11, both CTAs)
+    if (p.g.W > 1) {
+      // Slices of 32 KB are handed out by ticket, so the copy completes with whatever CTAs are resident.
+      constexpr long long SLICE = 2048;                  // 16-byte vectors
+      bool ok = true;
+      for (int step = 1; step < p.g.W && ok; ++step) {
+        const int r = (p.g.me + step) % p.g.W;
+        // rank r has announced that its chunk is complete (bounded wait, one lane polls)
+        if (lane == 0) {
+          const unsigned* f = reinterpret_cast<const unsigned*>(p.g.flags) + FLAG_ROWS_READY * 8 + r;
+          unsigned spins = 0;
+          while ((int)(ld_acquire_sys(f) - p.g.seq) < 0) {
+            if (++spins > (1u << 24)) { ok = false; break; }
+            __nanosleep(200);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        const uint4* src = reinterpret_cast<const uint4*>(p.g.peer_src[r]);
+        uint4* dst = reinterpret_cast<uint4*>(p.g.local) + (long long)r * p.g.chunk_vecs;
+        for (;;) {
+          unsigned ticket = 0;
+          if (lane == 0) ticket = atomicAdd(&p.g.counts[8 + r], 1u);
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          if (ticket >= p.g.target) break;
+          const long long v0 = (long long)ticket * SLICE;
+          const long long v1 = v0 + SLICE < p.g.chunk_vecs ? v0 + SLICE : p.g.chunk_vecs;
+          long long v = v0 + lane;
+          for (; v + 7 * 32 < v1; v += 8 * 32) {         // eight peer loads in flight per thread
+            uint4 t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = ld_nc_v4(src + v + k * 32);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) dst[v + k * 32] = t[k];
+          }
+          for (; v < v1; v += 32) dst[v] = ld_nc_v4(src + v);
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(&p.g.counts[r], 1u);
+        }
       }
       if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
     }
@@ -652,6 +739,7 @@ template <> struct KindTraits<KIND_TF32> { static constexpr int ESZ = 4; static 
 template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ESZ = 1; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
 
 int g_dbg_mn_lbo = -1, g_dbg_mn_sbo = -1;   // test hooks: override the MN-major descriptor strides
+GatherArgs g_pending_gather{};                // consumed (and cleared) by the next llmb_gemm call of this process
 int g_pair_mode = -1;                         // -1: read LLMB_GEMM_PAIR once; 0: single-CTA tiles; 1: CTA-pair tiles
 
 bool pair_mode() {
@@ -726,6 +814,13 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
                      ROW_ELEMS, BKE, (pair ? 128 : BN) / ROW_ELEMS, mn_swz) == 0) { tb = t3; b_3d = 1; }
   }
   GemmParams p;
+  p.g = g_pending_gather;
+  g_pending_gather.W = 0;
+  if (p.g.W > 1) {
+    // gathered A: K-major bf16 rows, CTA-pair kernel, whole 256-row tiles per chunk, no split-K
+    if (!pair || a_mn || KIND != KIND_F16 || p.g.tiles_per_chunk <= 0 || M != p.g.W * p.g.tiles_per_chunk * 2 * BM || epi == EPI_ACC_F32)
+      return LLMB_ERR_BAD_ARG;
+  }
   p.a_3d = a_3d; p.b_3d = b_3d;
   p.D = D; p.bias = bias; p.aux = aux; p.alpha = alpha;
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldaux = ldaux;
@@ -808,6 +903,17 @@ LLMB_API int llmb_gemm(void* D, const void* A, const void* B, const void* bias, 
   return LLMB_ERR_BAD_ARG;
 }
 
+// Arms the NEXT llmb_gemm call of this process to gather its A matrix from W ranks (see GatherArgs): A must be the
+// local [W*n, K] buffer, n a multiple of 256; peer_src[r] = address of chunk r in rank r's buffer; flags = this
+// rank's flag words; counts = 16 local counters that the caller zeroes (stream-ordered) before the GEMM.
+LLMB_API void llmb_gemm_set_gather(void* const* peer_src, void* local, const void* flags, unsigned* counts, long long chunk_bytes,
+                                   unsigned seq, int W, int me, int rows_per_rank) {
+  GatherArgs g{};
+  for (int r = 0; r < W && r < 8; ++r) g.peer_src[r] = peer_src[r];
+  g.local = local; g.flags = flags; g.counts = counts; g.chunk_vecs = chunk_bytes / 16;
+  g.seq = seq; g.target = (unsigned)((g.chunk_vecs + 2047) / 2048); g.W = W; g.me = me; g.tiles_per_chunk = rows_per_rank / (2 * BM);
+  g_pending_gather = g;
+}
 LLMB_API void llmb_gemm_debug_mn_strides(int lbo_bytes, int sbo_bytes) { g_dbg_mn_lbo = lbo_bytes; g_dbg_mn_sbo = sbo_bytes; }
 // 0: single-CTA 128x256 tiles, 1: CTA-pair 256x256 tiles (default; env LLMB_GEMM_PAIR=0 selects the former)
 LLMB_API void llmb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }

@@ -183,11 +183,19 @@ class GPT2:
             # backward scratch
             "dres": e(B, T, C), "dl_btc": e(B, T, C), "dl_bt4c": e(B, T, 4 * C),
         }
+        self._fused_gather = None
         if self.vocab_parallel:
             W = self.zero.world_size
             self.vslice = ((Vp + W - 1) // W + 7) // 8 * 8
             a["logits_slice"] = e(W * B * T, self.vslice)
             a["ce_stats"] = e(W * B * T, 4, dtype=f32)
+            # all-gather of the final LayerNorm rows fused into the slice GEMM (peer memory; bf16 tensor path, whole
+            # 256-row tiles per rank); LLMM_FUSED_GATHER=0 keeps the collective + GEMM pair
+            if (self.device.type == "cuda" and self.dtype == torch.bfloat16 and (B * T) % 256 == 0 and
+                    getattr(self.zero, "backend_name", "") == "p2p" and os.environ.get("LLMM_FUSED_GATHER", "1") != "0"):
+                from ..parallel.zero import FusedRowGather
+                self._fused_gather = FusedRowGather(self.zero.rank, W, self.device, B * T, C)
+                a["lnf"] = self._fused_gather.local.view(B, T, C)
         elif self.lm_head_chunks > 1:
             self.tile_width = ((Vp + self.lm_head_chunks - 1) // self.lm_head_chunks + 127) // 128 * 128
             a["logits_tile"] = e(B * T, self.tile_width)
@@ -211,13 +219,19 @@ class GPT2:
         a, z, V = self.acts, self.zero, self.config.vocab_size
         B, T, C = self.B, self.T, self.config.channels
         rows = B * T
-        self._lnf_all = z.all_gather_rows(a["lnf"].view(rows, C))
         self._tgt_all = z.all_gather_rows(self.targets_dev.view(rows))
         v0, w = self._vocab_slice()
         tile = a["logits_slice"][:, :max(w, 8)]
         stats = a["ce_stats"]
-        if w > 0:
-            ops.matmul_fwd(tile, self._lnf_all, p["wte"][v0:v0 + w])
+        fg = self._fused_gather
+        if fg is not None and w >= 8:
+            # ONE kernel: the other ranks' rows are pulled over NVLink by copier warps inside the slice GEMM
+            fg.gemm(tile, p["wte"][v0:v0 + w])
+            self._lnf_all = fg.buf
+        else:
+            self._lnf_all = z.all_gather_rows(a["lnf"].view(rows, C))
+            if w > 0:
+                ops.matmul_fwd(tile, self._lnf_all, p["wte"][v0:v0 + w])
         ops.chunked_ce_pass1(stats, tile, self._tgt_all, v0, w, V, True)
         # merge (max, sum-exp, target logit) over the vocabulary slices of all ranks
         allst = z.all_gather_rows(stats.unsqueeze(0))                      # [W, W·rows, 4]
@@ -322,6 +336,8 @@ class GPT2:
         if z is not None:
             z.before_head(backward=False)
             p = self.p
+        if self._fused_gather is not None:
+            self._fused_gather.wait_released()          # peers have finished reading the previous lnf rows
         ops.layernorm_fwd(a["lnf"], a["lnf_mean"], a["lnf_rstd"], a["residual3"][L - 1], p["lnfw"], p["lnfb"])
         dloss = 1.0 / (B * T * grad_accum_steps)
         self._dloss = dloss

@@ -274,6 +274,60 @@ class P2PBackend:
         self.arena.close()
 
 
+# ======================================================================================= fused row gather
+class FusedRowGather:
+    """All-gather of activation rows fused into the GEMM that consumes them (vocabulary-parallel LM head).
+
+    Every rank owns a [W·n, K] bf16 buffer in a symmetric arena and writes its own n rows in place (chunk ``rank``).
+    ``gemm`` launches ONE kernel: two copier warps per CTA pull the other ranks' chunks out of their arenas over
+    NVLink into the local buffer while the tensor-core tile loop already works on the local chunk, and a chunk's
+    tiles are fetched once it has landed (csrc/gemm.cu, GatherArgs).  Flags: ROWS_READY (6) = "my chunk is written",
+    ROWS_DONE (7) = "I have finished reading everybody's chunk"; both are sequence numbers, every wait is bounded."""
+    ROWS_READY, ROWS_DONE = 6, 7
+
+    def __init__(self, rank: int, world: int, device: torch.device, rows_per_rank: int, K: int):
+        from .symm import SymmetricArena
+        if rows_per_rank % 256:
+            raise ValueError("fused row gather needs rows per rank to be a multiple of 256")
+        self.rank, self.world, self.device, self.n, self.K = rank, world, device, rows_per_rank, K
+        self.chunk_bytes = rows_per_rank * K * 2
+        self.arena = SymmetricArena([("rows", world * self.chunk_bytes), ("counts", 64)], rank, world, device)
+        self.buf = self.arena.tensor("rows", torch.bfloat16).view(world * rows_per_rank, K)
+        self.local = self.buf[rank * rows_per_rank:(rank + 1) * rows_per_rank]
+        self.counts = self.arena.tensor("counts", torch.int32)
+        self.status = ops.status_word(device)
+        self.seq = 0
+        self.L = _lib.lib()
+        P, I, U, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_longlong
+        self.L.llmb_comm_signal.argtypes = [P, I, I, I, U, P]
+        self.L.llmb_comm_wait.argtypes = [P, I, U, I, P, P]
+        self.L.llmb_gemm_set_gather.argtypes = [P, P, P, P, LL, U, I, I, I]
+        self.L.llmb_gemm_set_gather.restype = None
+        self._peer_src = (ctypes.c_void_p * 8)()
+        off = self.arena.offsets["rows"]
+        for r in range(world):                      # chunk r inside rank r's buffer
+            self._peer_src[r] = self.arena.peer_bases[r] + off + r * self.chunk_bytes
+
+    def wait_released(self) -> None:
+        """Before the local chunk is overwritten: every rank has finished reading the previous contents."""
+        if self.seq:
+            _lib.check(self.L.llmb_comm_wait(self.arena.flags_ptr, self.ROWS_DONE, self.seq, self.world,
+                                             self.status.data_ptr(), _lib.stream()), "rows_wait")
+
+    def gemm(self, D: torch.Tensor, weight: torch.Tensor) -> None:
+        """D[W·n, N] = gathered rows · weightᵀ; call after the local chunk has been written on the current stream."""
+        self.seq += 1
+        st = _lib.stream()
+        _lib.check(self.L.llmb_comm_signal(self.arena.flags_peer_ptrs(), self.ROWS_READY, self.rank, self.world, self.seq, st),
+                   "rows_signal")
+        self.counts.zero_()
+        self.L.llmb_gemm_set_gather(self._peer_src, self.buf.data_ptr(), self.arena.flags_ptr, self.counts.data_ptr(),
+                                    self.chunk_bytes, self.seq, self.world, self.rank, self.n)
+        ops.gemm(D, self.buf, weight)
+        _lib.check(self.L.llmb_comm_signal(self.arena.flags_peer_ptrs(), self.ROWS_DONE, self.rank, self.world, self.seq, st),
+                   "rows_release")
+
+
 # ======================================================================================= engine
 class ZeroEngine:
     def __init__(self, stage: int, rank: int, world_size: int, device: torch.device, dist_ctx=None,

@@ -54,7 +54,7 @@ WORKER = textwrap.dedent('''
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     cfg = GPT2Config(max_seq_len=128, vocab_size=1000, num_layer=2, num_heads=2, channels=128, padded_vocab_size=1024)
     eng = ZeroEngine(stage, rank, W, torch.device("cuda", rank), backend=backend)
-    model = GPT2(cfg, "bf16", f"cuda:{rank}", zero=eng)
+    model = GPT2(cfg, "bf16", f"cuda:{rank}", zero=eng, vocab_parallel=os.environ.get("VP", "0") == "1")
     losses = []
     for step in range(1, 4):
         for micro in range(2):
@@ -80,8 +80,8 @@ def _port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _run(stage, backend, W, tmp):
-    out = os.path.join(tmp, f"z{stage}_{backend}.pt")
+def _run(stage, backend, W, tmp, **extra_env):
+    out = os.path.join(tmp, f"z{stage}_{backend}_{'_'.join(extra_env.values())}.pt")
     script = os.path.join(tmp, "worker.py")
     with open(script, "w") as f:
         f.write(WORKER)
@@ -90,7 +90,7 @@ def _run(stage, backend, W, tmp):
     for r in range(W):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(W), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port), STAGE=str(stage), BACKEND=backend, OUT=out, LLMB_ROOT=ROOT,
-                   NCCL_NVLS_ENABLE="0")
+                   NCCL_NVLS_ENABLE="0", **extra_env)
         procs.append(subprocess.Popen([sys.executable, script], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     logs = []
     for p in procs:
@@ -116,3 +116,18 @@ def test_p2p_matches_nccl(stage, tmp_path):
     rel = ((a["params"] - b["params"]).norm() / b["params"].norm()).item()
     assert rel < 2e-3, rel
     assert a["losses"][-1] < a["losses"][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gather_gemm_matches_collective_then_gemm(tmp_path):
+    """Vocabulary-parallel LM head: the slice GEMM with the all-gather of the activation rows fused in (copier
+    warps pulling the peer's rows while the tile loop runs) against all-gather followed by the plain GEMM, and
+    both against the replicated head."""
+    fused = _run(1, "p2p", 2, str(tmp_path), VP="1", LLMM_FUSED_GATHER="1")
+    plain = _run(1, "p2p", 2, str(tmp_path), VP="1", LLMM_FUSED_GATHER="0")
+    repl = _run(1, "p2p", 2, str(tmp_path), VP="0", LLMM_FUSED_GATHER="0")
+    assert fused["status"] == 0 and plain["status"] == 0
+    for lf, lp, lr in zip(fused["losses"], plain["losses"], repl["losses"]):
+        assert abs(lf - lp) < 1e-3 and abs(lf - lr) < 2e-2, (fused["losses"], plain["losses"], repl["losses"])
+    rel = ((fused["params"] - plain["params"]).norm() / plain["params"].norm()).item()
+    assert rel < 1e-4, rel
