@@ -5,6 +5,9 @@
     python profile_kernels.py gemm        # fc GEMM with the fused bias+GELU epilogue, its dinp (dGELU) and dW GEMMs
     python profile_kernels.py lmhead      # LM-head GEMM on 8192 rows + fused softmax/cross-entropy
     python profile_kernels.py layernorm   # LayerNorm forward + backward on 65536 x 768
+    python profile_kernels.py fusedgather # the all-gather-fused GEMM with four "ranks" emulated on ONE GPU: the peers'
+                                          # chunks are other local buffers and their flags are preset, so the single
+                                          # kernel (copier warps + tile loop) runs exactly as on a rank of a 4-GPU job
 
 Each case launches its kernels `--reps` times (default 2) and prints the device status word.  Meant to be run
 plain first and then under `ncu -k regex:<kernel> -c <n>` with the same command line; the per-step counterpart
@@ -78,7 +81,32 @@ def case_layernorm(reps):
         ops.layernorm_bwd(dx, dw, db, dout, x, w, mean, rstd)
 
 
-CASES = {"attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
+def case_fusedgather(reps):
+    import ctypes
+    from llm_mojo_b200.ops import _lib
+    W, me, n, K, N = 4, 1, 8192, 768, 6288
+    L = _lib.lib()
+    P, I, U, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_longlong
+    L.llmb_gemm_set_gather.argtypes = [P, P, P, P, LL, U, I, I, I]
+    L.llmb_gemm_set_gather.restype = None
+    peers = [(torch.randn(n, K, device="cuda") * 0.05).bfloat16() for _ in range(W)]     # chunk r as rank r holds it
+    local = torch.zeros(W * n, K, device="cuda", dtype=torch.bfloat16)
+    local[me * n:(me + 1) * n] = peers[me]
+    wt = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    out = torch.empty(W * n, N, device="cuda", dtype=torch.bfloat16)
+    flags = torch.full((64,), 1 << 20, dtype=torch.int32, device="cuda")                 # every rank has announced every sequence
+    counts = torch.zeros(16, dtype=torch.int32, device="cuda")
+    src = (ctypes.c_void_p * 8)(*[t.data_ptr() for t in peers])
+    for rep in range(reps):
+        counts.zero_()
+        L.llmb_gemm_set_gather(src, local.data_ptr(), flags.data_ptr(), counts.data_ptr(), n * K * 2, rep + 1, W, me, n)
+        ops.gemm(out, local, wt)
+    torch.cuda.synchronize()
+    want = torch.cat(peers).float() @ wt.float().t()
+    print("max abs diff vs fp32 reference", (out.float() - want).abs().max().item())
+
+
+CASES = {"fusedgather": case_fusedgather, "attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
