@@ -195,13 +195,18 @@ def _tc_kind(t: torch.Tensor):
 
 
 def _splits_for(M: int, N: int, K: int) -> int:
-    """Split-K factor for the dW GEMMs: fill one wave of 148 CTAs when the output has few tiles."""
-    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    """Split-K factor for the dW GEMMs (256x256 tiles on 74 CTA pairs): the number of splits that minimises
+    waves x (k-blocks per unit + a fixed per-unit cost for the prologue and the fp32 red.add epilogue)."""
+    tiles = max(1, ((M + 255) // 256) * ((N + 255) // 256))
     kb = (K + 63) // 64
-    tiles = max(tiles, 1)
-    if tiles >= 148:
-        return 1
-    return max(1, min(148 // tiles, kb // 4 if kb >= 4 else 1))
+    clusters = 74
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(16, kb // 8)) + 1):
+        waves = -(-tiles * s // clusters)
+        cost = waves * (kb / s + 24.0)
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> None:
