@@ -26,8 +26,11 @@ def parse_log(text: str, warmup: int):
         if m:
             steps.append({"step": int(m.group(1)), "loss": float(m.group(3)), "ms": float(m.group(4)),
                           "tok_s": float(m.group(5)), "device_ms": float(m.group(6)) if m.group(6) else None})
-        if line.startswith("[mem-report] "):
-            mem = json.loads(line[len("[mem-report] "):])
+        if line.startswith("[mem-report] "):          # ranks may interleave their lines: take the first JSON document
+            try:
+                mem, _ = json.JSONDecoder().raw_decode(line[len("[mem-report] "):])
+            except json.JSONDecodeError:
+                pass
     timed = steps[warmup:] if len(steps) > warmup else steps
     if not timed:
         return None
