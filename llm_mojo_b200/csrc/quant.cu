@@ -111,9 +111,12 @@ __global__ void dequantize_fp8_kernel(float* __restrict__ out, const uint8_t* __
 }
 
 // ------------------------------------------------------------------ NVFP4
-__device__ __forceinline__ float e2m1_value(int code) {   // code: 3-bit magnitude index
-  const float tab[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  return tab[code & 7];
+// magnitude of a 3-bit e2m1 index {0, 0.5, 1, 1.5, 2, 3, 4, 6}, built from its exponent / mantissa bits (no table:
+// a dynamically indexed local array would live in local memory and cost a load per element)
+__device__ __forceinline__ float e2m1_value(int code) {
+  const unsigned e = (code >> 1) & 3u, m = code & 1u;
+  const unsigned bits = e ? (((126u + e) << 23) | (m << 22)) : (m ? 0x3F000000u : 0u);
+  return __uint_as_float(bits);
 }
 // nearest grid point, ties away from zero (the larger magnitude); returns sign<<3 | index
 __device__ __forceinline__ int encode_e2m1_rne(float v) {
@@ -163,6 +166,26 @@ __device__ __forceinline__ void fwht16(float (&b)[16]) {
   }
 }
 
+// 16 consecutive bf16 values <-> 16 floats through two 16-byte accesses (the address must be 32-byte aligned)
+__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[16]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p), b = *reinterpret_cast<const uint4*>(p + 8);
+  const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = __bfloat1622float2(ha[i]), fb = __bfloat1622float2(hb[i]);
+    v[2 * i] = fa.x; v[2 * i + 1] = fa.y; v[8 + 2 * i] = fb.x; v[8 + 2 * i + 1] = fb.y;
+  }
+}
+__device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[16]) {
+  uint4 a, b;
+  __nv_bfloat162* ha = reinterpret_cast<__nv_bfloat162*>(&a);
+  __nv_bfloat162* hb = reinterpret_cast<__nv_bfloat162*>(&b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { ha[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]); hb[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]); }
+  *reinterpret_cast<uint4*>(p) = a; *reinterpret_cast<uint4*>(p + 8) = b;
+}
+
 // One thread quantises one block: BLOCK_ROWS x 16 elements along the block axis.
 //   axis 1: blocks run along the columns (K = last dim); axis 0: blocks run along the rows.
 // Outputs (each optional): packed e2m1 (logical [outer, K/2] with K the block axis), e4m3 scales
@@ -188,11 +211,28 @@ __global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restri
 
   float v[BLOCK_ROWS][16];
   float amax = 0.f;
+  // Vector I/O whenever 16 consecutive elements of the block are contiguous in memory: along the block axis for
+  // axis 1, across the 16 "outer" lines of a 16x16 block for axis 0 (bf16 storage, whole blocks, 32-byte aligned).
+  constexpr bool kBf16 = sizeof(T) == 2;
+  const bool vec_a = kBf16 && axis == 1 && (cols % 16) == 0 && (br + 1) * BLOCK_ROWS <= outer;
+  const bool vec_b = false;                               // (16 x 16 blocks along axis 0 take the cooperative kernel)
+  if (vec_b) {
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float t[16];
+      load16_bf16(reinterpret_cast<const __nv_bfloat16*>(x) + (long long)(kb * 16 + kk) * cols + br * BLOCK_ROWS, t);
+#pragma unroll
+      for (int rr = 0; rr < BLOCK_ROWS; ++rr) v[rr][kk] = t[rr & 15];
+    }
+  }
 #pragma unroll
   for (int rr = 0; rr < BLOCK_ROWS; ++rr) {
     const int o = br * BLOCK_ROWS + rr;
+    if (vec_a) load16_bf16(reinterpret_cast<const __nv_bfloat16*>(x) + (long long)o * cols + kb * 16, v[rr]);
+    else if (!vec_b) {
 #pragma unroll
-    for (int kk = 0; kk < 16; ++kk) v[rr][kk] = o < outer ? to_f<T>(x[addr(o, kb * 16 + kk)]) : 0.f;
+      for (int kk = 0; kk < 16; ++kk) v[rr][kk] = o < outer ? to_f<T>(x[addr(o, kb * 16 + kk)]) : 0.f;
+    }
     if (rht) {
 #pragma unroll
       for (int kk = 0; kk < 16; ++kk) v[rr][kk] *= hadamard_sign(kk);
@@ -223,12 +263,80 @@ __global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restri
           const unsigned long long flat = (unsigned long long)o * K + kb * 16 + kk + t;
           c[t] = encode_e2m1_sr(s, rng_uniform01(seed, ((unsigned long long)step << 32) | flat, stream));
         } else c[t] = encode_e2m1_rne(s);
-        if (deq) deq[addr(o, kb * 16 + kk + t)] = __float2bfloat16_rn((c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec);
+        const float dq = (c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec;
+        if (vec_a || vec_b) v[rr][kk + t] = dq;             // written out as vectors below
+        else if (deq) deq[addr(o, kb * 16 + kk + t)] = __float2bfloat16_rn(dq);
       }
       packed[kk / 2] = (uint8_t)(c[0] | (c[1] << 4));      // even index -> low nibble
     }
     if (q) *reinterpret_cast<uint2*>(q + ((long long)o * K + kb * 16) / 2) = *reinterpret_cast<uint2*>(packed);
+    if (vec_a && deq) store16_bf16(deq + (long long)o * cols + kb * 16, v[rr]);
   }
+  if (vec_b && deq) {
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float t[16];
+#pragma unroll
+      for (int rr = 0; rr < BLOCK_ROWS; ++rr) t[rr & 15] = v[rr][kk];
+      store16_bf16(deq + (long long)(kb * 16 + kk) * cols + br * BLOCK_ROWS, t);
+    }
+  }
+}
+
+// 16 x 16 blocks of bf16 storage: sixteen lanes share one block, each taking the 16 values of the block that are
+// contiguous in memory (a row of 16 k for axis 1, a k-row of 16 outer lines for axis 0).  The block amax is a
+// half-warp shuffle reduction, all memory traffic is two 16-byte accesses per lane each way, and nobody holds 256
+// values in registers.  Same rounding, scale encoding and RNG counters as the one-thread-per-block kernel.
+__global__ void __launch_bounds__(256) nvfp4_quantize16_coop_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ scales,
+                                                                   __nv_bfloat16* __restrict__ deq, const __nv_bfloat16* __restrict__ x,
+                                                                   const float* __restrict__ tensor_scale_ptr, int rows, int cols, int axis,
+                                                                   int sr, unsigned long long seed, unsigned long long stream, long long step,
+                                                                   long long n_col_tiles) {
+  const int outer = axis == 1 ? rows : cols, K = axis == 1 ? cols : rows;
+  const int kblocks = K / 16, tile_rows = outer / 16;
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / 16;       // block index (half-warp uniform)
+  const int l = threadIdx.x & 15;
+  if (gid >= (long long)tile_rows * kblocks) return;
+  int br, kb;
+  if (axis == 1) { br = (int)(gid / kblocks); kb = (int)(gid % kblocks); }
+  else { kb = (int)(gid / tile_rows); br = (int)(gid % tile_rows); }
+  // the 16 contiguous values of this lane: axis 1 -> (o = br*16 + l, k = kb*16 + 0..15); axis 0 -> (o = br*16 + 0..15, k = kb*16 + l)
+  const long long base = axis == 1 ? (long long)(br * 16 + l) * cols + kb * 16 : (long long)(kb * 16 + l) * cols + br * 16;
+  float v[16];
+  load16_bf16(x + base, v);
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
+  const float ts = *tensor_scale_ptr;
+  const float raw = (amax <= 0.f || ts <= 0.f) ? 1.0f : (amax / 6.0f) / ts;
+  const uint8_t sc_code = encode_e4m3(raw);
+  const float sc_dec = decode_e4m3(sc_code);
+  float sc_val = sc_dec * ts;
+  if (sc_val <= 0.f) sc_val = 1.0f;
+  const float inv = 1.0f / sc_val;
+  if (scales) {                                            // one scale per (outer line, k-block): lane l writes line br*16 + l
+    const int o = br * 16 + l;
+    scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(o, kb, n_col_tiles) : (long long)o * kblocks + kb] = sc_code;
+  }
+  uint8_t packed[8];
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    int c[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int o = axis == 1 ? br * 16 + l : br * 16 + i + t;
+      const int k = axis == 1 ? kb * 16 + i + t : kb * 16 + l;
+      const float sv = v[i + t] * inv;
+      if (sr) c[t] = encode_e2m1_sr(sv, rng_uniform01(seed, ((unsigned long long)step << 32) | ((unsigned long long)o * K + k), stream));
+      else c[t] = encode_e2m1_rne(sv);
+      v[i + t] = (c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec;
+    }
+    packed[i / 2] = (uint8_t)(c[0] | (c[1] << 4));
+  }
+  if (q) *reinterpret_cast<uint2*>(q + ((long long)(br * 16 + l) * K + kb * 16) / 2) = *reinterpret_cast<uint2*>(packed);   // axis 1 only
+  if (deq) store16_bf16(deq + base, v);
 }
 
 __global__ void nvfp4_tensor_scale_kernel(float* ts, const float* amax) {
@@ -275,6 +383,55 @@ LLMB_API int llmb_amax(float* out, const void* x, long long n, int dtype, cudaSt
   else amax_kernel<float><<<grid, 512, 0, st>>>((unsigned*)out, (const float*)x, n);
   return (int)cudaGetLastError();
 }
+// amax of the 16-point randomised Hadamard transform of x taken along `axis` (blocks of 16 consecutive columns
+// for axis 1, of 16 consecutive rows for axis 0), without materialising the transform: one thread per block.
+namespace {
+template <typename T>
+__global__ void amax_rht_kernel(unsigned* __restrict__ out_bits, const T* __restrict__ x, int rows, int cols, int axis) {
+  unsigned m = 0;
+  const long long nblocks = (long long)rows * cols / 16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nblocks; i += (long long)gridDim.x * blockDim.x) {
+    float v[16];
+    if (axis == 1) {
+      const T* p = x + i * 16;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) v[k] = to_f<T>(p[k]) * hadamard_sign(k);
+    } else {                                   // adjacent threads take adjacent columns of the same 16 rows: coalesced
+      const long long rb = i / cols; const int c = (int)(i % cols);
+      const T* p = x + rb * 16 * cols + c;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) v[k] = to_f<T>(p[(long long)k * cols]) * hadamard_sign(k);
+    }
+    fwht16(v);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) m = max(m, __float_as_uint(v[k]) & 0x7fffffffu);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ unsigned red[32];
+  const int lane = threadIdx.x % 32, wid = threadIdx.x / 32;
+  if (lane == 0) red[wid] = m;
+  __syncthreads();
+  if (wid == 0) {
+    m = lane < (int)(blockDim.x / 32) ? red[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) atomicMax(out_bits, m);
+  }
+}
+}  // namespace
+// rows (axis 0) or cols (axis 1) must be a multiple of 16
+LLMB_API int llmb_amax_rht(float* out, const void* x, int rows, int cols, int axis, int dtype, cudaStream_t st) {
+  if ((axis == 1 ? cols : rows) % 16) return LLMB_ERR_BAD_ARG;
+  cudaError_t e = cudaMemsetAsync(out, 0, sizeof(float), st);
+  if (e != cudaSuccess) return (int)e;
+  const long long nblocks = (long long)rows * cols / 16;
+  long long want = (nblocks + 255) / 256;
+  const int grid = (int)(want < 8LL * sm_count() ? (want < 1 ? 1 : want) : 8LL * sm_count());
+  if (dtype == LLMB_BF16) amax_rht_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((unsigned*)out, (const __nv_bfloat16*)x, rows, cols, axis);
+  else amax_rht_kernel<float><<<grid, 256, 0, st>>>((unsigned*)out, (const float*)x, rows, cols, axis);
+  return (int)cudaGetLastError();
+}
 LLMB_API int llmb_amax_state_floats() { return 4 + AMAX_HISTORY; }
 // state: llmb_amax_state_floats() floats, initialised to {1, 1, 0, 0, 0...}; fmt_max 448 (e4m3) / 57344 (e5m2)
 LLMB_API int llmb_amax_update(float* state, const float* amax_cur, float fmt_max, float margin_mult, cudaStream_t st) {
@@ -318,6 +475,12 @@ LLMB_API int llmb_nvfp4_quantize(void* q, void* scales, void* deq, const void* x
   const long long total = (long long)ceil_div(outer, block_rows) * (K / 16);
   const int threads = 128;
   const unsigned grid = (unsigned)ceil_div_ll(total, threads);
+  if (dtype == LLMB_BF16 && block_rows == 16 && !rht && cols % 16 == 0 && outer % 16 == 0 && (q == nullptr || axis == 1)) {
+    const long long lanes = total * 16;
+    nvfp4_quantize16_coop_kernel<<<(unsigned)ceil_div_ll(lanes, 256), 256, 0, st>>>((uint8_t*)q, (uint8_t*)scales, (__nv_bfloat16*)deq,
+        (const __nv_bfloat16*)x, tensor_scale, rows, cols, axis, sr, seed, stream, step, n_col_tiles);
+    return (int)cudaGetLastError();
+  }
 #define NVFP4_LAUNCH(T, BR) nvfp4_quantize_kernel<T, BR><<<grid, threads, 0, st>>>((uint8_t*)q, (uint8_t*)scales, (__nv_bfloat16*)deq, (const T*)x, tensor_scale, rows, cols, axis, rht, sr, seed, stream, step, n_col_tiles)
   if (dtype == LLMB_BF16) { if (block_rows == 1) NVFP4_LAUNCH(__nv_bfloat16, 1); else NVFP4_LAUNCH(__nv_bfloat16, 16); }
   else { if (block_rows == 1) NVFP4_LAUNCH(float, 1); else NVFP4_LAUNCH(float, 16); }

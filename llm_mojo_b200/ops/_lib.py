@@ -44,6 +44,7 @@ _SIGS = {
     "llmb_gemm_debug_mn_strides": [c_int, c_int],
     "llmb_gemm_set_pair_mode": [c_int],
     "llmb_amax": [c_p, c_p, c_ll, c_int, c_p],
+    "llmb_amax_rht": [c_p, c_p, c_int, c_int, c_int, c_int, c_p],
     "llmb_amax_state_floats": [],
     "llmb_amax_update": [c_p, c_p, c_f, c_f, c_p],
     "llmb_quantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_int, c_p],

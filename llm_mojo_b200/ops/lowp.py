@@ -246,9 +246,12 @@ def nvfp4_fake_quant(x: torch.Tensor, axis: int = 1, block_rows: int = 1, rht: b
     if x.is_cuda:
         amax = torch.empty(1, dtype=torch.float32, device=dev)
         src = x
-        if rht:       # the tensor amax must be taken on what is quantised (transform in fp32, as the kernel does)
-            src_for_amax = _rht_along(x.float(), axis)
-            compute_amax(amax, src_for_amax)
+        if rht:       # the tensor amax must be taken on what is quantised: amax of the transform, computed on the fly
+            if (rows if axis == 0 else cols) % 16 == 0 and x.is_contiguous():
+                check(lib().llmb_amax_rht(ptr(amax), ptr(x), rows, cols, axis, dtype_code(x), stream()), "amax_rht")
+                _count()
+            else:
+                compute_amax(amax, _rht_along(x.float(), axis))
         else:
             compute_amax(amax, src)
         L = lib()
