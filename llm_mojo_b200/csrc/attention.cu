@@ -1030,12 +1030,17 @@ __global__ void __launch_bounds__(BW_THREADS, 1) attn_bwd_dq2_kernel(const __gri
             if (lane == 0) mbar_arrive(&sdp_free[bf]);
           }
           float dv[32];
+          if (need_mask) {                    // chunk on the diagonal: keys after the query contribute nothing
+            const int lim = qi - (j * 64 + half * 32);      // columns x > lim are masked
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const int kcol = j * 64 + half * 32 + x;
-            float pr = ex2_approx(fmaf(__uint_as_float(rs[x]), p.scale_log2, -lse));
-            if (need_mask && kcol > qi) pr = 0.f;
-            dv[x] = pr * (__uint_as_float(rp[x]) - dsum);
+            for (int x = 0; x < 32; ++x) {
+              const float pr = x > lim ? 0.f : ex2_approx(fmaf(__uint_as_float(rs[x]), p.scale_log2, -lse));
+              dv[x] = pr * (__uint_as_float(rp[x]) - dsum);
+            }
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; ++x)
+              dv[x] = ex2_approx(fmaf(__uint_as_float(rs[x]), p.scale_log2, -lse)) * (__uint_as_float(rp[x]) - dsum);
           }
           // dQ product of chunk g-2 done: the dS buffer is free
           if (half == 0 && g >= 2 && !mbar_wait(&kv_empty[(g - 2) % DQ_NS], ((g - 2) / DQ_NS) & 1)) { BW_FAIL(); break; }
