@@ -6,6 +6,8 @@ compile-time define; here every kernel is pre-built so it is a runtime value.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Dict, List, Tuple
 
@@ -124,8 +126,12 @@ class Precision:
     def __post_init__(self):
         alias = {"float32": "fp32", "bfloat16": "bf16", "nvfp4": "fp4", "float8": "fp8"}
         self.name = alias.get(self.name, self.name)
+        if self.name in ("fp8b", "fp8_block"):          # fp8 with per-128 block scales instead of per-tensor delayed scaling
+            self.name, self.fp8_block_scales = "fp8", True
         if self.name not in ("fp32", "tf32", "bf16", "fp8", "fp4"):
             raise ValueError(f"unknown precision {self.name!r}")
+        if self.name == "fp8" and os.environ.get("LLMM_FP8_BLOCK", "") not in ("", "0"):
+            self.fp8_block_scales = True
 
     @property
     def storage(self) -> torch.dtype:

@@ -460,6 +460,120 @@ LLMB_API int llmb_nvfp4_tensor_scale(float* ts, const float* amax, cudaStream_t 
   nvfp4_tensor_scale_kernel<<<1, 1, 0, st>>>(ts, amax);
   return (int)cudaGetLastError();
 }
+// ------------------------------------------------------------------ FP8 with per-128 block scales (fake quantisation)
+// x (bf16) -> bf16 holding fp8(x / s) * s with one power-of-two scale s = 2^ceil(log2(amax / fmt_max)) per block:
+// 1 x 128 blocks along `axis` (activations, gradients) or 128 x 128 blocks (weights).  Power-of-two scales make
+// value x scale exactly representable in bf16, so the block-scaled product can run on the bf16 tensor path with
+// the numerics of a block-scaled FP8 GEMM.
+namespace {
+__device__ __forceinline__ float pow2_scale(float amax, float fmt_max) {
+  if (!(amax > 0.f) || isinf(amax)) return 1.0f;
+  int e; const float m = frexpf(amax / fmt_max, &e);     // amax / fmt_max = m * 2^e, m in [0.5, 1)
+  return ldexpf(1.0f, m == 0.5f ? e - 1 : e);
+}
+template <int FMT>
+__device__ __forceinline__ float fp8_round(float v) {     // value of the nearest fp8 number (saturating)
+  const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+// 1 x 128 blocks along the contiguous axis: sixteen lanes x 8 values per block
+template <int FMT>
+__global__ void __launch_bounds__(256) fp8_block_row_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, long long nblocks) {
+  const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / 16;
+  const int l = threadIdx.x & 15;
+  if (gid >= nblocks) return;
+  Pack<__nv_bfloat16> p; p.load(x + gid * 128 + l * 8);
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(p.v[k]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o, 16));
+  const float s = pow2_scale(amax, FMT == 0 ? 448.0f : 57344.0f), inv = 1.0f / s;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) p.v[k] = fp8_round<FMT>(p.v[k] * inv) * s;
+  p.store(out + gid * 128 + l * 8);
+}
+// 128 x 1 blocks along the rows: one thread per (row block, 8 adjacent columns); two sweeps over the 128 rows
+template <int FMT>
+__global__ void __launch_bounds__(128) fp8_block_col_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, int rows, int cols) {
+  const int cvecs = cols / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)(rows / 128) * cvecs) return;
+  const int rb = (int)(idx / cvecs), cv = (int)(idx % cvecs);
+  const __nv_bfloat16* src = x + (long long)rb * 128 * cols + cv * 8;
+  float amax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int r = 0; r < 128; ++r) {
+    Pack<__nv_bfloat16> p; p.load(src + (long long)r * cols);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax[k] = fmaxf(amax[k], fabsf(p.v[k]));
+  }
+  float s[8], inv[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { s[k] = pow2_scale(amax[k], FMT == 0 ? 448.0f : 57344.0f); inv[k] = 1.0f / s[k]; }
+  __nv_bfloat16* dst = out + (long long)rb * 128 * cols + cv * 8;
+  for (int r = 0; r < 128; ++r) {
+    Pack<__nv_bfloat16> p; p.load(src + (long long)r * cols);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p.v[k] = fp8_round<FMT>(p.v[k] * inv[k]) * s[k];
+    p.store(dst + (long long)r * cols);
+  }
+}
+// 128 x 128 blocks: one CTA of 256 threads per block
+template <int FMT>
+__global__ void __launch_bounds__(256) fp8_block_tile_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, int rows, int cols) {
+  const int tiles_c = cols / 128;
+  const int tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+  const __nv_bfloat16* src = x + (long long)tr * 128 * cols + tc * 128;
+  __nv_bfloat16* dst = out + (long long)tr * 128 * cols + tc * 128;
+  Pack<__nv_bfloat16> p[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {                           // 2048 vectors of 8 in the tile: thread t takes t, t + 256, ...
+    const int v = threadIdx.x + i * 256, r = v / 16, c = (v % 16) * 8;
+    p[i].load(src + (long long)r * cols + c);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(p[i].v[k]));
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float s = pow2_scale(amax, FMT == 0 ? 448.0f : 57344.0f), inv = 1.0f / s;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int v = threadIdx.x + i * 256, r = v / 16, c = (v % 16) * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p[i].v[k] = fp8_round<FMT>(p[i].v[k] * inv) * s;
+    p[i].store(dst + (long long)r * cols + c);
+  }
+}
+}  // namespace
+// mode 0: 1 x 128 blocks along axis 1 (cols % 128 == 0); mode 1: 128 x 1 blocks along axis 0 (rows % 128 == 0, cols % 8 == 0);
+// mode 2: 128 x 128 blocks (both % 128 == 0).  fmt 0 = e4m3, 1 = e5m2.  x and out are contiguous [rows, cols] bf16.
+LLMB_API int llmb_fp8_block_fake_quant(void* out, const void* x, int rows, int cols, int mode, int fmt, cudaStream_t st) {
+  auto* o = (__nv_bfloat16*)out; auto* in = (const __nv_bfloat16*)x;
+  if (mode == 0) {
+    if (cols % 128) return LLMB_ERR_BAD_ARG;
+    const long long nb = (long long)rows * cols / 128;
+    const unsigned grid = (unsigned)ceil_div_ll(nb * 16, 256);
+    if (fmt == 0) fp8_block_row_kernel<0><<<grid, 256, 0, st>>>(o, in, nb); else fp8_block_row_kernel<1><<<grid, 256, 0, st>>>(o, in, nb);
+  } else if (mode == 1) {
+    if (rows % 128 || cols % 8) return LLMB_ERR_BAD_ARG;
+    const unsigned grid = (unsigned)ceil_div_ll((long long)(rows / 128) * (cols / 8), 128);
+    if (fmt == 0) fp8_block_col_kernel<0><<<grid, 128, 0, st>>>(o, in, rows, cols); else fp8_block_col_kernel<1><<<grid, 128, 0, st>>>(o, in, rows, cols);
+  } else if (mode == 2) {
+    if (rows % 128 || cols % 128) return LLMB_ERR_BAD_ARG;
+    const unsigned grid = (unsigned)((rows / 128) * (cols / 128));
+    if (fmt == 0) fp8_block_tile_kernel<0><<<grid, 256, 0, st>>>(o, in, rows, cols); else fp8_block_tile_kernel<1><<<grid, 256, 0, st>>>(o, in, rows, cols);
+  } else return LLMB_ERR_BAD_ARG;
+  return (int)cudaGetLastError();
+}
+
 LLMB_API long long llmb_nvfp4_scale_bytes(long long outer, long long K, int swizzled) {
   const long long kb = K / 16;
   if (!swizzled) return outer * kb;

@@ -266,12 +266,12 @@ class GPT2:
 
     # ------------------------------------------------------------------ precision dispatch of the 4 linear sites
     def _site_mode(self, site: str, layer: int) -> str:
-        """bf16 | fp8 | fp4 for one linear site (``train_gpt2.mojo:287-347``: FP8 covers the four
+        """bf16 | fp8 | fp8b (per-128 block scales) | fp4 for one linear site (``train_gpt2.mojo:287-347``: FP8 covers the four
         linear layers of every block; NVFP4 covers only the MLP pair of layers [first, L-offset),
         the remaining sites of an fp4 run stay in bf16; LM head and attention are never low precision)."""
         pr = self.precision
         if pr.name == "fp8" and site in pr.fp8_sites:
-            return "fp8"
+            return "fp8b" if pr.fp8_block_scales else "fp8"
         if pr.name == "fp4" and site in ("fc", "fcproj") and pr.layer_in_fp4_range(layer, self.config.num_layer):
             return "fp4"
         return "bf16"
@@ -281,6 +281,9 @@ class GPT2:
         if mode == "fp8":
             from ..ops import lowp
             lowp.matmul_fwd_fp8(out, inp, weight, bias, self.lowp.site(site, layer), **kw)
+        elif mode == "fp8b":
+            from ..ops import lowp
+            lowp.matmul_fwd_fp8_block(out, inp, weight, bias, **kw)
         elif mode == "fp4":
             from ..ops import lowp
             lowp.matmul_fwd_fp4(out, inp, weight, bias, **kw)
@@ -292,6 +295,9 @@ class GPT2:
         if mode == "fp8":
             from ..ops import lowp
             lowp.matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, self.lowp.site(site, layer), **kw)
+        elif mode == "fp8b":
+            from ..ops import lowp
+            lowp.matmul_bwd_fp8_block(dinp, dweight, dbias, dout, inp, weight, **kw)
         elif mode == "fp4":
             from ..ops import lowp
             lowp.matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, rht=self.precision.fp4_rht,

@@ -237,7 +237,7 @@ def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> 
 
 
 def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> None:
-    """dinp = dout·W (⊙ gelu'(gelu_pre)); dweight += doutᵀ·inp; dbias += Σ_rows dout.
+    """dinp = dout·W (⊙ gelu'(gelu_pre)); dweight += doutᵀ·inp; dbias += Σ_rows dout (each output may be None).
 
     dweight / dbias are fp32 accumulators (llmm/matmul.mojo:3512-3563, DGELU epilogue :2789-2938)."""
     OC, C = weight.shape
@@ -252,7 +252,8 @@ def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> Non
                 gemm(di, d, weight, b_mn=True, epi=EPI_DGELU, aux=gelu_pre.view(rows, C), kind=kind)
             else:
                 gemm(di, d, weight, b_mn=True, epi=EPI_NONE, kind=kind)
-        gemm(dweight.view(OC, C), d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), kind=kind)
+        if dweight is not None:
+            gemm(dweight.view(OC, C), d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), kind=kind)
         if dbias is not None:
             dbias_reduce(dbias, d)
         return
@@ -261,7 +262,8 @@ def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> Non
         if gelu_pre is not None:
             g = g.float() * _gelu_grad_t(gelu_pre.view(rows, C).float())
         dinp.view(rows, C).copy_(g)
-    dweight.view(OC, C).add_((d.t() @ x).float())
+    if dweight is not None:
+        dweight.view(OC, C).add_((d.t() @ x).float())
     if dbias is not None:
         dbias += d.float().sum(0)
 

@@ -45,6 +45,7 @@ _SIGS = {
     "llmb_gemm_set_pair_mode": [c_int],
     "llmb_amax": [c_p, c_p, c_ll, c_int, c_p],
     "llmb_amax_rht": [c_p, c_p, c_int, c_int, c_int, c_int, c_p],
+    "llmb_fp8_block_fake_quant": [c_p, c_p, c_int, c_int, c_int, c_int, c_p],
     "llmb_amax_state_floats": [],
     "llmb_amax_update": [c_p, c_p, c_f, c_f, c_p],
     "llmb_quantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_int, c_p],

@@ -24,6 +24,7 @@ import torch
 from . import (EPI_ACC_F32, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESID, EPI_DGELU, EPI_NONE, _count, _gelu_grad_t, _gelu_t,
                _splits_for, dbias_reduce, gemm, scratch)
 from ._lib import check, dtype_code, lib, ptr, stream
+from . import matmul_fwd as ops_matmul_fwd, matmul_bwd as ops_matmul_bwd
 
 E4M3, E5M2 = 0, 1
 FMT_MAX = {E4M3: 448.0, E5M2: 57344.0}
@@ -352,3 +353,66 @@ def matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None, rh
         dweight.view(OC, C).add_((dd.float().t() @ dx.float()) * alpha)
         if dbias is not None:
             dbias += d.float().sum(0)
+
+
+# ------------------------------------------------------------------------------ FP8 with per-128 block scales
+def fp8_block_fake_quant(x: torch.Tensor, mode: int, fmt: int = E4M3) -> torch.Tensor:
+    """x [rows, cols] → same shape holding fp8(x / s)·s with one power-of-two scale s = 2^ceil(log2(amax / fmt_max))
+    per block.  ``mode`` 0: 1×128 blocks along the columns, 1: 128×1 blocks along the rows, 2: 128×128 blocks.
+    Power-of-two scales keep value × scale exactly representable in bf16, so a GEMM on these tensors has the
+    numerics of a block-scaled FP8 GEMM with fp32 accumulation (the per-128 scaling that the fp8 configuration of
+    the benchmark asks for; the reference itself scales per tensor, ``llmm/lowp.mojo:89-99``)."""
+    rows, cols = x.shape
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        xc = x.contiguous()
+        out = torch.empty_like(xc)
+        check(lib().llmb_fp8_block_fake_quant(ptr(out), ptr(xc), rows, cols, mode, fmt, stream()), "fp8_block_fake_quant")
+        _count()
+        return out
+    xf = x.float()
+    if mode == 0:
+        b = xf.reshape(rows, cols // 128, 128)
+        amax = b.abs().amax(dim=-1, keepdim=True)
+    elif mode == 1:
+        b = xf.reshape(rows // 128, 128, cols)
+        amax = b.abs().amax(dim=1, keepdim=True)
+    else:
+        b = xf.reshape(rows // 128, 128, cols // 128, 128)
+        amax = b.abs().amax(dim=(1, 3), keepdim=True)
+    ratio = amax / FMT_MAX[fmt]
+    s = torch.where(amax > 0, torch.exp2(torch.ceil(torch.log2(ratio.clamp_min(1e-45)))), torch.ones_like(amax))
+    dt = torch.float8_e4m3fn if fmt == E4M3 else torch.float8_e5m2
+    q = (b / s).clamp(-FMT_MAX[fmt], FMT_MAX[fmt]).to(dt).float() * s
+    return q.reshape(rows, cols).to(x.dtype)
+
+
+def fp8_block_usable(rows: int, C: int, OC: int) -> bool:
+    return rows % 128 == 0 and C % 128 == 0 and OC % 128 == 0
+
+
+def matmul_fwd_fp8_block(out, inp, weight, bias, *, pre_gelu=None, residual=None) -> None:
+    """Block-scaled FP8 forward: e4m3 activations in 1×128 blocks along the contraction, e4m3 weights in 128×128
+    blocks; the product runs on the bf16 tensor path (exact, see ``fp8_block_fake_quant``)."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    if not fp8_block_usable(rows, C, OC):
+        return ops_matmul_fwd(out, inp, weight, bias, pre_gelu=pre_gelu, residual=residual)
+    dx = fp8_block_fake_quant(inp.reshape(rows, C), 0, E4M3)
+    dw = fp8_block_fake_quant(weight, 2, E4M3)
+    ops_matmul_fwd(out, dx, dw, bias, pre_gelu=pre_gelu, residual=residual)
+
+
+def matmul_bwd_fp8_block(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> None:
+    """Block-scaled FP8 backward: the output gradient is e5m2 (1×128 along OC for dinp, 128×1 along the rows for
+    dW), the saved input e4m3 in 128×1 blocks along the rows, the weight e4m3 in 128×128 blocks."""
+    OC, C = weight.shape
+    rows = inp.numel() // C
+    if not fp8_block_usable(rows, C, OC):
+        return ops_matmul_bwd(dinp, dweight, dbias, dout, inp, weight, gelu_pre=gelu_pre)
+    d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
+    if dinp is not None:
+        ops_matmul_bwd(dinp, None, None, fp8_block_fake_quant(d, 0, E5M2), x, fp8_block_fake_quant(weight, 2, E4M3), gelu_pre=gelu_pre)
+    ops_matmul_bwd(None, dweight, None, fp8_block_fake_quant(d, 1, E5M2), fp8_block_fake_quant(x, 1, E4M3), weight)
+    if dbias is not None:
+        from . import dbias_reduce
+        dbias_reduce(dbias, d)

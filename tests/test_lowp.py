@@ -12,6 +12,7 @@ from llm_mojo_b200.models import GPT2
 from llm_mojo_b200.ops import lowp
 
 CFG = GPT2Config(max_seq_len=32, vocab_size=60, num_layer=6, num_heads=2, channels=32, padded_vocab_size=64)
+CFG_BLOCK = GPT2Config(max_seq_len=64, vocab_size=120, num_layer=3, num_heads=2, channels=128, padded_vocab_size=128)
 
 
 class _Fp32Storage(Precision):
@@ -88,14 +89,37 @@ def test_nvfp4_stochastic_rounding_is_unbiased():
     assert abs((det.float() * ts)[:, 1:].mean().item() - 0.7) > 0.02       # RNE alone is biased here
 
 
-@pytest.mark.parametrize("name,floor", [("fp8", 0.99), ("fp4", 0.93)])
+def test_fp8_block_scales_are_powers_of_two_and_values_lie_on_the_fp8_grid():
+    torch.manual_seed(1)
+    x = torch.randn(256, 384) * torch.logspace(-3, 3, 384)          # wide dynamic range across the columns
+    for mode in (0, 1, 2):
+        for fmt, dt in ((lowp.E4M3, torch.float8_e4m3fn), (lowp.E5M2, torch.float8_e5m2)):
+            q = lowp.fp8_block_fake_quant(x, mode, fmt)
+            # re-quantising is the identity: every value is scale x an fp8 number with the block's own scale
+            assert torch.equal(lowp.fp8_block_fake_quant(q, mode, fmt), q)
+            rel = ((q - x).norm() / x.norm()).item()
+            assert rel < (0.04 if fmt == lowp.E4M3 else 0.08), (mode, fmt, rel)
+            assert torch.equal(q.bfloat16().float(), q)               # exactly representable in bf16
+    # a per-tensor scale loses the small columns entirely; block scales keep them
+    small = x[:, :64]
+    per_tensor = (x / (x.abs().max() / 448)).to(torch.float8_e4m3fn).float() * (x.abs().max() / 448)
+    assert (per_tensor[:, :64] == 0).float().mean() > 0.5
+    assert ((lowp.fp8_block_fake_quant(x, 0)[:, :64] - small).norm() / small.norm()).item() < 0.04
+
+
+@pytest.mark.parametrize("name,floor", [("fp8", 0.99), ("fp8b", 0.99), ("fp4", 0.93)])
 def test_cross_precision_gradient_gate(name, floor):
     """Per-tensor cosine / relative-L2 of the low-precision gradients against the full-precision build."""
-    x, y = _batch()
-    ref = GPT2(CFG, "fp32", "cpu")
+    cfg = CFG_BLOCK if name == "fp8b" else CFG               # block scaling needs dimensions that are multiples of 128
+    g = torch.Generator().manual_seed(0)
+    t = torch.randint(0, cfg.vocab_size, (2, cfg.max_seq_len + 1), generator=g, dtype=torch.int32)
+    x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
+    ref = GPT2(cfg, "fp32", "cpu")
     ref.forward(x, y); ref.backward()
-    m = GPT2(CFG, _Fp32Storage(name), "cpu")
+    m = GPT2(cfg, _Fp32Storage(name), "cpu")
     m.forward(x, y); m.backward()
+    if name == "fp8b":
+        assert m._site_mode("qkv", 0) == "fp8b" and m._site_mode("fcproj", 2) == "fp8b"
     assert abs(m.read_loss() - ref.read_loss()) < 0.02
     rels = []
     for n_, g in m.g.items():
@@ -229,3 +253,34 @@ def test_low_precision_model_gradients_on_gpu(name, floor):
         assert cos > floor, (n_, cos)
     from llm_mojo_b200.ops import _lib
     assert _lib.read_status() == 0
+
+
+@gpu
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("fmt", [lowp.E4M3, lowp.E5M2])
+def test_fp8_block_kernel_matches_emulation(mode, fmt):
+    torch.manual_seed(2)
+    x = (torch.randn(256, 384) * torch.logspace(-2, 2, 384)).bfloat16()
+    want = lowp.fp8_block_fake_quant(x.float(), mode, fmt)
+    got = lowp.fp8_block_fake_quant(x.cuda(), mode, fmt).float().cpu()
+    assert torch.equal(got, want.bfloat16().float())
+
+
+@gpu
+def test_fp8_block_training_step_on_gpu():
+    from llm_mojo_b200.config import Precision
+    cfg = GPT2Config(max_seq_len=128, vocab_size=1000, num_layer=2, num_heads=2, channels=128, padded_vocab_size=1024)
+    g = torch.Generator().manual_seed(0)
+    t = torch.randint(0, cfg.vocab_size, (2, 129), generator=g, dtype=torch.int32)
+    x, y = t[:, :-1].contiguous(), t[:, 1:].contiguous()
+    ref = GPT2(cfg, "bf16", "cuda")
+    m = GPT2(cfg, Precision("fp8b"), "cuda")
+    assert m._site_mode("fc", 1) == "fp8b"
+    losses = []
+    for model in (ref, m):
+        model.forward(x, y); model.backward()
+        losses.append(model.read_loss())
+    assert abs(losses[0] - losses[1]) < 0.05
+    for n_ in ("qkvw", "fcw", "fcprojw", "wte"):
+        a, b = m.g[n_].flatten().float(), ref.g[n_].flatten().float()
+        assert torch.nn.functional.cosine_similarity(a, b, dim=0).item() > 0.98, n_
