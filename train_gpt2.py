@@ -5,7 +5,7 @@ Same flags as the reference binary (``train_gpt2.mojo:6649-6777``): -i -j -e -o 
 -k -u -q -c -v -m -s -g -a -x -z -pn -pr, and the environment variables RANK, WORLD_SIZE,
 ZERO_STAGE, LLMM_OUTPUT_DIR, LLMM_SAVE_EVERY, LLMM_USE_CPU, LLMM_RECOMPUTE, LLMM_MEM_REPORT,
 LLMM_TRACE.  Axes that are compile-time defines in the reference are runtime options here:
-``--precision fp32|tf32|bf16|fp8|fp4``, ``--synthetic``, ``--comm p2p|nccl|gloo``.
+``--precision fp32|tf32|bf16|fp8|fp8b|fp4``, ``--synthetic``, ``--comm p2p|nccl|gloo``.
 
 Multi-GPU: ``torchrun --nproc-per-node N train_gpt2.py -z 1 ...`` (rank/world from the env), or
 ``-pn N`` on a single command line, which re-launches this script under torchrun.
@@ -42,7 +42,7 @@ Options (mirroring Karpathy's train_gpt2.cu):
   -z <int>    zero_stage, ZeRO optimization stage 0/1/2/3 (default 0)
   -pn <int>   num_processes / world_size (default = 1)
   -pr <int>   process_rank (default = 0)
-  --precision <fp32|tf32|bf16|fp8|fp4>   (default bf16 on GPU, fp32 on CPU)
+  --precision <fp32|tf32|bf16|fp8|fp8b|fp4>   (default bf16 on GPU, fp32 on CPU; fp8b = fp8 with per-128 block scales)
   --synthetic 1     train on uniform random tokens (no data files needed)
   --comm <auto|p2p|nccl|gloo>  collective backend (default auto: peer-memory kernels on GPUs)
   --config <zero json>  read {zero_stage, world_size, precision, train_flags} from a zero/zeroN.json
