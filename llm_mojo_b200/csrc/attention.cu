@@ -7,18 +7,21 @@
 // permutes), keep S/P and the running output in TMEM / shared memory, and store only the
 // output [B,T,C] plus one log-sum-exp per row.
 //
-// Forward  : CTA = 128 query rows of one (batch, head), 256 threads: two threads share a row, each
-//            owning one 64-column half of the score tile (warps w and w+4 read the same TMEM lanes).
-//            S = Q K^T (tcgen05, 128x128 fp32 in TMEM) -> online softmax in registers ->
-//            P (bf16, swizzled smem) -> O += P V (tcgen05, O in TMEM, rescaled in place).
-// Backward : two deterministic kernels (no atomics).
-//   dK/dV  : CTA = 128 key rows; loops over 64-row query chunks:  S^T = K Q^T, dP^T = V dO^T,
-//            P^T and dS^T to smem, dV += P^T dO, dK += dS^T Q   (accumulators in TMEM).
-//   dQ     : CTA = 128 query rows; loops over 64-row key chunks:   S = Q K^T, dP = dO V^T,
-//            dS to smem, dQ += dS K.
+// Default kernels (persistent, warp-specialised; described where they are defined below):
+//   attn_fwd2_kernel      one CTA per SM, two independent tile streams, 64-key chunks
+//   attn_bwd_dkv2_kernel  dK/dV per 128-key tile over 64-row query chunks   } two deterministic kernels,
+//   attn_bwd_dq2_kernel   dQ per 128-row query tile over 64-key chunks      } no atomics
+// The first-generation kernels are kept as comparators (LLMB_ATTN_FWD=1 / LLMB_ATTN_BWD=1): one CTA per 128-row
+// tile, 256 threads, the phases MMA -> softmax -> MMA run one after another:
+//   Forward  : two threads share a row, each owning one 64-column half of the 128-key score tile;
+//              S = Q K^T (tcgen05, fp32 in TMEM) -> online softmax in registers -> P (bf16, swizzled smem)
+//              -> O += P V (tcgen05, O in TMEM, rescaled in place).
+//   dK/dV    : CTA = 128 key rows; loops over 64-row query chunks:  S^T = K Q^T, dP^T = V dO^T,
+//              P^T and dS^T to smem, dV += P^T dO, dK += dS^T Q   (accumulators in TMEM).
+//   dQ       : CTA = 128 query rows; loops over 64-row key chunks:   S = Q K^T, dP = dO V^T,
+//              dS to smem, dQ += dS K.
 // The MN-major UMMA descriptor lets the same TMA-written tile serve as a K-major operand of
-// one product and as the transposed operand of the next.  Two CTAs fit per SM (<= 112 KB of
-// shared memory, 256 TMEM columns each) so one CTA's MMAs overlap the other's softmax.
+// one product and as the transposed operand of the next.
 // LSE is stored in the log2 domain of the scaled scores: lse2 = m + log2(sum 2^(s2 - m)).
 #include "tc05.cuh"
 using namespace llmb;

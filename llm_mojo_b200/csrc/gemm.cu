@@ -739,7 +739,7 @@ template <> struct KindTraits<KIND_TF32> { static constexpr int ESZ = 4; static 
 template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ESZ = 1; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
 
 int g_dbg_mn_lbo = -1, g_dbg_mn_sbo = -1;   // test hooks: override the MN-major descriptor strides
-GatherArgs g_pending_gather{};                // consumed (and cleared) by the next llmb_gemm call of this process
+thread_local GatherArgs g_pending_gather{};   // armed by llmb_gemm_set_gather, consumed (and cleared) by the calling thread's next llmb_gemm
 int g_pair_mode = -1;                         // -1: read LLMB_GEMM_PAIR once; 0: single-CTA tiles; 1: CTA-pair tiles
 
 bool pair_mode() {
@@ -903,7 +903,7 @@ LLMB_API int llmb_gemm(void* D, const void* A, const void* B, const void* bias, 
   return LLMB_ERR_BAD_ARG;
 }
 
-// Arms the NEXT llmb_gemm call of this process to gather its A matrix from W ranks (see GatherArgs): A must be the
+// Arms the calling thread's NEXT llmb_gemm call to gather its A matrix from W ranks (see GatherArgs): A must be the
 // local [W*n, K] buffer, n a multiple of 256; peer_src[r] = address of chunk r in rank r's buffer; flags = this
 // rank's flag words; counts = 16 local counters that the caller zeroes (stream-ordered) before the GEMM.
 LLMB_API void llmb_gemm_set_gather(void* const* peer_src, void* local, const void* flags, unsigned* counts, long long chunk_bytes,
