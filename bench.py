@@ -9,7 +9,8 @@ synthetic uniform tokens.  The global batch is fixed, so per-GPU work shrinks wi
 Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks) with the
 tokens already resident on the GPU; `e2e` runs the same steps through the public `Trainer` API
 with the per-step pinned-host→device token copies and the device→host loss read inside the
-timed region.  `--impl reference` is the reference arm, `--impl torch` is a plain
+timed region.  `--impl reference` is the reference arm (the reference is a Mojo program and cannot be built
+without its compiler, so the arm reports itself unavailable), `--impl torch` is a plain
 PyTorch (cuBLAS + SDPA + NCCL DDP) comparator of the same model for on-box context.
 """
 from __future__ import annotations
@@ -23,7 +24,7 @@ import threading
 import time
 
 BASELINE_TOK_S_PER_GPU = 173010.0      # reference's best published per-GPU bf16 124M number (B=64, T=1024)
-REFERENCE_UNAVAILABLE = ("pip install of /root/reference fails (no setup.py/pyproject.toml); its only non-Mojo "
+REFERENCE_UNAVAILABLE = ("pip install of the reference tree fails (no setup.py/pyproject.toml); its only non-Mojo "
                          "trainer train_gpt2.py downloads the GPT-2 BPE vocabulary at start-up and there is no network")
 
 

@@ -17,8 +17,7 @@ CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libllmb200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
-# Sources that must not travel to (or be linked for) multi-GPU runs are listed in
-# .gpurunignore.multi; none exist at present, every kernel here is multicast-free.
+# Every kernel here is free of cluster-multicast TMA loads, so one library serves 1-GPU and multi-GPU runs.
 
 
 def _nvcc() -> str:
