@@ -85,6 +85,31 @@ def layer_calls(C: int, rows: int, Vp: int) -> None:
         print(f"bwd {name:8s} (dinp{'+dGELU' if gelu_pre is not None else ''}, dW, dbias) {ms:.3f} ms {4.0 * rows * OC * K / ms / 1e9:6.0f} TF/s")
 
 
+def lowp_rows(shapes, rows: int) -> None:
+    """bf16, fp8 and NVFP4 forward products of the same shapes (operands quantised outside the timed region)."""
+    from llm_mojo_b200.ops import lowp
+    one = torch.ones(1, device="cuda")
+    for name, N, K in shapes:
+        A = torch.randn(rows, K, device="cuda").bfloat16()
+        W = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        D = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * rows * N * K
+        ms = timed_flushed(lambda: ops.gemm(D, A, W))
+        print(f"{name:8s} {rows}x{N}x{K}  bf16  {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+        qa = torch.empty(rows, K, dtype=torch.uint8, device="cuda")
+        qw = torch.empty(N, K, dtype=torch.uint8, device="cuda")
+        lowp.quantize_fp8(qa, A, one, lowp.E4M3)
+        lowp.quantize_fp8(qw, W, one * 16, lowp.E4M3)
+        ms = timed_flushed(lambda: ops.gemm(D, qa, qw, alpha=one, kind=2, a_fmt=lowp.E4M3, b_fmt=lowp.E4M3))
+        print(f"   fp8 (per-tensor scale, CTA-pair 256x256 tiles)        {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+        if K % 32 == 0:
+            _, tsa, pa, sa = lowp.nvfp4_fake_quant(A, axis=1, block_rows=1, want_packed=True, want_deq=False)
+            _, tsw, pw, sw = lowp.nvfp4_fake_quant(W, axis=1, block_rows=16, want_packed=True, want_deq=False)
+            al = tsa * tsw
+            ms = timed_flushed(lambda: ops.gemm_nvfp4(D, pa, sa, pw, sw, K, alpha=al))
+            print(f"   nvfp4 (block-scaled tensor path, 128x128 tiles)       {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="d12")
@@ -92,6 +117,7 @@ def main(argv=None) -> int:
     ap.add_argument("-t", type=int, default=1024)
     ap.add_argument("--modes", default="1,0", help="1 = CTA-pair tiles, 0 = single-CTA tiles")
     ap.add_argument("--layer", action="store_true", help="time the fused per-layer calls with an L2 flush between launches")
+    ap.add_argument("--lowp", action="store_true", help="forward GEMMs on the fp8 (kind::f8f6f4) and NVFP4 (kind::mxf4nvf4) tensor paths")
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("bench_gemm needs a GPU")
@@ -107,6 +133,10 @@ def main(argv=None) -> int:
     if os.path.exists(pk):
         peak = json.load(open(pk)).get("bf16_tflops")
     shapes = [("qkv", 3 * C, C), ("attproj", C, C), ("fc", 4 * C, C), ("fcproj", C, 4 * C), ("lm_head", cfg.padded_vocab_size, C)]
+    if a.lowp:
+        lowp_rows(shapes[:4], rows)
+        print("kernel status", _lib.read_status())
+        return 0
     for name, N, K in shapes:
         A = torch.randn(rows, K, device="cuda").bfloat16()
         W = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()

@@ -158,13 +158,13 @@ __device__ __forceinline__ void epi4(const GemmParams& p, float (&v)[4], int row
   else *reinterpret_cast<uint2*>(dp) = o;
 }
 
-// One epilogue warp drains its 32 rows x BN columns of accumulator `tacc` (TMEM address incl. lane quarter).
-template <int EPI>
+// One epilogue warp drains its 32 rows x NCOLS columns of accumulator `tacc` (TMEM address incl. lane quarter).
+template <int EPI, int NCOLS = BN>
 __device__ __forceinline__ void epilogue_warp(const GemmParams& p, uint32_t tacc, unsigned char* stage, int row_base, int n0,
                                               float alpha, int lane) {
   const int rsub = lane >> 3, cl = lane & 7;
 #pragma unroll 1
-  for (int s = 0; s < BN / 64; ++s) {
+  for (int s = 0; s < NCOLS / 64; ++s) {
     if (n0 + s * 64 >= p.N) break;                      // warp-uniform
     uint32_t r0[32], r1[32];
     tmem_ld32(tacc + s * 64, r0);
@@ -886,6 +886,168 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   }
   return LLMB_ERR_BAD_ARG;
 }
+// ------------------------------------------------------------------------------------------------
+// Native NVFP4 GEMM:  D[M,N] = epi(alpha * sum_k (A[m,k] sfa[m,k/16]) (B[n,k] sfb[n,k/16])).
+// A and B are packed e2m1 (two values per byte, even index in the low nibble), K-major, K/2 bytes per
+// row; the ue4m3 block scales come in 128-row x 4-block atoms of 512 bytes (byte (r % 32) * 16 +
+// (r / 32) * 4 + block), atoms of one row block contiguous along K: the layout the tensor core's
+// scale path wants, so an atom goes from global to shared memory as one bulk copy and from there to
+// tensor memory as one tcgen05.cp.  One CTA per SM owns 128 x 128 tiles: two fp32 accumulators of 128
+// TMEM columns each (the epilogue of one tile overlaps the MMAs of the next), 16 columns of A scales
+// and 16 of B scales for the four k-steps (64 values each) of a stage.  A stage is 128 bytes = 256
+// values along K of both operands plus 2 KB of scales per operand.  Same warp roles as gemm_kernel.
+constexpr int NV_BN = 128;
+constexpr int NV_STAGES = 5;
+constexpr int NV_TILE = 128 * ROW_BYTES;               // 16 KB: 128 rows x 256 e2m1 values
+constexpr int NV_SF = 4 * 512;                         // scales of 128 rows x 16 blocks
+constexpr int NV_STAGE_BYTES = 2 * NV_TILE + 2 * NV_SF;
+constexpr int NV_SMEM_BYTES = NV_STAGES * NV_STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + 256;
+constexpr int NV_BKE = 256;                            // K values per stage
+constexpr uint32_t NV_SFA_COL = 256, NV_SFB_COL = 272; // TMEM columns behind the two accumulators
+
+struct Nvfp4Params {
+  GemmParams g;                                         // epilogue fields, tile counts, split-K (operand fields unused)
+  const unsigned char* sfa; const unsigned char* sfb;   // scale atoms of A ([ceil(M/128)][atoms_k][512]) and of B
+  int atoms_k;                                          // ceil(K / 64)
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Nvfp4Params q) {
+  const GemmParams& p = q.g;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* epi_stage = smem + NV_STAGES * NV_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 4 * EPI_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + NV_STAGES;
+  uint64_t* tfull_bar = empty_bar + NV_STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tmem_alloc<512>(tmem_slot);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_split = p.m_tiles * p.n_tiles;
+  const int total_units = tiles_per_split * p.splits;
+  auto unit_coords = [&](int unit, int& m_blk, int& n_blk, int& kb0, int& kb1) {
+    int split = unit / tiles_per_split, t = unit % tiles_per_split;
+    int band_sz = BAND * p.n_tiles;
+    int b = t / band_sz, r = t % band_sz;
+    int m_in_band = min(BAND, p.m_tiles - b * BAND);
+    m_blk = b * BAND + r % m_in_band;
+    n_blk = r / m_in_band;
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer: operand tiles by TMA, scale atoms by bulk copy
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x) {
+        int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+          unsigned char* sa = smem + stage * NV_STAGE_BYTES;
+          const int atoms = min(4, q.atoms_k - kb * 4);
+          const uint32_t sf_bytes = (uint32_t)atoms * 512u;
+          mbar_expect_tx(&full_bar[stage], 2 * NV_TILE + 2 * sf_bytes);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * ROW_BYTES, m_blk * BM);
+          tma_load_2d(sa + NV_TILE, &tmB, &full_bar[stage], kb * ROW_BYTES, n_blk * NV_BN);
+          bulk_load_1d(sa + 2 * NV_TILE, q.sfa + ((size_t)m_blk * q.atoms_k + (size_t)kb * 4) * 512, sf_bytes, &full_bar[stage]);
+          bulk_load_1d(sa + 2 * NV_TILE + NV_SF, q.sfb + ((size_t)n_blk * q.atoms_k + (size_t)kb * 4) * 512, sf_bytes, &full_bar[stage]);
+          if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer: scales to TMEM, then one MMA per 64 values of K
+    int stage = 0; uint32_t phase = 0;
+    int it = 0;
+    const uint64_t adesc0 = make_smem_desc(smem_u32(smem), 16, 1024, 2);
+    const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + NV_TILE, 16, 1024, 2);
+    const uint64_t sfa0 = make_sf_desc(smem_u32(smem) + 2 * NV_TILE);
+    const uint64_t sfb0 = make_sf_desc(smem_u32(smem) + 2 * NV_TILE + NV_SF);
+    const uint32_t idesc = make_idesc_nvfp4(BM, NV_BN);
+    const uint32_t sfa_t = tmem_base + NV_SFA_COL, sfb_t = tmem_base + NV_SFB_COL;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
+      int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { ok = false; break; }
+      fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * NV_BN;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
+        fence_after_sync();
+        const uint64_t soff = (uint64_t)(stage * (NV_STAGE_BYTES >> 4));
+        const int atoms = min(4, q.atoms_k - kb * 4);
+        if (elect_one()) {
+          for (int k = 0; k < atoms; ++k) {
+            tmem_cp_sf(sfa_t + 4 * k, sfa0 + soff + (uint64_t)(k * 32));
+            tmem_cp_sf(sfb_t + 4 * k, sfb0 + soff + (uint64_t)(k * 32));
+          }
+          for (int k = 0; k < atoms; ++k)
+            umma_nvfp4(d_tmem, adesc0 + soff + (uint64_t)(k * 2), bdesc0 + soff + (uint64_t)(k * 2), idesc, sfa_t + 4 * k, sfb_t + 4 * k,
+                       (kb > kb0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);               // operand tiles and scale atoms reusable once these have run
+        }
+        __syncwarp();
+        if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) break;
+      if (elect_one()) umma_commit(&tfull_bar[acc]);
+      __syncwarp();
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int qd = warp & 3;                // TMEM lane quarter this warp may access
+    int it = 0;
+    for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
+      int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+      fence_after_sync();
+      const float alpha = p.alpha ? *p.alpha : 1.0f;
+      epilogue_warp<EPI, NV_BN>(p, tmem_base + ((uint32_t)(qd * 32) << 16) + acc * NV_BN, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                                m_blk * BM + qd * 32, n_blk * NV_BN, alpha, lane);
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { fence_after_sync(); tmem_dealloc<512>(tmem_base); }
+}
+
+template <int EPI>
+int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const Nvfp4Params& q, int grid, cudaStream_t st) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, NV_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  gemm_nvfp4_kernel<EPI><<<grid, NUM_THREADS, NV_SMEM_BYTES, st>>>(ta, tb, q);
+  return (int)cudaGetLastError();
+}
 }  // namespace
 
 // D[M,N] = epi(alpha * A·B^T).  a_mn/b_mn = 1 when the operand is stored [K, M] / [K, N].
@@ -917,3 +1079,48 @@ LLMB_API void llmb_gemm_set_gather(void* const* peer_src, void* local, const voi
 LLMB_API void llmb_gemm_debug_mn_strides(int lbo_bytes, int sbo_bytes) { g_dbg_mn_lbo = lbo_bytes; g_dbg_mn_sbo = sbo_bytes; }
 // 0: single-CTA 128x256 tiles, 1: CTA-pair 256x256 tiles (default; env LLMB_GEMM_PAIR=0 selects the former)
 LLMB_API void llmb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
+
+// D[M,N] = epi(alpha * (A sfa)(B sfb)^T) on the NVFP4 tensor path (`kind::mxf4nvf4`, 16-value blocks, ue4m3 scales).
+// A [M, K/2] and B [N, K/2]: packed e2m1 bytes as llmb_nvfp4_quantize writes them (K % 32 == 0); sfa / sfb: its
+// swizzled scale buffers (llmb_nvfp4_scale_bytes(rows, K, 1) bytes, zero where no block exists).  D is bf16
+// except for epi 4 / 6 (fp32 accumulate with split-K / fp32 store); bias and aux are bf16.
+LLMB_API int llmb_gemm_nvfp4(void* D, const void* A, const void* B, const void* sfa, const void* sfb, const void* bias, void* aux,
+                             const float* alpha, int M, int N, int K, long long ldd, long long ldaux, int epi, int splits,
+                             int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 || N % 8) return LLMB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D) |
+       reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(sfb)) & 15) return LLMB_ERR_BAD_ARG;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)(K / 2), (uint64_t)(K / 2), BM, ROW_BYTES);
+  if (rc) return 1000 + rc;
+  rc = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)(K / 2), NV_BN, ROW_BYTES);
+  if (rc) return 1000 + rc;
+  Nvfp4Params q{};
+  GemmParams& p = q.g;
+  p.D = D; p.bias = bias; p.aux = aux; p.alpha = alpha;
+  p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldaux = ldaux;
+  p.bke = NV_BKE;
+  p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, NV_BN);
+  p.kb_total = ceil_div(K, NV_BKE);
+  if (splits < 1) splits = 1;
+  if (splits > p.kb_total) splits = p.kb_total;
+  if (epi != EPI_ACC_F32) splits = 1;
+  p.kb_per_split = ceil_div(p.kb_total, splits);
+  p.splits = ceil_div(p.kb_total, p.kb_per_split);
+  p.status = status;
+  p.bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
+  q.sfa = (const unsigned char*)sfa; q.sfb = (const unsigned char*)sfb;
+  q.atoms_k = ceil_div(K, 64);
+  const long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
+  const int grid = (int)(units < sm_count() ? units : sm_count());
+  switch (epi) {
+    case EPI_NONE: return launch_nvfp4<EPI_NONE>(ta, tb, q, grid, st);
+    case EPI_BIAS: return launch_nvfp4<EPI_BIAS>(ta, tb, q, grid, st);
+    case EPI_BIAS_GELU: return launch_nvfp4<EPI_BIAS_GELU>(ta, tb, q, grid, st);
+    case EPI_DGELU: return launch_nvfp4<EPI_DGELU>(ta, tb, q, grid, st);
+    case EPI_ACC_F32: return launch_nvfp4<EPI_ACC_F32>(ta, tb, q, grid, st);
+    case EPI_BIAS_RESID: return launch_nvfp4<EPI_BIAS_RESID>(ta, tb, q, grid, st);
+    case EPI_STORE_F32: return launch_nvfp4<EPI_STORE_F32>(ta, tb, q, grid, st);
+  }
+  return LLMB_ERR_BAD_ARG;
+}

@@ -189,6 +189,30 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// ---- block-scaled MMA (NVFP4: e2m1 operands, one ue4m3 scale per 16 elements along K) -------------
+// Instruction descriptor of the block-scaled kinds: [4,6) B scale id  [7,10) A format  [10,13) B format
+// [15] A major  [16] B major  [17,23) N >> 3  [23] scale format (0 = ue4m3, 1 = ue8m0)  [24,29) M >> 4
+// [29,31) A scale id  [31] K size (0 = 64 for 4-bit operands).  Accumulation is always fp32.
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) {
+  return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+// Shared-memory descriptor of one scale-factor atom: 32 rows of 16 bytes, no swizzle (8-row core matrices 128 B apart).
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) { return make_smem_desc(smem_addr, 16, 128, 0); }
+// Copies 32 rows x 16 bytes of shared memory into 4 TMEM columns of all four lane quarters (row r -> lane r of each
+// quarter): exactly the placement the block-scaled MMA expects for the scales of 128 rows x 4 blocks when the
+// shared-memory image is the 128 x 4 scale atom (byte (r % 32) * 16 + (r / 32) * 4 + block).  One thread issues;
+// the copy is ordered with this thread's earlier and later tcgen05.mma / tcgen05.cp.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= (A * sfa) (B * sfb)^T, M = 128, K = 64 e2m1 values per row; sfa / sfb: TMEM column addresses.
+__device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                           uint32_t sfb, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+
 
 // ------------------------------------------------------------------ CTA-pair (cta_group::2) forms
 // Two CTAs of a cluster of 2 run one 256-row MMA: each CTA stages its 128 rows of A and its

@@ -185,6 +185,17 @@ def gemm(D, A, B, *, a_mn=False, b_mn=False, epi=EPI_NONE, bias=None, aux=None, 
     _count()
 
 
+def gemm_nvfp4(D, qa, sfa, qb, sfb, K: int, *, epi=EPI_NONE, bias=None, aux=None, alpha=None, splits=1) -> None:
+    """Native NVFP4 GEMM (``tcgen05.mma.kind::mxf4nvf4``): D[M,N] = epi(alpha · (A·sfa)(B·sfb)ᵀ).  ``qa`` / ``qb`` are
+    the packed e2m1 bytes of A [M,K] and B [N,K] and ``sfa`` / ``sfb`` their swizzled ue4m3 block scales, as
+    ``nvfp4_fake_quant(..., want_packed=True)`` returns them (the cuBLASLt call of ``llmm/matmul.mojo:2038-2138``)."""
+    M, N = D.shape
+    check(lib().llmb_gemm_nvfp4(ptr(D), ptr(qa), ptr(qb), ptr(sfa), ptr(sfb), ptr(bias), ptr(aux), ptr(alpha), M, N, K,
+                                D.stride(0), aux.stride(0) if aux is not None else 0, epi, splits,
+                                ptr(status_word(D.device)), stream()), "gemm_nvfp4")
+    _count()
+
+
 def _tc_kind(t: torch.Tensor):
     """tcgen05 kind for a storage dtype: 0 (kind::f16, bf16 operands), 1 (kind::tf32, fp32 operands)."""
     if t.dtype == torch.bfloat16:
@@ -194,15 +205,15 @@ def _tc_kind(t: torch.Tensor):
     return None
 
 
-def _splits_for(M: int, N: int, K: int) -> int:
-    """Split-K factor for the dW GEMMs (256x256 tiles on 74 CTA pairs): the number of splits that minimises
-    waves x (k-blocks per unit + a fixed per-unit cost for the prologue and the fp32 red.add epilogue)."""
-    tiles = max(1, ((M + 255) // 256) * ((N + 255) // 256))
-    kb = (K + 63) // 64
-    clusters = 74
+def _splits_for(M: int, N: int, K: int, *, tile: int = 256, bk: int = 64, units: int = 74) -> int:
+    """Split-K factor for the dW GEMMs (by default 256x256 tiles on 74 CTA pairs, 64 values of K per stage): the
+    number of splits that minimises waves x (k-blocks per unit + a fixed per-unit cost for the prologue and the
+    fp32 red.add epilogue)."""
+    tiles = max(1, ((M + tile - 1) // tile) * ((N + tile - 1) // tile))
+    kb = (K + bk - 1) // bk
     best, best_cost = 1, None
     for s in range(1, max(1, min(16, kb // 8)) + 1):
-        waves = -(-tiles * s // clusters)
+        waves = -(-tiles * s // units)
         cost = waves * (kb / s + 24.0)
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost

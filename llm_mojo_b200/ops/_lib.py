@@ -41,6 +41,7 @@ _SIGS = {
     "llmb_sr_cast_bf16": [c_p, c_p, c_ll, c_ull, c_p],
     "llmb_gemm": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_int, c_int,
                   c_int, c_int, c_int, c_int, c_int, c_p, c_p],
+    "llmb_gemm_nvfp4": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int, c_p, c_p],
     "llmb_gemm_debug_mn_strides": [c_int, c_int],
     "llmb_gemm_set_pair_mode": [c_int],
     "llmb_amax": [c_p, c_p, c_ll, c_int, c_p],

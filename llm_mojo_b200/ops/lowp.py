@@ -17,12 +17,13 @@ throughput is that of the bf16 tensor path.  CPU tensors run an emulation of the
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
 
 from . import (EPI_ACC_F32, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESID, EPI_DGELU, EPI_NONE, _count, _gelu_grad_t, _gelu_t,
-               _splits_for, dbias_reduce, gemm, scratch)
+               _splits_for, dbias_reduce, gemm, gemm_nvfp4, scratch)
 from ._lib import check, dtype_code, lib, ptr, stream
 from . import matmul_fwd as ops_matmul_fwd, matmul_bwd as ops_matmul_bwd
 
@@ -237,10 +238,12 @@ def _e2m1_round(v: torch.Tensor, rnd: Optional[torch.Tensor]) -> torch.Tensor:
 
 def nvfp4_fake_quant(x: torch.Tensor, axis: int = 1, block_rows: int = 1, rht: bool = False, sr: bool = False,
                      seed: int = 0, stream_id: int = NVFP4_SR_STREAM, step: int = 0,
-                     want_packed: bool = False):
+                     want_packed: bool = False, want_deq: bool = True):
     """Quantise a 2-D tensor to NVFP4 along ``axis`` and return ``(deq, tensor_scale[, q, scales])``
     where ``deq`` (bf16, same layout as ``x``) holds value × block-scale and ``tensor_scale`` is the
-    fp32 second-level scale amax/(448·6) (``llmm/nvfp4_quant.mojo:528-724``)."""
+    fp32 second-level scale amax/(448·6) (``llmm/nvfp4_quant.mojo:528-724``).  ``q`` holds the packed e2m1 bytes
+    [outer, K/2] with the quantised axis innermost and ``scales`` the ue4m3 block scales in 128×4 atoms: the operands
+    of ``gemm_nvfp4``.  ``want_deq=False`` (GPU, with ``want_packed``) skips the bf16 image; ``deq`` is then None."""
     rows, cols = x.shape
     dev = x.device
     ts = torch.empty(1, dtype=torch.float32, device=dev)
@@ -257,7 +260,7 @@ def nvfp4_fake_quant(x: torch.Tensor, axis: int = 1, block_rows: int = 1, rht: b
             compute_amax(amax, src)
         L = lib()
         check(L.llmb_nvfp4_tensor_scale(ptr(ts), ptr(amax), stream()), "nvfp4_tensor_scale")
-        deq = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+        deq = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) if (want_deq or not want_packed) else None
         outer, K = (rows, cols) if axis == 1 else (cols, rows)
         q = torch.empty(outer * K // 2, dtype=torch.uint8, device=dev) if want_packed else None
         sc = torch.zeros(int(L.llmb_nvfp4_scale_bytes(outer, K, 1)), dtype=torch.uint8, device=dev) if want_packed else None
@@ -300,15 +303,39 @@ def _rht_along(x: torch.Tensor, axis: int) -> torch.Tensor:
     return hadamard16(x.t().contiguous()).t()
 
 
+def nvfp4_native(*dims: int) -> bool:
+    """True when the NVFP4 products run on the block-scaled tensor path (``gemm_nvfp4``) instead of the bf16 path
+    on dequantised operands: on by default on a GPU, ``LLMM_FP4_NATIVE=0`` selects the latter; every contraction
+    length in ``dims`` must be a multiple of 32 (16-byte rows of packed values)."""
+    return os.environ.get("LLMM_FP4_NATIVE", "1") not in ("0", "") and all(d % 32 == 0 for d in dims)
+
+
+def _qp(x, axis, block_rows, **kw):
+    """Packed NVFP4 operand: (bytes [outer, K/2], swizzled scales, tensor scale)."""
+    _, ts, q, sc = nvfp4_fake_quant(x, axis=axis, block_rows=block_rows, want_packed=True, want_deq=False, **kw)
+    return q, sc, ts
+
+
 def matmul_fwd_fp4(out, inp, weight, bias, *, pre_gelu=None, residual=None) -> None:
     """NVFP4 forward: activations 1x16 blocks, weights 16x16 blocks, RNE (``llmm/matmul.mojo:2038-2138``)."""
     OC, C = weight.shape
     rows = inp.numel() // C
     x = inp.reshape(rows, C)
+    o = out.view(rows, OC)
+    if out.is_cuda and nvfp4_native(C):
+        qx, sx, tsx = _qp(x, 1, 1)
+        qw, sw, tsw = _qp(weight, 1, 16)
+        alpha = tsx * tsw
+        if pre_gelu is not None:
+            gemm_nvfp4(o, qx, sx, qw, sw, C, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC), alpha=alpha)
+        elif residual is not None:
+            gemm_nvfp4(o, qx, sx, qw, sw, C, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC), alpha=alpha)
+        else:
+            gemm_nvfp4(o, qx, sx, qw, sw, C, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias, alpha=alpha)
+        return
     dx, tsx = nvfp4_fake_quant(x, axis=1, block_rows=1)
     dw, tsw = nvfp4_fake_quant(weight, axis=1, block_rows=16)
     alpha = tsx * tsw
-    o = out.view(rows, OC)
     if out.is_cuda:
         if pre_gelu is not None:
             gemm(o, dx, dw, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC), alpha=alpha)
@@ -328,6 +355,23 @@ def matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None, rh
     OC, C = weight.shape
     rows = inp.numel() // C
     d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
+    if dout.is_cuda and nvfp4_native(OC, rows):
+        # the packed operand of a product contracted over axis 0 is written transposed ([cols, rows/2]), so all three
+        # products are K-major x K-major on the block-scaled tensor path
+        if dinp is not None:
+            qd, sd, tsd = _qp(d, 1, 1, sr=sr, seed=seed, stream_id=NVFP4_SR_STREAM + 2, step=step)
+            qw, sw, tsw = _qp(weight, 0, 16)
+            gemm_nvfp4(dinp.view(rows, C), qd, sd, qw, sw, OC, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE,
+                       aux=gelu_pre.view(rows, C) if gelu_pre is not None else None, alpha=tsd * tsw)
+        usable_rht = rht and rows % 16 == 0
+        qd, sd, tsd = _qp(d, 0, 1, rht=usable_rht, sr=sr, seed=seed, stream_id=NVFP4_SR_STREAM + 3, step=step)
+        qx, sx, tsx = _qp(x, 0, 1, rht=usable_rht)
+        gemm_nvfp4(dweight.view(OC, C), qd, sd, qx, sx, rows, epi=EPI_ACC_F32,
+                   splits=_splits_for(OC, C, rows, tile=128, bk=256, units=148),
+                   alpha=tsd * tsx * ((1.0 / 16.0) if usable_rht else 1.0))
+        if dbias is not None:
+            dbias_reduce(dbias, d)
+        return
     if dinp is not None:
         dd, tsd = nvfp4_fake_quant(d, axis=1, block_rows=1, sr=sr, seed=seed, stream_id=NVFP4_SR_STREAM + 2, step=step)
         dw, tsw = nvfp4_fake_quant(weight, axis=0, block_rows=16)        # contraction runs over OC for dgrad

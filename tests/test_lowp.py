@@ -284,3 +284,76 @@ def test_fp8_block_training_step_on_gpu():
     for n_ in ("qkvw", "fcw", "fcprojw", "wte"):
         a, b = m.g[n_].flatten().float(), ref.g[n_].flatten().float()
         assert torch.nn.functional.cosine_similarity(a, b, dim=0).item() > 0.98, n_
+
+
+def _nvfp4_operands(M, N, K, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    a = (torch.randn(M, K, generator=g) * (1 + torch.arange(K) % 7)).bfloat16().cuda()
+    b = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    da, tsa, qa, sa = lowp.nvfp4_fake_quant(a, axis=1, block_rows=1, want_packed=True)
+    db, tsb, qb, sb = lowp.nvfp4_fake_quant(b, axis=1, block_rows=16 if N % 16 == 0 else 1, want_packed=True)
+    return da, qa, sa, db, qb, sb, tsa * tsb
+
+
+@gpu
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (200, 136, 1600), (128, 128, 64), (1024, 768, 3072)])
+def test_native_nvfp4_gemm_matches_fp32_product_of_dequantised_operands(M, N, K):
+    """tcgen05 kind::mxf4nvf4 on the packed operands == fp32 product of (value x block scale) x tensor scales."""
+    from llm_mojo_b200 import ops
+    da, qa, sa, db, qb, sb, alpha = _nvfp4_operands(M, N, K)
+    want = (da.float() @ db.float().t()) * alpha
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_nvfp4(out, qa, sa, qb, sb, K, alpha=alpha)
+    torch.cuda.synchronize()
+    err = (out.float() - want).norm() / want.norm()
+    assert err.item() < 4e-3, err.item()
+    # fp32 store: only the accumulation order differs
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm_nvfp4(out32, qa, sa, qb, sb, K, epi=ops.EPI_STORE_F32, alpha=alpha)
+    assert ((out32 - want).norm() / want.norm()).item() < 1e-5
+
+
+@gpu
+def test_native_nvfp4_gemm_epilogues_and_split_k():
+    from llm_mojo_b200 import ops
+    M, N, K = 384, 256, 8192
+    da, qa, sa, db, qb, sb, alpha = _nvfp4_operands(M, N, K, seed=1)
+    base = (da.float() @ db.float().t()) * alpha
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    pre = torch.empty_like(out)
+    ops.gemm_nvfp4(out, qa, sa, qb, sb, K, epi=ops.EPI_BIAS_GELU, bias=bias, aux=pre, alpha=alpha)
+    want_pre = (base + bias.float()).bfloat16()
+    assert ((pre.float() - want_pre.float()).norm() / want_pre.float().norm()).item() < 4e-3
+    want = torch.nn.functional.gelu(pre.float(), approximate="tanh")
+    assert ((out.float() - want).norm() / want.norm()).item() < 4e-3
+    ops.gemm_nvfp4(out, qa, sa, qb, sb, K, epi=ops.EPI_BIAS_RESID, bias=bias, aux=res, alpha=alpha)
+    want = base + bias.float() + res.float()
+    assert ((out.float() - want).norm() / want.norm()).item() < 4e-3
+    acc = torch.ones(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm_nvfp4(acc, qa, sa, qb, sb, K, epi=ops.EPI_ACC_F32, splits=4, alpha=alpha)
+    assert (((acc - 1.0) - base).norm() / base.norm()).item() < 1e-4
+
+
+@gpu
+def test_nvfp4_linear_native_matches_emulated(monkeypatch):
+    """One linear layer forward + backward: the block-scaled tensor path against the bf16 path on dequantised operands."""
+    rows, C, OC = 512, 256, 384
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    w = (torch.randn(OC, C, generator=g) * 0.05).bfloat16().cuda()
+    b = torch.randn(OC, generator=g).bfloat16().cuda()
+    d = (torch.randn(rows, OC, generator=g) * 0.01).bfloat16().cuda()
+    res = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("LLMM_FP4_NATIVE", mode)
+        out = torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda")
+        lowp.matmul_fwd_fp4(out, x, w, b)
+        dinp = torch.empty(rows, C, dtype=torch.bfloat16, device="cuda")
+        dw = torch.zeros(OC, C, dtype=torch.float32, device="cuda")
+        db = torch.zeros(OC, dtype=torch.float32, device="cuda")
+        lowp.matmul_bwd_fp4(dinp, dw, db, d, x, w, seed=7, step=2)
+        res[mode] = (out.float(), dinp.float(), dw, db)
+    for got, want in zip(res["1"], res["0"]):
+        assert ((got - want).norm() / want.norm()).item() < 5e-3
