@@ -895,13 +895,17 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
 // tensor memory as one tcgen05.cp.  One CTA per SM owns 128 x 128 tiles: two fp32 accumulators of 128
 // TMEM columns each (the epilogue of one tile overlaps the MMAs of the next), 16 columns of A scales
 // and 16 of B scales for the four k-steps (64 values each) of a stage.  A stage is 128 bytes = 256
-// values along K of both operands plus 2 KB of scales per operand.  Same warp roles as gemm_kernel.
+// values along K of both operands plus 2 KB of scales per operand.  Eight epilogue warps: warp % 4 is the
+// 32-row band (TMEM lane quarter), (warp - 2) / 4 the 64-column half; bf16 results leave (and auxiliary
+// inputs arrive) as one 128-byte-swizzled 32 x 64 box per warp by TMA, like the CTA-pair kernel's; fp32
+// outputs and layouts without a tensor map use the register epilogue on four of the warps.
 constexpr int NV_BN = 128;
-constexpr int NV_STAGES = 5;
+constexpr int NV_STAGES = 4;
+constexpr int NV_THREADS = 320;                        // TMA producer, MMA issuer, 8 epilogue warps
 constexpr int NV_TILE = 128 * ROW_BYTES;               // 16 KB: 128 rows x 256 e2m1 values
 constexpr int NV_SF = 4 * 512;                         // scales of 128 rows x 16 blocks
 constexpr int NV_STAGE_BYTES = 2 * NV_TILE + 2 * NV_SF;
-constexpr int NV_SMEM_BYTES = NV_STAGES * NV_STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + 256;
+constexpr int NV_SMEM_BYTES = NV_STAGES * NV_STAGE_BYTES + 8 * EPI_STAGE_BYTES + 1024 + 256;
 constexpr int NV_BKE = 256;                            // K values per stage
 constexpr uint32_t NV_SFA_COL = 256, NV_SFB_COL = 272; // TMEM columns behind the two accumulators
 
@@ -912,26 +916,30 @@ struct Nvfp4Params {
 };
 
 template <int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Nvfp4Params q) {
+__global__ void __launch_bounds__(NV_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, const Nvfp4Params q) {
+  using Cfg = EpiCfg<EPI>;
   const GemmParams& p = q.g;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* epi_stage = smem + NV_STAGES * NV_STAGE_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 4 * EPI_STAGE_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 8 * EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + NV_STAGES;
   uint64_t* tfull_bar = empty_bar + NV_STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* aux_bar = tempty_bar + 2;              // [8] one per epilogue warp: auxiliary-input box landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   if (threadIdx.x == 0) {
     for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }
+    for (int w = 0; w < 8; ++w) mbar_init(&aux_bar[w], 1);
     *abort_flag = 0;
     fence_barrier_init();
-    prefetch_tmap(&tmA); prefetch_tmap(&tmB);
+    prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmD); prefetch_tmap(&tmAux);
   }
   if (warp == 1) tmem_alloc<512>(tmem_slot);
   fence_before_sync();
@@ -1014,21 +1022,65 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int qd = warp & 3;                // TMEM lane quarter this warp may access
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    const int qd = warp & 3, e = warp - 2, hc = e >> 2;   // TMEM lane quarter, warp slot, 64-column half
+    const bool tma_epi = !Cfg::F32_OUT && p.tma_epi;      // warp-uniform
+    unsigned char* buf = epi_stage + e * EPI_STAGE_BYTES; // two 4 KB boxes
+    uint64_t* abar = &aux_bar[e];
+    uint32_t aux_phase = 0;
     int it = 0;
     for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
       int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      const int row0 = m_blk * BM + qd * 32, col0 = n_blk * NV_BN + hc * 64;
+      const bool valid = row0 < p.M && col0 < p.N;        // warp-uniform
+      if (tma_epi && Cfg::AUX_IN && valid) {              // the auxiliary box travels while the tile's MMAs run
+        if (lane == 0) {
+          bulk_wait_read<0>();                            // the previous tile's store has read the buffer
+          mbar_expect_tx(abar, SLAB_BYTES);
+          tma_load_2d(buf, &tmAux, abar, col0, row0);
+        }
+        __syncwarp();
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
       fence_after_sync();
       const float alpha = p.alpha ? *p.alpha : 1.0f;
-      epilogue_warp<EPI, NV_BN>(p, tmem_base + ((uint32_t)(qd * 32) << 16) + acc * NV_BN, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
-                                m_blk * BM + qd * 32, n_blk * NV_BN, alpha, lane);
+      const uint32_t tacc = tmem_base + ((uint32_t)(qd * 32) << 16) + acc * NV_BN;
+      if (!tma_epi) {
+        if (e < 4) epilogue_warp<EPI, NV_BN>(p, tacc, buf, row0, n_blk * NV_BN, alpha, lane);
+      } else if (valid) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tacc + hc * 64, r0);
+        tmem_ld32(tacc + hc * 64 + 32, r1);
+        tmem_wait_ld();
+        if (Cfg::AUX_IN) {
+          if (!mbar_wait(abar, aux_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
+          aux_phase ^= 1;
+        } else {
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+        }
+        epi_slab_bf16<EPI>(p, r0, r1, buf, col0, alpha, lane);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          if (Cfg::TWO_OUT) {
+            tma_store_2d(&tmAux, buf, col0, row0);
+            tma_store_2d(&tmD, buf + SLAB_BYTES, col0, row0);
+          } else {
+            tma_store_2d(&tmD, buf, col0, row0);
+          }
+          bulk_commit();
+        }
+      }
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+    if (tma_epi) {                                        // no copy may still read this CTA's shared memory at exit
+      if (lane == 0) bulk_wait<0>();
+      __syncwarp();
     }
   }
 
@@ -1038,14 +1090,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 template <int EPI>
-int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const Nvfp4Params& q, int grid, cudaStream_t st) {
+int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& taux, const Nvfp4Params& q,
+                 int grid, cudaStream_t st) {
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, NV_SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  gemm_nvfp4_kernel<EPI><<<grid, NUM_THREADS, NV_SMEM_BYTES, st>>>(ta, tb, q);
+  gemm_nvfp4_kernel<EPI><<<grid, NV_THREADS, NV_SMEM_BYTES, st>>>(ta, tb, td, taux, q);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -1111,16 +1164,26 @@ LLMB_API int llmb_gemm_nvfp4(void* D, const void* A, const void* B, const void* 
   p.bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
   q.sfa = (const unsigned char*)sfa; q.sfb = (const unsigned char*)sfb;
   q.atoms_k = ceil_div(K, 64);
+  // bf16 outputs (and bf16 auxiliary tensors) travel by TMA when their layout allows a tensor map
+  CUtensorMap td = ta, taux = ta;
+  const bool needs_aux = epi == EPI_BIAS_GELU || epi == EPI_DGELU || epi == EPI_BIAS_RESID;
+  if (epi != EPI_ACC_F32 && epi != EPI_STORE_F32 && (ldd * 2) % 16 == 0 &&
+      (!needs_aux || (aux && (reinterpret_cast<uintptr_t>(aux) & 15) == 0 && (ldaux * 2) % 16 == 0))) {
+    int ok = make_tmap_2d(&td, D, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldd, 32, 64) == 0;
+    if (ok && needs_aux)
+      ok = make_tmap_2d(&taux, aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldaux, 32, 64) == 0;
+    p.tma_epi = ok;
+  }
   const long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
   const int grid = (int)(units < sm_count() ? units : sm_count());
   switch (epi) {
-    case EPI_NONE: return launch_nvfp4<EPI_NONE>(ta, tb, q, grid, st);
-    case EPI_BIAS: return launch_nvfp4<EPI_BIAS>(ta, tb, q, grid, st);
-    case EPI_BIAS_GELU: return launch_nvfp4<EPI_BIAS_GELU>(ta, tb, q, grid, st);
-    case EPI_DGELU: return launch_nvfp4<EPI_DGELU>(ta, tb, q, grid, st);
-    case EPI_ACC_F32: return launch_nvfp4<EPI_ACC_F32>(ta, tb, q, grid, st);
-    case EPI_BIAS_RESID: return launch_nvfp4<EPI_BIAS_RESID>(ta, tb, q, grid, st);
-    case EPI_STORE_F32: return launch_nvfp4<EPI_STORE_F32>(ta, tb, q, grid, st);
+    case EPI_NONE: return launch_nvfp4<EPI_NONE>(ta, tb, td, taux, q, grid, st);
+    case EPI_BIAS: return launch_nvfp4<EPI_BIAS>(ta, tb, td, taux, q, grid, st);
+    case EPI_BIAS_GELU: return launch_nvfp4<EPI_BIAS_GELU>(ta, tb, td, taux, q, grid, st);
+    case EPI_DGELU: return launch_nvfp4<EPI_DGELU>(ta, tb, td, taux, q, grid, st);
+    case EPI_ACC_F32: return launch_nvfp4<EPI_ACC_F32>(ta, tb, td, taux, q, grid, st);
+    case EPI_BIAS_RESID: return launch_nvfp4<EPI_BIAS_RESID>(ta, tb, td, taux, q, grid, st);
+    case EPI_STORE_F32: return launch_nvfp4<EPI_STORE_F32>(ta, tb, td, taux, q, grid, st);
   }
   return LLMB_ERR_BAD_ARG;
 }

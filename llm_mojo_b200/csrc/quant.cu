@@ -335,7 +335,22 @@ __global__ void __launch_bounds__(256) nvfp4_quantize16_coop_kernel(uint8_t* __r
     }
     packed[i / 2] = (uint8_t)(c[0] | (c[1] << 4));
   }
-  if (q) *reinterpret_cast<uint2*>(q + ((long long)(br * 16 + l) * K + kb * 16) / 2) = *reinterpret_cast<uint2*>(packed);   // axis 1 only
+  if (q) {
+    uint2 mine = *reinterpret_cast<uint2*>(packed);
+    if (axis == 0) {
+      // this lane holds one k of sixteen outer lines; the packed row of outer line br*16 + l wants the sixteen k of that
+      // line: a 16 x 16 nibble transpose across the half-warp (nibble l of lane s becomes nibble s of lane l)
+      uint2 t = make_uint2(0u, 0u);
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        const uint32_t wlo = __shfl_sync(0xffffffffu, mine.x, s, 16), whi = __shfl_sync(0xffffffffu, mine.y, s, 16);
+        const uint32_t nib = ((l < 8 ? wlo : whi) >> ((l & 7) * 4)) & 15u;
+        if (s < 8) t.x |= nib << (s * 4); else t.y |= nib << ((s - 8) * 4);
+      }
+      mine = t;
+    }
+    *reinterpret_cast<uint2*>(q + ((long long)(br * 16 + l) * K + kb * 16) / 2) = mine;
+  }
   if (deq) store16_bf16(deq + base, v);
 }
 
@@ -589,7 +604,7 @@ LLMB_API int llmb_nvfp4_quantize(void* q, void* scales, void* deq, const void* x
   const long long total = (long long)ceil_div(outer, block_rows) * (K / 16);
   const int threads = 128;
   const unsigned grid = (unsigned)ceil_div_ll(total, threads);
-  if (dtype == LLMB_BF16 && block_rows == 16 && !rht && cols % 16 == 0 && outer % 16 == 0 && (q == nullptr || axis == 1)) {
+  if (dtype == LLMB_BF16 && block_rows == 16 && !rht && cols % 16 == 0 && outer % 16 == 0 && K % 16 == 0) {
     const long long lanes = total * 16;
     nvfp4_quantize16_coop_kernel<<<(unsigned)ceil_div_ll(lanes, 256), 256, 0, st>>>((uint8_t*)q, (uint8_t*)scales, (__nv_bfloat16*)deq,
         (const __nv_bfloat16*)x, tensor_scale, rows, cols, axis, sr, seed, stream, step, n_col_tiles);
