@@ -37,6 +37,12 @@ __device__ __forceinline__ uint32_t squares32(uint64_t ctr, uint64_t key) {
 __device__ __forceinline__ float rng_uniform01(uint64_t seed, uint64_t ctr, uint64_t stream) {
   return (float)(squares32(ctr, rng_key(seed, stream)) >> 8) * (1.0f / 16777216.0f);
 }
+// Two 16-bit uniforms from one draw (stochastic rounding of a pair of values: the draw is the cost of the kernel).
+__device__ __forceinline__ void rng_uniform01_pair(uint64_t key, uint64_t ctr, float (&u)[2]) {
+  const uint32_t r = squares32(ctr, key);
+  u[0] = (float)(r >> 16) * (1.0f / 65536.0f);
+  u[1] = (float)(r & 0xffffu) * (1.0f / 65536.0f);
+}
 
 // ------------------------------------------------------------------ amax
 template <typename T>
@@ -129,16 +135,11 @@ __device__ __forceinline__ int encode_e2m1_rne(float v) {
 // stochastic rounding between the two bracketing grid points: P(up) = (|v| - lo) / (hi - lo)
 __device__ __forceinline__ int encode_e2m1_sr(float v, float rnd) {
   const float a = fminf(fabsf(v), 6.0f);
-  int lo = 0;
-#pragma unroll
-  for (int i = 1; i < 8; ++i) if (a >= e2m1_value(i)) lo = i;
-  int idx = lo;
-  if (lo < 7) {
-    const float l = e2m1_value(lo), h = e2m1_value(lo + 1);
-    const float pup = (a - l) / (h - l);
-    if (rnd < pup) idx = lo + 1;
-  }
-  return (v < 0.f ? 8 : 0) | idx;
+  // position on the index axis of the grid {0, .5, 1, 1.5, 2, 3, 4, 6}: the integer part is the lower bracket, the
+  // fraction the distance to it in units of the local spacing
+  const float t = a < 2.0f ? a * 2.0f : (a < 4.0f ? a + 2.0f : a * 0.5f + 4.0f);
+  const int lo = (int)t;
+  return (v < 0.f ? 8 : 0) | (lo + ((rnd < t - (float)lo) ? 1 : 0));
 }
 __device__ __forceinline__ uint8_t encode_e4m3(float v) { return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
 __device__ __forceinline__ float decode_e4m3(uint8_t c) {
@@ -247,6 +248,7 @@ __global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restri
   float sc_val = sc_dec * ts;
   if (sc_val <= 0.f) sc_val = 1.0f;
   const float inv = 1.0f / sc_val;
+  const uint64_t key = sr ? rng_key(seed, stream) : 0ull;
 #pragma unroll
   for (int rr = 0; rr < BLOCK_ROWS; ++rr) {
     const int o = br * BLOCK_ROWS + rr;
@@ -256,13 +258,13 @@ __global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restri
 #pragma unroll
     for (int kk = 0; kk < 16; kk += 2) {
       int c[2];
+      float u[2] = {0.f, 0.f};
+      if (sr) rng_uniform01_pair(key, ((unsigned long long)step << 32) | ((unsigned long long)o * K + kb * 16 + kk), u);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         const float s = v[rr][kk + t] * inv;
-        if (sr) {
-          const unsigned long long flat = (unsigned long long)o * K + kb * 16 + kk + t;
-          c[t] = encode_e2m1_sr(s, rng_uniform01(seed, ((unsigned long long)step << 32) | flat, stream));
-        } else c[t] = encode_e2m1_rne(s);
+        if (sr) c[t] = encode_e2m1_sr(s, u[t]);
+        else c[t] = encode_e2m1_rne(s);
         const float dq = (c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec;
         if (vec_a || vec_b) v[rr][kk + t] = dq;             // written out as vectors below
         else if (deq) deq[addr(o, kb * 16 + kk + t)] = __float2bfloat16_rn(dq);
@@ -316,6 +318,7 @@ __global__ void __launch_bounds__(256) nvfp4_quantize16_coop_kernel(uint8_t* __r
   float sc_val = sc_dec * ts;
   if (sc_val <= 0.f) sc_val = 1.0f;
   const float inv = 1.0f / sc_val;
+  const uint64_t key = sr ? rng_key(seed, stream) : 0ull;
   if (scales) {                                            // one scale per (outer line, k-block): lane l writes line br*16 + l
     const int o = br * 16 + l;
     scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(o, kb, n_col_tiles) : (long long)o * kblocks + kb] = sc_code;
@@ -324,12 +327,16 @@ __global__ void __launch_bounds__(256) nvfp4_quantize16_coop_kernel(uint8_t* __r
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
     int c[2];
+    float u[2] = {0.f, 0.f};
+    if (sr) {                                             // one draw per pair, counted at the pair's first element
+      const int o = axis == 1 ? br * 16 + l : br * 16 + i;
+      const int k = axis == 1 ? kb * 16 + i : kb * 16 + l;
+      rng_uniform01_pair(key, ((unsigned long long)step << 32) | ((unsigned long long)o * K + k), u);
+    }
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
-      const int o = axis == 1 ? br * 16 + l : br * 16 + i + t;
-      const int k = axis == 1 ? kb * 16 + i + t : kb * 16 + l;
       const float sv = v[i + t] * inv;
-      if (sr) c[t] = encode_e2m1_sr(sv, rng_uniform01(seed, ((unsigned long long)step << 32) | ((unsigned long long)o * K + k), stream));
+      if (sr) c[t] = encode_e2m1_sr(sv, u[t]);
       else c[t] = encode_e2m1_rne(sv);
       v[i + t] = (c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec;
     }

@@ -357,3 +357,27 @@ def test_nvfp4_linear_native_matches_emulated(monkeypatch):
         res[mode] = (out.float(), dinp.float(), dw, db)
     for got, want in zip(res["1"], res["0"]):
         assert ((got - want).norm() / want.norm()).item() < 5e-3
+
+
+@gpu
+@pytest.mark.parametrize("axis", [1, 0])
+def test_nvfp4_stochastic_rounding_on_device_is_unbiased_and_counter_based(axis):
+    x = torch.randn(128, 256).bfloat16().cuda()
+    acc = torch.zeros(128, 256, device="cuda")
+    n = 64
+    for s in range(n):
+        deq, ts = lowp.nvfp4_fake_quant(x, axis=axis, sr=True, seed=5, step=s)
+        acc += deq.float() * ts
+    rne, ts = lowp.nvfp4_fake_quant(x, axis=axis)
+    err_sr = (acc / n - x.float()).abs().mean().item()
+    err_rne = (rne.float() * ts - x.float()).abs().mean().item()
+    assert err_sr < 0.5 * err_rne, (err_sr, err_rne)
+    a, _ = lowp.nvfp4_fake_quant(x, axis=axis, sr=True, seed=5, step=3)
+    b, _ = lowp.nvfp4_fake_quant(x, axis=axis, sr=True, seed=5, step=3)
+    c, _ = lowp.nvfp4_fake_quant(x, axis=axis, sr=True, seed=5, step=4)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    # neighbouring elements share one draw but use different bits of it: their rounding directions are uncorrelated
+    up = ((a.float() * ts) > x.float()).float()
+    pairs = up.reshape(-1, 2) if axis == 1 else up.t().reshape(-1, 2)
+    corr = torch.corrcoef(pairs.t())[0, 1].abs().item()
+    assert corr < 0.05, corr
