@@ -102,6 +102,11 @@ def lowp_rows(shapes, rows: int) -> None:
         lowp.quantize_fp8(qw, W, one * 16, lowp.E4M3)
         ms = timed_flushed(lambda: ops.gemm(D, qa, qw, alpha=one, kind=2, a_fmt=lowp.E4M3, b_fmt=lowp.E4M3))
         print(f"   fp8 (per-tensor scale, CTA-pair 256x256 tiles)        {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+        if rows % 128 == 0 and N % 128 == 0 and K % 128 == 0:
+            ba, sfa = lowp.fp8_block_quant(A, 0, lowp.E4M3)
+            bw, sfw = lowp.fp8_block_quant(W, 2, lowp.E4M3)
+            ms = timed_flushed(lambda: ops.gemm_mxfp8(D, ba, sfa, bw, sfw))
+            print(f"   fp8, per-128 block scales (MXFP8 tensor path, 128x128 tiles) {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
         if K % 32 == 0:
             _, tsa, pa, sa = lowp.nvfp4_fake_quant(A, axis=1, block_rows=1, want_packed=True, want_deq=False)
             _, tsw, pw, sw = lowp.nvfp4_fake_quant(W, axis=1, block_rows=16, want_packed=True, want_deq=False)

@@ -906,16 +906,21 @@ constexpr int NV_TILE = 128 * ROW_BYTES;               // 16 KB: 128 rows x 256 
 constexpr int NV_SF = 4 * 512;                         // scales of 128 rows x 16 blocks
 constexpr int NV_STAGE_BYTES = 2 * NV_TILE + 2 * NV_SF;
 constexpr int NV_SMEM_BYTES = NV_STAGES * NV_STAGE_BYTES + 8 * EPI_STAGE_BYTES + 1024 + 256;
-constexpr int NV_BKE = 256;                            // K values per stage
+constexpr int NV_BKE = 256;                            // K values per stage (NVFP4)
+constexpr int NV_BKE_MX = 128;                         // K values per stage (MXFP8)
 constexpr uint32_t NV_SFA_COL = 256, NV_SFB_COL = 272; // TMEM columns behind the two accumulators
 
 struct Nvfp4Params {
   GemmParams g;                                         // epilogue fields, tile counts, split-K (operand fields unused)
   const unsigned char* sfa; const unsigned char* sfb;   // scale atoms of A ([ceil(M/128)][atoms_k][512]) and of B
-  int atoms_k;                                          // ceil(K / 64)
+  int atoms_k;                                          // scale atoms along K: ceil(K / 64) for NVFP4, ceil(K / 128) for MXFP8
+  uint32_t idesc;
 };
 
-template <int EPI>
+// MX = 1 runs the same pipeline for MXFP8 (`kind::mxf8f6f4`, e4m3 / e5m2 bytes, one ue8m0 scale per 32 values of K): a
+// stage is then 128 values of K, ONE scale atom per operand serves its four MMAs (K = 32 each), which select their byte of
+// the atom's TMEM columns through the scale ids of the instruction descriptor.
+template <int MX, int EPI>
 __global__ void __launch_bounds__(NV_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, const Nvfp4Params q) {
@@ -969,13 +974,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
           unsigned char* sa = smem + stage * NV_STAGE_BYTES;
-          const int atoms = min(4, q.atoms_k - kb * 4);
+          constexpr int APS = MX ? 1 : 4;                 // scale atoms per stage
+          const int atoms = min(APS, q.atoms_k - kb * APS);
           const uint32_t sf_bytes = (uint32_t)atoms * 512u;
           mbar_expect_tx(&full_bar[stage], 2 * NV_TILE + 2 * sf_bytes);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * ROW_BYTES, m_blk * BM);
           tma_load_2d(sa + NV_TILE, &tmB, &full_bar[stage], kb * ROW_BYTES, n_blk * NV_BN);
-          bulk_load_1d(sa + 2 * NV_TILE, q.sfa + ((size_t)m_blk * q.atoms_k + (size_t)kb * 4) * 512, sf_bytes, &full_bar[stage]);
-          bulk_load_1d(sa + 2 * NV_TILE + NV_SF, q.sfb + ((size_t)n_blk * q.atoms_k + (size_t)kb * 4) * 512, sf_bytes, &full_bar[stage]);
+          bulk_load_1d(sa + 2 * NV_TILE, q.sfa + ((size_t)m_blk * q.atoms_k + (size_t)kb * APS) * 512, sf_bytes, &full_bar[stage]);
+          bulk_load_1d(sa + 2 * NV_TILE + NV_SF, q.sfb + ((size_t)n_blk * q.atoms_k + (size_t)kb * APS) * 512, sf_bytes, &full_bar[stage]);
           if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -988,7 +994,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + NV_TILE, 16, 1024, 2);
     const uint64_t sfa0 = make_sf_desc(smem_u32(smem) + 2 * NV_TILE);
     const uint64_t sfb0 = make_sf_desc(smem_u32(smem) + 2 * NV_TILE + NV_SF);
-    const uint32_t idesc = make_idesc_nvfp4(BM, NV_BN);
+    const uint32_t idesc = q.idesc;
     const uint32_t sfa_t = tmem_base + NV_SFA_COL, sfb_t = tmem_base + NV_SFB_COL;
     bool ok = true;
     for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
@@ -1002,6 +1008,21 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
         fence_after_sync();
         const uint64_t soff = (uint64_t)(stage * (NV_STAGE_BYTES >> 4));
+        if (MX) {
+          const int nk = min(4, (p.K - kb * NV_BKE_MX + 31) / 32);
+          if (elect_one()) {
+            tmem_cp_sf(sfa_t, sfa0 + soff);
+            tmem_cp_sf(sfb_t, sfb0 + soff);
+            for (int k = 0; k < nk; ++k)
+              umma_mxfp8(d_tmem, adesc0 + soff + (uint64_t)(k * 2), bdesc0 + soff + (uint64_t)(k * 2),
+                         idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sfa_t | ((uint32_t)k << 30), sfb_t | ((uint32_t)k << 30),
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);
+          }
+          __syncwarp();
+          if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
+          continue;
+        }
         const int atoms = min(4, q.atoms_k - kb * 4);
         if (elect_one()) {
           for (int k = 0; k < atoms; ++k) {
@@ -1089,16 +1110,16 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (warp == 1) { fence_after_sync(); tmem_dealloc<512>(tmem_base); }
 }
 
-template <int EPI>
+template <int MX, int EPI>
 int launch_nvfp4(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, const CUtensorMap& taux, const Nvfp4Params& q,
                  int grid, cudaStream_t st) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, NV_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<MX, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, NV_SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  gemm_nvfp4_kernel<EPI><<<grid, NV_THREADS, NV_SMEM_BYTES, st>>>(ta, tb, td, taux, q);
+  gemm_nvfp4_kernel<MX, EPI><<<grid, NV_THREADS, NV_SMEM_BYTES, st>>>(ta, tb, td, taux, q);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -1137,24 +1158,28 @@ LLMB_API void llmb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
 // A [M, K/2] and B [N, K/2]: packed e2m1 bytes as llmb_nvfp4_quantize writes them (K % 32 == 0); sfa / sfb: its
 // swizzled scale buffers (llmb_nvfp4_scale_bytes(rows, K, 1) bytes, zero where no block exists).  D is bf16
 // except for epi 4 / 6 (fp32 accumulate with split-K / fp32 store); bias and aux are bf16.
-LLMB_API int llmb_gemm_nvfp4(void* D, const void* A, const void* B, const void* sfa, const void* sfb, const void* bias, void* aux,
-                             const float* alpha, int M, int N, int K, long long ldd, long long ldaux, int epi, int splits,
-                             int* status, cudaStream_t st) {
+namespace {
+template <int MX>
+int gemm_block_scaled(void* D, const void* A, const void* B, const void* sfa, const void* sfb, const void* bias, void* aux,
+                      const float* alpha, int M, int N, int K, int a_fmt, int b_fmt, long long ldd, long long ldaux, int epi,
+                      int splits, int* status, cudaStream_t st) {
+  constexpr int EPB = MX ? 1 : 2;                         // elements per byte
+  constexpr int BKE = MX ? NV_BKE_MX : NV_BKE;
   if (M <= 0 || N <= 0 || K <= 0 || K % 32 || N % 8) return LLMB_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D) |
        reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(sfb)) & 15) return LLMB_ERR_BAD_ARG;
   CUtensorMap ta, tb;
-  int rc = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)(K / 2), (uint64_t)(K / 2), BM, ROW_BYTES);
+  int rc = make_tmap_2d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)(K / EPB), (uint64_t)(K / EPB), BM, ROW_BYTES);
   if (rc) return 1000 + rc;
-  rc = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)(K / 2), (uint64_t)(K / 2), NV_BN, ROW_BYTES);
+  rc = make_tmap_2d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)N, (uint64_t)(K / EPB), (uint64_t)(K / EPB), NV_BN, ROW_BYTES);
   if (rc) return 1000 + rc;
   Nvfp4Params q{};
   GemmParams& p = q.g;
   p.D = D; p.bias = bias; p.aux = aux; p.alpha = alpha;
   p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldaux = ldaux;
-  p.bke = NV_BKE;
+  p.bke = BKE;
   p.m_tiles = ceil_div(M, BM); p.n_tiles = ceil_div(N, NV_BN);
-  p.kb_total = ceil_div(K, NV_BKE);
+  p.kb_total = ceil_div(K, BKE);
   if (splits < 1) splits = 1;
   if (splits > p.kb_total) splits = p.kb_total;
   if (epi != EPI_ACC_F32) splits = 1;
@@ -1163,7 +1188,8 @@ LLMB_API int llmb_gemm_nvfp4(void* D, const void* A, const void* B, const void* 
   p.status = status;
   p.bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
   q.sfa = (const unsigned char*)sfa; q.sfb = (const unsigned char*)sfb;
-  q.atoms_k = ceil_div(K, 64);
+  q.atoms_k = ceil_div(K, MX ? 128 : 64);
+  q.idesc = MX ? make_idesc_mxfp8((uint32_t)a_fmt, (uint32_t)b_fmt, BM, NV_BN) : make_idesc_nvfp4(BM, NV_BN);
   // bf16 outputs (and bf16 auxiliary tensors) travel by TMA when their layout allows a tensor map
   CUtensorMap td = ta, taux = ta;
   const bool needs_aux = epi == EPI_BIAS_GELU || epi == EPI_DGELU || epi == EPI_BIAS_RESID;
@@ -1177,13 +1203,29 @@ LLMB_API int llmb_gemm_nvfp4(void* D, const void* A, const void* B, const void* 
   const long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
   const int grid = (int)(units < sm_count() ? units : sm_count());
   switch (epi) {
-    case EPI_NONE: return launch_nvfp4<EPI_NONE>(ta, tb, td, taux, q, grid, st);
-    case EPI_BIAS: return launch_nvfp4<EPI_BIAS>(ta, tb, td, taux, q, grid, st);
-    case EPI_BIAS_GELU: return launch_nvfp4<EPI_BIAS_GELU>(ta, tb, td, taux, q, grid, st);
-    case EPI_DGELU: return launch_nvfp4<EPI_DGELU>(ta, tb, td, taux, q, grid, st);
-    case EPI_ACC_F32: return launch_nvfp4<EPI_ACC_F32>(ta, tb, td, taux, q, grid, st);
-    case EPI_BIAS_RESID: return launch_nvfp4<EPI_BIAS_RESID>(ta, tb, td, taux, q, grid, st);
-    case EPI_STORE_F32: return launch_nvfp4<EPI_STORE_F32>(ta, tb, td, taux, q, grid, st);
+    case EPI_NONE: return launch_nvfp4<MX, EPI_NONE>(ta, tb, td, taux, q, grid, st);
+    case EPI_BIAS: return launch_nvfp4<MX, EPI_BIAS>(ta, tb, td, taux, q, grid, st);
+    case EPI_BIAS_GELU: return launch_nvfp4<MX, EPI_BIAS_GELU>(ta, tb, td, taux, q, grid, st);
+    case EPI_DGELU: return launch_nvfp4<MX, EPI_DGELU>(ta, tb, td, taux, q, grid, st);
+    case EPI_ACC_F32: return launch_nvfp4<MX, EPI_ACC_F32>(ta, tb, td, taux, q, grid, st);
+    case EPI_BIAS_RESID: return launch_nvfp4<MX, EPI_BIAS_RESID>(ta, tb, td, taux, q, grid, st);
+    case EPI_STORE_F32: return launch_nvfp4<MX, EPI_STORE_F32>(ta, tb, td, taux, q, grid, st);
   }
   return LLMB_ERR_BAD_ARG;
+}
+}  // namespace
+
+LLMB_API int llmb_gemm_nvfp4(void* D, const void* A, const void* B, const void* sfa, const void* sfb, const void* bias, void* aux,
+                             const float* alpha, int M, int N, int K, long long ldd, long long ldaux, int epi, int splits,
+                             int* status, cudaStream_t st) {
+  return gemm_block_scaled<0>(D, A, B, sfa, sfb, bias, aux, alpha, M, N, K, 0, 0, ldd, ldaux, epi, splits, status, st);
+}
+
+// The same product on the MXFP8 tensor path (`kind::mxf8f6f4`): A [M, K] and B [N, K] are e4m3 (fmt 0) or e5m2 (fmt 1) bytes,
+// sfa / sfb one ue8m0 scale (byte = biased exponent of a power of two) per row and 32 values of K in the same 128 x 4 atoms,
+// ceil(K / 128) atoms per row block.
+LLMB_API int llmb_gemm_mxfp8(void* D, const void* A, const void* B, const void* sfa, const void* sfb, const void* bias, void* aux,
+                             const float* alpha, int M, int N, int K, int a_fmt, int b_fmt, long long ldd, long long ldaux,
+                             int epi, int splits, int* status, cudaStream_t st) {
+  return gemm_block_scaled<1>(D, A, B, sfa, sfb, bias, aux, alpha, M, N, K, a_fmt, b_fmt, ldd, ldaux, epi, splits, status, st);
 }

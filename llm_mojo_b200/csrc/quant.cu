@@ -574,6 +574,101 @@ __global__ void __launch_bounds__(256) fp8_block_tile_kernel(__nv_bfloat16* __re
     p[i].store(dst + (long long)r * cols + c);
   }
 }
+// Block-scaled FP8 operands for the MXFP8 tensor path.  One CTA of 256 threads per 128 x 128 tile of x [rows, cols]:
+// GRAN 0 = one scale per tile row (1 x 128 blocks), 1 = one per tile column (128 x 1), 2 = one per tile; TRANS writes the
+// bytes transposed ([cols, rows]: the K-major operand of a product contracted over the rows).  The scales go out as the
+// tensor core wants them: ue8m0 bytes, one per "outer" line (row of the written matrix) and 32 values of K, four equal
+// bytes per 128-block, in 128-line x 4 atoms of 512 bytes, atoms of one line block contiguous along K.
+template <int FMT, int GRAN, int TRANS>
+__global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                              const __nv_bfloat16* __restrict__ x, int rows, int cols) {
+  __shared__ float red[16][128];                          // GRAN 1: partial column maxima; GRAN 2: warp maxima in red[0]
+  __shared__ float line_scale[128];                       // scale of outer line o of the written tile
+  __shared__ __align__(16) uint8_t tile[TRANS ? 128 * 144 : 16];
+  const int tiles_c = cols / 128;
+  const int tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+  const int t = threadIdx.x, g = t >> 4, l = t & 15;      // g: row group (rows g + 16 i), l: 8-column slot
+  const __nv_bfloat16* src = x + (long long)tr * 128 * cols + tc * 128;
+  const float fmax = FMT == 0 ? 448.0f : 57344.0f;
+  Pack<__nv_bfloat16> p[8];
+  float rmax[8];
+  float cmax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    p[i].load(src + (long long)(g + 16 * i) * cols + l * 8);
+    rmax[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const float a = fabsf(p[i].v[k]); rmax[i] = fmaxf(rmax[i], a); cmax[k] = fmaxf(cmax[k], a); }
+  }
+  float s_row[8], s_col[8];
+  if (GRAN == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], o, 16));
+      s_row[i] = pow2_scale(rmax[i], fmax);
+      if (l == 0) line_scale[g + 16 * i] = s_row[i];
+    }
+  } else if (GRAN == 1) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) red[g][l * 8 + k] = cmax[k];
+    __syncthreads();
+    if (t < 128) {
+      float m = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) m = fmaxf(m, red[j][t]);
+      line_scale[t] = pow2_scale(m, fmax);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s_col[k] = line_scale[l * 8 + k];
+  } else {
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, rmax[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((t & 31) == 0) red[0][t >> 5] = m;
+    __syncthreads();
+    m = red[0][0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) m = fmaxf(m, red[0][j]);
+    const float s = pow2_scale(m, fmax);
+    if (t < 128) line_scale[t] = s;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_row[i] = s;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint8_t b[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float inv = 1.0f / (GRAN == 1 ? s_col[k] : s_row[i]);      // a power of two: exact
+      b[k] = (uint8_t)__nv_cvt_float_to_fp8(p[i].v[k] * inv, __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+    }
+    const int r = g + 16 * i;
+    if (TRANS) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) tile[(l * 8 + k) * 144 + r] = b[k];
+    } else {
+      *reinterpret_cast<uint2*>(q + (long long)(tr * 128 + r) * cols + tc * 128 + l * 8) = *reinterpret_cast<uint2*>(b);
+    }
+  }
+  __syncthreads();
+  if (TRANS) {                                            // 128 lines of 128 bytes = 1024 chunks of 16 bytes
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int ch = t + j * 256, c = ch >> 3, part = ch & 7;
+      *reinterpret_cast<uint4*>(q + (long long)(tc * 128 + c) * rows + tr * 128 + part * 16) =
+          *reinterpret_cast<const uint4*>(&tile[c * 144 + part * 16]);
+    }
+  }
+  if (t < 128) {
+    const uint32_t e = (__float_as_uint(line_scale[t]) >> 23) & 0xffu;   // ue8m0: the biased exponent of the power of two
+    const long long atom = TRANS ? (long long)tc * (rows / 128) + tr : (long long)tr * tiles_c + tc;
+    *reinterpret_cast<uint32_t*>(sf + atom * 512 + (t & 31) * 16 + (t >> 5) * 4) = e * 0x01010101u;
+  }
+}
 }  // namespace
 // mode 0: 1 x 128 blocks along axis 1 (cols % 128 == 0); mode 1: 128 x 1 blocks along axis 0 (rows % 128 == 0, cols % 8 == 0);
 // mode 2: 128 x 128 blocks (both % 128 == 0).  fmt 0 = e4m3, 1 = e5m2.  x and out are contiguous [rows, cols] bf16.
@@ -593,6 +688,24 @@ LLMB_API int llmb_fp8_block_fake_quant(void* out, const void* x, int rows, int c
     const unsigned grid = (unsigned)((rows / 128) * (cols / 128));
     if (fmt == 0) fp8_block_tile_kernel<0><<<grid, 256, 0, st>>>(o, in, rows, cols); else fp8_block_tile_kernel<1><<<grid, 256, 0, st>>>(o, in, rows, cols);
   } else return LLMB_ERR_BAD_ARG;
+  return (int)cudaGetLastError();
+}
+
+// x [rows, cols] bf16 (both multiples of 128) -> fp8 bytes q and ue8m0 scale atoms sf for llmb_gemm_mxfp8.
+// gran 0: 1 x 128 blocks (q [rows, cols]); gran 1: 128 x 1 blocks, written transposed (q [cols, rows]); gran 2: 128 x 128
+// blocks, q [rows, cols] or, with transpose, [cols, rows].  sf: (rows / 128) * (cols / 128) * 512 bytes.  fmt 0 e4m3, 1 e5m2.
+LLMB_API int llmb_fp8_block_quant(void* q, void* sf, const void* x, int rows, int cols, int gran, int fmt, int transpose,
+                                  cudaStream_t st) {
+  if (rows % 128 || cols % 128 || fmt < 0 || fmt > 1) return LLMB_ERR_BAD_ARG;
+  const unsigned grid = (unsigned)((rows / 128) * (cols / 128));
+  auto* qo = (uint8_t*)q; auto* so = (uint8_t*)sf; auto* in = (const __nv_bfloat16*)x;
+#define FP8Q(F, G, T) fp8_block_quant_kernel<F, G, T><<<grid, 256, 0, st>>>(qo, so, in, rows, cols)
+  if (gran == 0 && !transpose) { if (fmt == 0) FP8Q(0, 0, 0); else FP8Q(1, 0, 0); }
+  else if (gran == 1 && transpose) { if (fmt == 0) FP8Q(0, 1, 1); else FP8Q(1, 1, 1); }
+  else if (gran == 2 && !transpose) { if (fmt == 0) FP8Q(0, 2, 0); else FP8Q(1, 2, 0); }
+  else if (gran == 2 && transpose) { if (fmt == 0) FP8Q(0, 2, 1); else FP8Q(1, 2, 1); }
+  else return LLMB_ERR_BAD_ARG;
+#undef FP8Q
   return (int)cudaGetLastError();
 }
 

@@ -196,6 +196,10 @@ __device__ __forceinline__ void umma_ss(uint32_t tmem_d, uint64_t adesc, uint64_
 __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) {
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
+// MXFP8: e4m3 (0) / e5m2 (1) operands, ue8m0 scales, K = 32 per MMA; the scale ids ([4,6) and [29,31)) are or-ed in per MMA.
+__host__ __device__ constexpr uint32_t make_idesc_mxfp8(uint32_t a_fmt, uint32_t b_fmt, uint32_t M, uint32_t N) {
+  return (a_fmt << 7) | (b_fmt << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24);
+}
 // Shared-memory descriptor of one scale-factor atom: 32 rows of 16 bytes, no swizzle (8-row core matrices 128 B apart).
 __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) { return make_smem_desc(smem_addr, 16, 128, 0); }
 // Copies 32 rows x 16 bytes of shared memory into 4 TMEM columns of all four lane quarters (row r -> lane r of each
@@ -204,6 +208,14 @@ __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) { return ma
 // the copy is ordered with this thread's earlier and later tcgen05.mma / tcgen05.cp.
 __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= (A * sfa) (B * sfb)^T, M = 128, K = 32 fp8 values per row, one scale per row: byte `id` of the TMEM columns at
+// sfa / sfb, where id is given both in the top two bits of the address and in the descriptor's scale id.
+__device__ __forceinline__ void umma_mxfp8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                           uint32_t sfb, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
 }
 // D[tmem] (+)= (A * sfa) (B * sfb)^T, M = 128, K = 64 e2m1 values per row; sfa / sfb: TMEM column addresses.
 __device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,

@@ -196,6 +196,18 @@ def gemm_nvfp4(D, qa, sfa, qb, sfb, K: int, *, epi=EPI_NONE, bias=None, aux=None
     _count()
 
 
+def gemm_mxfp8(D, qa, sfa, qb, sfb, *, a_fmt=0, b_fmt=0, epi=EPI_NONE, bias=None, aux=None, alpha=None, splits=1) -> None:
+    """Native MXFP8 GEMM (``tcgen05.mma.kind::mxf8f6f4.block_scale``): D[M,N] = epi(alpha · (A·sfa)(B·sfb)ᵀ) with fp8
+    bytes ``qa`` [M,K] / ``qb`` [N,K] (format 0 = e4m3, 1 = e5m2) and one ue8m0 scale per row and 32 values of K in 128×4
+    atoms, as ``lowp.fp8_block_quant`` writes them."""
+    M, N = D.shape
+    K = qa.shape[1]
+    check(lib().llmb_gemm_mxfp8(ptr(D), ptr(qa), ptr(qb), ptr(sfa), ptr(sfb), ptr(bias), ptr(aux), ptr(alpha), M, N, K, a_fmt, b_fmt,
+                                D.stride(0), aux.stride(0) if aux is not None else 0, epi, splits,
+                                ptr(status_word(D.device)), stream()), "gemm_mxfp8")
+    _count()
+
+
 def _tc_kind(t: torch.Tensor):
     """tcgen05 kind for a storage dtype: 0 (kind::f16, bf16 operands), 1 (kind::tf32, fp32 operands)."""
     if t.dtype == torch.bfloat16:

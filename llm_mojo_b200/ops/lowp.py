@@ -23,7 +23,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import (EPI_ACC_F32, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESID, EPI_DGELU, EPI_NONE, _count, _gelu_grad_t, _gelu_t,
-               _splits_for, dbias_reduce, gemm, gemm_nvfp4, scratch)
+               _splits_for, dbias_reduce, gemm, gemm_mxfp8, gemm_nvfp4, scratch)
 from ._lib import check, dtype_code, lib, ptr, stream
 from . import matmul_fwd as ops_matmul_fwd, matmul_bwd as ops_matmul_bwd
 
@@ -434,13 +434,44 @@ def fp8_block_usable(rows: int, C: int, OC: int) -> bool:
     return rows % 128 == 0 and C % 128 == 0 and OC % 128 == 0
 
 
+def fp8_block_quant(x: torch.Tensor, gran: int, fmt: int = E4M3, transpose: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """GPU only: x [rows, cols] bf16 → (fp8 bytes, ue8m0 scale atoms), the operands of ``gemm_mxfp8``.  ``gran`` 0 = 1×128
+    blocks, 1 = 128×1 blocks (written transposed: bytes [cols, rows]), 2 = 128×128 blocks (either orientation).  Same
+    scales and rounding as ``fp8_block_fake_quant`` modes 0 / 1 / 2."""
+    rows, cols = x.shape
+    q = torch.empty((cols, rows) if transpose else (rows, cols), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((rows // 128) * (cols // 128) * 512, dtype=torch.uint8, device=x.device)
+    check(lib().llmb_fp8_block_quant(ptr(q), ptr(sf), ptr(x.contiguous()), rows, cols, gran, fmt, int(transpose), stream()),
+          "fp8_block_quant")
+    _count()
+    return q, sf
+
+
+def fp8_block_native() -> bool:
+    """Block-scaled FP8 products on the MXFP8 tensor path (default on a GPU); ``LLMM_FP8B_NATIVE=0`` runs them on the
+    bf16 path over fake-quantised operands (same numerics, the path the tests compare against)."""
+    return os.environ.get("LLMM_FP8B_NATIVE", "1") not in ("0", "")
+
+
 def matmul_fwd_fp8_block(out, inp, weight, bias, *, pre_gelu=None, residual=None) -> None:
     """Block-scaled FP8 forward: e4m3 activations in 1×128 blocks along the contraction, e4m3 weights in 128×128
-    blocks; the product runs on the bf16 tensor path (exact, see ``fp8_block_fake_quant``)."""
+    blocks, power-of-two scales; on a GPU the product runs on the MXFP8 tensor path (the per-128 scale repeated for its
+    four 32-value blocks), otherwise on fake-quantised operands (exact, see ``fp8_block_fake_quant``)."""
     OC, C = weight.shape
     rows = inp.numel() // C
     if not fp8_block_usable(rows, C, OC):
         return ops_matmul_fwd(out, inp, weight, bias, pre_gelu=pre_gelu, residual=residual)
+    if out.is_cuda and inp.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and fp8_block_native():
+        qx, sx = fp8_block_quant(inp.reshape(rows, C), 0, E4M3)
+        qw, sw = fp8_block_quant(weight, 2, E4M3)
+        o = out.view(rows, OC)
+        if pre_gelu is not None:
+            gemm_mxfp8(o, qx, sx, qw, sw, epi=EPI_BIAS_GELU, bias=bias, aux=pre_gelu.view(rows, OC))
+        elif residual is not None:
+            gemm_mxfp8(o, qx, sx, qw, sw, epi=EPI_BIAS_RESID, bias=bias, aux=residual.view(rows, OC))
+        else:
+            gemm_mxfp8(o, qx, sx, qw, sw, epi=EPI_BIAS if bias is not None else EPI_NONE, bias=bias)
+        return
     dx = fp8_block_fake_quant(inp.reshape(rows, C), 0, E4M3)
     dw = fp8_block_fake_quant(weight, 2, E4M3)
     ops_matmul_fwd(out, dx, dw, bias, pre_gelu=pre_gelu, residual=residual)
@@ -454,9 +485,22 @@ def matmul_bwd_fp8_block(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=No
     if not fp8_block_usable(rows, C, OC):
         return ops_matmul_bwd(dinp, dweight, dbias, dout, inp, weight, gelu_pre=gelu_pre)
     d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
+    if dout.is_cuda and dout.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and inp.dtype == torch.bfloat16 and fp8_block_native():
+        # operands of a product contracted over the rows (or over OC for the weight) are written transposed: all K-major
+        if dinp is not None:
+            qd, sd = fp8_block_quant(d, 0, E5M2)
+            qw, sw = fp8_block_quant(weight, 2, E4M3, transpose=True)
+            gemm_mxfp8(dinp.view(rows, C), qd, sd, qw, sw, a_fmt=E5M2, b_fmt=E4M3, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE,
+                       aux=gelu_pre.view(rows, C) if gelu_pre is not None else None)
+        qd, sd = fp8_block_quant(d, 1, E5M2, transpose=True)
+        qx, sx = fp8_block_quant(x, 1, E4M3, transpose=True)
+        gemm_mxfp8(dweight.view(OC, C), qd, sd, qx, sx, a_fmt=E5M2, b_fmt=E4M3, epi=EPI_ACC_F32,
+                   splits=_splits_for(OC, C, rows, tile=128, bk=128, units=148))
+        if dbias is not None:
+            dbias_reduce(dbias, d)
+        return
     if dinp is not None:
         ops_matmul_bwd(dinp, None, None, fp8_block_fake_quant(d, 0, E5M2), x, fp8_block_fake_quant(weight, 2, E4M3), gelu_pre=gelu_pre)
     ops_matmul_bwd(None, dweight, None, fp8_block_fake_quant(d, 1, E5M2), fp8_block_fake_quant(x, 1, E4M3), weight)
     if dbias is not None:
-        from . import dbias_reduce
         dbias_reduce(dbias, d)

@@ -381,3 +381,64 @@ def test_nvfp4_stochastic_rounding_on_device_is_unbiased_and_counter_based(axis)
     pairs = up.reshape(-1, 2) if axis == 1 else up.t().reshape(-1, 2)
     corr = torch.corrcoef(pairs.t())[0, 1].abs().item()
     assert corr < 0.05, corr
+
+
+@gpu
+@pytest.mark.parametrize("gran,transpose,fmt", [(0, False, 0), (1, True, 1), (2, False, 0), (2, True, 0)])
+def test_fp8_block_quant_bytes_and_scales_decode_to_the_fake_quantised_tensor(gran, transpose, fmt):
+    rows, cols = 256, 384
+    x = (torch.randn(rows, cols) * torch.logspace(-2, 2, cols)).bfloat16().cuda()
+    q, sf = lowp.fp8_block_quant(x, gran, fmt, transpose)
+    want = lowp.fp8_block_fake_quant(x, gran, fmt).float()
+    vals = q.view(torch.float8_e4m3fn if fmt == 0 else torch.float8_e5m2).float()
+    outer, K = vals.shape
+    sfc = sf.cpu().view(outer // 128, K // 128, 32, 4, 4)                 # [line block][k atom][line % 32][line / 32][4 equal bytes]
+    assert (sfc == sfc[..., :1]).all()
+    e = sfc[..., 0].permute(0, 3, 2, 1).reshape(outer, K // 128).float()  # line = lb*128 + (l/32)*32 + l%32
+    scale = torch.exp2(e - 127.0).cuda().repeat_interleave(128, dim=1)
+    got = vals * scale
+    got = got.t() if transpose else got
+    assert torch.equal(got, want)
+
+
+@gpu
+@pytest.mark.parametrize("M,N,K", [(256, 384, 512), (128, 128, 128), (1024, 768, 3072)])
+def test_native_mxfp8_gemm_matches_product_of_fake_quantised_operands(M, N, K):
+    from llm_mojo_b200 import ops
+    g = torch.Generator().manual_seed(2)
+    a = (torch.randn(M, K, generator=g) * (1 + torch.arange(K) % 5)).bfloat16().cuda()
+    b = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    qa, sa = lowp.fp8_block_quant(a, 0, lowp.E5M2)
+    qb, sb = lowp.fp8_block_quant(b, 2, lowp.E4M3)
+    want = lowp.fp8_block_fake_quant(a, 0, lowp.E5M2).float() @ lowp.fp8_block_fake_quant(b, 2, lowp.E4M3).float().t()
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.gemm_mxfp8(out32, qa, sa, qb, sb, a_fmt=lowp.E5M2, b_fmt=lowp.E4M3, epi=ops.EPI_STORE_F32)
+    assert ((out32 - want).norm() / want.norm()).item() < 1e-5
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    bias = torch.randn(N, device="cuda").bfloat16()
+    ops.gemm_mxfp8(out, qa, sa, qb, sb, a_fmt=lowp.E5M2, b_fmt=lowp.E4M3, epi=ops.EPI_BIAS, bias=bias)
+    w2 = want + bias.float()
+    assert ((out.float() - w2).norm() / w2.norm()).item() < 4e-3
+
+
+@gpu
+def test_fp8_block_linear_native_matches_fake_quant_path(monkeypatch):
+    rows, C, OC = 512, 256, 384
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    w = (torch.randn(OC, C, generator=g) * 0.05).bfloat16().cuda()
+    b = torch.randn(OC, generator=g).bfloat16().cuda()
+    d = (torch.randn(rows, OC, generator=g) * 0.01).bfloat16().cuda()
+    res = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("LLMM_FP8B_NATIVE", mode)
+        out = torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda")
+        pre = torch.empty_like(out)
+        lowp.matmul_fwd_fp8_block(out, x, w, b, pre_gelu=pre)
+        dinp = torch.empty(rows, C, dtype=torch.bfloat16, device="cuda")
+        dw = torch.zeros(OC, C, dtype=torch.float32, device="cuda")
+        db = torch.zeros(OC, dtype=torch.float32, device="cuda")
+        lowp.matmul_bwd_fp8_block(dinp, dw, db, d, x, w)
+        res[mode] = (out.float(), pre.float(), dinp.float(), dw, db)
+    for got, want in zip(res["1"], res["0"]):
+        assert ((got - want).norm() / want.norm()).item() < 5e-3
