@@ -584,10 +584,10 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restric
                                                               const __nv_bfloat16* __restrict__ x, int rows, int cols) {
   __shared__ float red[16][128];                          // GRAN 1: partial column maxima; GRAN 2: warp maxima in red[0]
   __shared__ float line_scale[128];                       // scale of outer line o of the written tile
-  __shared__ __align__(16) uint8_t tile[TRANS ? 128 * 144 : 16];
+  __shared__ __align__(16) uint8_t tile[TRANS ? 128 * 128 : 16];   // transposed bytes, 8-byte chunks XOR-swizzled by line / 8
   const int tiles_c = cols / 128;
   const int tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
-  const int t = threadIdx.x, g = t >> 4, l = t & 15;      // g: row group (rows g + 16 i), l: 8-column slot
+  const int t = threadIdx.x, g = t >> 4, l = t & 15;      // g: row group (rows 8 g + i), l: 8-column slot
   const __nv_bfloat16* src = x + (long long)tr * 128 * cols + tc * 128;
   const float fmax = FMT == 0 ? 448.0f : 57344.0f;
   Pack<__nv_bfloat16> p[8];
@@ -595,7 +595,7 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restric
   float cmax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    p[i].load(src + (long long)(g + 16 * i) * cols + l * 8);
+    p[i].load(src + (long long)(8 * g + i) * cols + l * 8);
     rmax[i] = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) { const float a = fabsf(p[i].v[k]); rmax[i] = fmaxf(rmax[i], a); cmax[k] = fmaxf(cmax[k], a); }
@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restric
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], o, 16));
       s_row[i] = pow2_scale(rmax[i], fmax);
-      if (l == 0) line_scale[g + 16 * i] = s_row[i];
+      if (l == 0) line_scale[8 * g + i] = s_row[i];
     }
   } else if (GRAN == 1) {
 #pragma unroll
@@ -638,6 +638,7 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restric
 #pragma unroll
     for (int i = 0; i < 8; ++i) s_row[i] = s;
   }
+  uint8_t bt[8][8];                                      // [column slot k][row i]: the transposed 8 x 8 block of this thread
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     uint8_t b[8];
@@ -645,22 +646,25 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restric
     for (int k = 0; k < 8; ++k) {
       const float inv = 1.0f / (GRAN == 1 ? s_col[k] : s_row[i]);      // a power of two: exact
       b[k] = (uint8_t)__nv_cvt_float_to_fp8(p[i].v[k] * inv, __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+      bt[k][i] = b[k];
     }
-    const int r = g + 16 * i;
-    if (TRANS) {
+    if (!TRANS) *reinterpret_cast<uint2*>(q + (long long)(tr * 128 + 8 * g + i) * cols + tc * 128 + l * 8) = *reinterpret_cast<uint2*>(b);
+  }
+  if (TRANS) {
+    // line c = 8 l + k of the transposed tile holds rows 8 g .. 8 g + 7 in its 8-byte chunk g, stored at chunk g ^ l:
+    // the sixteen lanes that share g hit sixteen different chunks of their lines (no bank conflicts)
 #pragma unroll
-      for (int k = 0; k < 8; ++k) tile[(l * 8 + k) * 144 + r] = b[k];
-    } else {
-      *reinterpret_cast<uint2*>(q + (long long)(tr * 128 + r) * cols + tc * 128 + l * 8) = *reinterpret_cast<uint2*>(b);
-    }
+    for (int k = 0; k < 8; ++k)
+      *reinterpret_cast<uint2*>(&tile[(l * 8 + k) * 128 + ((g ^ l) << 3)]) = *reinterpret_cast<uint2*>(bt[k]);
   }
   __syncthreads();
-  if (TRANS) {                                            // 128 lines of 128 bytes = 1024 chunks of 16 bytes
+  if (TRANS) {                                            // 128 lines of 128 bytes = 1024 pieces of 16 bytes
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int ch = t + j * 256, c = ch >> 3, part = ch & 7;
-      *reinterpret_cast<uint4*>(q + (long long)(tc * 128 + c) * rows + tr * 128 + part * 16) =
-          *reinterpret_cast<const uint4*>(&tile[c * 144 + part * 16]);
+      const int ch = t + j * 256, c = ch >> 3, part = ch & 7, ls = c >> 3;
+      uint4 v = *reinterpret_cast<const uint4*>(&tile[c * 128 + ((part ^ (ls >> 1)) << 4)]);
+      if (ls & 1) v = make_uint4(v.z, v.w, v.x, v.y);     // odd swizzle: the two chunks of the pair are exchanged
+      *reinterpret_cast<uint4*>(q + (long long)(tc * 128 + c) * rows + tr * 128 + part * 16) = v;
     }
   }
   if (t < 128) {

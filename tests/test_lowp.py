@@ -143,6 +143,23 @@ def test_fp4_layer_range_matches_reference_policy():
 
 
 # ------------------------------------------------------------------------------ GPU
+def test_native_path_switches_and_split_k_choice(monkeypatch):
+    from llm_mojo_b200 import ops
+    monkeypatch.delenv("LLMM_FP4_NATIVE", raising=False)
+    assert lowp.nvfp4_native(768, 65536) and not lowp.nvfp4_native(768, 1000)      # 16-byte rows of packed values
+    monkeypatch.setenv("LLMM_FP4_NATIVE", "0")
+    assert not lowp.nvfp4_native(768)
+    monkeypatch.delenv("LLMM_FP8B_NATIVE", raising=False)
+    assert lowp.fp8_block_native()
+    monkeypatch.setenv("LLMM_FP8B_NATIVE", "0")
+    assert not lowp.fp8_block_native()
+    # wgrad of a 124M layer on 128x128 tiles: 6 x 24 = 144 tiles on 148 CTAs already fill the machine once
+    assert ops._splits_for(768, 3072, 65536, tile=128, bk=256, units=148) == 1
+    # a 768 x 768 wgrad has 36 tiles: split-K fills the other CTAs
+    assert ops._splits_for(768, 768, 65536, tile=128, bk=256, units=148) == 4
+    assert 1 <= ops._splits_for(768, 768, 65536) <= 16
+
+
 gpu = pytest.mark.gpu
 
 
