@@ -106,13 +106,13 @@ def lowp_rows(shapes, rows: int) -> None:
             ba, sfa = lowp.fp8_block_quant(A, 0, lowp.E4M3)
             bw, sfw = lowp.fp8_block_quant(W, 2, lowp.E4M3)
             ms = timed_flushed(lambda: ops.gemm_mxfp8(D, ba, sfa, bw, sfw))
-            print(f"   fp8, per-128 block scales (MXFP8 tensor path, 128x128 tiles) {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+            print(f"   fp8, per-128 block scales (MXFP8 tensor path, 128x256 tiles) {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
         if K % 32 == 0:
             _, tsa, pa, sa = lowp.nvfp4_fake_quant(A, axis=1, block_rows=1, want_packed=True, want_deq=False)
             _, tsw, pw, sw = lowp.nvfp4_fake_quant(W, axis=1, block_rows=16, want_packed=True, want_deq=False)
             al = tsa * tsw
             ms = timed_flushed(lambda: ops.gemm_nvfp4(D, pa, sa, pw, sw, K, alpha=al))
-            print(f"   nvfp4 (block-scaled tensor path, 128x128 tiles)       {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
+            print(f"   nvfp4 (block-scaled tensor path, 128x256 tiles)       {ms:.3f} ms {fl / ms / 1e9:7.0f} TF/s")
 
 
 def main(argv=None) -> int:

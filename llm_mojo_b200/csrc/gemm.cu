@@ -887,39 +887,49 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   return LLMB_ERR_BAD_ARG;
 }
 // ------------------------------------------------------------------------------------------------
-// Native NVFP4 GEMM:  D[M,N] = epi(alpha * sum_k (A[m,k] sfa[m,k/16]) (B[n,k] sfb[n,k/16])).
-// A and B are packed e2m1 (two values per byte, even index in the low nibble), K-major, K/2 bytes per
-// row; the ue4m3 block scales come in 128-row x 4-block atoms of 512 bytes (byte (r % 32) * 16 +
-// (r / 32) * 4 + block), atoms of one row block contiguous along K: the layout the tensor core's
-// scale path wants, so an atom goes from global to shared memory as one bulk copy and from there to
-// tensor memory as one tcgen05.cp.  One CTA per SM owns 128 x 128 tiles: two fp32 accumulators of 128
-// TMEM columns each (the epilogue of one tile overlaps the MMAs of the next), 16 columns of A scales
-// and 16 of B scales for the four k-steps (64 values each) of a stage.  A stage is 128 bytes = 256
-// values along K of both operands plus 2 KB of scales per operand.  Eight epilogue warps: warp % 4 is the
-// 32-row band (TMEM lane quarter), (warp - 2) / 4 the 64-column half; bf16 results leave (and auxiliary
-// inputs arrive) as one 128-byte-swizzled 32 x 64 box per warp by TMA, like the CTA-pair kernel's; fp32
-// outputs and layouts without a tensor map use the register epilogue on four of the warps.
-constexpr int NV_BN = 128;
-constexpr int NV_STAGES = 4;
+// Native block-scaled GEMMs:  D[M,N] = epi(alpha * sum_k (A[m,k] sfa[m,k/B]) (B[n,k] sfb[n,k/B])).
+// NVFP4 (MX = 0): A and B are packed e2m1 (two values per byte, even index in the low nibble), one ue4m3
+// scale per 16 values (`kind::mxf4nvf4.block_scale.scale_vec::4X`, K = 64 per MMA).  MXFP8 (MX = 1): e4m3 /
+// e5m2 bytes, one ue8m0 scale per 32 values (`kind::mxf8f6f4.block_scale`, K = 32 per MMA).  Both operands
+// K-major.  The scales come in 128-row x 4-block atoms of 512 bytes (byte (r % 32) * 16 + (r / 32) * 4 +
+// block), atoms of one row block contiguous along K: the layout the tensor core's scale path wants, so an
+// atom goes from global to shared memory as part of one bulk copy and from there to tensor memory as one
+// tcgen05.cp (32 rows x 16 bytes -> 4 columns, replicated to the four lane quarters), issued by the MMA
+// thread just ahead of the MMAs that use it.
+//
+// One CTA per SM owns 128 x 256 tiles.  A stage is 128 bytes of K per row (256 e2m1 / 128 fp8 values): A
+// 16 KB, B 32 KB, scales 2 + 4 KB; four MMAs per stage.  Tensor memory: 48 columns of scales (A: 4 per
+// k-step, B: 8 per k-step) do not leave room for two 256-column fp32 accumulators, so these OVERLAP in one
+// 64-column slab: accumulator 0 = [0, 256), accumulator 1 = [192, 448), scales from 448.  The epilogue of a
+// tile reads the shared slab first and says so (`tover`); the next tile's MMAs start when it is read and the
+// tile before that has been drained completely (`tempty`), so the epilogue of one tile still overlaps the
+// MMAs of the next.
+// Eight epilogue warps: warp % 4 is the 32-row band (TMEM lane quarter), (warp - 2) / 4 the 128-column half,
+// two 64-column slabs per warp; bf16 results leave (and auxiliary inputs arrive) as 128-byte-swizzled 32 x 64
+// boxes by TMA; fp32 outputs and layouts without a tensor map use the register epilogue on four warps.
+constexpr int NV_BN = 256;
+constexpr int NV_STAGES = 3;
 constexpr int NV_THREADS = 320;                        // TMA producer, MMA issuer, 8 epilogue warps
-constexpr int NV_TILE = 128 * ROW_BYTES;               // 16 KB: 128 rows x 256 e2m1 values
-constexpr int NV_SF = 4 * 512;                         // scales of 128 rows x 16 blocks
-constexpr int NV_STAGE_BYTES = 2 * NV_TILE + 2 * NV_SF;
-constexpr int NV_SMEM_BYTES = NV_STAGES * NV_STAGE_BYTES + 8 * EPI_STAGE_BYTES + 1024 + 256;
+constexpr int NV_A_TILE = 128 * ROW_BYTES;             // 16 KB
+constexpr int NV_B_TILE = 256 * ROW_BYTES;             // 32 KB
+constexpr int NV_SF = 4 * 512;                         // scales of 128 rows x one stage (NVFP4: 4 atoms; MXFP8: 1)
+constexpr int NV_STAGE_BYTES = NV_A_TILE + NV_B_TILE + 3 * NV_SF;     // 54 KB
+constexpr int NV_EPI_BYTES = 8 * EPI_STAGE_BYTES;      // two 4 KB boxes per epilogue warp
+constexpr int NV_BAR_BYTES = 256;
+constexpr int NV_SMEM_BYTES = 232448;                  // the whole CTA budget: 3 stages + boxes + barriers + 768 B of alignment slack
+static_assert(NV_STAGES * NV_STAGE_BYTES + NV_EPI_BYTES + NV_BAR_BYTES + 768 == NV_SMEM_BYTES, "shared-memory budget");
 constexpr int NV_BKE = 256;                            // K values per stage (NVFP4)
 constexpr int NV_BKE_MX = 128;                         // K values per stage (MXFP8)
-constexpr uint32_t NV_SFA_COL = 256, NV_SFB_COL = 272; // TMEM columns behind the two accumulators
+constexpr uint32_t NV_ACC1_COL = 192, NV_SFA_COL = 448, NV_SFB_COL = 464;
 
 struct Nvfp4Params {
   GemmParams g;                                         // epilogue fields, tile counts, split-K (operand fields unused)
-  const unsigned char* sfa; const unsigned char* sfb;   // scale atoms of A ([ceil(M/128)][atoms_k][512]) and of B
+  const unsigned char* sfa; const unsigned char* sfb;   // scale atoms of A ([ceil(M/128)][atoms_k][512]) and of B ([ceil(N/128)][atoms_k][512])
   int atoms_k;                                          // scale atoms along K: ceil(K / 64) for NVFP4, ceil(K / 128) for MXFP8
+  int b_row_blocks;                                     // ceil(N / 128)
   uint32_t idesc;
 };
 
-// MX = 1 runs the same pipeline for MXFP8 (`kind::mxf8f6f4`, e4m3 / e5m2 bytes, one ue8m0 scale per 32 values of K): a
-// stage is then 128 values of K, ONE scale atom per operand serves its four MMAs (K = 32 each), which select their byte of
-// the atom's TMEM columns through the scale ids of the instruction descriptor.
 template <int MX, int EPI>
 __global__ void __launch_bounds__(NV_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -928,20 +938,25 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const GemmParams& p = q.g;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (smem - smem_raw > 768) {                          // the alignment slack this launch was given does not cover the base it got
+    if (threadIdx.x == 0) atomicExch(p.status, LLMB_ERR_BAD_ARG);
+    return;
+  }
   unsigned char* epi_stage = smem + NV_STAGES * NV_STAGE_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + 8 * EPI_STAGE_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + NV_EPI_BYTES);
   uint64_t* empty_bar = full_bar + NV_STAGES;
-  uint64_t* tfull_bar = empty_bar + NV_STAGES;
-  uint64_t* tempty_bar = tfull_bar + 2;
-  uint64_t* aux_bar = tempty_bar + 2;              // [8] one per epilogue warp: auxiliary-input box landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 8);
+  uint64_t* tfull_bar = empty_bar + NV_STAGES;     // [2] accumulator complete
+  uint64_t* tempty_bar = tfull_bar + 2;            // [2] accumulator drained (8 warps)
+  uint64_t* tover_bar = tempty_bar + 2;            // [2] the slab it shares with the other accumulator is read (4 warps)
+  uint64_t* aux_bar = tover_bar + 2;               // [16] two per epilogue warp: auxiliary-input box landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   if (threadIdx.x == 0) {
     for (int s = 0; s < NV_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); }
-    for (int w = 0; w < 8; ++w) mbar_init(&aux_bar[w], 1);
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], 8); mbar_init(&tover_bar[a], 4); }
+    for (int w = 0; w < 16; ++w) mbar_init(&aux_bar[w], 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmA); prefetch_tmap(&tmB); prefetch_tmap(&tmD); prefetch_tmap(&tmAux);
@@ -964,6 +979,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     kb0 = split * p.kb_per_split;
     kb1 = min(p.kb_total, kb0 + p.kb_per_split);
   };
+  constexpr int APS = MX ? 1 : 4;                   // scale atoms per row block and stage
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer: operand tiles by TMA, scale atoms by bulk copy
@@ -971,39 +987,45 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
+        const int rb0 = 2 * n_blk;                      // the tile's two 128-row blocks of B scales; the second may not exist
+        const bool second = rb0 + 1 < q.b_row_blocks;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
           unsigned char* sa = smem + stage * NV_STAGE_BYTES;
-          constexpr int APS = MX ? 1 : 4;                 // scale atoms per stage
+          unsigned char* sb = sa + NV_A_TILE;
+          unsigned char* sf = sb + NV_B_TILE;           // [A][B rows 0..127][B rows 128..255], 2 KB each
           const int atoms = min(APS, q.atoms_k - kb * APS);
           const uint32_t sf_bytes = (uint32_t)atoms * 512u;
-          mbar_expect_tx(&full_bar[stage], 2 * NV_TILE + 2 * sf_bytes);
+          mbar_expect_tx(&full_bar[stage], NV_A_TILE + NV_B_TILE + (second ? 3u : 2u) * sf_bytes);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * ROW_BYTES, m_blk * BM);
-          tma_load_2d(sa + NV_TILE, &tmB, &full_bar[stage], kb * ROW_BYTES, n_blk * NV_BN);
-          bulk_load_1d(sa + 2 * NV_TILE, q.sfa + ((size_t)m_blk * q.atoms_k + (size_t)kb * APS) * 512, sf_bytes, &full_bar[stage]);
-          bulk_load_1d(sa + 2 * NV_TILE + NV_SF, q.sfb + ((size_t)n_blk * q.atoms_k + (size_t)kb * APS) * 512, sf_bytes, &full_bar[stage]);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * ROW_BYTES, n_blk * NV_BN);
+          const size_t koff = (size_t)kb * APS;
+          bulk_load_1d(sf, q.sfa + ((size_t)m_blk * q.atoms_k + koff) * 512, sf_bytes, &full_bar[stage]);
+          bulk_load_1d(sf + NV_SF, q.sfb + ((size_t)rb0 * q.atoms_k + koff) * 512, sf_bytes, &full_bar[stage]);
+          if (second) bulk_load_1d(sf + 2 * NV_SF, q.sfb + ((size_t)(rb0 + 1) * q.atoms_k + koff) * 512, sf_bytes, &full_bar[stage]);
           if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer: scales to TMEM, then one MMA per 64 values of K
+    // ------------------------------------------------------------ MMA issuer: scales to TMEM, then four MMAs per stage
     int stage = 0; uint32_t phase = 0;
     int it = 0;
     const uint64_t adesc0 = make_smem_desc(smem_u32(smem), 16, 1024, 2);
-    const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + NV_TILE, 16, 1024, 2);
-    const uint64_t sfa0 = make_sf_desc(smem_u32(smem) + 2 * NV_TILE);
-    const uint64_t sfb0 = make_sf_desc(smem_u32(smem) + 2 * NV_TILE + NV_SF);
+    const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + NV_A_TILE, 16, 1024, 2);
+    const uint64_t sfa0 = make_sf_desc(smem_u32(smem) + NV_A_TILE + NV_B_TILE);
+    const uint64_t sfb0 = make_sf_desc(smem_u32(smem) + NV_A_TILE + NV_B_TILE + NV_SF);
     const uint32_t idesc = q.idesc;
     const uint32_t sfa_t = tmem_base + NV_SFA_COL, sfb_t = tmem_base + NV_SFB_COL;
     bool ok = true;
     for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
       int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
       const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) { ok = false; break; }
+      // this accumulator's previous tile is drained, and the previous tile (other accumulator) has read the shared columns
+      if (!mbar_wait(&tempty_bar[acc], ((it >> 1) & 1) ^ 1)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(&tover_bar[acc ^ 1], ((it - 1) >> 1) & 1)) { ok = false; break; }
       fence_after_sync();
-      const uint32_t d_tmem = tmem_base + acc * NV_BN;
+      const uint32_t d_tmem = tmem_base + (acc ? NV_ACC1_COL : 0u);
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&full_bar[stage], phase)) { ok = false; break; }
         fence_after_sync();
@@ -1013,26 +1035,26 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (elect_one()) {
             tmem_cp_sf(sfa_t, sfa0 + soff);
             tmem_cp_sf(sfb_t, sfb0 + soff);
+            tmem_cp_sf(sfb_t + 4, sfb0 + soff + (uint64_t)(NV_SF >> 4));
             for (int k = 0; k < nk; ++k)
               umma_mxfp8(d_tmem, adesc0 + soff + (uint64_t)(k * 2), bdesc0 + soff + (uint64_t)(k * 2),
                          idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4), sfa_t | ((uint32_t)k << 30), sfb_t | ((uint32_t)k << 30),
                          (kb > kb0 || k > 0) ? 1u : 0u);
             umma_commit(&empty_bar[stage]);
           }
-          __syncwarp();
-          if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
-          continue;
-        }
-        const int atoms = min(4, q.atoms_k - kb * 4);
-        if (elect_one()) {
-          for (int k = 0; k < atoms; ++k) {
-            tmem_cp_sf(sfa_t + 4 * k, sfa0 + soff + (uint64_t)(k * 32));
-            tmem_cp_sf(sfb_t + 4 * k, sfb0 + soff + (uint64_t)(k * 32));
+        } else {
+          const int atoms = min(4, q.atoms_k - kb * 4);
+          if (elect_one()) {
+            for (int k = 0; k < atoms; ++k) {
+              tmem_cp_sf(sfa_t + 4 * k, sfa0 + soff + (uint64_t)(k * 32));
+              tmem_cp_sf(sfb_t + 8 * k, sfb0 + soff + (uint64_t)(k * 32));
+              tmem_cp_sf(sfb_t + 8 * k + 4, sfb0 + soff + (uint64_t)((NV_SF >> 4) + k * 32));
+            }
+            for (int k = 0; k < atoms; ++k)
+              umma_nvfp4(d_tmem, adesc0 + soff + (uint64_t)(k * 2), bdesc0 + soff + (uint64_t)(k * 2), idesc, sfa_t + 4 * k, sfb_t + 8 * k,
+                         (kb > kb0 || k > 0) ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);             // operand tiles and scale atoms reusable once these have run
           }
-          for (int k = 0; k < atoms; ++k)
-            umma_nvfp4(d_tmem, adesc0 + soff + (uint64_t)(k * 2), bdesc0 + soff + (uint64_t)(k * 2), idesc, sfa_t + 4 * k, sfb_t + 4 * k,
-                       (kb > kb0 || k > 0) ? 1u : 0u);
-          umma_commit(&empty_bar[stage]);               // operand tiles and scale atoms reusable once these have run
         }
         __syncwarp();
         if (++stage == NV_STAGES) { stage = 0; phase ^= 1; }
@@ -1044,56 +1066,91 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
-    const int qd = warp & 3, e = warp - 2, hc = e >> 2;   // TMEM lane quarter, warp slot, 64-column half
+    const int qd = warp & 3, e = warp - 2, hc = e >> 2;   // TMEM lane quarter, warp slot, 128-column half
     const bool tma_epi = !Cfg::F32_OUT && p.tma_epi;      // warp-uniform
     unsigned char* buf = epi_stage + e * EPI_STAGE_BYTES; // two 4 KB boxes
-    uint64_t* abar = &aux_bar[e];
-    uint32_t aux_phase = 0;
+    uint64_t* abar = &aux_bar[e * 2];
+    uint32_t aux_phase = 0;                               // bit ls: phase of abar[ls]
+    uint32_t nstores = 0;                                 // slabs stored so far (plain epilogues alternate the two boxes)
     int it = 0;
     for (int unit = blockIdx.x; unit < total_units && !*abort_flag; unit += gridDim.x, ++it) {
       int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int row0 = m_blk * BM + qd * 32, col0 = n_blk * NV_BN + hc * 64;
-      const bool valid = row0 < p.M && col0 < p.N;        // warp-uniform
-      if (tma_epi && Cfg::AUX_IN && valid) {              // the auxiliary box travels while the tile's MMAs run
+      const int row0 = m_blk * BM + qd * 32, colh = n_blk * NV_BN + hc * 128;
+      // the slab shared with the other accumulator goes first: the last 64 columns of accumulator 0, the first 64 of
+      // accumulator 1; the four warps that own it report it read
+      const bool reporter = tma_epi ? (hc == (acc ? 0 : 1)) : (e < 4);
+      const int first = (acc == 0 && hc == 1) ? 1 : 0;
+      if (tma_epi && Cfg::AUX_IN && row0 < p.M) {         // the auxiliary boxes travel while the tile's MMAs run
         if (lane == 0) {
-          bulk_wait_read<0>();                            // the previous tile's store has read the buffer
-          mbar_expect_tx(abar, SLAB_BYTES);
-          tma_load_2d(buf, &tmAux, abar, col0, row0);
+          bulk_wait_read<0>();                            // the previous tile's stores have read the boxes
+          for (int ls = 0; ls < 2; ++ls)
+            if (colh + ls * 64 < p.N) {
+              mbar_expect_tx(&abar[ls], SLAB_BYTES);
+              tma_load_2d(buf + ls * SLAB_BYTES, &tmAux, &abar[ls], colh + ls * 64, row0);
+            }
         }
         __syncwarp();
       }
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
       fence_after_sync();
       const float alpha = p.alpha ? *p.alpha : 1.0f;
-      const uint32_t tacc = tmem_base + ((uint32_t)(qd * 32) << 16) + acc * NV_BN;
+      const uint32_t tacc = tmem_base + ((uint32_t)(qd * 32) << 16) + (acc ? NV_ACC1_COL : 0u);
       if (!tma_epi) {
         if (e < 4) epilogue_warp<EPI, NV_BN>(p, tacc, buf, row0, n_blk * NV_BN, alpha, lane);
-      } else if (valid) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(tacc + hc * 64, r0);
-        tmem_ld32(tacc + hc * 64 + 32, r1);
-        tmem_wait_ld();
-        if (Cfg::AUX_IN) {
-          if (!mbar_wait(abar, aux_phase)) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
-          aux_phase ^= 1;
-        } else {
-          if (lane == 0) bulk_wait_read<0>();
+        if (reporter) {
+          fence_before_sync();
           __syncwarp();
+          if (lane == 0) mbar_arrive(&tover_bar[acc]);
         }
-        epi_slab_bf16<EPI>(p, r0, r1, buf, col0, alpha, lane);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          if (Cfg::TWO_OUT) {
-            tma_store_2d(&tmAux, buf, col0, row0);
-            tma_store_2d(&tmD, buf + SLAB_BYTES, col0, row0);
-          } else {
-            tma_store_2d(&tmD, buf, col0, row0);
+      } else {
+        bool ok = true;
+#pragma unroll 1
+        for (int j = 0; j < 2; ++j) {
+          const int ls = j ^ first;
+          const int col0 = colh + ls * 64;
+          const bool valid = row0 < p.M && col0 < p.N;    // warp-uniform
+          uint32_t r0[32], r1[32];
+          if (valid) {
+            tmem_ld32(tacc + hc * 128 + ls * 64, r0);
+            tmem_ld32(tacc + hc * 128 + ls * 64 + 32, r1);
+            tmem_wait_ld();
           }
-          bulk_commit();
+          if (j == 0 && reporter) {
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tover_bar[acc]);
+          }
+          if (!valid) continue;
+          unsigned char* box;
+          if (Cfg::AUX_IN) {
+            box = buf + ls * SLAB_BYTES;
+            if (!mbar_wait(&abar[ls], (aux_phase >> ls) & 1)) { ok = false; break; }
+            aux_phase ^= 1u << ls;
+          } else if (Cfg::TWO_OUT) {
+            box = buf;                                    // pre-activation box, result box behind it
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+          } else {
+            box = buf + (nstores++ & 1) * SLAB_BYTES;     // alternate boxes: only the store before last must have been read
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+          }
+          epi_slab_bf16<EPI>(p, r0, r1, box, col0, alpha, lane);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            if (Cfg::TWO_OUT) {
+              tma_store_2d(&tmAux, box, col0, row0);
+              tma_store_2d(&tmD, box + SLAB_BYTES, col0, row0);
+            } else {
+              tma_store_2d(&tmD, box, col0, row0);
+            }
+            bulk_commit();
+          }
         }
+        if (!ok) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); break; }
       }
       fence_before_sync();
       __syncwarp();
@@ -1189,6 +1246,7 @@ int gemm_block_scaled(void* D, const void* A, const void* B, const void* sfa, co
   p.bias_vec = (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
   q.sfa = (const unsigned char*)sfa; q.sfb = (const unsigned char*)sfb;
   q.atoms_k = ceil_div(K, MX ? 128 : 64);
+  q.b_row_blocks = ceil_div(N, 128);
   q.idesc = MX ? make_idesc_mxfp8((uint32_t)a_fmt, (uint32_t)b_fmt, BM, NV_BN) : make_idesc_nvfp4(BM, NV_BN);
   // bf16 outputs (and bf16 auxiliary tensors) travel by TMA when their layout allows a tensor map
   CUtensorMap td = ta, taux = ta;

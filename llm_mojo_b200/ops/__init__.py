@@ -217,11 +217,12 @@ def _tc_kind(t: torch.Tensor):
     return None
 
 
-def _splits_for(M: int, N: int, K: int, *, tile: int = 256, bk: int = 64, units: int = 74) -> int:
-    """Split-K factor for the dW GEMMs (by default 256x256 tiles on 74 CTA pairs, 64 values of K per stage): the
-    number of splits that minimises waves x (k-blocks per unit + a fixed per-unit cost for the prologue and the
-    fp32 red.add epilogue)."""
-    tiles = max(1, ((M + tile - 1) // tile) * ((N + tile - 1) // tile))
+def _splits_for(M: int, N: int, K: int, *, tile: int = 256, tile_n: int = 0, bk: int = 64, units: int = 74) -> int:
+    """Split-K factor for the dW GEMMs (by default 256x256 tiles on 74 CTA pairs, 64 values of K per stage; the
+    block-scaled kernels have 128x256 tiles on 148 CTAs): the number of splits that minimises waves x (k-blocks per
+    unit + a fixed per-unit cost for the prologue and the fp32 red.add epilogue)."""
+    tile_n = tile_n or tile
+    tiles = max(1, ((M + tile - 1) // tile) * ((N + tile_n - 1) // tile_n))
     kb = (K + bk - 1) // bk
     best, best_cost = 1, None
     for s in range(1, max(1, min(16, kb // 8)) + 1):

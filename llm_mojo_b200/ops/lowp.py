@@ -367,7 +367,7 @@ def matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None, rh
         qd, sd, tsd = _qp(d, 0, 1, rht=usable_rht, sr=sr, seed=seed, stream_id=NVFP4_SR_STREAM + 3, step=step)
         qx, sx, tsx = _qp(x, 0, 1, rht=usable_rht)
         gemm_nvfp4(dweight.view(OC, C), qd, sd, qx, sx, rows, epi=EPI_ACC_F32,
-                   splits=_splits_for(OC, C, rows, tile=128, bk=256, units=148),
+                   splits=_splits_for(OC, C, rows, tile=128, tile_n=256, bk=256, units=148),
                    alpha=tsd * tsx * ((1.0 / 16.0) if usable_rht else 1.0))
         if dbias is not None:
             dbias_reduce(dbias, d)
@@ -495,7 +495,7 @@ def matmul_bwd_fp8_block(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=No
         qd, sd = fp8_block_quant(d, 1, E5M2, transpose=True)
         qx, sx = fp8_block_quant(x, 1, E4M3, transpose=True)
         gemm_mxfp8(dweight.view(OC, C), qd, sd, qx, sx, a_fmt=E5M2, b_fmt=E4M3, epi=EPI_ACC_F32,
-                   splits=_splits_for(OC, C, rows, tile=128, bk=128, units=148))
+                   splits=_splits_for(OC, C, rows, tile=128, tile_n=256, bk=128, units=148))
         if dbias is not None:
             dbias_reduce(dbias, d)
         return

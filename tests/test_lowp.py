@@ -153,10 +153,10 @@ def test_native_path_switches_and_split_k_choice(monkeypatch):
     assert lowp.fp8_block_native()
     monkeypatch.setenv("LLMM_FP8B_NATIVE", "0")
     assert not lowp.fp8_block_native()
-    # wgrad of a 124M layer on 128x128 tiles: 6 x 24 = 144 tiles on 148 CTAs already fill the machine once
-    assert ops._splits_for(768, 3072, 65536, tile=128, bk=256, units=148) == 1
-    # a 768 x 768 wgrad has 36 tiles: split-K fills the other CTAs
-    assert ops._splits_for(768, 768, 65536, tile=128, bk=256, units=148) == 4
+    # wgrad of a 124M layer on 128x256 tiles: 6 x 12 = 72 tiles, two splits fill the 148 CTAs once
+    assert ops._splits_for(768, 3072, 65536, tile=128, tile_n=256, bk=256, units=148) == 2
+    # a 768 x 768 wgrad has 18 tiles: eight splits
+    assert ops._splits_for(768, 768, 65536, tile=128, tile_n=256, bk=256, units=148) == 8
     assert 1 <= ops._splits_for(768, 768, 65536) <= 16
 
 
