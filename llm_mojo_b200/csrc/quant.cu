@@ -16,6 +16,7 @@
 // the NVFP4 GEMM's arithmetic.
 #include "common.cuh"
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 using namespace llmb;
 
 namespace {
@@ -37,13 +38,6 @@ __device__ __forceinline__ uint32_t squares32(uint64_t ctr, uint64_t key) {
 __device__ __forceinline__ float rng_uniform01(uint64_t seed, uint64_t ctr, uint64_t stream) {
   return (float)(squares32(ctr, rng_key(seed, stream)) >> 8) * (1.0f / 16777216.0f);
 }
-// Two 16-bit uniforms from one draw (stochastic rounding of a pair of values: the draw is the cost of the kernel).
-__device__ __forceinline__ void rng_uniform01_pair(uint64_t key, uint64_t ctr, float (&u)[2]) {
-  const uint32_t r = squares32(ctr, key);
-  u[0] = (float)(r >> 16) * (1.0f / 65536.0f);
-  u[1] = (float)(r & 0xffffu) * (1.0f / 65536.0f);
-}
-
 // ------------------------------------------------------------------ amax
 template <typename T>
 __global__ void amax_kernel(unsigned* __restrict__ out_bits, const T* __restrict__ x, long long n) {
@@ -124,22 +118,17 @@ __device__ __forceinline__ float e2m1_value(int code) {
   const unsigned bits = e ? (((126u + e) << 23) | (m << 22)) : (m ? 0x3F000000u : 0u);
   return __uint_as_float(bits);
 }
-// nearest grid point, ties away from zero (the larger magnitude); returns sign<<3 | index
-__device__ __forceinline__ int encode_e2m1_rne(float v) {
-  const float a = fabsf(v);
-  int idx;
-  if (a < 0.25f) idx = 0; else if (a < 0.75f) idx = 1; else if (a < 1.25f) idx = 2; else if (a < 1.75f) idx = 3;
-  else if (a < 2.5f) idx = 4; else if (a < 3.5f) idx = 5; else if (a < 5.0f) idx = 6; else idx = 7;
-  return (v < 0.f ? 8 : 0) | idx;
+// Two values to e2m1 by the hardware convert (round to nearest, ties to even, saturating): lo in the low nibble.
+__device__ __forceinline__ uint32_t e2m1x2_rn(float lo, float hi) {
+  return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
 }
-// stochastic rounding between the two bracketing grid points: P(up) = (|v| - lo) / (hi - lo)
-__device__ __forceinline__ int encode_e2m1_sr(float v, float rnd) {
-  const float a = fminf(fabsf(v), 6.0f);
-  // position on the index axis of the grid {0, .5, 1, 1.5, 2, 3, 4, 6}: the integer part is the lower bracket, the
-  // fraction the distance to it in units of the local spacing
-  const float t = a < 2.0f ? a * 2.0f : (a < 4.0f ? a + 2.0f : a * 0.5f + 4.0f);
-  const int lo = (int)t;
-  return (v < 0.f ? 8 : 0) | (lo + ((rnd < t - (float)lo) ? 1 : 0));
+// Four values to e2m1 with stochastic rounding by the hardware convert: it adds random bits below the kept mantissa
+// bit and truncates, P(up) = distance to the lower neighbour / spacing; `rbits` are 32 uniform bits, a disjoint
+// field per value.  v0 lands in the lowest nibble of the 16-bit result (the instruction packs its first operand highest).
+__device__ __forceinline__ uint32_t e2m1x4_rs(float v0, float v1, float v2, float v3, uint32_t rbits) {
+  uint16_t q;
+  asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;" : "=h"(q) : "f"(v3), "f"(v2), "f"(v1), "f"(v0), "r"(rbits));
+  return (uint32_t)q;
 }
 __device__ __forceinline__ uint8_t encode_e4m3(float v) { return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
 __device__ __forceinline__ float decode_e4m3(uint8_t c) {
@@ -256,20 +245,22 @@ __global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restri
     if (scales) scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(o, kb, n_col_tiles) : (long long)o * kblocks + kb] = sc_code;
     uint8_t packed[8];
 #pragma unroll
-    for (int kk = 0; kk < 16; kk += 2) {
-      int c[2];
-      float u[2] = {0.f, 0.f};
-      if (sr) rng_uniform01_pair(key, ((unsigned long long)step << 32) | ((unsigned long long)o * K + kb * 16 + kk), u);
+    for (int kk = 0; kk < 16; kk += 4) {
+      const float s0 = v[rr][kk] * inv, s1 = v[rr][kk + 1] * inv, s2 = v[rr][kk + 2] * inv, s3 = v[rr][kk + 3] * inv;
+      uint32_t code4;                                     // four codes, value kk in the lowest nibble
+      if (sr)                                             // one draw per four values, counted at the first of them
+        code4 = e2m1x4_rs(s0, s1, s2, s3, squares32(((unsigned long long)step << 32) | ((unsigned long long)o * K + kb * 16 + kk), key));
+      else code4 = e2m1x2_rn(s0, s1) | (e2m1x2_rn(s2, s3) << 8);
+      packed[kk / 2] = (uint8_t)code4; packed[kk / 2 + 1] = (uint8_t)(code4 >> 8);
+      if (deq) {
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const float s = v[rr][kk + t] * inv;
-        if (sr) c[t] = encode_e2m1_sr(s, u[t]);
-        else c[t] = encode_e2m1_rne(s);
-        const float dq = (c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec;
-        if (vec_a || vec_b) v[rr][kk + t] = dq;             // written out as vectors below
-        else if (deq) deq[addr(o, kb * 16 + kk + t)] = __float2bfloat16_rn(dq);
+        for (int t = 0; t < 4; ++t) {
+          const int c = (code4 >> (4 * t)) & 15;
+          const float dq = (c & 8 ? -1.f : 1.f) * e2m1_value(c) * sc_dec;
+          if (vec_a || vec_b) v[rr][kk + t] = dq;           // written out as vectors below
+          else deq[addr(o, kb * 16 + kk + t)] = __float2bfloat16_rn(dq);
+        }
       }
-      packed[kk / 2] = (uint8_t)(c[0] | (c[1] << 4));      // even index -> low nibble
     }
     if (q) *reinterpret_cast<uint2*>(q + ((long long)o * K + kb * 16) / 2) = *reinterpret_cast<uint2*>(packed);
     if (vec_a && deq) store16_bf16(deq + (long long)o * cols + kb * 16, v[rr]);
@@ -325,22 +316,22 @@ __global__ void __launch_bounds__(256) nvfp4_quantize16_coop_kernel(uint8_t* __r
   }
   uint8_t packed[8];
 #pragma unroll
-  for (int i = 0; i < 16; i += 2) {
-    int c[2];
-    float u[2] = {0.f, 0.f};
-    if (sr) {                                             // one draw per pair, counted at the pair's first element
+  for (int i = 0; i < 16; i += 4) {
+    const float s0 = v[i] * inv, s1 = v[i + 1] * inv, s2 = v[i + 2] * inv, s3 = v[i + 3] * inv;
+    uint32_t code4;
+    if (sr) {                                             // one draw per four values, counted at the first of them
       const int o = axis == 1 ? br * 16 + l : br * 16 + i;
       const int k = axis == 1 ? kb * 16 + i : kb * 16 + l;
-      rng_uniform01_pair(key, ((unsigned long long)step << 32) | ((unsigned long long)o * K + k), u);
-    }
+      code4 = e2m1x4_rs(s0, s1, s2, s3, squares32(((unsigned long long)step << 32) | ((unsigned long long)o * K + k), key));
+    } else code4 = e2m1x2_rn(s0, s1) | (e2m1x2_rn(s2, s3) << 8);
+    packed[i / 2] = (uint8_t)code4; packed[i / 2 + 1] = (uint8_t)(code4 >> 8);
+    if (deq) {
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const float sv = v[i + t] * inv;
-      if (sr) c[t] = encode_e2m1_sr(sv, u[t]);
-      else c[t] = encode_e2m1_rne(sv);
-      v[i + t] = (c[t] & 8 ? -1.f : 1.f) * e2m1_value(c[t]) * sc_dec;
+      for (int t = 0; t < 4; ++t) {
+        const int c = (code4 >> (4 * t)) & 15;
+        v[i + t] = (c & 8 ? -1.f : 1.f) * e2m1_value(c) * sc_dec;
+      }
     }
-    packed[i / 2] = (uint8_t)(c[0] | (c[1] << 4));
   }
   if (q) {
     uint2 mine = *reinterpret_cast<uint2*>(packed);

@@ -221,12 +221,18 @@ def hadamard16(x: torch.Tensor, inverse: bool = False) -> torch.Tensor:
 
 
 def _e2m1_round(v: torch.Tensor, rnd: Optional[torch.Tensor]) -> torch.Tensor:
-    """Round |v| onto the e2m1 grid: nearest with ties away from zero, or stochastically."""
+    """Round |v| onto the e2m1 grid: nearest with ties to the even code (what the hardware convert
+    ``cvt.rn.satfinite.e2m1x2.f32`` of the GPU kernels does), or stochastically."""
     a = v.abs().clamp(max=6.0)
     grid = E2M1_GRID.to(v.device)
     if rnd is None:
         mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=v.device)
-        idx = torch.bucketize(a.contiguous(), mids, right=True)
+        a = a.contiguous()
+        idx = torch.bucketize(a, mids, right=True)                       # a tie goes up ...
+        tie_down = torch.zeros_like(a, dtype=torch.bool)
+        for j in (0, 2, 4, 6):                                           # ... unless the lower neighbour is the even code
+            tie_down |= a == mids[j]
+        idx = idx - tie_down.long()
     else:
         lo = (torch.bucketize(a.contiguous(), grid, right=True) - 1).clamp(0, 7)
         hi = (lo + 1).clamp(max=7)

@@ -106,7 +106,22 @@ def case_fusedgather(reps):
     print("max abs diff vs fp32 reference", (out.float() - want).abs().max().item())
 
 
-CASES = {"fusedgather": case_fusedgather, "attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
+def case_nvfp4(reps):
+    """NVFP4 linear layer pieces: stochastic-rounding quantise (both orientations), native block-scaled GEMM."""
+    from llm_mojo_b200.ops import lowp
+    rows, C, OC = 8192, 1600, 6400
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w = (torch.randn(OC, C, device="cuda") * 0.02).bfloat16()
+    d = torch.randn(rows, OC, device="cuda").bfloat16()
+    out = torch.empty(rows, OC, device="cuda", dtype=torch.bfloat16)
+    dinp = torch.empty(rows, C, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(OC, C, device="cuda")
+    for i in range(reps):
+        lowp.matmul_fwd_fp4(out, x, w, None)
+        lowp.matmul_bwd_fp4(dinp, dw, None, d, x, w, seed=1, step=i)
+
+
+CASES = {"nvfp4": case_nvfp4, "fusedgather": case_fusedgather, "attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
