@@ -35,6 +35,15 @@ __device__ __forceinline__ uint32_t squares32(uint64_t ctr, uint64_t key) {
   x = x * x + y; x = (x >> 32) | (x << 32);
   return (uint32_t)((x * x + z) >> 32);
 }
+// The 64-bit output variant (one more round): eight values' worth of random bits for the stochastic-rounding converts.
+__device__ __forceinline__ uint64_t squares64(uint64_t ctr, uint64_t key) {
+  uint64_t x = ctr * key, y = x, z = y + key;
+  x = x * x + y; x = (x >> 32) | (x << 32);
+  x = x * x + z; x = (x >> 32) | (x << 32);
+  x = x * x + y; x = (x >> 32) | (x << 32);
+  x = x * x + z; const uint64_t t = x; x = (x >> 32) | (x << 32);
+  return t ^ ((x * x + y) >> 32);
+}
 __device__ __forceinline__ float rng_uniform01(uint64_t seed, uint64_t ctr, uint64_t stream) {
   return (float)(squares32(ctr, rng_key(seed, stream)) >> 8) * (1.0f / 16777216.0f);
 }
@@ -244,13 +253,15 @@ __global__ void nvfp4_quantize_kernel(uint8_t* __restrict__ q, uint8_t* __restri
     if (o >= outer) continue;
     if (scales) scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(o, kb, n_col_tiles) : (long long)o * kblocks + kb] = sc_code;
     uint8_t packed[8];
+    uint64_t rbits = 0;
 #pragma unroll
     for (int kk = 0; kk < 16; kk += 4) {
       const float s0 = v[rr][kk] * inv, s1 = v[rr][kk + 1] * inv, s2 = v[rr][kk + 2] * inv, s3 = v[rr][kk + 3] * inv;
       uint32_t code4;                                     // four codes, value kk in the lowest nibble
-      if (sr)                                             // one draw per four values, counted at the first of them
-        code4 = e2m1x4_rs(s0, s1, s2, s3, squares32(((unsigned long long)step << 32) | ((unsigned long long)o * K + kb * 16 + kk), key));
-      else code4 = e2m1x2_rn(s0, s1) | (e2m1x2_rn(s2, s3) << 8);
+      if (sr) {                                           // one 64-bit draw per eight values, counted at the first of them
+        if ((kk & 4) == 0) rbits = squares64(((unsigned long long)step << 32) | ((unsigned long long)o * K + kb * 16 + kk), key);
+        code4 = e2m1x4_rs(s0, s1, s2, s3, (uint32_t)(rbits >> ((kk & 4) * 8)));
+      } else code4 = e2m1x2_rn(s0, s1) | (e2m1x2_rn(s2, s3) << 8);
       packed[kk / 2] = (uint8_t)code4; packed[kk / 2 + 1] = (uint8_t)(code4 >> 8);
       if (deq) {
 #pragma unroll
@@ -315,14 +326,18 @@ __global__ void __launch_bounds__(256) nvfp4_quantize16_coop_kernel(uint8_t* __r
     scales[n_col_tiles > 0 ? nvfp4_scale_swizzle_offset(o, kb, n_col_tiles) : (long long)o * kblocks + kb] = sc_code;
   }
   uint8_t packed[8];
+  uint64_t rbits = 0;
 #pragma unroll
   for (int i = 0; i < 16; i += 4) {
     const float s0 = v[i] * inv, s1 = v[i + 1] * inv, s2 = v[i + 2] * inv, s3 = v[i + 3] * inv;
     uint32_t code4;
-    if (sr) {                                             // one draw per four values, counted at the first of them
-      const int o = axis == 1 ? br * 16 + l : br * 16 + i;
-      const int k = axis == 1 ? kb * 16 + i : kb * 16 + l;
-      code4 = e2m1x4_rs(s0, s1, s2, s3, squares32(((unsigned long long)step << 32) | ((unsigned long long)o * K + k), key));
+    if (sr) {                                             // one 64-bit draw per eight values, counted at the first of them
+      if ((i & 4) == 0) {
+        const int o = axis == 1 ? br * 16 + l : br * 16 + i;
+        const int k = axis == 1 ? kb * 16 + i : kb * 16 + l;
+        rbits = squares64(((unsigned long long)step << 32) | ((unsigned long long)o * K + k), key);
+      }
+      code4 = e2m1x4_rs(s0, s1, s2, s3, (uint32_t)(rbits >> ((i & 4) * 8)));
     } else code4 = e2m1x2_rn(s0, s1) | (e2m1x2_rn(s2, s3) << 8);
     packed[i / 2] = (uint8_t)code4; packed[i / 2 + 1] = (uint8_t)(code4 >> 8);
     if (deq) {
