@@ -187,6 +187,136 @@ __global__ void __launch_bounds__(1024, 1) classifier_stream_kernel(__nv_bfloat1
   if (tid == 0) bulk_wait<0>();             // shared memory must outlive the last store
 }
 
+// The same streaming kernel with the row traffic on its own warp.  In the kernel above thread 0 waits for the previous
+// row's store to have read its buffer before it may prefetch the next row, and everybody waits for thread 0 at the next
+// barrier: the store's read-out is serialised with the row's arithmetic.  Here warps 0..30 (992 threads, named barrier 1)
+// only compute; warp 31 moves rows: it stores a buffer once the compute warps hand it over (`done`), waits for that
+// store to have read the buffer and refills it with the row after next (`full`).  Per row the steady state is
+// max(arithmetic, (arithmetic + store + load) / 2) instead of store + arithmetic.
+__global__ void __launch_bounds__(1024, 1) classifier_stream2_kernel(__nv_bfloat16* __restrict__ logits, float* __restrict__ losses,
+                                                                     const int* __restrict__ targets, float dloss, int rows, int V,
+                                                                     int Vp, int write_dlogits, int buf_bytes, int* status) {
+  using T = __nv_bfloat16;
+  constexpr int N = 8;
+  constexpr int NC = 992, NCW = 31;                       // compute threads / warps
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ uint64_t full[2], done[2];
+  __shared__ float red[32];
+  __shared__ float bcast[2];
+  __shared__ int fail_s;
+  const int tid = threadIdx.x, lane = tid % 32, wid = tid / 32;
+  const uint32_t row_bytes = (uint32_t)Vp * 2;
+  const int nvec = Vp / N;
+  if (tid == 0) {
+    mbar_init(&full[0], 1); mbar_init(&full[1], 1); mbar_init(&done[0], 1); mbar_init(&done[1], 1);
+    fail_s = 0; fence_barrier_init();
+  }
+  __syncthreads();
+  auto csync = [] { asm volatile("bar.sync 1, 992;" ::: "memory"); };
+
+  if (wid == NCW) {
+    // ------------------------------------------------------------ row mover (one lane)
+    if (lane == 0) {
+      for (int j = 0; j < 2; ++j) {
+        const long long r = (long long)blockIdx.x + (long long)j * gridDim.x;
+        if (r < rows) { mbar_expect_tx(&full[j], row_bytes); bulk_load_1d(smraw + (size_t)j * buf_bytes, logits + (size_t)r * Vp, row_bytes, &full[j]); }
+      }
+      int it = 0;
+      for (int r = blockIdx.x; r < rows; r += gridDim.x, ++it) {
+        const int b = it & 1;
+        unsigned char* buf = smraw + (size_t)b * buf_bytes;
+        if (!mbar_wait(&done[b], (it >> 1) & 1)) { atomicExch(status, LLMB_ERR_TIMEOUT); break; }
+        if (write_dlogits) { bulk_store_1d(logits + (size_t)r * Vp, buf, row_bytes); bulk_commit(); }
+        const long long rn = (long long)r + 2ll * gridDim.x;
+        if (rn < rows) {
+          if (write_dlogits) bulk_wait_read<0>();         // the store has read the buffer
+          mbar_expect_tx(&full[b], row_bytes);
+          bulk_load_1d(buf, logits + (size_t)rn * Vp, row_bytes, &full[b]);
+        }
+      }
+      bulk_wait<0>();                                     // shared memory must outlive the last store
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- compute warps
+  const float L2E = 1.4426950408889634f;
+  const int nfull = V / N;                                // vectors entirely below V
+  int it = 0;
+  for (int r = blockIdx.x; r < rows; r += gridDim.x, ++it) {
+    const int b = it & 1;
+    T* row_s = reinterpret_cast<T*>(smraw + (size_t)b * buf_bytes);
+    if (!mbar_wait(&full[b], (it >> 1) & 1)) { atomicExch(status, LLMB_ERR_TIMEOUT); fail_s = 1; }
+    csync();
+    if (fail_s) break;
+    // pass 1: row maximum over the real vocabulary
+    float mx = -INFINITY;
+    for (int v = tid; v < nfull; v += NC) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) mx = fmaxf(mx, p.v[k]);
+    }
+    for (int v = nfull + tid; v < nvec; v += NC) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) if (v * N + k < V) mx = fmaxf(mx, p.v[k]);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) red[wid] = mx;
+    csync();
+    if (wid == 0) { float m = lane < NCW ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bcast[0] = m; }
+    csync();
+    mx = bcast[0];
+    const int tgt = targets[r];
+    const float x_tgt = __bfloat162float(row_s[tgt]);     // read before the buffer is overwritten
+    csync();
+    // pass 2: e = 2^((x - max) log2 e), once per element, written back over the row
+    float sum = 0.f;
+    const float mb = mx * L2E;
+    for (int v = tid; v < nfull; v += NC) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) { p.v[k] = ex2_fast(fmaf(p.v[k], L2E, -mb)); sum += p.v[k]; }
+      if (write_dlogits) p.store(row_s + v * N);
+    }
+    for (int v = nfull + tid; v < nvec; v += NC) {
+      Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+      for (int k = 0; k < N; ++k) { p.v[k] = (v * N + k < V) ? ex2_fast(fmaf(p.v[k], L2E, -mb)) : 0.f; sum += p.v[k]; }
+      if (write_dlogits) p.store(row_s + v * N);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) red[wid] = sum;
+    csync();
+    if (wid == 0) { float s = lane < NCW ? red[lane] : 0.f; s = warp_sum(s); if (lane == 0) bcast[1] = s; }
+    csync();
+    sum = bcast[1];
+    if (tid == 0 && losses) losses[r] = -(x_tgt - mx - logf(sum));
+    if (write_dlogits) {
+      // pass 3: dlogits = (e / sum - 1[target]) dloss in place (padded columns hold e = 0); the target column is
+      // corrected afterwards by one thread; then the row is handed to the mover
+      const float inv = dloss / sum;
+      for (int v = tid; v < nvec; v += NC) {
+        Pack<T> p; p.load(row_s + v * N);
+#pragma unroll
+        for (int k = 0; k < N; ++k) p.v[k] *= inv;
+        p.store(row_s + v * N);
+      }
+      fence_proxy_async();                                // these writes, before the mover's bulk store reads them
+      csync();
+      if (tid == 0) {
+        const float e_t = ex2_fast(fmaf(x_tgt, L2E, -mb));
+        row_s[tgt] = __float2bfloat16(__bfloat162float(__float2bfloat16(e_t)) * inv - dloss);
+        fence_proxy_async();
+        mbar_arrive(&done[b]);
+      }
+    } else {
+      csync();                                            // everyone is done with the buffer before it is reloaded
+      if (tid == 0) mbar_arrive(&done[b]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void softmax_rows_kernel(float* __restrict__ out, const T* __restrict__ inp, int V, int ld, float inv_temp) {
   __shared__ float red[32];
@@ -212,13 +342,19 @@ LLMB_API int llmb_fused_classifier(void* logits, float* losses, const int* targe
   if (dtype == LLMB_BF16) {
     if (Vp % 8) return LLMB_ERR_BAD_ARG;
     static int stream_on = -1;
-    if (stream_on < 0) { const char* e = getenv("LLMB_CLASSIFIER_STREAM"); stream_on = (e && e[0] == '0') ? 0 : 1; }
+    if (stream_on < 0) { const char* e = getenv("LLMB_CLASSIFIER_STREAM"); stream_on = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : 1; }
     const int buf_bytes = (Vp * 2 + 127) & ~127;
     if (stream_on && status && 2 * buf_bytes <= 224 * 1024 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
-      cudaFuncSetAttribute(classifier_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * buf_bytes);
       const int grid = rows < sm_count() ? rows : sm_count();
-      classifier_stream_kernel<<<grid, 1024, 2 * buf_bytes, st>>>((__nv_bfloat16*)logits, losses, targets, dloss, rows, V, Vp,
-                                                                 write_dlogits, buf_bytes, status);
+      if (stream_on == 2) {                               // LLMB_CLASSIFIER_STREAM=2: row traffic on thread 0 of the compute block
+        cudaFuncSetAttribute(classifier_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * buf_bytes);
+        classifier_stream_kernel<<<grid, 1024, 2 * buf_bytes, st>>>((__nv_bfloat16*)logits, losses, targets, dloss, rows, V, Vp,
+                                                                   write_dlogits, buf_bytes, status);
+      } else {
+        cudaFuncSetAttribute(classifier_stream2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * buf_bytes);
+        classifier_stream2_kernel<<<grid, 1024, 2 * buf_bytes, st>>>((__nv_bfloat16*)logits, losses, targets, dloss, rows, V, Vp,
+                                                                    write_dlogits, buf_bytes, status);
+      }
       return (int)cudaGetLastError();
     }
     size_t smem = (size_t)Vp * 2;
