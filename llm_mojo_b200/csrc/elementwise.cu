@@ -182,18 +182,27 @@ LLMB_API int llmb_gelu_bwd(void* dinp, const void* inp, const void* dout, long l
 // ---------------------------------------------------------------- dbias: dbias[c] += sum_rows dout[row, c]
 // Stage 1: grid (col blocks, row slabs); each block owns 32*N columns... threads (8 row lanes x 32 col vecs).
 // partial[slab][c] written to scratch; stage 2 sums slabs in order (deterministic) and accumulates.
-template <typename T>
-__global__ void dbias_partial_kernel(float* __restrict__ partial, const T* __restrict__ dout, int rows, int OC, int rows_per_slab) {
+template <typename T, int RL>
+__global__ void __launch_bounds__(256) dbias_partial_kernel(float* __restrict__ partial, const T* __restrict__ dout, int rows, int OC, int rows_per_slab) {
   constexpr int N = Pack<T>::N;
-  __shared__ float sm[8][32 * N + 1];
-  int cv = threadIdx.x % 32, rl = threadIdx.x / 32;  // 256 threads: 8 row lanes
-  int c0 = (blockIdx.x * 32 + cv) * N;
+  constexpr int CV = 256 / RL;                           // column vectors per block; RL row lanes
+  __shared__ float sm[RL][CV * N + 1];
+  int cv = threadIdx.x % CV, rl = threadIdx.x / CV;
+  int c0 = (blockIdx.x * CV + cv) * N;
   int r0 = blockIdx.y * rows_per_slab, r1 = min(rows, r0 + rows_per_slab);
   float acc[N];
 #pragma unroll
   for (int k = 0; k < N; ++k) acc[k] = 0.f;
   if (c0 < OC) {
-    for (int r = r0 + rl; r < r1; r += 8) {
+    int r = r0 + rl;
+    for (; r + 3 * RL < r1; r += 4 * RL) {              // four independent loads in flight per thread
+      Pack<T> p0, p1, p2, p3;
+      p0.load(dout + (size_t)r * OC + c0); p1.load(dout + (size_t)(r + RL) * OC + c0);
+      p2.load(dout + (size_t)(r + 2 * RL) * OC + c0); p3.load(dout + (size_t)(r + 3 * RL) * OC + c0);
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] += (p0.v[k] + p1.v[k]) + (p2.v[k] + p3.v[k]);
+    }
+    for (; r < r1; r += RL) {
       Pack<T> p; p.load(dout + (size_t)r * OC + c0);
 #pragma unroll
       for (int k = 0; k < N; ++k) acc[k] += p.v[k];
@@ -202,24 +211,49 @@ __global__ void dbias_partial_kernel(float* __restrict__ partial, const T* __res
 #pragma unroll
   for (int k = 0; k < N; ++k) sm[rl][cv * N + k] = acc[k];
   __syncthreads();
-  for (int c = threadIdx.x; c < 32 * N; c += blockDim.x) {
-    int col = blockIdx.x * 32 * N + c;
+  for (int c = threadIdx.x; c < CV * N; c += blockDim.x) {
+    int col = blockIdx.x * CV * N + c;
     if (col < OC) {
       float s = 0.f;
 #pragma unroll
-      for (int l = 0; l < 8; ++l) s += sm[l][c];
+      for (int l = 0; l < RL; ++l) s += sm[l][c];
       partial[(size_t)blockIdx.y * OC + col] = s;
     }
   }
 }
-__global__ void dbias_final_kernel(float* __restrict__ dbias, const float* __restrict__ partial, int OC, int slabs) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= OC) return;
-  float s = 0.f;
-  for (int i = 0; i < slabs; ++i) s += partial[(size_t)i * OC + c];
-  dbias[c] += s;
+// narrow matrices get more row lanes per block (fewer columns per block) so that the grid still fills the machine
+template <typename T>
+void dbias_partial_launch(float* partial, const T* dout, int rows, int OC, int rows_per_slab, int slabs, cudaStream_t st) {
+  constexpr int N = Pack<T>::N;
+  const int want = 6 * sm_count();
+  if (ceil_div(OC, 32 * N) * slabs >= want)
+    dbias_partial_kernel<T, 8><<<dim3(ceil_div(OC, 32 * N), slabs), 256, 0, st>>>(partial, dout, rows, OC, rows_per_slab);
+  else if (ceil_div(OC, 16 * N) * slabs >= want)
+    dbias_partial_kernel<T, 16><<<dim3(ceil_div(OC, 16 * N), slabs), 256, 0, st>>>(partial, dout, rows, OC, rows_per_slab);
+  else
+    dbias_partial_kernel<T, 32><<<dim3(ceil_div(OC, 8 * N), slabs), 256, 0, st>>>(partial, dout, rows, OC, rows_per_slab);
 }
-LLMB_API int llmb_dbias_slabs(int rows) { int s = ceil_div(rows, 512); return s > 128 ? 128 : (s < 1 ? 1 : s); }
+// Stage 2: 32 columns per block, eight threads per column each summing every eighth slab (independent loads in flight
+// instead of one thread walking all slabs), then a fixed-order sum of the eight: deterministic.
+__global__ void __launch_bounds__(256) dbias_final_kernel(float* __restrict__ dbias, const float* __restrict__ partial, int OC, int slabs) {
+  __shared__ float sm[8][33];
+  const int cl = threadIdx.x % 32, sl = threadIdx.x / 32;
+  const int c = blockIdx.x * 32 + cl;
+  float s = 0.f;
+  if (c < OC) {
+#pragma unroll 4
+    for (int i = sl; i < slabs; i += 8) s += partial[(size_t)i * OC + c];
+  }
+  sm[sl][cl] = s;
+  __syncthreads();
+  if (sl == 0 && c < OC) {
+    float t = 0.f;
+#pragma unroll
+    for (int l = 0; l < 8; ++l) t += sm[l][cl];
+    dbias[c] += t;
+  }
+}
+LLMB_API int llmb_dbias_slabs(int rows) { int s = ceil_div(rows, 128); return s > 128 ? 128 : (s < 1 ? 1 : s); }
 LLMB_API long long llmb_dbias_scratch_bytes(int rows, int OC) { return (long long)llmb_dbias_slabs(rows) * OC * sizeof(float); }
 LLMB_API int llmb_dbias(float* dbias, const void* dout, float* scratch, long long scratch_bytes, int rows, int OC,
                         int dtype, cudaStream_t st) {
@@ -228,14 +262,12 @@ LLMB_API int llmb_dbias(float* dbias, const void* dout, float* scratch, long lon
   int rows_per_slab = ceil_div(rows, slabs);
   if (dtype == LLMB_BF16) {
     if (OC % 8) return LLMB_ERR_BAD_ARG;
-    dim3 grid(ceil_div(OC, 32 * 8), slabs);
-    dbias_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(scratch, (const __nv_bfloat16*)dout, rows, OC, rows_per_slab);
+    dbias_partial_launch<__nv_bfloat16>(scratch, (const __nv_bfloat16*)dout, rows, OC, rows_per_slab, slabs, st);
   } else {
     if (OC % 4) return LLMB_ERR_BAD_ARG;
-    dim3 grid(ceil_div(OC, 32 * 4), slabs);
-    dbias_partial_kernel<float><<<grid, 256, 0, st>>>(scratch, (const float*)dout, rows, OC, rows_per_slab);
+    dbias_partial_launch<float>(scratch, (const float*)dout, rows, OC, rows_per_slab, slabs, st);
   }
-  dbias_final_kernel<<<ceil_div(OC, 256), 256, 0, st>>>(dbias, scratch, OC, slabs);
+  dbias_final_kernel<<<ceil_div(OC, 32), 256, 0, st>>>(dbias, scratch, OC, slabs);
   return (int)cudaGetLastError();
 }
 
@@ -307,15 +339,13 @@ LLMB_API int llmb_dbias_noalloc(float* dbias, const void* dout, int rows, int OC
   const int rows_per_slab = ceil_div(rows, slabs);
   if (dtype == LLMB_BF16) {
     if (OC % 8) return LLMB_ERR_BAD_ARG;
-    dim3 grid(ceil_div(OC, 32 * 8), slabs);
-    dbias_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(scratch, (const __nv_bfloat16*)dout, rows, OC, rows_per_slab);
+    dbias_partial_launch<__nv_bfloat16>(scratch, (const __nv_bfloat16*)dout, rows, OC, rows_per_slab, slabs, st);
   } else if (dtype == LLMB_F32) {
     if (OC % 4) return LLMB_ERR_BAD_ARG;
-    dim3 grid(ceil_div(OC, 32 * 4), slabs);
-    dbias_partial_kernel<float><<<grid, 256, 0, st>>>(scratch, (const float*)dout, rows, OC, rows_per_slab);
+    dbias_partial_launch<float>(scratch, (const float*)dout, rows, OC, rows_per_slab, slabs, st);
   } else {
     return LLMB_ERR_BAD_ARG;
   }
-  dbias_final_kernel<<<ceil_div(OC, 256), 256, 0, st>>>(dbias, scratch, OC, slabs);
+  dbias_final_kernel<<<ceil_div(OC, 32), 256, 0, st>>>(dbias, scratch, OC, slabs);
   return (int)cudaGetLastError();
 }
