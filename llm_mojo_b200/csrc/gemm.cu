@@ -74,6 +74,7 @@ struct GemmParams {
   int io_f32;                  // 1: D, bias and aux are fp32 (tf32 kind); 0: bf16
   int tma_epi;                 // 1: bf16 outputs leave (and auxiliary inputs arrive) by TMA; 0: register/shared-memory epilogue
   int bias_vec;                // bias pointer is 16-byte aligned (vector loads)
+  float* colsum;               // EPI_DGELU, TMA epilogue: colsum[n] += sum over rows of the (bf16) result, i.e. the bias gradient of the layer below
   int dbg;                     // measurement switches: 1 = drain accumulators without storing, 2 = always fetch tile (0,0), 8 = skip the GELU math
   int* status;
 };
@@ -694,6 +695,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           epi_slab_bf16<EPI>(p, r0, r1, buf, col0, alpha, lane);
           fence_proxy_async();
           __syncwarp();
+          if (EPI == EPI_DGELU && p.colsum) {
+            // column sums of the slab as stored (bf16): lane l adds up columns 2l and 2l + 1 of the warp's rows out of the
+            // swizzled box (conflict-free: the 32 lanes read the 128 bytes of one row) and adds them to colsum
+            float s0 = 0.f, s1 = 0.f;
+            const int nrows = min(32, p.M - row0);
+#pragma unroll 8
+            for (int r = 0; r < nrows; ++r) {
+              const uint32_t w = *reinterpret_cast<const uint32_t*>(buf + r * 128 + ((((lane >> 2) ^ (r & 7))) << 4) + (lane & 3) * 4);
+              s0 += __uint_as_float(w << 16); s1 += __uint_as_float(w & 0xffff0000u);
+            }
+            const int col = col0 + 2 * lane;
+            if (col < p.N) {
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.colsum + col), "f"(s0) : "memory");
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(p.colsum + col + 1), "f"(s1) : "memory");
+            }
+          }
           if (lane == 0 && !(p.dbg & 1)) {
             if (Cfg::TWO_OUT) {
               tma_store_2d(&tmAux, buf, col0, row0);
@@ -739,6 +756,7 @@ template <> struct KindTraits<KIND_TF32> { static constexpr int ESZ = 4; static 
 template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ESZ = 1; static constexpr CUtensorMapDataType DT = CU_TENSOR_MAP_DATA_TYPE_UINT8; };
 
 int g_dbg_mn_lbo = -1, g_dbg_mn_sbo = -1;   // test hooks: override the MN-major descriptor strides
+thread_local float* g_pending_colsum = nullptr;   // armed by llmb_gemm_set_colsum, consumed by the calling thread's next llmb_gemm
 thread_local GatherArgs g_pending_gather{};   // armed by llmb_gemm_set_gather, consumed (and cleared) by the calling thread's next llmb_gemm
 int g_pair_mode = -1;                         // -1: read LLMB_GEMM_PAIR once; 0: single-CTA tiles; 1: CTA-pair tiles
 
@@ -816,6 +834,9 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   GemmParams p;
   p.g = g_pending_gather;
   g_pending_gather.W = 0;
+  p.colsum = g_pending_colsum;
+  g_pending_colsum = nullptr;
+  if (p.colsum && !(pair && epi == EPI_DGELU && KIND == KIND_F16)) return LLMB_ERR_BAD_ARG;
   if (p.g.W > 1) {
     // gathered A: K-major bf16 rows, CTA-pair kernel, whole 256-row tiles per chunk, no split-K
     if (!pair || a_mn || KIND != KIND_F16 || p.g.tiles_per_chunk <= 0 || M != p.g.W * p.g.tiles_per_chunk * 2 * BM || epi == EPI_ACC_F32)
@@ -861,6 +882,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
         ok = make_tmap_2d(&taux, aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldaux, 32, 64) == 0;
       p.tma_epi = ok;
     }
+    if (p.colsum && !p.tma_epi) return LLMB_ERR_BAD_ARG;   // the column sums are taken in the TMA epilogue only
     switch (epi) {
       case EPI_NONE: return launch_pair<KIND, EPI_NONE>(ta, tb, td, taux, p, grid2, st);
       case EPI_BIAS: return launch_pair<KIND, EPI_BIAS>(ta, tb, td, taux, p, grid2, st);
@@ -1207,6 +1229,9 @@ LLMB_API void llmb_gemm_set_gather(void* const* peer_src, void* local, const voi
   g.seq = seq; g.target = (unsigned)((g.chunk_vecs + 2047) / 2048); g.W = W; g.me = me; g.tiles_per_chunk = rows_per_rank / (2 * BM);
   g_pending_gather = g;
 }
+// Arms the calling thread's NEXT llmb_gemm call (bf16, epilogue 3 = dGELU, CTA-pair kernel with the TMA epilogue) to add the column
+// sums of its result to colsum[N] (fp32, red.add): the bias gradient of the layer that produced the pre-activations.
+LLMB_API void llmb_gemm_set_colsum(float* colsum) { g_pending_colsum = colsum; }
 LLMB_API void llmb_gemm_debug_mn_strides(int lbo_bytes, int sbo_bytes) { g_dbg_mn_lbo = lbo_bytes; g_dbg_mn_sbo = sbo_bytes; }
 // 0: single-CTA 128x256 tiles, 1: CTA-pair 256x256 tiles (default; env LLMB_GEMM_PAIR=0 selects the former)
 LLMB_API void llmb_gemm_set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }

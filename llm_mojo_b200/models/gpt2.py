@@ -425,8 +425,11 @@ class GPT2:
                 ops.gelu_fwd(gelu_out, a["fch"][l])       # train_gpt2.mojo:4490-4502
             else:
                 gelu_out = a["fch_gelu"][l]
-            self._linear_bwd("fcproj", l, dl4, g["fcprojw"][l], g["fcprojb"][l], dres, gelu_out, p["fcprojw"][l], gelu_pre=a["fch"][l])
-            self._linear_bwd("fc", l, dl, g["fcw"][l], g["fcb"][l], dl4, a["ln2"][l], p["fcw"][l])
+            # bf16 MLP: the fc bias gradient (column sums of dl4) is taken in the epilogue of the GEMM that writes dl4
+            fc_dbias_upstream = self._site_mode("fcproj", l) == "bf16" and self._site_mode("fc", l) == "bf16"
+            kw = {"dinp_colsum": g["fcb"][l]} if fc_dbias_upstream else {}
+            self._linear_bwd("fcproj", l, dl4, g["fcprojw"][l], g["fcprojb"][l], dres, gelu_out, p["fcprojw"][l], gelu_pre=a["fch"][l], **kw)
+            self._linear_bwd("fc", l, dl, g["fcw"][l], None if fc_dbias_upstream else g["fcb"][l], dl4, a["ln2"][l], p["fcw"][l])
             ops.layernorm_bwd(dres, g["ln2w"][l], g["ln2b"][l], dl, a["residual2"][l], p["ln2w"][l],
                               a["ln2_mean"][l], a["ln2_rstd"][l], accumulate=True)
             self._linear_bwd("attproj", l, dl, g["attprojw"][l], g["attprojb"][l], dres, a["atty"][l], p["attprojw"][l])

@@ -174,11 +174,14 @@ EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_DGELU, EPI_ACC_F32, EPI_BIAS_RESID, EPI_S
 
 
 def gemm(D, A, B, *, a_mn=False, b_mn=False, epi=EPI_NONE, bias=None, aux=None, alpha=None, splits=1,
-         kind: int = 0, a_fmt: int = 0, b_fmt: int = 0) -> None:
+         kind: int = 0, a_fmt: int = 0, b_fmt: int = 0, colsum=None) -> None:
     """Raw tcgen05 GEMM: D[M,N] = epi(A·Bᵀ).  A is [M,K] (or [K,M] when ``a_mn``), B is [N,K]
-    (or [K,N] when ``b_mn``); all row-major with arbitrary row pitch."""
+    (or [K,N] when ``b_mn``); all row-major with arbitrary row pitch.  ``colsum`` (fp32 [N], dGELU epilogue of
+    the bf16 kernel only, see ``colsum_usable``) accumulates the column sums of D inside the epilogue."""
     M, N = D.shape
     K = A.shape[0] if a_mn else A.shape[1]
+    if colsum is not None:
+        lib().llmb_gemm_set_colsum(ptr(colsum))
     check(lib().llmb_gemm(ptr(D), ptr(A), ptr(B), ptr(bias), ptr(aux), ptr(alpha), M, N, K, A.stride(0), B.stride(0),
                           D.stride(0), aux.stride(0) if aux is not None else 0, int(a_mn), int(b_mn), kind, a_fmt,
                           b_fmt, epi, splits, ptr(status_word(D.device)), stream()), "gemm")
@@ -206,6 +209,18 @@ def gemm_mxfp8(D, qa, sfa, qb, sfb, *, a_fmt=0, b_fmt=0, epi=EPI_NONE, bias=None
                                 D.stride(0), aux.stride(0) if aux is not None else 0, epi, splits,
                                 ptr(status_word(D.device)), stream()), "gemm_mxfp8")
     _count()
+
+
+def colsum_usable(D: torch.Tensor, aux: torch.Tensor) -> bool:
+    """The dGELU GEMM can add the column sums of its result (the bias gradient of the layer below) in its epilogue when
+    it runs as the bf16 CTA-pair kernel with the TMA epilogue: 16-byte aligned bf16 rows of D and aux."""
+    if not (D.is_cuda and D.dtype == torch.bfloat16 and aux.dtype == torch.bfloat16 and GEMM_IMPL == "tcgen05"):
+        return False
+    if os.environ.get("LLMB_GEMM_PAIR", "1") == "0" or os.environ.get("LLMB_GEMM_TMA_EPI", "1") == "0":
+        return False
+    if os.environ.get("LLMM_FUSED_FC_DBIAS", "1") == "0":
+        return False
+    return (D.data_ptr() | aux.data_ptr()) % 16 == 0 and (D.stride(0) * 2) % 16 == 0 and (aux.stride(0) * 2) % 16 == 0
 
 
 def _tc_kind(t: torch.Tensor):
@@ -260,8 +275,10 @@ def matmul_fwd(out, inp, weight, bias=None, *, pre_gelu=None, residual=None) -> 
     o.copy_(y)
 
 
-def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> None:
+def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None, dinp_colsum=None) -> None:
     """dinp = dout·W (⊙ gelu'(gelu_pre)); dweight += doutᵀ·inp; dbias += Σ_rows dout (each output may be None).
+    ``dinp_colsum`` (fp32 [C]) += Σ_rows dinp: the bias gradient of the layer whose output gradient dinp is, taken
+    inside the dGELU epilogue when the kernel allows it, by a separate reduction otherwise.
 
     dweight / dbias are fp32 accumulators (llmm/matmul.mojo:3512-3563, DGELU epilogue :2789-2938)."""
     OC, C = weight.shape
@@ -273,9 +290,15 @@ def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> Non
         if dinp is not None:
             di = dinp.view(rows, C)
             if gelu_pre is not None:
-                gemm(di, d, weight, b_mn=True, epi=EPI_DGELU, aux=gelu_pre.view(rows, C), kind=kind)
+                aux = gelu_pre.view(rows, C)
+                fused = dinp_colsum is not None and kind == 0 and colsum_usable(di, aux)
+                gemm(di, d, weight, b_mn=True, epi=EPI_DGELU, aux=aux, kind=kind, colsum=dinp_colsum if fused else None)
+                if dinp_colsum is not None and not fused:
+                    dbias_reduce(dinp_colsum, di)
             else:
                 gemm(di, d, weight, b_mn=True, epi=EPI_NONE, kind=kind)
+                if dinp_colsum is not None:
+                    dbias_reduce(dinp_colsum, di)
         if dweight is not None:
             gemm(dweight.view(OC, C), d, x, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), kind=kind)
         if dbias is not None:
@@ -286,6 +309,8 @@ def matmul_bwd(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=None) -> Non
         if gelu_pre is not None:
             g = g.float() * _gelu_grad_t(gelu_pre.view(rows, C).float())
         dinp.view(rows, C).copy_(g)
+        if dinp_colsum is not None:
+            dinp_colsum += dinp.view(rows, C).float().sum(0)
     if dweight is not None:
         dweight.view(OC, C).add_((d.t() @ x).float())
     if dbias is not None:

@@ -44,6 +44,7 @@ _SIGS = {
     "llmb_gemm_nvfp4": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int, c_p, c_p],
     "llmb_gemm_mxfp8": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int, c_p, c_p],
     "llmb_fp8_block_quant": [c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_p],
+    "llmb_gemm_set_colsum": [c_p],
     "llmb_gemm_debug_mn_strides": [c_int, c_int],
     "llmb_gemm_set_pair_mode": [c_int],
     "llmb_amax": [c_p, c_p, c_ll, c_int, c_p],

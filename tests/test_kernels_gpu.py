@@ -298,3 +298,23 @@ def test_nan_census(dtype):
     assert ops.nan_census(x) == (0, 0)
     x[5] = float("nan"); x[77777] = float("nan"); x[999_999] = float("inf"); x[123] = float("-inf"); x[124] = float("inf")
     assert ops.nan_census(x) == (2, 3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,OC,C", [(1024, 768, 3072), (520, 256, 1024)])
+def test_dgelu_gemm_adds_the_column_sums_of_its_result(rows, OC, C, monkeypatch):
+    """matmul_bwd(dinp_colsum=...): the bias gradient of the layer below, taken in the dGELU epilogue, equals the
+    separate reduction over the stored (bf16) result; rows that do not fill the last tile are left out."""
+    d, w = rnd(rows, OC, scale=0.1).to(DEV), rnd(OC, C, scale=0.05).to(DEV)
+    pre, x = rnd(rows, C).to(DEV), rnd(rows, C).to(DEV)
+    res = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("LLMM_FUSED_FC_DBIAS", mode)
+        dinp = torch.empty(rows, C, dtype=torch.bfloat16, device=DEV)
+        col = torch.full((C,), 0.5, device=DEV)                      # accumulates on top of what is there
+        ops.matmul_bwd(dinp, None, None, d, x, w, gelu_pre=pre, dinp_colsum=col)
+        res[mode] = (dinp, col)
+    assert torch.equal(res["1"][0], res["0"][0])
+    want = res["1"][0].float().sum(0) + 0.5
+    close(res["1"][1], want, 1e-3 * math.sqrt(rows), 1e-3, "fused column sums")
+    close(res["0"][1], want, 1e-3 * math.sqrt(rows), 1e-3, "separate column sums")
