@@ -15,6 +15,12 @@
 // MN-major (the UMMA descriptor and the TMA box change, not the data), which is how dinp
 // (B = W as stored) and dW (A = dout^T, B = inp^T as stored) run without any transposes.
 // Split-K work units reduce through fp32 red.global.add into the (fp32) gradient buffer.
+//
+// Three kernels share these parts: gemm_kernel (the design above, kept as the single-CTA comparator),
+// gemm_pair_kernel (the default: two CTAs per 256 x 256 tile with cta_group::2 MMAs, eight epilogue warps, TMA-store
+// epilogue, optional all-gather of A from peer GPUs and optional column sums of the result) and gemm_nvfp4_kernel
+// (block-scaled NVFP4 / MXFP8 operands with their scales in tensor memory, 128 x 256 tiles); each is described where
+// it is defined.
 #include <stdlib.h>
 #include "tc05.cuh"
 using namespace llmb;

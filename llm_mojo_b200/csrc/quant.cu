@@ -10,10 +10,13 @@
 //
 // B200 design: FP8 operands feed tcgen05 kind::f8f6f4 GEMMs directly in whatever majorness the
 // trainer stores them (no transposed copies: the UMMA descriptor handles MN-major e4m3/e5m2).
-// The NVFP4 kernels emit both the packed format (bytes + scales) and the dequantised value x
-// block-scale in bf16; every e2m1 x e4m3 product is exactly representable in bf16, so a bf16
+// The NVFP4 kernels emit the packed format (bytes + scales in the 128 x 4 atoms that the block-scaled
+// tensor path reads, the operands of llmb_gemm_nvfp4) and, on request, the dequantised value x
+// block-scale in bf16: every e2m1 x e4m3 product is exactly representable in bf16, so a bf16
 // tensor-core GEMM over those values with the fp32 tensor scales folded into alpha reproduces
-// the NVFP4 GEMM's arithmetic.
+// the NVFP4 GEMM's arithmetic (the emulation the native kernel is tested against).  Rounding uses
+// the hardware converts (cvt.rn / cvt.rs to e2m1).  llmb_fp8_block_quant does the same for FP8 with
+// per-128 power-of-two scales (fp8 bytes + ue8m0 scale atoms, the operands of llmb_gemm_mxfp8).
 #include "common.cuh"
 #include <cuda_fp8.h>
 #include <cuda_fp4.h>
