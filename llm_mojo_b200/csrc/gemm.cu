@@ -423,6 +423,44 @@ __device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_
   }
 }
 
+// The two halves of the bias + GELU epilogue, so that the pre-activation box can start leaving by TMA while the GELU of the
+// same slab is still being computed: first alpha, bias and the bf16 pre-activations (kept in registers as well) ...
+__device__ __forceinline__ void epi_slab_pre(const GemmParams& p, const uint32_t (&r0)[32], const uint32_t (&r1)[32],
+                                             unsigned char* buf, int col0, float alpha, int lane, uint4 (&pre)[8]) {
+  unsigned char* myrow = buf + lane * 128;
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(c < 4 ? r0[(c & 3) * 8 + j] : r1[(c & 3) * 8 + j]) * alpha;
+    const int col = col0 + c * 8;
+    if (bias && col < p.N) {
+      float b[8];
+      if (p.bias_vec) unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = __bfloat162float(bias[col + j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += b[j];
+    }
+    pre[c] = pack8(v);
+    *reinterpret_cast<uint4*>(myrow + ((c ^ (lane & 7)) << 4)) = pre[c];
+  }
+}
+// ... then GELU of those bf16 values into the second box.
+__device__ __forceinline__ void epi_slab_gelu(const GemmParams& p, const uint4 (&pre)[8], unsigned char* buf, int lane) {
+  unsigned char* myrow = buf + lane * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float x[8]; unpack8(pre[c], x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = (p.dbg & 8) ? x[j] : gelu_fast_f(x[j]);
+    *reinterpret_cast<uint4*>(myrow + ((c ^ (lane & 7)) << 4)) = pack8(x);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // CTA-pair variant: a cluster of two CTAs computes a 256 x 256 tile with cta_group::2 MMAs.  Each
 // CTA stages its own 128 rows of A and its own 128-row half of B (half the B traffic per SM, and
@@ -697,6 +735,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             buf = wstage;
             if (lane == 0) bulk_wait_read<0>();           // the previous slab's stores have read the buffer
             __syncwarp();
+          }
+          if (Cfg::TWO_OUT) {
+            uint4 pre[8];
+            epi_slab_pre(p, r0, r1, buf, col0, alpha, lane, pre);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && !(p.dbg & 1)) { tma_store_2d(&tmAux, buf, col0, row0); bulk_commit(); }
+            epi_slab_gelu(p, pre, buf + SLAB_BYTES, lane);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && !(p.dbg & 1)) { tma_store_2d(&tmD, buf + SLAB_BYTES, col0, row0); bulk_commit(); }
+            continue;
           }
           epi_slab_bf16<EPI>(p, r0, r1, buf, col0, alpha, lane);
           fence_proxy_async();
