@@ -9,23 +9,30 @@ synthetic uniform tokens.  The global batch is fixed, so per-GPU work shrinks wi
 Prints ONE JSON line on rank 0.  `value` is device-timed (CUDA events, max over ranks) with the
 tokens already resident on the GPU; `e2e` runs the same steps through the public `Trainer` API
 with the per-step pinned-host→device token copies and the device→host loss read inside the
-timed region.  `--impl reference` is the reference arm (the reference is a Mojo program and cannot be built
-without its compiler, so the arm reports itself unavailable), `--impl torch` is a plain
-PyTorch (cuBLAS + SDPA + NCCL DDP) comparator of the same model for on-box context.
+timed region.  `--impl reference` is the reference arm: it runs the reference's own PyTorch trainer
+(`train_gpt2.py`, NCCL DDP + cuBLAS + SDPA + fused AdamW; its Mojo trainer needs a compiler that is not
+available) unmodified from `baseline/_ref` as a child process of every rank, on the same model,
+batch and optimizer settings, and reads the step times that trainer prints.  `--impl torch` is a
+plain PyTorch comparator built on this package's own model code, for on-box context only.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
+import shutil
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
 BASELINE_TOK_S_PER_GPU = 173010.0      # reference's best published per-GPU bf16 124M number (B=64, T=1024)
-REFERENCE_UNAVAILABLE = ("pip install of the reference tree fails (no setup.py/pyproject.toml); its only non-Mojo "
-                         "trainer train_gpt2.py downloads the GPT-2 BPE vocabulary at start-up and there is no network")
+ROOT = os.path.dirname(os.path.abspath(__file__))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_TOKENIZER_STANDIN = os.path.join(ROOT, "baseline", "tokenizer_standin")
+METRIC = "GPT-2 124M train tokens/sec (device-timed, max over ranks)"
 
 
 def parse():
@@ -156,7 +163,7 @@ def run_ours(args, rank, world, local_rank):
     tokens = args.total_batch * args.steps
     value = tokens / (dev_ms / 1e3)
     out = {
-        "metric": "GPT-2 124M train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tok/s",
+        "metric": METRIC, "value": value, "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world),
         "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "ours",
@@ -174,6 +181,98 @@ def run_ours(args, rank, world, local_rank):
                       "d2h_bytes_per_step": 8 * world, "ms_per_step": e2e_ms_max / args.steps,
                       "api": "llm_mojo_b200.trainer.Trainer.train_step"}
     return out
+
+
+_REF_STEP = re.compile(r"step\s+(\d+)/(\d+) \| train loss ([0-9.naif+-]+) \|.*\(([0-9.]+) ms \| ([0-9.]+) tok/s\)")
+
+
+def run_reference(args, rank, world, local_rank):
+    """Reference arm: the reference's own trainer, unmodified, as a child process of this rank.
+
+    The child is `baseline/_ref/train_gpt2.py` (a plain copy of the reference tree; it has no
+    setup.py, so a copy is its install) with the flags of the headline config: d12, B=64, T=1024,
+    2**19 tokens per step, bf16 autocast, SDPA flash attention, DDP (`--zero_stage 0`), AdamW
+    lr 6e-4 / wd 0.1 / betas (0.9, 0.95), warm-up + cosine, clip 1.0, sampling / validation /
+    tensor dumps off.  Under torchrun every rank starts one child, which inherits RANK / LOCAL_RANK /
+    WORLD_SIZE / MASTER_* and joins the NCCL group itself (`train_gpt2.py:1886`).  Tokens come from a
+    synthetic uniform shard in the reference's own .bin format, long enough that the loader never
+    reloads it inside the run.  The trainer builds the GPT-2 tiktoken encoding at start-up, which
+    needs a download; the directory `baseline/tokenizer_standin` (first on the child's PYTHONPATH)
+    supplies an encoding of the same size instead - it is never used to tokenize in this run.
+
+    `value` is computed from the step times the trainer prints (host clock around the whole step,
+    closed by `torch.cuda.synchronize()`, `train_gpt2.py:2316-2330`; rank 0 cannot finish a step
+    before the gradient all-reduce has seen every rank, so its time is the max over ranks).  `e2e`
+    is the wall clock this process sees between the arrival of two step lines, so it also contains
+    the loader, the host-to-device token copies and the loss read of every step.
+    """
+    import numpy as np
+    script = os.path.join(REF_DIR, "train_gpt2.py")
+    if not os.path.exists(script):
+        return {"impl": "reference", "unavailable": "baseline/_ref/train_gpt2.py is missing (copy the reference tree there)"}
+    B, T, K, W = args.batch, args.seq, args.steps, args.warmup
+    if args.total_batch % (B * T * world):
+        return {"impl": "reference", "unavailable": f"total batch {args.total_batch} not divisible by {B}x{T}x{world}"}
+    ga = args.total_batch // (B * T * world)
+    work = tempfile.mkdtemp(prefix=f"refarm_r{rank}_")
+    try:
+        from llm_mojo_b200.utils.dataloader import write_datafile
+        ntok = min((K + W) * args.total_batch + B * T * world + 1, 2 ** 28)
+        shard = os.path.join(work, "synthetic_uniform.bin")
+        write_datafile(shard, np.random.default_rng(1234).integers(0, 50257, size=ntok, dtype=np.uint16))
+        cmd = [sys.executable, "-u", script, "--model", args.model, "--batch_size", str(B), "--sequence_length", str(T),
+               "--total_batch_size", str(args.total_batch), "--dtype", "bfloat16", "--flash", "1", "--zero_stage", "0",
+               "--learning_rate", "6e-4", "--warmup_iters", "10", "--learning_rate_decay_frac", "0.1",
+               "--weight_decay", "0.1", "--grad_clip", "1.0", "--sample_every", "0", "--val_loss_every", "0",
+               "--write_tensors", "0", "--compile", os.environ.get("BENCH_REF_COMPILE", "0"),
+               "--num_iterations", str(K + W), "--input_bin", shard, "--input_val_bin", ""]
+        env = dict(os.environ)
+        env["PYTHONPATH"] = os.pathsep.join([REF_TOKENIZER_STANDIN] + ([env["PYTHONPATH"]] if env.get("PYTHONPATH") else []))
+        env.setdefault("MASTER_ADDR", "127.0.0.1")
+        sampler = ClockSampler(local_rank)
+        child = subprocess.Popen(cmd, cwd=work, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        steps, arrival, tail = [], [], []
+        for line in child.stdout:
+            tail = (tail + [line.rstrip()])[-12:]
+            m = _REF_STEP.search(line)
+            if m:
+                steps.append((int(m.group(1)), float(m.group(3)), float(m.group(4))))
+                arrival.append(time.perf_counter())
+                if len(steps) == W and rank == 0:
+                    sampler.start()
+        rc = child.wait()
+        clocks = sampler.stop() if (rank == 0 and sampler.proc is not None) else None
+        if rank != 0:
+            return None
+        if rc != 0 or len(steps) < K + W:
+            why = next((l for l in reversed(tail) if "Error" in l or "error" in l), tail[-1] if tail else "no output")
+            return {"impl": "reference", "unavailable": f"train_gpt2.py exited {rc} after {len(steps)} of {K + W} steps: {why[:300]}"}
+        timed = steps[W:W + K]
+        ms = sum(t[2] for t in timed)
+        e2e_ms = (arrival[W + K - 1] - arrival[W - 1]) * 1e3 if W >= 1 else ms
+        tokens = args.total_batch * K
+        value = tokens / (ms / 1e3)
+        return {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world), "dtype": "bf16",
+            "data": "synthetic uniform tokens (reference .bin shard), random-init weights", "impl": "reference",
+            "config": {"model": f"gpt2-124M ({args.model})", "global_batch": args.total_batch // T, "seq_len": T,
+                       "micro_batch": B, "grad_accum": ga, "tokens_per_step": args.total_batch, "parallelism": f"dp{world}",
+                       "optimizer": "AdamW (fused) lr 6e-4 warmup+cosine, clip 1.0, fp32 params under bf16 autocast",
+                       "l2": "inputs larger than L2 (per-layer activations 100-400 MB, logits 6.6 GB)"},
+            "same_config": True, "clocks": clocks, "gpu_launches": None, "final_loss": timed[-1][1],
+            "code": "baseline/_ref/train_gpt2.py (unmodified), torch.compile " +
+                    ("on" if os.environ.get("BENCH_REF_COMPILE", "0") == "1" else "off (its default)"),
+            "timing": "the trainer's own per-step host clock closed by torch.cuda.synchronize(); rank 0's steps end after the "
+                      "gradient all-reduce, i.e. at the max over ranks",
+            "tokenizer": "stand-in tiktoken_ext.openai_public on PYTHONPATH (no network for vocab.bpe); unused in the run",
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tok/s", "ms_per_step": e2e_ms / K,
+                    "h2d_bytes_per_step": 2 * B * T * 8 * ga * world, "d2h_bytes_per_step": 8 * world,
+                    "api": "train_gpt2.py command line; wall clock between its step lines (loader + H2D + step + loss read)"},
+        }
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
 
 
 def run_torch(args, rank, world, local_rank):
@@ -243,7 +342,7 @@ def run_torch(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item()
     value = args.total_batch * args.steps / (ms / 1e3)
-    return {"metric": "GPT-2 124M train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tok/s",
+    return {"metric": METRIC, "value": value, "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world),
             "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights", "impl": "torch",
@@ -257,8 +356,13 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", rank))
     if args.impl == "reference":
+        # no CUDA context and no process group here: the reference's trainer, started as a child, owns both
+        try:
+            out = run_reference(args, rank, world, local_rank)
+        except Exception as e:                                        # the arm never fails the driver's run
+            out = {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
         if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}), flush=True)
+            print(json.dumps(out), flush=True)
         return 0
     import torch
     import torch.distributed as dist

@@ -34,7 +34,7 @@ def sources() -> List[str]:
 def _digest(path: str) -> str:
     h = hashlib.sha256()
     for name in sorted(os.listdir(CSRC)):
-        if name.endswith(".cuh") or name == os.path.basename(path):
+        if name.endswith((".cuh", ".h")) or name == os.path.basename(path):
             with open(os.path.join(CSRC, name), "rb") as f:
                 h.update(f.read())
     h.update(" ".join(NVCC_FLAGS).encode())

@@ -67,13 +67,38 @@ def test_gradient_dump_gate_fp32_vs_itself(tmp_path):
     assert not compare_grad_dumps.compare(a, b, verbose=False)
 
 
-def test_bench_reference_arm_reports_unavailable():
-    """--impl reference never runs our code: it prints the `unavailable` JSON line and exits 0."""
+def test_bench_reference_arm_line(tmp_path):
+    """--impl reference never runs our code.  With the reference tree in place it runs that tree's own trainer (tiny
+    config here, on CPU) and reports its step times; without it, it prints the `unavailable` JSON line.  Exit code 0 both ways."""
     import subprocess
-    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference"], capture_output=True, text=True, timeout=300)
+    cmd = [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--batch", "1", "--seq", "16",
+           "--total-batch", "32", "--steps", "2", "--warmup", "1"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, cwd=str(tmp_path))
     assert r.returncode == 0
     line = json.loads(r.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and "unavailable" in line
+    assert line["impl"] == "reference"
+    if os.path.exists(os.path.join(ROOT, "baseline", "_ref", "train_gpt2.py")):
+        assert "unavailable" not in line, line
+        assert line["steps"] == 2 and line["value"] > 0 and line["e2e"]["value"] > 0
+        assert line["config"]["tokens_per_step"] == 32
+    else:
+        assert "unavailable" in line
+
+
+def test_tokenizer_standin_shape():
+    """The offline stand-in for tiktoken's GPT-2 plugin yields an encoding with GPT-2's size and end-of-text id."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "tokenizer_standin"))
+    try:
+        import importlib
+        spec = importlib.util.spec_from_file_location(
+            "standin_openai_public", os.path.join(ROOT, "baseline", "tokenizer_standin", "tiktoken_ext", "openai_public.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        c = mod.ENCODING_CONSTRUCTORS["gpt2"]()
+        assert c["explicit_n_vocab"] == 50257 and c["special_tokens"]["<|endoftext|>"] == 50256
+        assert len(c["mergeable_ranks"]) == 50256 and sorted(c["mergeable_ranks"].values()) == list(range(50256))
+    finally:
+        sys.path.pop(0)
 
 
 @pytest.mark.parametrize("precision", ["fp32", "fp8", "fp4"])
