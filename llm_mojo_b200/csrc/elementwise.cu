@@ -316,9 +316,11 @@ LLMB_API int llmb_cast_f32_to_bf16(void* out, const float* in, long long n, cuda
 #include "llmb_noalloc.h"
 static __device__ __align__(256) float g_dbias_noalloc_scratch[LLMB_DBIAS_NOALLOC_MAX_FLOATS];
 
+#include <mutex>
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;      // host threads may make their first call on a device at the same time
 }
 
 LLMB_API int llmb_dbias_noalloc(float* dbias, const void* dout, int rows, int OC, int dtype, cudaStream_t st) {
@@ -329,13 +331,18 @@ LLMB_API int llmb_dbias_noalloc(float* dbias, const void* dout, int rows, int OC
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return LLMB_ERR_BAD_ARG;
-  if (!g_noalloc_ptr[dev]) {   // set-up, once per device, with that device current
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_dbias_noalloc_scratch);
-    if (e != cudaSuccess) return (int)e;
-    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  if ((reinterpret_cast<uintptr_t>(dout) & 15) || (reinterpret_cast<uintptr_t>(dbias) & 3)) return LLMB_ERR_BAD_ARG;   // 16-byte row loads
+  float* scratch;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {   // set-up, once per device, with that device current
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_dbias_noalloc_scratch);
+      if (e != cudaSuccess) return (int)e;
+      g_noalloc_ptr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_noalloc_ptr[dev];
   }
-  float* scratch = g_noalloc_ptr[dev];
   const int rows_per_slab = ceil_div(rows, slabs);
   if (dtype == LLMB_BF16) {
     if (OC % 8) return LLMB_ERR_BAD_ARG;

@@ -27,7 +27,9 @@ extern "C" {
 /* dbias[c] += sum over rows of dout[row, c], for c in [0, OC).
  *
  *   dbias  fp32 [OC], device memory, accumulated into (not overwritten)
- *   dout   [rows, OC] row-major, bf16 (dtype 1) or fp32 (dtype 0); OC a multiple of 8 (bf16) / 4 (fp32)
+ *   dout   [rows, OC] row-major, bf16 (dtype 1) or fp32 (dtype 0); OC a multiple of 8 (bf16) / 4 (fp32);
+ *          the pointer must be 16-byte aligned (the kernels read rows with 16-byte loads; with those OC
+ *          every row then is).  A misaligned pointer is refused with code 2.
  *   st     stream to launch on
  *
  * Returns 0 on success, 2 (bad argument) when llmb_dbias_slabs(rows)*OC exceeds

@@ -307,11 +307,13 @@ class GPT2:
 
     # ------------------------------------------------------------------ forward
     def forward(self, inputs: torch.Tensor, targets: Optional[torch.Tensor] = None,
-                grad_accum_steps: int = 1, B: Optional[int] = None, T: Optional[int] = None) -> None:
+                grad_accum_steps: int = 1, B: Optional[int] = None, T: Optional[int] = None,
+                on_inputs_copied=None) -> None:
         """One micro-step forward.  ``inputs`` / ``targets`` are int32 host (ideally pinned) or
         device tensors of B·T tokens.  With targets the classifier also leaves dlogits in
         ``acts['logits']`` (llm.c design, ``train_gpt2.mojo:3751-3848``) and the micro-step's mean
-        loss / grad_accum_steps is added to ``loss_acc`` on the device."""
+        loss / grad_accum_steps is added to ``loss_acc`` on the device.  ``on_inputs_copied`` is called once
+        the host-to-device token copies are enqueued (a loader records its buffer-reuse event there)."""
         if B is None:
             B, T = inputs.shape
         if (B, T) != (self.B, self.T):
@@ -321,6 +323,8 @@ class GPT2:
         self.inputs_dev.copy_(inputs.view(B, T), non_blocking=True)
         if targets is not None:
             self.targets_dev.copy_(targets.view(B, T), non_blocking=True)
+        if on_inputs_copied is not None:      # the host buffers may be reused once these two copies have run
+            on_inputs_copied()
         z = self.zero
         if z is not None:
             z.before_embedding()

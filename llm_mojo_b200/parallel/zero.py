@@ -120,6 +120,9 @@ class TorchDistBackend:
     def sync(self) -> None:
         pass
 
+    def rearm_after_timeout(self) -> None:
+        pass
+
     def close(self) -> None:
         pass
 
@@ -268,6 +271,14 @@ class P2PBackend:
         ev = torch.cuda.Event()
         ev.record(self.stream)
         torch.cuda.current_stream().wait_event(ev)
+
+    def rearm_after_timeout(self) -> None:
+        """After a bounded wait expired some blocks of a kernel left early, so the "last block" launch counters
+        of this rank's arena can be non-zero; the next launch would then mis-detect its last block.  Zero them."""
+        from .symm import _HDR_FLAGS, _HDR_SCALARS, _HDR_COUNTERS
+        torch.cuda.synchronize(self.device)
+        self.arena._mem[_HDR_FLAGS + _HDR_SCALARS:_HDR_FLAGS + _HDR_SCALARS + _HDR_COUNTERS].zero_()
+        torch.cuda.synchronize(self.device)
 
     def close(self) -> None:
         torch.cuda.synchronize()
@@ -626,6 +637,10 @@ class ZeroEngine:
             self.window_events = [None, None]
 
     # ------------------------------------------------------------------ misc
+    def rearm_after_timeout(self) -> None:
+        if self.backend is not None:
+            self.backend.rearm_after_timeout()
+
     def mean_scalar(self, value: float) -> float:
         if self.world_size == 1 or not dist.is_initialized():
             return value
@@ -685,6 +700,12 @@ class ZeroEngine:
         state, mm, vv = ckpt.read_state_checkpoint(state_path, m.m.numel())
         m.m.copy_(mm.to(self.device))
         m.v.copy_(vv.to(self.device))
+        # Peers read this rank's parameter memory directly (stage 3 pulls shards, stages 1/2 were pushed into): nobody
+        # may start a forward pass before every rank's load has landed in device memory.
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if self.world_size > 1 and dist.is_initialized():
+            dist.barrier()
         return state
 
     def memory_report(self) -> dict:

@@ -8,6 +8,14 @@ One process drives one GPU.  ``Trainer.train_step()`` is one optimizer step: ``g
 micro-steps (pinned-host batch → async H2D → forward → backward, the next batch being read on a
 worker thread meanwhile), gradient reduction (ZeRO engine), global-norm clip computed on the
 device, AdamW.  The only host synchronisation is the loss read at the end of the step.
+
+Failure handling (``train_gpt2.mojo:6871-6876``, ``llmm/zero.mojo:73-108``): every step starts by polling the
+job's sticky abort key, and the loss read also reads the status word that kernels with bounded waits set when a
+wait expires.  A non-zero status means this step's collectives did not complete: the rank re-arms its
+communication state, sets the abort key and raises ``DeviceWaitExpired`` instead of returning a loss, and every
+peer raises ``PeerAborted`` at its next step or barrier, so a supervisor can restart the job from the last
+checkpoint.  Phases in which ranks do different amounts of host work (checkpoint write, validation, sampling) end
+with a host barrier, so no rank enters the bounded device waits of the next step while another is still busy.
 """
 from __future__ import annotations
 
@@ -68,6 +76,10 @@ class TrainArgs:
     tokenizer_path: str = "gpt2_tokenizer.bin"
 
 
+class DeviceWaitExpired(RuntimeError):
+    """A bounded device-side wait (peer flag or mbarrier) gave up during the step: its results are not valid."""
+
+
 class SyntheticLoader:
     """Uniform tokens in [0, V): inputs and targets (inputs shifted by one), pinned host memory."""
 
@@ -93,6 +105,9 @@ class SyntheticLoader:
 
     def prefetch(self):
         pass
+
+    def mark_consumed(self):
+        pass                                  # batches are never rewritten
 
     def reset(self):
         self._i = 0
@@ -126,6 +141,12 @@ class Trainer:
         self.grad_accum = total // tokens_per_fwdbwd
         self.total_batch_size = total
 
+        self.dist_ctx = dist_ctx
+        self.coord = dist_ctx.coord if dist_ctx is not None else None
+        if self.coord is None and world_size > 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+            from .parallel.runtime import Coordinator
+            store = torch.distributed.distributed_c10d._get_default_store()
+            self.coord = Coordinator(store, rank, world_size, prefix=f"llmb/{os.environ.get('TORCHELASTIC_RUN_ID', 'job')}/trainer")
         self.zero = None
         if world_size > 1 or args.zero_stage > 0:
             from .parallel.zero import ZeroEngine
@@ -166,6 +187,8 @@ class Trainer:
         """One optimizer step.  Returns loss / norm / lr / device_ms (CUDA events) / host ms."""
         a, m = self.args, self.model
         t0 = time.perf_counter()
+        if self.coord is not None:
+            self.coord.raise_if_aborted()               # a peer failed: stop before entering device-side waits
         if self._ev:
             self._ev[0].record()
         for micro in range(self.grad_accum):
@@ -177,7 +200,8 @@ class Trainer:
             if not (last and a.overfit_single_batch):
                 self.train_loader.prefetch()
             with self.tracer.cuda_span("forward"):
-                m.forward(x, y, self.grad_accum, B=a.batch_size, T=a.seq_len)
+                m.forward(x, y, self.grad_accum, B=a.batch_size, T=a.seq_len,
+                          on_inputs_copied=self.train_loader.mark_consumed)
             with self.tracer.cuda_span("backward"):
                 m.backward(self.grad_accum, micro)
         if self._nanscan:                               # LLMM_DEBUG_TENSOR_NANSCAN=1: census of the accumulated gradients
@@ -195,6 +219,7 @@ class Trainer:
         out = {"lr": lr, "step": self.step}
         if read_loss:
             loss = m.read_loss()                       # the step's only host synchronisation
+            self._check_device_status()
             if self.zero is not None:
                 loss = self.zero.mean_scalar(loss)
             out["loss"] = loss
@@ -205,6 +230,35 @@ class Trainer:
         out["ms"] = (time.perf_counter() - t0) * 1e3
         self.step += 1
         return out
+
+    # ------------------------------------------------------------------ failure handling
+    def _check_device_status(self) -> None:
+        """Read the status word right after the loss (the stream is idle, so this is one 4-byte copy).  Non-zero:
+        some bounded wait expired, i.e. a peer stalled or died and this step's reductions are not valid."""
+        if self.device.type != "cuda":
+            return
+        from .ops import _lib
+        status = _lib.read_status(self.device)
+        if status == 0:
+            return
+        _lib.status_word(self.device).zero_()
+        if self.zero is not None:
+            self.zero.rearm_after_timeout()
+        why = f"a bounded device wait expired in step {self.step} (status {status})"
+        self.abort(why)
+        raise DeviceWaitExpired(f"rank {self.rank}: {why}")
+
+    def abort(self, reason: str) -> None:
+        """Make every peer's next step / barrier raise ``PeerAborted``."""
+        if self.coord is not None:
+            self.coord.abort(reason)
+
+    def host_barrier(self) -> None:
+        """Ranks meet on the host (sticky-abort barrier) after a phase of uneven host work."""
+        if self.coord is not None:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            self.coord.barrier()
 
     # ------------------------------------------------------------------ evaluation / sampling
     @torch.no_grad()
@@ -217,8 +271,9 @@ class Trainer:
         m.loss_acc.zero_()
         for _ in range(n):
             x, y = self.val_loader.next_batch()
-            m.forward(x, y, n, B=a.batch_size, T=a.seq_len)
+            m.forward(x, y, n, B=a.batch_size, T=a.seq_len, on_inputs_copied=self.val_loader.mark_consumed)
         loss = m.read_loss()
+        self._check_device_status()
         return self.zero.mean_scalar(loss) if self.zero is not None else loss
 
     @torch.no_grad()
@@ -278,15 +333,18 @@ class Trainer:
             step, last = self.step, self.step == N
             if a.val_loss_every > 0 and (step % a.val_loss_every == 0 or last) and self.val_loader is not None:
                 self.print0(f"val loss {self.validate():.6f}")
+                self.host_barrier()
             if a.sample_every > 0 and (step > 0 and step % a.sample_every == 0 or last):
                 ids = self.sample(a.gen_tokens)
                 self.print0("generating:\n---")
                 self.print0(self.tokenizer.decode_sequence(ids) if self.tokenizer.has_initialized
                             else " ".join(str(i) for i in ids))
                 self.print0("---")
+                self.host_barrier()
             if a.checkpoint_every > 0 and a.output_log_dir and ((step > 0 and step % a.checkpoint_every == 0) or last):
                 self.save(step)
                 self.print0(f"Writing checkpoint at step {step}")
+                self.host_barrier()                     # rank 0 writes the whole model; the others wait here, not on the device
             if last:
                 break
             r = self.train_step()

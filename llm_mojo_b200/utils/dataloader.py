@@ -7,7 +7,12 @@ from MT19937 seeded ``42 + rank``; draw counting for exact resume).
 
 B200-first additions: batches are produced into *pinned* host tensors so the trainer can
 issue an asynchronous H2D copy, and ``prefetch()`` reads the next batch on a worker thread
-while the GPU runs the current micro-step.
+while the GPU runs the current micro-step.  A pinned buffer is only rewritten once the
+host-to-device copies that read it have run: the consumer calls ``mark_consumed()`` right after
+it has enqueued those copies, which records a CUDA event for the buffer, and the producer
+waits for that event (on the worker thread, so the training thread is not blocked) before it
+writes into the buffer again.  ``state()`` may be called while a batch is prefetched: it then
+reports the position from which that batch was produced, so a resumed run reads it again.
 """
 from __future__ import annotations
 
@@ -75,6 +80,9 @@ class DataLoader:
         self._cur = 0
         self._prefetch_thread: Optional[threading.Thread] = None
         self._prefetched = False
+        self._pre_state: Optional[dict] = None          # position before the prefetched batch was produced
+        self._copy_events = [None, None]                # per buffer: CUDA event after the H2D copies that read it
+        self._copy_pending = [False, False]
         self.inputs, self.targets = self._bufs[0]
 
         self._open(self.files[0])
@@ -161,8 +169,26 @@ class DataLoader:
     def _produce(self, slot: int) -> None:
         if self.current_sample_idx >= self.shard_num_samples:
             self._advance()
+        if self._copy_pending[slot]:                    # the device may not have read the old contents yet
+            self._copy_events[slot].synchronize()
+            self._copy_pending[slot] = False
         self._load_batch_into(*self._bufs[slot])
         self.current_sample_idx += 1
+
+    def mark_consumed(self) -> None:
+        """Call right after enqueuing the asynchronous host-to-device copies of the current batch (on the
+        stream that carries them): the buffer is not rewritten before those copies have run.  The events
+        are created once per buffer and reused, so steady-state steps allocate nothing."""
+        if not (torch.cuda.is_available() and self._bufs[self._cur][0].is_pinned()):
+            return
+        if self._copy_events[self._cur] is None:
+            self._copy_events[self._cur] = torch.cuda.Event()
+        self._copy_events[self._cur].record()
+        self._copy_pending[self._cur] = True
+
+    def _snapshot(self) -> dict:
+        return {"should_shuffle": int(self.should_shuffle), "shuffle_draws": self.shuffle_draws,
+                "current_shard_idx": self.current_shard_idx, "current_sample_idx": self.current_sample_idx}
 
     def _join_prefetch(self, discard: bool = False) -> None:
         if self._prefetch_thread is not None:
@@ -176,6 +202,7 @@ class DataLoader:
         if self._prefetched or self._prefetch_thread is not None:
             return
         slot = 1 - self._cur
+        self._pre_state = self._snapshot()
         self._prefetch_thread = threading.Thread(target=self._produce, args=(slot,), daemon=True)
         self._prefetch_thread.start()
         self._prefetched = True
@@ -193,12 +220,12 @@ class DataLoader:
 
     # -- resume ----------------------------------------------------------------------
     def state(self) -> dict:
+        """Position of the next batch ``next_batch()`` will return.  With a batch already prefetched that is the
+        position the prefetch started from (a shard change it triggered is replayed by ``restore`` + the next read)."""
         self._join_prefetch()
         if self._prefetched:
-            raise RuntimeError("checkpoint the loader before prefetching the next batch")
-        return {"should_shuffle": int(self.should_shuffle), "shuffle_draws": self.shuffle_draws,
-                "current_shard_idx": self.current_shard_idx,
-                "current_sample_idx": self.current_sample_idx}
+            return dict(self._pre_state)
+        return self._snapshot()
 
     def restore(self, should_shuffle: int, shuffle_draws: int, current_shard_idx: int,
                 current_sample_idx: int) -> None:

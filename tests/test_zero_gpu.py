@@ -41,6 +41,32 @@ def test_bounded_wait_expires_cleanly():
         status.zero_()
 
 
+def test_train_step_raises_when_a_device_wait_expired():
+    """The host withholds a flag: a bounded wait on the training stream gives up and sets the status word; the step
+    that follows must raise instead of returning a loss, and the trainer must be usable again afterwards."""
+    from llm_mojo_b200.trainer import DeviceWaitExpired, TrainArgs, Trainer
+    L = _lib.lib()
+    L.llmb_comm_wait.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    L.llmb_comm_set_wait_budget.argtypes = [ctypes.c_uint]
+    tr = Trainer(TrainArgs(load_filename="d6", batch_size=2, seq_len=64, total_batch_size=128, max_steps=10,
+                           synthetic=True, val_loss_every=0, sample_every=0))
+    assert tr.device.type == "cuda"
+    first = tr.train_step()
+    assert first["loss"] == first["loss"]
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = _lib.status_word(tr.device)
+    assert L.llmb_comm_set_wait_budget(1 << 10) == 0
+    try:
+        assert L.llmb_comm_wait(flags.data_ptr(), 0, 1, 1, status.data_ptr(), _lib.stream()) == 0   # nothing sets flag 0
+        with pytest.raises(DeviceWaitExpired):
+            tr.train_step()
+    finally:
+        L.llmb_comm_set_wait_budget(1 << 24)
+    assert _lib.read_status(tr.device) == 0               # re-armed
+    again = tr.train_step()
+    assert again["loss"] == again["loss"]
+
+
 WORKER = textwrap.dedent('''
     import os, sys, json, torch, torch.distributed as dist
     sys.path.insert(0, os.environ["LLMB_ROOT"])

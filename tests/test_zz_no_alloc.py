@@ -50,12 +50,23 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         fp32 = dout.float().sum(0)
         tol = 1e-3 * math.sqrt(rows)
         for call in (1, 2):              # dbias accumulates: after n calls it holds n times the column sums
+            torch.cuda.synchronize()
             before = torch.cuda.memory_allocated()
+            free_before = torch.cuda.mem_get_info()[0]
             assert fn(got.data_ptr(), dout.data_ptr(), rows, OC, code, stream) == 0
             torch.cuda.synchronize()
             assert torch.cuda.memory_allocated() == before      # nothing went through torch's allocator
+            if call == 2:                # the driver's own count of free bytes also sees a raw cudaMalloc; the first call
+                assert torch.cuda.mem_get_info()[0] >= free_before      # on a device may still load the kernels' module
             assert torch.allclose(got, call * want, atol=tol, rtol=1e-3)
             assert torch.allclose(got, call * fp32, atol=2 * tol, rtol=1e-3)
+
+
+def test_noalloc_rejects_misaligned_rows():
+    fn, _, _ = _symbol()
+    dout = torch.zeros(64 * 768 + 8, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(768, device="cuda")
+    assert fn(out.data_ptr(), dout.data_ptr() + 2, 64, 768, 1, torch.cuda.current_stream().cuda_stream) == 2
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch():
