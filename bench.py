@@ -174,6 +174,7 @@ def run_ours(args, rank, world, local_rank):
                    "l2": "inputs larger than L2 (per-layer activations 100-400 MB, logits 6.6 GB)"},
         "clocks": clocks, "gpu_launches": launches, "final_loss": final_loss, "kernel_status": status,
         "gemm_impl": ops.GEMM_IMPL, "attn_impl": ops.ATTN_IMPL, "host_enqueue_ms_per_step": host_enqueue_ms / args.steps,
+        "comm_backend": (tr.zero.backend_name if tr.zero is not None else "none (one GPU)"),
     }
     if e2e_ms_max:
         h2d = 2 * B * T * 4 * ga          # inputs + targets, int32, per step per rank

@@ -3,8 +3,10 @@
 
 Parity: ``calibrate_fp8_scales.mojo:1-57``: run N fp8 training steps, track the running minimum of every
 ``AmaxState.scale`` (the smallest scale seen = the largest amax), divide by a safety factor (2) and print
-the table, one ``site.layer.operand scale`` line each plus a JSON blob that ``--static-scales`` of a
-later run can load."""
+the table, one ``site.layer.operand scale`` line each, and with ``--out`` a JSON file that a later run loads
+with ``train_gpt2.py --precision fp8 --fp8-static-scales <file>`` (or ``LLMM_FP8_STATIC_SCALES=<file>``): that run
+uses one constant per (site, operand) - the minimum over the layers - and launches no amax or scale-update kernel.
+On a machine without a GPU the calibration runs the fp8 emulation of the CPU path (slow; small models only)."""
 from __future__ import annotations
 
 import argparse
@@ -13,6 +15,7 @@ import sys
 
 import torch
 
+from llm_mojo_b200.config import Precision
 from llm_mojo_b200.models import GPT2
 
 
@@ -25,10 +28,8 @@ def main(argv=None) -> int:
     ap.add_argument("--safety", type=float, default=2.0)
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
-    if not torch.cuda.is_available():
-        print("calibration runs the fp8 tensor-core path and needs a GPU")
-        return 1
-    model = GPT2(a.model, "fp8", "cuda")
+    on_gpu = torch.cuda.is_available()
+    model = GPT2(a.model, Precision("fp8", fp32_storage=not on_gpu), "cuda" if on_gpu else "cpu")
     T = min(a.t, model.config.max_seq_len)
     g = torch.Generator().manual_seed(3)
     mins = {}

@@ -61,14 +61,12 @@ def run_infer(model: GPT2, tokenizer: Tokenizer, prompt, gen_tokens: int, seed: 
 
 def run_eval(model: GPT2, path: str, B: int, T: int) -> float:
     loader = EvalDataLoader(path, B, T)
-    correct = total = 0
+    correct = 0
     for _ in range(loader.num_batches):
         loader.next_batch()
         model.forward(loader.inputs, loader.targets, B=B, T=T)
         model.read_loss()
-        n_here = min(loader.can_fit_examples, loader.end_example_index - (loader.current_example_index - loader.can_fit_examples))
         correct += eval_stat_correct(loader, model.acts["losses"])
-        total += max(0, min(loader.can_fit_examples, n_here))
     total = loader.end_example_index - loader.start_example_index
     acc = correct / max(total, 1)
     print(f"HellaSwag: {correct}/{total} = {acc:.4f}")

@@ -122,6 +122,7 @@ class Precision:
     fp4_last_offset: int = 2          # layers [first, L - offset) run NVFP4
     fp4_rht: bool = True
     fp4_sr: bool = True
+    fp32_storage: bool = False        # low-precision GEMM numerics over fp32 tensors (the emulation that runs on a CPU)
 
     def __post_init__(self):
         alias = {"float32": "fp32", "bfloat16": "bf16", "nvfp4": "fp4", "float8": "fp8"}
@@ -135,7 +136,7 @@ class Precision:
 
     @property
     def storage(self) -> torch.dtype:
-        return torch.float32 if self.name in ("fp32", "tf32") else torch.bfloat16
+        return torch.float32 if self.name in ("fp32", "tf32") or self.fp32_storage else torch.bfloat16
 
     @property
     def use_master(self) -> bool:

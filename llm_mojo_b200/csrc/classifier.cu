@@ -334,7 +334,55 @@ __global__ void softmax_rows_kernel(float* __restrict__ out, const T* __restrict
   float inv = 1.f / bc;
   for (int i = tid; i < V; i += blockDim.x) out[(size_t)row * V + i] = expf(to_f<T>(g[i]) * inv_temp - mx) * inv;
 }
+
+// dlogits = probs * (dprobs - sum_k dprobs[k] * probs[k]) over the first V columns of a row (one block per row);
+// columns V..ld-1 of dlogits are zeroed.  (llmm/softmax.mojo:632, softmax_bwd)
+__global__ void softmax_bwd_kernel(float* __restrict__ dlogits, const float* __restrict__ dprobs, const float* __restrict__ probs,
+                                   int V, int ld) {
+  __shared__ float red[32];
+  __shared__ float bc;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid % 32, wid = tid / 32, nw = blockDim.x / 32;
+  const float* dp = dprobs + (size_t)row * ld;
+  const float* pr = probs + (size_t)row * ld;
+  float dot = 0.f;
+  for (int i = tid; i < V; i += blockDim.x) dot = fmaf(dp[i], pr[i], dot);
+  dot = warp_sum(dot); if (lane == 0) red[wid] = dot; __syncthreads();
+  if (wid == 0) { float t = lane < nw ? red[lane] : 0.f; t = warp_sum(t); if (lane == 0) bc = t; } __syncthreads();
+  dot = bc;
+  float* out = dlogits + (size_t)row * ld;
+  for (int i = tid; i < ld; i += blockDim.x) out[i] = i < V ? pr[i] * (dp[i] - dot) : 0.f;
+}
+
+// Unfused cross-entropy over stored probabilities (llmm/crossentropy.mojo:110, :284): loss = -log p[target];
+// backward writes only the target slot, dprobs[target] = -dloss / p[target] (the caller zeroes dprobs first).
+__global__ void crossentropy_fwd_kernel(float* __restrict__ losses, const float* __restrict__ probs, const int* __restrict__ targets,
+                                        int rows, int ld) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows) losses[i] = -logf(probs[(size_t)i * ld + targets[i]]);
+}
+__global__ void crossentropy_bwd_kernel(float* __restrict__ dprobs, const float* __restrict__ dlosses, const float* __restrict__ probs,
+                                        const int* __restrict__ targets, int rows, int ld) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows) { const size_t o = (size_t)i * ld + targets[i]; dprobs[o] = -dlosses[i] / probs[o]; }
+}
 }  // namespace
+
+LLMB_API int llmb_softmax_bwd(float* dlogits, const float* dprobs, const float* probs, int rows, int V, int ld, cudaStream_t st) {
+  if (rows <= 0 || V <= 0 || ld < V) return LLMB_ERR_BAD_ARG;
+  softmax_bwd_kernel<<<rows, 256, 0, st>>>(dlogits, dprobs, probs, V, ld);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_crossentropy_fwd(float* losses, const float* probs, const int* targets, int rows, int ld, cudaStream_t st) {
+  if (rows <= 0) return LLMB_ERR_BAD_ARG;
+  crossentropy_fwd_kernel<<<ceil_div(rows, 256), 256, 0, st>>>(losses, probs, targets, rows, ld);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_crossentropy_bwd(float* dprobs, const float* dlosses, const float* probs, const int* targets, int rows, int ld,
+                                   cudaStream_t st) {
+  if (rows <= 0) return LLMB_ERR_BAD_ARG;
+  crossentropy_bwd_kernel<<<ceil_div(rows, 256), 256, 0, st>>>(dprobs, dlosses, probs, targets, rows, ld);
+  return (int)cudaGetLastError();
+}
 
 // logits [rows, Vp] are overwritten with dlogits when write_dlogits != 0.
 LLMB_API int llmb_fused_classifier(void* logits, float* losses, const int* targets, float dloss, int rows, int V,

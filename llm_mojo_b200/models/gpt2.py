@@ -68,7 +68,8 @@ class GPT2:
     def __init__(self, source: str | GPT2Config, precision: Precision | str = "bf16",
                  device: str | torch.device = "cpu", zero=None, recompute: bool = False,
                  init_seed: int = INIT_RNG_SEED, params_flat: Optional[torch.Tensor] = None,
-                 lm_head_chunks: Optional[int] = None, vocab_parallel: Optional[bool] = None):
+                 lm_head_chunks: Optional[int] = None, vocab_parallel: Optional[bool] = None,
+                 fp8_static_scales=None):
         self.precision = precision if isinstance(precision, Precision) else Precision(precision)
         self.device = torch.device(device)
         self.recompute = recompute or os.environ.get("LLMM_RECOMPUTE", "") not in ("", "0")
@@ -138,6 +139,9 @@ class GPT2:
         if self.precision.name == "fp8":
             from ..ops.lowp import LowpState
             self.lowp = LowpState(cfg.num_layer, self.device)
+            table = fp8_static_scales or os.environ.get("LLMM_FP8_STATIC_SCALES", "")
+            if table:      # calibrated constants instead of delayed scaling: no amax / scale-update kernels in the step
+                self.lowp.set_static_scales(LowpState.read_scale_table(table) if isinstance(table, str) else table)
 
     # ------------------------------------------------------------------ views / layout
     def _views(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:

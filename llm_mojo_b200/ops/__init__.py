@@ -503,6 +503,46 @@ def softmax_rows(logits2d: torch.Tensor, vocab_size: int, temperature: float = 1
     return torch.softmax(logits2d[:, :vocab_size].float() / temperature, dim=-1)
 
 
+def softmax_bwd(dprobs: torch.Tensor, probs: torch.Tensor, vocab_size: int) -> torch.Tensor:
+    """Gradient of a row softmax with respect to its logits: ``p ∘ (dp − Σ_k dp_k p_k)`` over the first
+    ``vocab_size`` columns, zero in the padded tail; fp32 ``[rows, ld]`` in and out (llmm/softmax.mojo:632)."""
+    rows, ld = probs.shape
+    if probs.is_cuda:
+        out = torch.empty_like(probs, dtype=torch.float32)
+        check(lib().llmb_softmax_bwd(ptr(out), ptr(dprobs), ptr(probs), rows, vocab_size, ld, stream()), "softmax_bwd")
+        _count()
+        return out
+    p, dp = probs[:, :vocab_size].float(), dprobs[:, :vocab_size].float()
+    out = torch.zeros(rows, ld, dtype=torch.float32)
+    out[:, :vocab_size] = p * (dp - (dp * p).sum(-1, keepdim=True))
+    return out
+
+
+def crossentropy_fwd(probs: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+    """Unfused cross-entropy over stored probabilities ``[rows, ld]`` fp32: ``−log p[target]``
+    (llmm/crossentropy.mojo:110).  The training path uses ``fused_classifier`` instead."""
+    rows, ld = probs.shape
+    if probs.is_cuda:
+        out = torch.empty(rows, dtype=torch.float32, device=probs.device)
+        check(lib().llmb_crossentropy_fwd(ptr(out), ptr(probs), ptr(targets), rows, ld, stream()), "crossentropy_fwd")
+        _count()
+        return out
+    return -torch.log(probs.float().gather(1, targets.long().view(-1, 1)).squeeze(1))
+
+
+def crossentropy_bwd(dprobs: torch.Tensor, dlosses: torch.Tensor, probs: torch.Tensor, targets: torch.Tensor) -> None:
+    """Writes ``dprobs[row, target] = −dloss / p[row, target]``; every other entry of ``dprobs`` is left as it is
+    (llmm/crossentropy.mojo:284)."""
+    rows, ld = probs.shape
+    if probs.is_cuda:
+        check(lib().llmb_crossentropy_bwd(ptr(dprobs), ptr(dlosses), ptr(probs), ptr(targets), rows, ld, stream()),
+              "crossentropy_bwd")
+        _count()
+        return
+    idx = targets.long().view(-1, 1)
+    dprobs.scatter_(1, idx, (-dlosses.float().view(-1, 1) / probs.float().gather(1, idx)).to(dprobs.dtype))
+
+
 # ----------------------------------------------------------------------------- optimizer
 def adamw_update(params, master, grads, m, v, *, lr, beta1, beta2, eps, weight_decay, grad_scale, step,
                  seed: int = 0, stochastic_rounding: bool = False, dev_scale=None) -> None:

@@ -35,6 +35,9 @@ _SIGS = {
     "llmb_ce_loss": [c_p, c_p, c_int, c_p],
     "llmb_ce_pass2": [c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_f, c_int, c_p],
     "llmb_softmax_rows": [c_p, c_p, c_int, c_int, c_int, c_f, c_int, c_p],
+    "llmb_softmax_bwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_p],
+    "llmb_crossentropy_fwd": [c_p, c_p, c_p, c_int, c_int, c_p],
+    "llmb_crossentropy_bwd": [c_p, c_p, c_p, c_p, c_int, c_int, c_p],
     "llmb_adamw": [c_p, c_p, c_p, c_p, c_p, c_ll, c_f, c_f, c_f, c_f, c_f, c_f, c_p, c_int, c_ull, c_int, c_int, c_p],
     "llmb_norm_sq_blocks": [],
     "llmb_global_norm_sq": [c_p, c_p, c_ll, c_p, c_int, c_p],

@@ -56,6 +56,16 @@ class AmaxState:
         self.state[1] = 1.0
         self.amax = torch.zeros(1, dtype=torch.float32, device=device)
         self.host_step = 0
+        self.static = False
+
+    def set_static(self, scale: float) -> None:
+        """Freeze the scale at a calibrated constant: ``update_scale`` then does nothing, so neither the amax
+        reduction nor the scale-update kernel runs for this operand (``llmm/lowp.mojo:880-935``, the reference's
+        fastest FP8 mode).  Values beyond the calibrated range saturate in the encoder instead of overflowing."""
+        if not (scale > 0 and math.isfinite(scale)):
+            raise ValueError(f"static scale must be positive and finite, got {scale}")
+        self.state[0], self.state[1] = float(scale), 1.0 / float(scale)
+        self.static = True
 
     @property
     def scale(self) -> torch.Tensor:
@@ -67,6 +77,8 @@ class AmaxState:
 
     def update_scale(self, x: torch.Tensor) -> None:
         """amax(x) → scale for this step (pre-push history; own amax during warm-up) → push."""
+        if self.static:
+            return
         compute_amax(self.amax, x)
         if x.is_cuda:
             check(lib().llmb_amax_update(ptr(self.state), ptr(self.amax), FMT_MAX[self.fmt], self.margin_mult, stream()),
@@ -122,6 +134,39 @@ class LowpState:
 
     def site(self, name: str, layer: int) -> LinearSite:
         return self.sites[(name, layer)]
+
+    ROLES = ("inp", "weight", "dout")
+
+    def set_static_scales(self, table: Dict[str, float], per_layer: bool = False) -> None:
+        """Switch every site to static scaling from a table of ``site.layer.role`` (what ``calibrate_fp8_scales.py``
+        writes) and / or ``site.role`` entries.  Default, as in the reference (``fp8_static_scale``,
+        ``llmm/lowp.mojo:999``): ONE constant per (site, role) shared by all layers, the minimum over the layers in
+        the table (the smallest scale is the safe one).  ``per_layer`` keeps each layer's own entry where present."""
+        shared: Dict[Tuple[str, str], float] = {}
+        for key, val in table.items():
+            parts = key.split(".")
+            if len(parts) == 3:
+                sr = (parts[0], parts[2])
+            elif len(parts) == 2:
+                sr = (parts[0], parts[1])
+            else:
+                raise ValueError(f"bad static-scale key {key!r}")
+            if sr[0] not in self.SITES or sr[1] not in self.ROLES:
+                raise ValueError(f"unknown (site, role) pair in static-scale key {key!r}")
+            shared[sr] = min(shared.get(sr, float("inf")), float(val))
+        for (s, l), st in self.sites.items():
+            for role in self.ROLES:
+                if (s, role) not in shared:
+                    raise ValueError(f"static-scale table has no entry for {s}.{role}")
+                own = table.get(f"{s}.{l}.{role}") if per_layer else None
+                getattr(st, role).set_static(float(own) if own is not None else shared[(s, role)])
+
+    @staticmethod
+    def read_scale_table(path: str) -> Dict[str, float]:
+        import json
+        with open(path) as f:
+            blob = json.load(f)
+        return {k: float(v) for k, v in (blob["scales"] if "scales" in blob else blob).items()}
 
     def min_scales(self) -> Dict[str, float]:
         """Current scale of every state (the fp8 calibration tool tracks their running minima)."""

@@ -74,6 +74,7 @@ class TrainArgs:
     synthetic: bool = False                   # uniform random tokens instead of files
     comm_backend: str = "auto"                # auto | p2p | nccl | gloo
     tokenizer_path: str = "gpt2_tokenizer.bin"
+    fp8_static_scales: str = ""               # JSON table from calibrate_fp8_scales.py: static instead of delayed scaling
 
 
 class DeviceWaitExpired(RuntimeError):
@@ -152,7 +153,8 @@ class Trainer:
             from .parallel.zero import ZeroEngine
             self.zero = ZeroEngine(args.zero_stage, rank, world_size, self.device, dist_ctx=dist_ctx,
                                    backend=args.comm_backend)
-        self.model = GPT2(args.load_filename, self.precision, self.device, zero=self.zero, recompute=args.recompute)
+        self.model = GPT2(args.load_filename, self.precision, self.device, zero=self.zero, recompute=args.recompute,
+                          fp8_static_scales=args.fp8_static_scales or None)
         cfg = self.model.config
         if args.synthetic:
             self.train_loader = SyntheticLoader(B, T, cfg.vocab_size, rank)

@@ -293,6 +293,23 @@ def test_attention_fwd_bwd(B, T, NH):
         close(dqkv[..., i * C:(i + 1) * C], r_dqkv[..., i * C:(i + 1) * C], 2e-2, 3e-2, nm)
 
 
+def test_unfused_softmax_bwd_and_crossentropy():
+    g = torch.Generator().manual_seed(11)
+    rows, V, ld = 300, 50257, 50304
+    logits = torch.randn(rows, ld, generator=g) * 2
+    tgt = torch.randint(0, V, (rows,), generator=g, dtype=torch.int32)
+    dloss = torch.randn(rows, generator=g)
+    probs_c = torch.zeros(rows, ld)
+    probs_c[:, :V] = ops.softmax_rows(logits, V)
+    probs = probs_c.to(DEV)
+    close(ops.crossentropy_fwd(probs, tgt.to(DEV)), ops.crossentropy_fwd(probs_c, tgt), 1e-5, 1e-5, "crossentropy fwd", strict=True)
+    dprobs_c, dprobs = torch.zeros(rows, ld), torch.zeros(rows, ld, device=DEV)
+    ops.crossentropy_bwd(dprobs_c, dloss, probs_c, tgt)
+    ops.crossentropy_bwd(dprobs, dloss.to(DEV), probs, tgt.to(DEV))
+    close(dprobs, dprobs_c, 1e-3, 1e-5, "crossentropy bwd", strict=True)
+    close(ops.softmax_bwd(dprobs, probs, V), ops.softmax_bwd(dprobs_c, probs_c, V), 1e-5, 1e-4, "softmax bwd", strict=True)
+
+
 def test_attention_persistent_loops_large():
     """B=16, NH=12, T=1024: 768 work items on at most 148 CTAs, so every persistent CTA walks several items per
     tile stream (barrier phase wrap, TMEM hand-back between items, the heavy/light tile alternation).  Oracle: the

@@ -459,3 +459,37 @@ def test_fp8_block_linear_native_matches_fake_quant_path(monkeypatch):
         res[mode] = (out.float(), pre.float(), dinp.float(), dw, db)
     for got, want in zip(res["1"], res["0"]):
         assert ((got - want).norm() / want.norm()).item() < 5e-3
+
+
+def test_fp8_static_scales_round_trip(tmp_path):
+    """calibrate_fp8_scales.py writes a table; a run that loads it trains with frozen scales: one constant per
+    (site, operand) = the minimum over layers, and update_scale no longer touches the state (CPU emulation)."""
+    import json
+    import calibrate_fp8_scales
+    from llm_mojo_b200.config import GPT2Config
+    from llm_mojo_b200.models import GPT2
+    from llm_mojo_b200.ops.lowp import LowpState
+    out = tmp_path / "scales.json"
+    assert calibrate_fp8_scales.main(["--model", "d6", "--steps", "3", "-b", "2", "-t", "32", "--out", str(out)]) == 0
+    table = json.load(open(out))["scales"]
+    assert len(table) == 6 * 4 * 3 and all(v > 0 for v in table.values())
+    m = GPT2("d6", Precision("fp8", fp32_storage=True), "cpu", fp8_static_scales=str(out))
+    for site in LowpState.SITES:
+        for role in LowpState.ROLES:
+            want = min(table[f"{site}.{l}.{role}"] for l in range(6))
+            for l in range(6):
+                st = getattr(m.lowp.site(site, l), role)
+                assert st.static and abs(float(st.scale) - want) < 1e-6 * want
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, m.config.vocab_size, (2, 33), generator=g, dtype=torch.int32)
+    losses = []
+    for step in range(4):
+        m.forward(toks[:, :-1].contiguous(), toks[:, 1:].contiguous())
+        m.backward()
+        m.update(step + 1, 1e-3)
+        losses.append(m.read_loss())
+    assert all(l == l for l in losses) and losses[-1] < losses[0]
+    st = m.lowp.site("fc", 1).inp
+    assert st.host_step == 0                                # the delayed-scaling machinery never ran
+    with pytest.raises(ValueError):
+        m.lowp.set_static_scales({"qkv.0.inp": 1.0})        # incomplete table

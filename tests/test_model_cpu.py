@@ -121,3 +121,27 @@ def test_debug_nan_scan_cpu():
     m.g["lnfw"].view(-1)[1] = float("-inf")
     assert m.debug_nan_scan("grads") == {"wpe": (1, 0), "lnfw": (0, 2)}
     assert ops.nan_census(torch.tensor([1.0, float("nan"), float("inf")])) == (1, 1)
+
+
+def test_unfused_softmax_and_crossentropy_match_autograd():
+    """softmax backward and the unfused cross-entropy pair against autograd (the reference's stand-alone ops,
+    llmm/softmax.mojo:632 and llmm/crossentropy.mojo:110 / :284)."""
+    import torch
+    from llm_mojo_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    rows, V, ld = 6, 37, 40
+    logits = torch.randn(rows, ld, generator=g, requires_grad=True)
+    tgt = torch.randint(0, V, (rows,), generator=g, dtype=torch.int32)
+    probs_v = torch.softmax(logits[:, :V], dim=-1)
+    losses = -torch.log(probs_v.gather(1, tgt.long().view(-1, 1))).squeeze(1)
+    dloss = torch.randn(rows, generator=g)
+    (losses * dloss).sum().backward()
+    probs = torch.zeros(rows, ld)
+    probs[:, :V] = probs_v.detach()
+    assert torch.allclose(ops.softmax_rows(logits.detach(), V), probs[:, :V], atol=1e-6)
+    assert torch.allclose(ops.crossentropy_fwd(probs, tgt), losses.detach(), atol=1e-6)
+    dprobs = torch.zeros(rows, ld)
+    ops.crossentropy_bwd(dprobs, dloss, probs, tgt)
+    dlogits = ops.softmax_bwd(dprobs, probs, V)
+    assert torch.allclose(dlogits, logits.grad, atol=1e-5)
+    assert torch.all(dlogits[:, V:] == 0)

@@ -113,3 +113,40 @@ def test_short_training_run_per_precision(precision, tmp_path):
     losses = [tr.train_step()["loss"] for _ in range(5)]
     assert all(torch.isfinite(torch.tensor(l)) for l in losses)
     assert losses[-1] < losses[0]
+
+
+def test_record_run_result_parses_the_trainers_own_lines(tmp_path):
+    """The reporting tool reads the trainer's step / val-loss lines and the eval tool's HellaSwag line."""
+    import record_run_result as rr
+    from llm_mojo_b200.utils.logger import format_step_line
+    log = tmp_path / "train.log"
+    lines = ["val loss 10.900000"]
+    for s in range(1, 9):
+        lines.append(format_step_line(s, 8, 11.0 - s * 0.1, float("nan"), 1.5, float("nan"), 3e-4, 100.0 + s, 0.4, "bf16", 5000 + s, 99.0))
+    lines.append("val loss 10.100000")
+    log.write_text("\n".join(lines) + "\n")
+    ev = tmp_path / "eval.log"
+    ev.write_text("HellaSwag: 2965/10042 = 0.2953\n")
+    res = rr.record("tiny", str(log), str(ev), str(tmp_path / "results"))
+    assert res["steps_run"] == 8 and res["val_loss_final"] == 10.1 and res["val_loss_best"] == 10.1
+    assert abs(res["ms_per_step_median"] - 106.5) < 1e-6
+    lo, hi = res["hellaswag"]["wilson95"]
+    assert lo < 0.2953 < hi and hi - lo < 0.02
+    assert "| tiny | 8/8 |" in rr.table(str(tmp_path / "results"))
+
+
+def test_gate_lock_serialises_and_reports_holders(tmp_path, monkeypatch):
+    import subprocess, time
+    lock = str(tmp_path / "gate.lock")
+    env = dict(os.environ, LLMB_GATE_LOCK=lock)
+    gate = os.path.join(ROOT, "gate.py")
+    holder = subprocess.Popen([sys.executable, gate, "run", sys.executable, "-c", "import time; time.sleep(3)"], env=env,
+                              stdout=subprocess.PIPE, text=True)
+    time.sleep(1.0)
+    st = subprocess.run([sys.executable, gate, "status"], env=env, capture_output=True, text=True)
+    assert "held by" in st.stdout and "gate.py run" in st.stdout and st.stdout.count("pid=") >= 2   # runner and its child
+    t0 = time.time()
+    second = subprocess.run([sys.executable, gate, "run", sys.executable, "-c", "print('second ran')"], env=env,
+                            capture_output=True, text=True, timeout=60)
+    assert "second ran" in second.stdout and time.time() - t0 > 1.0       # it had to wait for the holder
+    holder.wait(timeout=30)

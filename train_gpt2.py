@@ -43,6 +43,7 @@ Options (mirroring Karpathy's train_gpt2.cu):
   -pn <int>   num_processes / world_size (default = 1)
   -pr <int>   process_rank (default = 0)
   --precision <fp32|tf32|bf16|fp8|fp8b|fp4>   (default bf16 on GPU, fp32 on CPU; fp8b = fp8 with per-128 block scales)
+  --fp8-static-scales <json>  with --precision fp8: fixed scales from calibrate_fp8_scales.py instead of delayed scaling
   --synthetic 1     train on uniform random tokens (no data files needed)
   --comm <auto|p2p|nccl|gloo>  collective backend (default auto: peer-memory kernels on GPUs)
   --config <zero json>  read {zero_stage, world_size, precision, train_flags} from a zero/zeroN.json
@@ -58,7 +59,7 @@ _FLAGS = {
     "-a": ("overfit_single_batch", int), "-x": ("max_steps", int), "-z": ("zero_stage", int),
     "--precision": ("precision", str), "--synthetic": ("synthetic", lambda v: bool(int(v))),
     "--comm": ("comm_backend", str), "--grad-clip": ("grad_clip", float), "--beta2": ("beta2", float),
-    "--recompute": ("recompute", lambda v: bool(int(v))),
+    "--recompute": ("recompute", lambda v: bool(int(v))), "--fp8-static-scales": ("fp8_static_scales", str),
 }
 
 
