@@ -65,8 +65,28 @@ struct GatherArgs {
   int W, me, tiles_per_chunk;  // W = 0: no gather
 };
 
+// Parameter pull fused into a GEMM (ZeRO-3): the kernel's copier warps copy up to 8 segments of weights out of their
+// owners' parameter shards (plain 16-byte loads over NVLink, or local memory for the rank's own part) into this
+// rank's layer window while the tensor-core tile loop of the SAME kernel runs.  The segments may belong to the B
+// operand of this GEMM (then its TMA producer waits for them) or to the operand of a later GEMM of the layer, which
+// only checks the counters: every weight then arrives under the math of a tile loop.  Owners announce "my shard
+// holds the parameters of optimizer step seq" at flag kind PARAM; all waits are bounded.
+struct PullArgs {
+  const void* src[8];          // segment source (peer or local shard memory), 16-byte aligned
+  void* dst[8];                // segment destination inside the local window
+  long long vecs[8];           // 16-byte vectors per segment
+  const void* flags;           // this rank's flag words
+  unsigned* counts;            // [16] zeroed before the launch: [s] = slices of segment s landed, [8 + s] = slice tickets
+  const unsigned* wait_counts[8];   // counters this GEMM's B operand depends on ...
+  unsigned wait_target[8];          // ... and the value each must reach
+  unsigned seq;                // parameter sequence number the owners must have announced (0: none yet, no wait)
+  int owner[8];
+  int nseg, nwait, W;          // nseg = 0: nothing to pull; nwait = 0: nothing to wait for
+};
+
 struct GemmParams {
   GatherArgs g;
+  PullArgs pull;
   void* D; const void* bias; void* aux; const float* alpha;
   int M, N, K;                 // K in elements
   long long ldd, ldaux;
@@ -471,6 +491,7 @@ constexpr int B2_STAGE = 128 * ROW_BYTES;             // 16 KB: this CTA's half 
 constexpr int STAGE2_BYTES = A_STAGE + B2_STAGE;      // 32 KB
 constexpr int PAIR_THREADS = 384;                      // TMA producer, MMA issuer, 8 epilogue warps, 2 gather copier warps
 constexpr int FLAG_ROWS_READY = 6;                     // flag kind (layout of comm.cu: flags[kind][8 ranks])
+constexpr int FLAG_PARAM = 3;                          // owners announce the optimizer step their parameter shard holds
 constexpr int SMEM2_TAIL = 512;                        // barriers, TMEM slot, abort flag
 template <int EPI> constexpr int smem2_bytes() { return EpiCfg<EPI>::STAGES * STAGE2_BYTES + 4 * EpiCfg<EPI>::WARP_STAGE + 1024 + SMEM2_TAIL; }
 
@@ -538,7 +559,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t lead_full0 = mapa_u32(smem_u32(&full_bar[0]), 0);
       bool ok = true;
       int landed = -1;
-      for (int unit = cluster_id; unit < total_units && !*abort_flag; unit += num_clusters) {
+      // B operand pulled from peers (by this kernel's copier warps or by an earlier kernel's): all of it must have landed
+      for (int w = 0; w < p.pull.nwait && ok; ++w) {
+        unsigned spins = 0;
+        while ((int)(ld_acquire_gpu(p.pull.wait_counts[w]) - p.pull.wait_target[w]) < 0) {
+          if (++spins > (1u << 24)) { ok = false; break; }
+          __nanosleep(100);
+        }
+      }
+      if (p.pull.nwait) fence_proxy_async_all();          // the copiers' generic-proxy stores before this warp's TMA reads
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
+      for (int unit = cluster_id; unit < total_units && ok && !*abort_flag; unit += num_clusters) {
         int m_blk, n_blk, kb0, kb1; unit_coords(unit, m_blk, n_blk, kb0, kb1);
         int m0 = m_blk * 2 * BM + (int)cta * BM, n0 = n_blk * BN + (int)cta * 128;
         if (p.dbg & 2) { m0 = (int)cta * BM; n0 = (int)cta * 128; }
@@ -670,6 +701,47 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __threadfence();
           __syncwarp();
           if (lane == 0) atomicAdd(&p.g.counts[r], 1u);
+        }
+      }
+      if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
+    } else if (p.pull.nseg > 0) {
+      // ZeRO-3 parameter pull: same ticketed 32 KB slices, one list of segments instead of one chunk per rank
+      constexpr long long SLICE = 2048;                  // 16-byte vectors
+      bool ok = true;
+      for (int sgm = 0; sgm < p.pull.nseg && ok; ++sgm) {
+        if (p.pull.seq && lane == 0) {                    // the owner's shard holds this step's parameters
+          const unsigned* f = reinterpret_cast<const unsigned*>(p.pull.flags) + FLAG_PARAM * 8 + p.pull.owner[sgm];
+          unsigned spins = 0;
+          while ((int)(ld_acquire_sys(f) - p.pull.seq) < 0) {
+            if (++spins > (1u << 24)) { ok = false; break; }
+            __nanosleep(200);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        const uint4* src = reinterpret_cast<const uint4*>(p.pull.src[sgm]);
+        uint4* dst = reinterpret_cast<uint4*>(p.pull.dst[sgm]);
+        const long long nvec = p.pull.vecs[sgm];
+        const unsigned target = (unsigned)((nvec + SLICE - 1) / SLICE);
+        for (;;) {
+          unsigned ticket = 0;
+          if (lane == 0) ticket = atomicAdd(&p.pull.counts[8 + sgm], 1u);
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          if (ticket >= target) break;
+          const long long v0 = (long long)ticket * SLICE;
+          const long long v1 = v0 + SLICE < nvec ? v0 + SLICE : nvec;
+          long long v = v0 + lane;
+          for (; v + 7 * 32 < v1; v += 8 * 32) {         // eight loads in flight per thread
+            uint4 t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = ld_nc_v4(src + v + k * 32);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) dst[v + k * 32] = t[k];
+          }
+          for (; v < v1; v += 32) dst[v] = ld_nc_v4(src + v);
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(&p.pull.counts[sgm], 1u);
         }
       }
       if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.status, LLMB_ERR_TIMEOUT); }
@@ -814,6 +886,7 @@ template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ESZ = 1; stati
 int g_dbg_mn_lbo = -1, g_dbg_mn_sbo = -1;   // test hooks: override the MN-major descriptor strides
 thread_local float* g_pending_colsum = nullptr;   // armed by llmb_gemm_set_colsum, consumed by the calling thread's next llmb_gemm
 thread_local GatherArgs g_pending_gather{};   // armed by llmb_gemm_set_gather, consumed (and cleared) by the calling thread's next llmb_gemm
+thread_local PullArgs g_pending_pull{};       // armed by llmb_gemm_set_pull, consumed (and cleared) the same way
 int g_pair_mode = -1;                         // -1: read LLMB_GEMM_PAIR once; 0: single-CTA tiles; 1: CTA-pair tiles
 
 bool pair_mode() {
@@ -890,6 +963,9 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   GemmParams p;
   p.g = g_pending_gather;
   g_pending_gather.W = 0;
+  p.pull = g_pending_pull;
+  g_pending_pull.nseg = 0; g_pending_pull.nwait = 0;
+  if ((p.pull.nseg > 0 || p.pull.nwait > 0) && (!pair || p.g.W > 1)) return LLMB_ERR_BAD_ARG;   // copier warps exist in the pair kernel only
   p.colsum = g_pending_colsum;
   g_pending_colsum = nullptr;
   if (p.colsum && !(pair && epi == EPI_DGELU && KIND == KIND_F16)) return LLMB_ERR_BAD_ARG;
@@ -1284,6 +1360,25 @@ LLMB_API void llmb_gemm_set_gather(void* const* peer_src, void* local, const voi
   g.local = local; g.flags = flags; g.counts = counts; g.chunk_vecs = chunk_bytes / 16;
   g.seq = seq; g.target = (unsigned)((g.chunk_vecs + 2047) / 2048); g.W = W; g.me = me; g.tiles_per_chunk = rows_per_rank / (2 * BM);
   g_pending_gather = g;
+}
+// Arms the calling thread's NEXT llmb_gemm call (CTA-pair kernel) with a parameter pull and / or a wait (see PullArgs).
+// Segment s copies nbytes[s] bytes (a multiple of 16, both addresses 16-byte aligned) from src[s] (memory of rank
+// owner[s], mapped here) to dst[s]; counts = 16 counters zeroed (stream-ordered) before the launch.  wait_counts[i]
+// must reach wait_bytes[i] / 32 KB (rounded up) before the GEMM's B operand is read.  seq: parameter sequence number
+// every owner must have announced (0 = parameters as loaded, nothing to wait for).
+LLMB_API int llmb_gemm_set_pull(const void* const* src, void* const* dst, const long long* nbytes, const int* owner, int nseg,
+                                const void* flags, unsigned seq, unsigned* counts, const unsigned* const* wait_counts,
+                                const long long* wait_bytes, int nwait, int W) {
+  if (nseg < 0 || nseg > 8 || nwait < 0 || nwait > 8) return LLMB_ERR_BAD_ARG;
+  PullArgs a{};
+  for (int i = 0; i < nseg; ++i) {
+    if ((reinterpret_cast<uintptr_t>(src[i]) | reinterpret_cast<uintptr_t>(dst[i]) | (uintptr_t)nbytes[i]) & 15) return LLMB_ERR_BAD_ARG;
+    a.src[i] = src[i]; a.dst[i] = dst[i]; a.vecs[i] = nbytes[i] / 16; a.owner[i] = owner[i];
+  }
+  for (int i = 0; i < nwait; ++i) { a.wait_counts[i] = wait_counts[i]; a.wait_target[i] = (unsigned)((wait_bytes[i] / 16 + 2047) / 2048); }
+  a.flags = flags; a.counts = counts; a.seq = seq; a.nseg = nseg; a.nwait = nwait; a.W = W;
+  g_pending_pull = a;
+  return 0;
 }
 // Arms the calling thread's NEXT llmb_gemm call (bf16, epilogue 3 = dGELU, CTA-pair kernel with the TMA epilogue) to add the column
 // sums of its result to colsum[N] (fp32, red.add): the bias gradient of the layer that produced the pre-activations.

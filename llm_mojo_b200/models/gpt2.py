@@ -292,6 +292,8 @@ class GPT2:
             from ..ops import lowp
             lowp.matmul_fwd_fp4(out, inp, weight, bias, **kw)
         else:
+            if self.zero is not None:
+                self.zero.arm_linear(site, layer, backward=False)     # ZeRO-3: weight pulls ride on the layer GEMMs
             ops.matmul_fwd(out, inp, weight, bias, **kw)
 
     def _linear_bwd(self, site, layer, dinp, dweight, dbias, dout, inp, weight, **kw) -> None:
@@ -307,6 +309,8 @@ class GPT2:
             lowp.matmul_bwd_fp4(dinp, dweight, dbias, dout, inp, weight, rht=self.precision.fp4_rht,
                                 sr=self.precision.fp4_sr, seed=self.rng_seed, step=self.micro_steps_done, **kw)
         else:
+            if self.zero is not None:
+                self.zero.arm_linear(site, layer, backward=True)      # armed for the input-gradient GEMM, the first one launched
             ops.matmul_bwd(dinp, dweight, dbias, dout, inp, weight, **kw)
 
     # ------------------------------------------------------------------ forward

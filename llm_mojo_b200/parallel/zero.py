@@ -409,6 +409,7 @@ class ZeroEngine:
             self.embed_valid = False
             self.window_layers = {}
             self.window_events = [None, None]
+            self._setup_fused_pull(p2p)
         # ---- optimizer state (sharded for stage >= 1)
         n_opt = S if self.stage >= 1 else self.padded if W > 1 else P
         self.n_opt = n_opt
@@ -473,10 +474,12 @@ class ZeroEngine:
 
     # ------------------------------------------------------------------ parameter residency (stage 3)
     def _gather_layer(self, l: int, prefetch: bool = False) -> None:
-        """Make layer ``l``'s parameters resident in window ``l % 2``.  With ``prefetch`` (peer-memory
+        """Make layer ``l``'s parameters resident in window ``l % 2``.  (Fused mode: its small tensors only.)  With ``prefetch`` (peer-memory
         backend) the pull kernel runs on the comm stream, after everything already queued on the main
         stream (the previous occupant of the window may still be in use there), and the main stream
         only waits for it when the layer is actually needed."""
+        if getattr(self, "fused_z3", False):
+            return self._gather_layer_small(l, prefetch)
         if l in self.window_layers:
             return
         slot = l % 2
@@ -495,6 +498,124 @@ class ZeroEngine:
             self.window_events[slot] = done
         else:
             self.backend.gather_ranges(self.param_shard, self.S, self._segs(l), win)
+            self.window_events[slot] = None
+        self.window_layers[l] = slot
+        self._view_bucket(l, win, self.model.p)
+
+
+    # ------------------------------------------------------------------ stage 3: weight pulls fused into the layer GEMMs
+    WEIGHTS = ("qkvw", "attprojw", "fcw", "fcprojw")
+    SITE_WEIGHT = {"qkv": "qkvw", "attproj": "attprojw", "fc": "fcw", "fcproj": "fcprojw"}
+
+    def _setup_fused_pull(self, p2p: bool) -> None:
+        """With the peer-memory backend on bf16 tensor-core GEMMs the four weight matrices of a layer are not gathered
+        by a collective kernel: the copier warps of the layer's GEMM kernels pull them out of their owners' shards
+        while the tile loops run (``csrc/gemm.cu``, PullArgs).  Every GEMM that reads a weight carries the pull of the
+        NEXT weight in execution order (forward: qkv, attproj, fc, fcproj, next layer's qkv ...; backward the reverse),
+        so a weight has landed when its own GEMM starts; the first GEMM of a pass pulls its own operand as well and
+        waits for it.  Only the small tensors of a layer (LayerNorm parameters, biases) still come by the gather kernel.
+        ``LLMM_FUSED_Z3=0`` selects the whole-layer gather, prefetched one layer ahead."""
+        m = self.model
+        self.fused_z3 = bool(p2p and self.world_size > 1 and m.dtype == torch.bfloat16 and m.precision.name == "bf16"
+                             and ops.GEMM_IMPL == "tcgen05" and os.environ.get("LLMB_GEMM_PAIR", "1") != "0"
+                             and os.environ.get("LLMM_FUSED_Z3", "1") != "0")
+        if not self.fused_z3:
+            return
+        L = m.config.num_layer
+        self._pull_counts = torch.zeros(2 * L * 4 + 2, 16, dtype=torch.int32, device=self.device)
+        self._pull_order = {False: [(l, w) for l in range(L) for w in self.WEIGHTS],
+                            True: [(l, w) for l in reversed(range(L)) for w in reversed(self.WEIGHTS)]}
+        self._pull_pos = {ph: {k: i for i, k in enumerate(o)} for ph, o in self._pull_order.items()}
+        self._pulled: Dict[Tuple[int, str], Tuple[int, List[Tuple[int, int]]]] = {}    # weight -> (counts row, [(segment, bytes)])
+        self._pull_job = 0
+        lib = self.backend.L
+        P, I, U, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_longlong
+        lib.llmb_gemm_set_pull.argtypes = [ctypes.POINTER(P), ctypes.POINTER(P), ctypes.POINTER(LL), ctypes.POINTER(I), I, P, U, P,
+                                           ctypes.POINTER(P), ctypes.POINTER(LL), I, I]
+        lib.llmb_gemm_set_pull.restype = I
+        # window offsets of a layer's tensors (the window holds the bucket's ranges back to back)
+        self._win_off, k = {}, 0
+        for n, (b, e) in zip(LAYER_TENSORS, self.buckets[0]):
+            self._win_off[n] = k
+            k += e - b
+
+    def _weight_segments(self, l: int, name: str) -> List[Tuple[int, int, int, int]]:
+        """(owner, source address, destination address, bytes) for every piece of weight ``name`` of layer ``l``."""
+        A, S = self.backend.arena, self.S
+        b, e = self.model.tensor_range(name, l)
+        win = self.windows[l % 2]
+        out = []
+        for r in range(self.world_size):
+            own = intersect((b, e), (r * S, (r + 1) * S))
+            if own is None:
+                continue
+            src = A.peer_bases[r] + A.offsets["params"] + (own[0] - r * S) * 2
+            dst = win.data_ptr() + (self._win_off[name] + own[0] - b) * 2
+            out.append((r, src, dst, (own[1] - own[0]) * 2))
+        return out
+
+    def begin_pass(self, backward: bool) -> None:
+        """Start of a forward or backward pass: the pull counters are zeroed (stream-ordered behind the previous pass)."""
+        if getattr(self, "fused_z3", False):
+            self._pull_counts.zero_()
+            self._pulled.clear()
+            self._pull_job = 0
+
+    def arm_linear(self, site: str, l: int, backward: bool) -> None:
+        """Called right before the GEMM that reads the weight of ``site`` in layer ``l`` (forward GEMM, or the input-
+        gradient GEMM in backward): arms that GEMM with the pull of the next weight and the wait for its own."""
+        if not getattr(self, "fused_z3", False):
+            return
+        name = self.SITE_WEIGHT[site]
+        order, pos = self._pull_order[backward], self._pull_pos[backward][(l, name)]
+        todo = []
+        if (l, name) not in self._pulled:
+            todo.append((l, name))                          # first GEMM of the pass: its own operand
+        if pos + 1 < len(order):
+            todo.append(order[pos + 1])
+        row = self._pull_job
+        self._pull_job += 1
+        segs = []
+        for key in todo:
+            mine = []
+            for seg in self._weight_segments(*key):
+                mine.append((len(segs), seg[3]))
+                segs.append(seg)
+            self._pulled[key] = (row, mine)
+        if len(segs) > 8:
+            raise RuntimeError("a weight pull of more than 8 segments does not fit one GEMM launch")
+        wrow, wsegs = self._pulled[(l, name)]
+        P, LL, I = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+        n = len(segs)
+        src = (P * 8)(*[s_[1] for s_ in segs]); dst = (P * 8)(*[s_[2] for s_ in segs])
+        nb = (LL * 8)(*[s_[3] for s_ in segs]); own = (I * 8)(*[s_[0] for s_ in segs])
+        base = self._pull_counts.data_ptr()
+        wc = (P * 8)(*[base + (wrow * 16 + i) * 4 for i, _ in wsegs]); wb = (LL * 8)(*[nbytes for _, nbytes in wsegs])
+        A = self.backend.arena
+        _lib.check(self.backend.L.llmb_gemm_set_pull(src, dst, nb, own, n, A.flags_ptr, self.backend.param_seq,
+                                                     base + row * 64, wc, wb, len(wsegs), self.world_size), "gemm_set_pull")
+
+    def _gather_layer_small(self, l: int, prefetch: bool = False) -> None:
+        """Fused mode: only the LayerNorm parameters and biases of layer ``l`` come by the gather kernel."""
+        if l in self.window_layers:
+            return
+        slot = l % 2
+        for victim in [k for k, v in self.window_layers.items() if v == slot]:
+            del self.window_layers[victim]
+            for n in LAYER_TENSORS:
+                self.model.p[n].t.pop(victim, None)
+        win = self.windows[slot]
+        segs = [sg for n, sg in zip(LAYER_TENSORS, self._segs(l)) if n not in self.WEIGHTS]
+        if prefetch:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream())
+            self.backend.stream.wait_event(ready)
+            self.backend.gather_ranges(self.param_shard, self.S, segs, win, stream=self.backend.stream)
+            done = torch.cuda.Event()
+            done.record(self.backend.stream)
+            self.window_events[slot] = done
+        else:
+            self.backend.gather_ranges(self.param_shard, self.S, segs, win)
             self.window_events[slot] = None
         self.window_layers[l] = slot
         self._view_bucket(l, win, self.model.p)
@@ -532,12 +653,16 @@ class ZeroEngine:
     # ------------------------------------------------------------------ hooks called by the model
     def before_embedding(self, backward: bool = False) -> None:
         self._params_ready()
+        if not backward:
+            self.begin_pass(False)
         if self.stage == 3:
             self._gather_embed()
         if backward and self.stage >= 2:
             self._next_pool("embed")
 
     def before_head(self, backward: bool) -> None:
+        if backward:
+            self.begin_pass(True)
         if self.stage == 3:
             self._gather_embed()
         if backward and self.stage >= 2:

@@ -95,7 +95,8 @@ WORKER = textwrap.dedent('''
     full = model.full_params().float().cpu()
     st = _lib.read_status()
     if rank == 0:
-        torch.save({"params": full, "losses": losses, "status": st, "norm": float(norm)}, os.environ["OUT"])
+        torch.save({"params": full, "losses": losses, "status": st, "norm": float(norm),
+                    "fused_z3": bool(getattr(eng, "fused_z3", False))}, os.environ["OUT"])
     dist.barrier()
     eng.close()
     dist.destroy_process_group()
@@ -157,3 +158,17 @@ def test_fused_gather_gemm_matches_collective_then_gemm(tmp_path):
         assert abs(lf - lp) < 1e-3 and abs(lf - lr) < 2e-2, (fused["losses"], plain["losses"], repl["losses"])
     rel = ((fused["params"] - plain["params"]).norm() / plain["params"].norm()).item()
     assert rel < 1e-4, rel
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_zero3_weight_pull_inside_gemm_matches_gather_kernel(tmp_path):
+    """ZeRO-3 on the peer-memory backend: the layer weights pulled by the copier warps of the layer's own GEMM kernels
+    (default) against the stand-alone gather kernel prefetched one layer ahead.  The same bytes land in the same
+    windows, so losses and parameters must agree to the last bit."""
+    fused = _run(3, "p2p", 2, str(tmp_path), LLMM_FUSED_Z3="1")
+    plain = _run(3, "p2p", 2, str(tmp_path), LLMM_FUSED_Z3="0")
+    assert fused["status"] == 0 and plain["status"] == 0
+    assert fused["fused_z3"] and not plain["fused_z3"]
+    assert fused["losses"] == plain["losses"], (fused["losses"], plain["losses"])
+    assert torch.equal(fused["params"], plain["params"])
+    assert fused["losses"][-1] < fused["losses"][0]
