@@ -29,7 +29,7 @@ namespace {
 constexpr int MAX_RANKS = 8;
 constexpr int MAX_SEGS = 40;
 enum { FLAG_READY = 0, FLAG_DONE = 1, FLAG_READY2 = 2, FLAG_PARAM = 3, FLAG_SCALAR = 4, FLAG_DONE2 = 5, FLAG_ROWS_READY = 6,
-       FLAG_ROWS_DONE = 7, NUM_FLAG_KINDS = 8 };
+       FLAG_ROWS_DONE = 7, FLAG_STATS_READY = 8, FLAG_STATS_DONE = 9, NUM_FLAG_KINDS = 10 };
 
 struct PeerPtrs { void* p[MAX_RANKS]; };
 struct SegList {
@@ -295,6 +295,32 @@ __global__ void scalar_allreduce_kernel(float* __restrict__ out, const float* __
   }
 }
 
+// ------------------------------------------------------------------ cross-rank merge of softmax statistics
+// Vocabulary-parallel LM head: every rank holds {max, sum-exp, target logit, -} of ITS vocabulary slice for ALL rows in a
+// symmetric buffer.  Each rank reads the W copies of a row with peer loads and writes the statistics of the whole
+// vocabulary to a local buffer: max over ranks, sum-exps rescaled to it, target logits added (exactly one rank's is
+// non-zero).  READY: "my slice's statistics are written"; DONE: "I have read everybody's" (the buffers may be rewritten).
+__global__ void __launch_bounds__(256) ce_stats_merge_kernel(float4* __restrict__ out, PeerPtrs stats, long long rows, void* my_flags,
+                                                            PeerPtrs flags, int me, int W, unsigned seq, unsigned* counter, int* status) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < W; ++r) st_release_sys(flag_ptr(flags.p[r], FLAG_STATS_READY, me), seq);
+  }
+  if (!wait_all(my_flags, FLAG_STATS_READY, seq, W, status)) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += (long long)gridDim.x * blockDim.x) {
+    float4 v[MAX_RANKS];
+    float m = -INFINITY;
+    for (int r = 0; r < W; ++r) { v[r] = reinterpret_cast<const float4*>(stats.p[r])[i]; m = fmaxf(m, v[r].x); }
+    float sum = 0.f, tgt = 0.f;
+    for (int r = 0; r < W; ++r) {
+      if (v[r].y > 0.f) sum += v[r].y * expf(v[r].x - m);       // an empty slice has max -inf and sum 0
+      tgt += v[r].z;
+    }
+    out[i] = make_float4(m, sum, tgt, 0.f);
+  }
+  signal_all_last_block(counter, flags, FLAG_STATS_DONE, me, seq, W);
+}
+
 struct SegArgs { int n; const int* owner; const long long* src_off; const long long* dst_off; const long long* len; };
 bool fill(SegList& s, int n, const int* owner, const long long* src, const long long* dst, const long long* len) {
   if (n < 0 || n > MAX_SEGS) return false;
@@ -399,6 +425,16 @@ LLMB_API int llmb_comm_signal(void* const* flag_ptrs, int kind, int me, int W, u
 }
 LLMB_API int llmb_comm_wait(void* my_flags, int kind, unsigned seq, int W, int* status, cudaStream_t st) {
   wait_flags_kernel<<<1, 32, 0, st>>>(my_flags, kind, seq, W, status);
+  return (int)cudaGetLastError();
+}
+// out [rows] float4 (local) = statistics merged over the W ranks' symmetric `stats` buffers; see ce_stats_merge_kernel
+LLMB_API int llmb_comm_ce_stats_merge(void* out, void* const* stats_ptrs, long long rows, void* my_flags, void* const* flag_ptrs,
+                                      int me, int W, unsigned seq, unsigned* counter, int* status, int blocks, cudaStream_t st) {
+  if (rows <= 0 || W < 1 || W > MAX_RANKS) return LLMB_ERR_BAD_ARG;
+  long long need = ceil_div_ll(rows, 256);
+  const int grid = (int)(need < blocks ? need : blocks);
+  ce_stats_merge_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<float4*>(out), to_peers(stats_ptrs, W), rows, my_flags,
+                                              to_peers(flag_ptrs, W), me, W, seq, counter, status);
   return (int)cudaGetLastError();
 }
 LLMB_API int llmb_comm_scalar_allreduce(float* out, const float* in, void* my_scalars, void* const* scalar_ptrs, void* my_flags,

@@ -80,9 +80,10 @@ class GPT2:
         # Vocabulary-parallel LM head: every rank holds the logits of ALL ranks' rows for its 1/W slice of the
         # vocabulary (activation all-gather -> slice GEMM -> cross-entropy with the log-sum-exp merged across
         # ranks -> reduce-scatter of the hidden-state gradient).  The reference evaluated and rejected this on
-        # PCIe (README.md:153); it needs a ZeRO engine with world_size > 1 and stage < 3.
+        # PCIe (README.md:153); it needs a ZeRO engine with world_size > 1.  Under ZeRO-3 the slice is a view of the
+        # gathered embedding window, which the token embedding needs in full anyway.
         vp = os.environ.get("LLMM_VOCAB_PARALLEL", "") not in ("", "0") if vocab_parallel is None else vocab_parallel
-        self.vocab_parallel = bool(vp and zero is not None and zero.world_size > 1 and zero.stage < 3)
+        self.vocab_parallel = bool(vp and zero is not None and zero.world_size > 1)
         self.checkpoint_path = source if isinstance(source, str) else ""
         # ---- three load paths: config/descriptor (random init), .bin, .safetensors
         if params_flat is not None:
@@ -195,7 +196,9 @@ class GPT2:
             a["ce_stats"] = e(W * B * T, 4, dtype=f32)
             # all-gather of the final LayerNorm rows fused into the slice GEMM (peer memory; bf16 tensor path, whole
             # 256-row tiles per rank); LLMM_FUSED_GATHER=0 keeps the collective + GEMM pair
+            # (every rank must own at least 8 vocabulary columns: the peer-memory path is collective)
             if (self.device.type == "cuda" and self.dtype == torch.bfloat16 and (B * T) % 256 == 0 and
+                    Vp - (W - 1) * self.vslice >= 8 and
                     getattr(self.zero, "backend_name", "") == "p2p" and os.environ.get("LLMM_FUSED_GATHER", "1") != "0"):
                 from ..parallel.zero import FusedRowGather
                 self._fused_gather = FusedRowGather(self.zero.rank, W, self.device, B * T, C)
@@ -228,14 +231,21 @@ class GPT2:
         tile = a["logits_slice"][:, :max(w, 8)]
         stats = a["ce_stats"]
         fg = self._fused_gather
-        if fg is not None and w >= 8:
-            # ONE kernel: the other ranks' rows are pulled over NVLink by copier warps inside the slice GEMM
-            fg.gemm(tile, p["wte"][v0:v0 + w])
+        if fg is not None:
+            # peer-memory path: this slice's statistics go into the symmetric buffer, ONE kernel merges all ranks' copies
+            fg.stats_writable()
+            fg.gemm(tile, p["wte"][v0:v0 + w])              # the other ranks' rows are pulled over NVLink inside the slice GEMM
             self._lnf_all = fg.buf
-        else:
-            self._lnf_all = z.all_gather_rows(a["lnf"].view(rows, C))
-            if w > 0:
-                ops.matmul_fwd(tile, self._lnf_all, p["wte"][v0:v0 + w])
+            ops.chunked_ce_pass1(fg.stats, tile, self._tgt_all, v0, w, V, True)
+            fg.merge_stats(stats)
+            losses_all = torch.empty(stats.shape[0], dtype=torch.float32, device=stats.device)
+            ops.chunked_ce_loss(losses_all, stats)
+            a["losses"].view(-1).copy_(losses_all[z.rank * rows:(z.rank + 1) * rows])
+            self.loss_acc += a["losses"].sum() * dloss
+            return
+        self._lnf_all = z.all_gather_rows(a["lnf"].view(rows, C))
+        if w > 0:
+            ops.matmul_fwd(tile, self._lnf_all, p["wte"][v0:v0 + w])
         ops.chunked_ce_pass1(stats, tile, self._tgt_all, v0, w, V, True)
         # merge (max, sum-exp, target logit) over the vocabulary slices of all ranks
         allst = z.all_gather_rows(stats.unsqueeze(0))                      # [W, W·rows, 4]
@@ -254,6 +264,19 @@ class GPT2:
         tile = a["logits_slice"][:, :max(w, 8)]
         n_all = tile.shape[0]
         partial = ops.scratch("vp_dlnf", n_all * C * a["lnf"].element_size(), tile.device).view(a["lnf"].dtype)[:n_all * C].view(n_all, C)
+        fg = self._fused_gather
+        if fg is not None:
+            # peer-memory path: the hidden-state gradient of all rows in fp32, summed over ranks by the reduce kernel
+            # (bf16 on the wire), each rank keeping its own rows
+            p32 = ops.scratch("vp_dlnf32", n_all * C * 4, tile.device).view(torch.float32)[:n_all * C].view(n_all, C)
+            own32 = ops.scratch("vp_dlnf_own", (n_all // z.world_size) * C * 4, tile.device).view(torch.float32)[:(n_all // z.world_size) * C]
+            ops.chunked_ce_pass2(tile, a["ce_stats"], self._tgt_all, v0, w, V, self._dloss)
+            ops.gemm(p32, tile, p["wte"][v0:v0 + w], b_mn=True, epi=ops.EPI_STORE_F32)
+            ops.gemm(g["wte"][v0:v0 + w], tile, self._lnf_all, a_mn=True, b_mn=True, epi=ops.EPI_ACC_F32,
+                     splits=ops._splits_for(w, C, n_all))
+            z.reduce_scatter_rows_f32(p32.view(-1), own32)
+            dl.view(-1).copy_(own32)
+            return
         if w > 0:
             # dloss keeps the per-rank convention 1/(rows·accum): the slice's weight gradient then already
             # carries the factor W that the later mean over ranks removes

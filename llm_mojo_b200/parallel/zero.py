@@ -170,9 +170,10 @@ class P2PBackend:
     def _arr(vals: Sequence[int], ctype=ctypes.c_longlong):
         return (ctype * max(len(vals), 1))(*vals)
 
-    def reduce_ranges(self, src, segs, shard, dst, accumulate, allreduce, norm_acc=None) -> None:
+    def reduce_ranges(self, src, segs, shard, dst, accumulate, allreduce, norm_acc=None, scale=None) -> None:
         """Same contract as TorchDistBackend.reduce_ranges; asynchronous on the comm stream.  ``norm_acc``
-        (1 fp32) additionally receives the sum of squares of the reduced values this rank owns."""
+        (1 fp32) additionally receives the sum of squares of the reduced values this rank owns.  ``scale``
+        multiplies every contribution before it goes on the wire (default 1/W: the mean; 1.0: the sum)."""
         A, W, me = self.arena, self.world, self.rank
         total = sum(n for _, n, _ in segs)
         if total > self.send_cap:
@@ -200,7 +201,7 @@ class P2PBackend:
         send_name, recv_name = f"send{half}", f"recv{half}"
         send_ptr = A.base + A.offsets[send_name]
         _lib.check(self.L.llmb_comm_pack(send_ptr, src.data_ptr(), len(segs), self._arr(src_offs), self._arr(k_off),
-                                         self._arr(lens), 1.0 / W, A.flags_ptr, A.flags_peer_ptrs(), me, W, seq,
+                                         self._arr(lens), (1.0 / W) if scale is None else float(scale), A.flags_ptr, A.flags_peer_ptrs(), me, W, seq,
                                          self.send_last[half], A.counter_ptr(0), self.status.data_ptr(), self.blocks, st),
                    "comm_pack")
         self.send_last[half] = seq
@@ -294,7 +295,7 @@ class FusedRowGather:
     NVLink into the local buffer while the tensor-core tile loop already works on the local chunk, and a chunk's
     tiles are fetched once it has landed (csrc/gemm.cu, GatherArgs).  Flags: ROWS_READY (6) = "my chunk is written",
     ROWS_DONE (7) = "I have finished reading everybody's chunk"; both are sequence numbers, every wait is bounded."""
-    ROWS_READY, ROWS_DONE = 6, 7
+    ROWS_READY, ROWS_DONE, STATS_READY, STATS_DONE = 6, 7, 8, 9
 
     def __init__(self, rank: int, world: int, device: torch.device, rows_per_rank: int, K: int):
         from .symm import SymmetricArena
@@ -302,7 +303,11 @@ class FusedRowGather:
             raise ValueError("fused row gather needs rows per rank to be a multiple of 256")
         self.rank, self.world, self.device, self.n, self.K = rank, world, device, rows_per_rank, K
         self.chunk_bytes = rows_per_rank * K * 2
-        self.arena = SymmetricArena([("rows", world * self.chunk_bytes), ("counts", 64)], rank, world, device)
+        self.arena = SymmetricArena([("rows", world * self.chunk_bytes), ("counts", 64),
+                                     ("stats", world * rows_per_rank * 16)], rank, world, device)
+        # per-row softmax statistics of this rank's vocabulary slice, read by every peer in merge_stats()
+        self.stats = self.arena.tensor("stats", torch.float32).view(world * rows_per_rank, 4)
+        self.stats_seq = 0
         self.buf = self.arena.tensor("rows", torch.bfloat16).view(world * rows_per_rank, K)
         self.local = self.buf[rank * rows_per_rank:(rank + 1) * rows_per_rank]
         self.counts = self.arena.tensor("counts", torch.int32)
@@ -314,6 +319,7 @@ class FusedRowGather:
         self.L.llmb_comm_wait.argtypes = [P, I, U, I, P, P]
         self.L.llmb_gemm_set_gather.argtypes = [P, P, P, P, LL, U, I, I, I]
         self.L.llmb_gemm_set_gather.restype = None
+        self.L.llmb_comm_ce_stats_merge.argtypes = [P, ctypes.POINTER(P), LL, P, ctypes.POINTER(P), I, I, U, P, P, I, P]
         self._peer_src = (ctypes.c_void_p * 8)()
         off = self.arena.offsets["rows"]
         for r in range(world):                      # chunk r inside rank r's buffer
@@ -324,6 +330,22 @@ class FusedRowGather:
         if self.seq:
             _lib.check(self.L.llmb_comm_wait(self.arena.flags_ptr, self.ROWS_DONE, self.seq, self.world,
                                              self.status.data_ptr(), _lib.stream()), "rows_wait")
+
+    def stats_writable(self) -> None:
+        """Before ``stats`` is rewritten: every rank has read the previous contents."""
+        if self.stats_seq:
+            _lib.check(self.L.llmb_comm_wait(self.arena.flags_ptr, self.STATS_DONE, self.stats_seq, self.world,
+                                             self.status.data_ptr(), _lib.stream()), "stats_wait")
+
+    def merge_stats(self, out: torch.Tensor) -> None:
+        """out [W·n, 4] (local) = the ranks' ``stats`` merged into the statistics of the whole vocabulary: one kernel,
+        peer loads, no collective library (``csrc/comm.cu``, ce_stats_merge_kernel)."""
+        self.stats_seq += 1
+        A = self.arena
+        _lib.check(self.L.llmb_comm_ce_stats_merge(out.data_ptr(), A.peer_ptrs("stats"), self.stats.shape[0], A.flags_ptr,
+                                                   A.flags_peer_ptrs(), self.rank, self.world, self.stats_seq,
+                                                   A.counter_ptr(8), self.status.data_ptr(), 148, _lib.stream()), "ce_stats_merge")
+        ops._count()
 
     def gemm(self, D: torch.Tensor, weight: torch.Tensor) -> None:
         """D[W·n, N] = gathered rows · weightᵀ; call after the local chunk has been written on the current stream."""
@@ -781,6 +803,22 @@ class ZeroEngine:
         out = torch.empty((self.world_size * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         dist.all_gather_into_tensor(out, t.contiguous())
         return out
+
+    def reduce_scatter_rows_f32(self, partial: torch.Tensor, out: torch.Tensor) -> None:
+        """out [n·C] fp32 = rows [r·n, (r+1)·n) of the SUM over ranks of partial [W·n·C] fp32, through the peer-memory
+        reduce kernel (bf16 on the wire), in pieces that fit the send buffers; joins the main stream when done."""
+        W, be = self.world_size, self.backend
+        total, n = partial.numel(), partial.numel() // W
+        lo, hi = self.rank * n, (self.rank + 1) * n
+        cap = be.send_cap
+        for c0 in range(0, total, cap):
+            c1 = min(total, c0 + cap)
+            own = intersect((c0, c1), (lo, hi))
+            # positions are relative to this piece; ``shard`` is the owned part of it, ``dst`` starts at the first owned element
+            shard = (own[0] - c0, own[1] - c0) if own else (0, 0)
+            dst = out[own[0] - lo:] if own else out
+            be.reduce_ranges(partial[c0:c1], [(0, c1 - c0, 0)], shard, dst, False, False, scale=1.0)
+        be.sync()
 
     def reduce_scatter_rows(self, t: torch.Tensor) -> torch.Tensor:
         """Sum of [W·n, ...] over ranks; rank r keeps rows [r·n, (r+1)·n)."""

@@ -156,8 +156,10 @@ def test_fused_gather_gemm_matches_collective_then_gemm(tmp_path):
     assert fused["status"] == 0 and plain["status"] == 0
     for lf, lp, lr in zip(fused["losses"], plain["losses"], repl["losses"]):
         assert abs(lf - lp) < 1e-3 and abs(lf - lr) < 2e-2, (fused["losses"], plain["losses"], repl["losses"])
+    # the two runs round the hidden-state gradient differently on the wire (fp32 partial -> bf16 per rank -> fp32 sum in the
+    # peer kernel, bf16 partial -> bf16 sum in the library), so parameters agree like the p2p-vs-NCCL runs above, not bitwise
     rel = ((fused["params"] - plain["params"]).norm() / plain["params"].norm()).item()
-    assert rel < 1e-4, rel
+    assert rel < 2e-3, rel
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -172,3 +174,20 @@ def test_zero3_weight_pull_inside_gemm_matches_gather_kernel(tmp_path):
     assert fused["losses"] == plain["losses"], (fused["losses"], plain["losses"])
     assert torch.equal(fused["params"], plain["params"])
     assert fused["losses"][-1] < fused["losses"][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_vocab_parallel_head_under_zero3(tmp_path):
+    """The vocabulary-parallel LM head (slice GEMM with the row gather fused in, statistics merged and the hidden
+    gradient reduced by peer-memory kernels) together with ZeRO-3 parameter sharding, against ZeRO-3 with the
+    replicated head."""
+    vp = _run(3, "p2p", 2, str(tmp_path), VP="1")
+    repl = _run(3, "p2p", 2, str(tmp_path), VP="0")
+    assert vp["status"] == 0 and repl["status"] == 0
+    for a, b in zip(vp["losses"], repl["losses"]):
+        assert abs(a - b) < 2e-2, (vp["losses"], repl["losses"])
+    # the two heads compute the loss gradient along different routes (chunked statistics + bf16 wire vs the fused classifier), so
+    # after three AdamW steps the parameters agree to a few 1e-3, like any two bf16 runs
+    rel = ((vp["params"] - repl["params"]).norm() / repl["params"].norm()).item()
+    assert rel < 5e-3, rel
+    assert vp["losses"][-1] < vp["losses"][0]
