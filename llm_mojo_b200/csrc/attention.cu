@@ -251,6 +251,13 @@ __global__ void __launch_bounds__(BW_THREADS, 1) attn_bwd_dq2_kernel(const __gri
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_free[ab]);
+      if (p.dbias) {                          // qkv bias gradient, dQ part: column sums of this warp's 32 rows
+        float cv[32];
+#pragma unroll
+        for (int x = 0; x < 32; ++x) cv[x] = pend_qi < p.T ? __uint_as_float(r[x]) * p.scale : 0.f;
+        const float cs = warp_colsum32(cv, lane);
+        atomicAdd(p.dbias + pend_h * HS + grp * 32 + lane, cs);
+      }
       if (pend_qi < p.T) {
         __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)pend_b * p.T + pend_qi) * (3 * (size_t)p.C) + pend_h * HS + grp * 32;
         const float sc = p.scale;             // dS was stored without the 1/sqrt(HS) factor
@@ -466,6 +473,17 @@ __global__ void __launch_bounds__(BW_THREADS, 1) attn_bwd_dkv2_kernel(const __gr
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_free[ab]);
+      if (p.dbias) {                          // qkv bias gradient, dK and dV parts
+        float cv[32];
+#pragma unroll
+        for (int x = 0; x < 32; ++x) cv[x] = pend_kj < p.T ? __uint_as_float(rk[x]) * p.scale : 0.f;
+        const float ck = warp_colsum32(cv, lane);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) cv[x] = pend_kj < p.T ? __uint_as_float(rv[x]) : 0.f;
+        const float cvv = warp_colsum32(cv, lane);
+        atomicAdd(p.dbias + p.C + pend_h * HS + grp * 32 + lane, ck);
+        atomicAdd(p.dbias + 2 * p.C + pend_h * HS + grp * 32 + lane, cvv);
+      }
       if (pend_kj < p.T) {
         __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)pend_b * p.T + pend_kj) * (3 * (size_t)p.C) + pend_h * HS + grp * 32;
         const float sc = p.scale;             // dS^T was stored without the 1/sqrt(HS) factor
@@ -556,13 +574,21 @@ LLMB_API int llmb_attention_fwd(void* out, float* lse, const void* qkv, int B, i
 }
 
 // dqkv [B,T,3C] bf16 (fully overwritten); dvec: 16-byte aligned fp32 scratch of B*NH*(T + 128*ceil(T/64)) + 4 elements.
+LLMB_API int llmb_attention_bwd_dbias(void* dqkv, float* dbias, float* dvec, const void* dout, const void* qkv, const void* out,
+                                      const float* lse, int B, int T, int NH, int* status, cudaStream_t st);
 LLMB_API int llmb_attention_bwd(void* dqkv, float* dvec, const void* dout, const void* qkv, const void* out,
                                 const float* lse, int B, int T, int NH, int* status, cudaStream_t st) {
+  return llmb_attention_bwd_dbias(dqkv, nullptr, dvec, dout, qkv, out, lse, B, T, NH, status, st);
+}
+// As llmb_attention_bwd; with dbias != nullptr (fp32 [3C]) additionally dbias[c] += sum over all B*T rows of dqkv[:, c], i.e. the
+// gradient of the qkv bias, taken from the fp32 accumulators in the kernels' epilogues (atomic adds: not bitwise reproducible).
+LLMB_API int llmb_attention_bwd_dbias(void* dqkv, float* dbias, float* dvec, const void* dout, const void* qkv, const void* out,
+                                      const float* lse, int B, int T, int NH, int* status, cudaStream_t st) {
   const int C = NH * HS;
   CUtensorMap tq, td;
   int rc = make_qkv_map(&tq, qkv, B, T, 3 * C); if (rc) return 1000 + rc;
   rc = make_qkv_map(&td, dout, B, T, C); if (rc) return 1000 + rc;
-  AttnParams p{}; p.out = dqkv; p.lse = const_cast<float*>(lse); p.dout = dout; p.dvec = dvec;
+  AttnParams p{}; p.out = dqkv; p.lse = const_cast<float*>(lse); p.dout = dout; p.dvec = dvec; p.dbias = dbias;
   p.B = B; p.T = T; p.NH = NH; p.C = C; p.scale = 0.125f; p.scale_log2 = 0.125f * 1.4426950408889634f; p.status = status;
   static bool attr = false;
   if (!attr) {

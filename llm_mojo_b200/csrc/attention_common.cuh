@@ -22,6 +22,7 @@ struct AttnParams {
   int B, T, NH, C;
   float scale_log2;     // (1/sqrt(HS)) * log2(e)
   float scale;          // 1/sqrt(HS)
+  float* dbias;         // bwd, optional: fp32 [3C], += column sums of dqkv (the gradient of the qkv bias)
   int* status;
 };
 
@@ -65,7 +66,23 @@ __device__ __forceinline__ void mma_kmn(uint32_t d, uint32_t a_addr, uint32_t b_
   for (int k = 0; k < nk; ++k) umma_ss<KIND_F16>(d, ad + 2 * k, bd + 128 * k, idesc, (acc_first || k > 0) ? 1u : 0u);
 }
 
-#define ATTN_FAIL() do { atomicExch(p.status, LLMB_ERR_TIMEOUT); fail = 1; } while (0)
+// Column sums across a warp: every lane holds 32 values (one row, 32 columns); afterwards lane c holds the sum of
+// column c over the 32 lanes.  Butterfly reduce-scatter: 31 shuffles instead of 32 x 5.
+template <int NLEFT>
+__device__ __forceinline__ void colsum_step(float (&v)[32], int lane) {
+  constexpr int H = NLEFT / 2;
+  const bool upper = (lane & H) != 0;
+#pragma unroll
+  for (int i = 0; i < H; ++i) {
+    const float send = upper ? v[i] : v[i + H];
+    const float keep = upper ? v[i + H] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, H);
+  }
+}
+__device__ __forceinline__ float warp_colsum32(float (&v)[32], int lane) {
+  colsum_step<32>(v, lane); colsum_step<16>(v, lane); colsum_step<8>(v, lane); colsum_step<4>(v, lane); colsum_step<2>(v, lane);
+  return v[0];
+}
 
 // a 128-row tile is fetched as two 64-row boxes (same swizzled layout, one tensor map for every tile size)
 __device__ __forceinline__ void load128(unsigned char* dst, const CUtensorMap* t, uint64_t* bar, int col, int row, int b) {

@@ -78,20 +78,23 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(T* __restrict__ out, float*
 // Backward.  dres[row] (+)= LN'(dout[row]); partial dgamma/dbeta per block into scratch.
 // Each warp walks rows grid-stride and keeps dgamma/dbeta partials for its lanes' channels in
 // registers; warps of a block are then combined in fixed order through shared memory.
-template <typename T, int PER_LANE, bool ACCUM>
+// SUMOUT: the column sums of the values written to dres are a third per-block partial (the bias gradient of the
+// linear layer whose output gradient dres is), taken from the values as stored (after rounding to T).
+template <typename T, int PER_LANE, bool ACCUM, bool SUMOUT = false>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float* __restrict__ partial,
                                                     const T* __restrict__ dout, const T* __restrict__ inp,
                                                     const T* __restrict__ w, const float* __restrict__ mean_i,
                                                     const float* __restrict__ rstd_i, int rows, int C) {
   constexpr int N = Pack<T>::N;
-  extern __shared__ float sm[];  // [warps][2][C]
+  constexpr int NS = SUMOUT ? 3 : 2;
+  extern __shared__ float sm[];  // [warps][NS][C]
   const int lane = threadIdx.x % 32, wid = threadIdx.x / 32, nwarps = blockDim.x / 32;
   const int nvec = C / N;
-  float dg[PER_LANE][N], db[PER_LANE][N];
+  float dg[PER_LANE][N], db[PER_LANE][N], ds[SUMOUT ? PER_LANE : 1][N];
 #pragma unroll
   for (int i = 0; i < PER_LANE; ++i) {
 #pragma unroll
-    for (int k = 0; k < N; ++k) { dg[i][k] = 0.f; db[i][k] = 0.f; }
+    for (int k = 0; k < N; ++k) { dg[i][k] = 0.f; db[i][k] = 0.f; if (SUMOUT) ds[i][k] = 0.f; }
   }
   for (int row = blockIdx.x * nwarps + wid; row < rows; row += gridDim.x * nwarps) {
     float mean = mean_i[row], rstd = rstd_i[row];
@@ -136,6 +139,7 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float
           float n_ = (x.v[k] - mean) * rstd;
           float g = (d.v[k] * ww.v[k] - s1 - n_ * s2) * rstd;
           o.v[k] = ACCUM ? o.v[k] + g : g;
+          if (SUMOUT) ds[i][k] += round_to<T>(o.v[k]);
         }
         o.store(dres + (size_t)row * C + vc * N);
       }
@@ -148,38 +152,40 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(T* __restrict__ dres, float
     if (vc < nvec) {
 #pragma unroll
       for (int k = 0; k < N; ++k) {
-        sm[(wid * 2 + 0) * C + vc * N + k] = dg[i][k];
-        sm[(wid * 2 + 1) * C + vc * N + k] = db[i][k];
+        sm[(wid * NS + 0) * C + vc * N + k] = dg[i][k];
+        sm[(wid * NS + 1) * C + vc * N + k] = db[i][k];
+        if (SUMOUT) sm[(wid * NS + 2) * C + vc * N + k] = ds[i][k];
       }
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+  for (int c = threadIdx.x; c < NS * C; c += blockDim.x) {
     int which = c / C, cc = c % C;
     float s = 0.f;
-    for (int wdx = 0; wdx < nwarps; ++wdx) s += sm[(wdx * 2 + which) * C + cc];
-    partial[(size_t)blockIdx.x * 2 * C + c] = s;
+    for (int wdx = 0; wdx < nwarps; ++wdx) s += sm[(wdx * NS + which) * C + cc];
+    partial[(size_t)blockIdx.x * NS * C + c] = s;
   }
 }
 
 // dw[c] += sum_i partial[i][c], db[c] += sum_i partial[i][C + c] over the per-block partial rows.  A block of
 // 32 x 8 threads owns 32 adjacent columns of the 2C-wide partial matrix: 8 row groups walk the rows in parallel
 // (coalesced 128-byte reads) and are combined in fixed order through shared memory.
-__global__ void __launch_bounds__(256) ln_bwd_final_kernel(float* __restrict__ dw, float* __restrict__ db,
+__global__ void __launch_bounds__(256) ln_bwd_final_kernel(float* __restrict__ dw, float* __restrict__ db, float* __restrict__ dsum,
                                                           const float* __restrict__ partial, int C, int nblocks) {
   __shared__ float red[8][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + tx;
+  const int NS = dsum ? 3 : 2;                           // dsum: third partial = column sums of the stored dres
   float s = 0.f;
-  if (c < 2 * C)
-    for (int i = ty; i < nblocks; i += 8) s += partial[(size_t)i * 2 * C + c];
+  if (c < NS * C)
+    for (int i = ty; i < nblocks; i += 8) s += partial[(size_t)i * NS * C + c];
   red[ty][tx] = s;
   __syncthreads();
-  if (ty == 0 && c < 2 * C) {
+  if (ty == 0 && c < NS * C) {
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) t += red[k][tx];
-    if (c < C) dw[c] += t; else db[c - C] += t;
+    if (c < C) dw[c] += t; else if (c < 2 * C) db[c - C] += t; else dsum[c - 2 * C] += t;
   }
 }
 
@@ -209,16 +215,21 @@ int ln_fwd_launch(void* out, float* mean, float* rstd, void* resid_out, const vo
 
 template <typename T, int PER_LANE>
 int ln_bwd_launch_n(void* dres, float* partial, const void* dout, const void* inp, const void* w, const float* mean,
-                    const float* rstd, int rows, int C, int accumulate, int grid, cudaStream_t st) {
-  size_t smem = (size_t)8 * 2 * C * sizeof(float);
+                    const float* rstd, int rows, int C, int accumulate, int grid, cudaStream_t st, bool sumout = false) {
+  size_t smem = (size_t)8 * (sumout ? 3 : 2) * C * sizeof(float);
+  if (smem > 220 * 1024) return LLMB_ERR_BAD_ARG;
   auto kern_a = ln_bwd_kernel<T, PER_LANE, true>;
   auto kern_n = ln_bwd_kernel<T, PER_LANE, false>;
+  auto kern_as = ln_bwd_kernel<T, PER_LANE, true, true>;
+  auto kern_ns = ln_bwd_kernel<T, PER_LANE, false, true>;
   if (smem > 48 * 1024) {
     cudaFuncSetAttribute(kern_a, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(kern_n, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(kern_as, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(kern_ns, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
-  if (accumulate) kern_a<<<grid, 256, smem, st>>>((T*)dres, partial, (const T*)dout, (const T*)inp, (const T*)w, mean, rstd, rows, C);
-  else kern_n<<<grid, 256, smem, st>>>((T*)dres, partial, (const T*)dout, (const T*)inp, (const T*)w, mean, rstd, rows, C);
+  auto kern = sumout ? (accumulate ? kern_as : kern_ns) : (accumulate ? kern_a : kern_n);
+  kern<<<grid, 256, smem, st>>>((T*)dres, partial, (const T*)dout, (const T*)inp, (const T*)w, mean, rstd, rows, C);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -232,20 +243,31 @@ LLMB_API int llmb_layernorm_fwd(void* out, float* mean, float* rstd, void* resid
 
 LLMB_API int llmb_layernorm_bwd_blocks(int rows) { int g = sm_count() * 2; int need = ceil_div(rows, 8); return need < g ? need : g; }
 LLMB_API long long llmb_layernorm_bwd_scratch_bytes(int rows, int C) {
-  return (long long)llmb_layernorm_bwd_blocks(rows) * 2 * C * sizeof(float);
+  return (long long)llmb_layernorm_bwd_blocks(rows) * 3 * C * sizeof(float);      // room for the optional column-sum partial
 }
 
 // dres (+)= LN-backward(dout); dw += ..., db += ...  (dw/db fp32).  accumulate=1 adds into dres.
+LLMB_API int llmb_layernorm_bwd_colsum(void* dres, float* dw, float* db, float* dsum, float* scratch, long long scratch_bytes,
+                                       const void* dout, const void* inp, const void* w, const float* mean,
+                                       const float* rstd, int rows, int C, int accumulate, int dtype, cudaStream_t st);
 LLMB_API int llmb_layernorm_bwd(void* dres, float* dw, float* db, float* scratch, long long scratch_bytes,
                                 const void* dout, const void* inp, const void* w, const float* mean,
                                 const float* rstd, int rows, int C, int accumulate, int dtype, cudaStream_t st) {
+  return llmb_layernorm_bwd_colsum(dres, dw, db, nullptr, scratch, scratch_bytes, dout, inp, w, mean, rstd, rows, C, accumulate, dtype, st);
+}
+// As llmb_layernorm_bwd; with dsum != nullptr additionally dsum[c] += sum over rows of the values written to dres[:, c]
+// (fp32 [C]): the bias gradient of the linear layer whose output gradient dres is, without another pass over dres.
+LLMB_API int llmb_layernorm_bwd_colsum(void* dres, float* dw, float* db, float* dsum, float* scratch, long long scratch_bytes,
+                                       const void* dout, const void* inp, const void* w, const float* mean,
+                                       const float* rstd, int rows, int C, int accumulate, int dtype, cudaStream_t st) {
   int grid = llmb_layernorm_bwd_blocks(rows);
-  if (scratch_bytes < (long long)grid * 2 * C * (long long)sizeof(float)) return LLMB_ERR_BAD_ARG;
+  const bool sumout = dsum != nullptr;
+  if (scratch_bytes < (long long)grid * (sumout ? 3 : 2) * C * (long long)sizeof(float)) return LLMB_ERR_BAD_ARG;
   int rc;
   if (dtype == LLMB_BF16) {
     int per = ceil_div(C / 8, 32);
     if (C % 8) return LLMB_ERR_BAD_ARG;
-#define LN_CASE(P) rc = ln_bwd_launch_n<__nv_bfloat16, P>(dres, scratch, dout, inp, w, mean, rstd, rows, C, accumulate, grid, st)
+#define LN_CASE(P) rc = ln_bwd_launch_n<__nv_bfloat16, P>(dres, scratch, dout, inp, w, mean, rstd, rows, C, accumulate, grid, st, sumout)
     if (per <= 2) LN_CASE(2); else if (per <= 3) LN_CASE(3); else if (per <= 4) LN_CASE(4); else if (per <= 5) LN_CASE(5);
     else if (per <= 7) LN_CASE(7); else if (per <= 8) LN_CASE(8); else if (per <= 12) LN_CASE(12); else if (per <= 16) LN_CASE(16);
     else return LLMB_ERR_BAD_ARG;
@@ -253,13 +275,13 @@ LLMB_API int llmb_layernorm_bwd(void* dres, float* dw, float* db, float* scratch
   } else {
     int per = ceil_div(C / 4, 32);
     if (C % 4) return LLMB_ERR_BAD_ARG;
-#define LN_CASE(P) rc = ln_bwd_launch_n<float, P>(dres, scratch, dout, inp, w, mean, rstd, rows, C, accumulate, grid, st)
+#define LN_CASE(P) rc = ln_bwd_launch_n<float, P>(dres, scratch, dout, inp, w, mean, rstd, rows, C, accumulate, grid, st, sumout)
     if (per <= 2) LN_CASE(2); else if (per <= 4) LN_CASE(4); else if (per <= 6) LN_CASE(6); else if (per <= 8) LN_CASE(8);
     else if (per <= 10) LN_CASE(10); else if (per <= 13) LN_CASE(13); else if (per <= 16) LN_CASE(16);
     else return LLMB_ERR_BAD_ARG;
 #undef LN_CASE
   }
   if (rc) return rc;
-  ln_bwd_final_kernel<<<ceil_div(2 * C, 32), 256, 0, st>>>(dw, db, scratch, C, grid);
+  ln_bwd_final_kernel<<<ceil_div((sumout ? 3 : 2) * C, 32), 256, 0, st>>>(dw, db, dsum, scratch, C, grid);
   return (int)cudaGetLastError();
 }

@@ -445,9 +445,15 @@ class GPT2:
                 ops.lm_head_bwd_tile(dl, g["wte"][c0:c0 + w], tile, a["lnf"], p["wte"][c0:c0 + w], accumulate=k > 0)
         else:                                  # dlogits are already in acts['logits']
             ops.matmul_bwd(dl, g["wte"], None, a["logits"], a["lnf"], p["wte"])
+        # The bias gradients of attproj and fcproj are the column sums of the residual-stream gradient at the point where a
+        # LayerNorm backward has just written it, so that kernel takes them in the same pass.  fcprojb of layer l is
+        # produced one layer earlier (by ln1 of layer l + 1, or by the final LayerNorm): possible only where the
+        # gradient tensors of all layers exist at once (no per-bucket pools, i.e. ZeRO stage < 2).
+        ln_dbias = os.environ.get("LLMM_FUSED_LN_DBIAS", "1") != "0"
+        ln_dbias_prev = ln_dbias and (z is None or z.stage < 2)
         # bucket 2: final layernorm
         ops.layernorm_bwd(dres, g["lnfw"], g["lnfb"], dl, a["residual3"][L - 1], p["lnfw"], a["lnf_mean"], a["lnf_rstd"],
-                          accumulate=False)
+                          accumulate=False, dres_colsum=g["fcprojb"][L - 1] if ln_dbias_prev else None)
         if z is not None:
             z.grads_ready("head", last_micro_step)
         for l in range(L - 1, -1, -1):
@@ -463,15 +469,21 @@ class GPT2:
             # bf16 MLP: the fc bias gradient (column sums of dl4) is taken in the epilogue of the GEMM that writes dl4
             fc_dbias_upstream = self._site_mode("fcproj", l) == "bf16" and self._site_mode("fc", l) == "bf16"
             kw = {"dinp_colsum": g["fcb"][l]} if fc_dbias_upstream else {}
-            self._linear_bwd("fcproj", l, dl4, g["fcprojw"][l], g["fcprojb"][l], dres, gelu_out, p["fcprojw"][l], gelu_pre=a["fch"][l], **kw)
+            self._linear_bwd("fcproj", l, dl4, g["fcprojw"][l], None if ln_dbias_prev else g["fcprojb"][l], dres, gelu_out,
+                             p["fcprojw"][l], gelu_pre=a["fch"][l], **kw)
             self._linear_bwd("fc", l, dl, g["fcw"][l], None if fc_dbias_upstream else g["fcb"][l], dl4, a["ln2"][l], p["fcw"][l])
             ops.layernorm_bwd(dres, g["ln2w"][l], g["ln2b"][l], dl, a["residual2"][l], p["ln2w"][l],
-                              a["ln2_mean"][l], a["ln2_rstd"][l], accumulate=True)
-            self._linear_bwd("attproj", l, dl, g["attprojw"][l], g["attprojb"][l], dres, a["atty"][l], p["attprojw"][l])
-            ops.attention_bwd(dqkv, dl, a["qkv"][l], a["atty"][l], a["lse"][l], NH)
-            self._linear_bwd("qkv", l, dl, g["qkvw"][l], g["qkvb"][l], dqkv, a["ln1"][l], p["qkvw"][l])
+                              a["ln2_mean"][l], a["ln2_rstd"][l], accumulate=True,
+                              dres_colsum=g["attprojb"][l] if ln_dbias else None)
+            self._linear_bwd("attproj", l, dl, g["attprojw"][l], None if ln_dbias else g["attprojb"][l], dres, a["atty"][l],
+                             p["attprojw"][l])
+            # the qkv bias gradient (column sums of dqkv) comes out of the attention-backward epilogues
+            attn_dbias = os.environ.get("LLMM_FUSED_QKV_DBIAS", "1") != "0"
+            ops.attention_bwd(dqkv, dl, a["qkv"][l], a["atty"][l], a["lse"][l], NH, dbias=g["qkvb"][l] if attn_dbias else None)
+            self._linear_bwd("qkv", l, dl, g["qkvw"][l], None if attn_dbias else g["qkvb"][l], dqkv, a["ln1"][l], p["qkvw"][l])
             ops.layernorm_bwd(dres, g["ln1w"][l], g["ln1b"][l], dl, x_in, p["ln1w"][l],
-                              a["ln1_mean"][l], a["ln1_rstd"][l], accumulate=True)
+                              a["ln1_mean"][l], a["ln1_rstd"][l], accumulate=True,
+                              dres_colsum=g["fcprojb"][l - 1] if (ln_dbias_prev and l > 0) else None)
             if z is not None:
                 z.grads_ready(l, last_micro_step)
         if z is not None:

@@ -110,20 +110,22 @@ def residual_layernorm_fwd(residual_out, out, mean, rstd, inp1, inp2, weight, bi
             rstd.view(rows).copy_(r.view(rows))
 
 
-def layernorm_bwd(dresidual, dweight, dbias, dout, inp, weight, mean, rstd, accumulate: bool = True) -> None:
+def layernorm_bwd(dresidual, dweight, dbias, dout, inp, weight, mean, rstd, accumulate: bool = True,
+                  dres_colsum=None) -> None:
     """dresidual (+)= LN'(dout); dweight += Σ dout·norm; dbias += Σ dout (fp32 grads).
 
     With ``accumulate`` the input gradient is added into ``dresidual`` — the fused
-    residual-backward of llmm/layernorm.mojo:2426-2614."""
+    residual-backward of llmm/layernorm.mojo:2426-2614.  ``dres_colsum`` (fp32 [C]) += Σ_rows of the values written
+    to ``dresidual``: the bias gradient of the linear layer whose output gradient that is, taken in the same pass."""
     C = weight.numel()
     rows = inp.numel() // C
     if dout.is_cuda:
         L = lib()
         nb = L.llmb_layernorm_bwd_scratch_bytes(rows, C)
         s = scratch("layernorm_bwd", nb, dout.device)
-        check(L.llmb_layernorm_bwd(ptr(dresidual), ptr(dweight), ptr(dbias), ptr(s), s.numel(), ptr(dout), ptr(inp),
-                                   ptr(weight), ptr(mean), ptr(rstd), rows, C, int(accumulate), dtype_code(dout),
-                                   stream()), "layernorm_bwd")
+        check(L.llmb_layernorm_bwd_colsum(ptr(dresidual), ptr(dweight), ptr(dbias), ptr(dres_colsum), ptr(s), s.numel(),
+                                          ptr(dout), ptr(inp), ptr(weight), ptr(mean), ptr(rstd), rows, C, int(accumulate),
+                                          dtype_code(dout), stream()), "layernorm_bwd")
         _count(2)
     else:
         d = dout.reshape(rows, C).float()
@@ -138,6 +140,8 @@ def layernorm_bwd(dresidual, dweight, dbias, dout, inp, weight, mean, rstd, accu
             dr += g.to(dr.dtype)
         else:
             dr.copy_(g)
+        if dres_colsum is not None:
+            dres_colsum += dr.float().sum(0)
 
 
 # ----------------------------------------------------------------------------- GELU
@@ -379,16 +383,21 @@ def attention_fwd(out, lse, qkv, num_heads: int) -> None:
     lse.copy_(l * math.log2(math.e))
 
 
-def attention_bwd(dqkv, dout, qkv, out, lse, num_heads: int) -> None:
-    """dqkv = ∂/∂qkv of causal attention (llmm/attention.mojo:5033-5276)."""
+def attention_bwd(dqkv, dout, qkv, out, lse, num_heads: int, dbias=None) -> None:
+    """dqkv = ∂/∂qkv of causal attention (llmm/attention.mojo:5033-5276).  ``dbias`` (fp32 [3C]) += Σ_rows dqkv: the
+    gradient of the qkv bias, taken in the kernels' epilogues on the tensor-core path, by a reduction otherwise."""
     B, T, C3 = qkv.shape
     C = C3 // 3
     hs = C // num_heads
     if qkv.is_cuda and ATTN_IMPL == "tcgen05" and hs == 64 and qkv.dtype == torch.bfloat16:
         dvec = scratch("attn_dvec", B * num_heads * (T + 128 * ((T + 63) // 64)) * 4 + 16, qkv.device)
-        check(lib().llmb_attention_bwd(ptr(dqkv), ptr(dvec), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T, num_heads,
-                                       ptr(status_word(qkv.device)), stream()), "attention_bwd")
+        check(lib().llmb_attention_bwd_dbias(ptr(dqkv), ptr(dbias), ptr(dvec), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T,
+                                             num_heads, ptr(status_word(qkv.device)), stream()), "attention_bwd")
         _count(3)
+        return
+    if dbias is not None:
+        attention_bwd(dqkv, dout, qkv, out, lse, num_heads)
+        dbias_reduce(dbias, dqkv.view(B * T, C3))
         return
     if qkv.is_cuda:      # library comparator: recompute through SDPA under autograd
         with torch.enable_grad():

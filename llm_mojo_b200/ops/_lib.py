@@ -30,6 +30,7 @@ _SIGS = {
     "llmb_layernorm_fwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p],
     "llmb_layernorm_bwd_scratch_bytes": [c_int, c_int],
     "llmb_layernorm_bwd": [c_p, c_p, c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
+    "llmb_layernorm_bwd_colsum": [c_p, c_p, c_p, c_p, c_p, c_ll, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
     "llmb_fused_classifier": [c_p, c_p, c_p, c_f, c_int, c_int, c_int, c_int, c_int, c_p, c_p],
     "llmb_ce_pass1": [c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_p],
     "llmb_ce_loss": [c_p, c_p, c_int, c_p],
@@ -66,6 +67,7 @@ _SIGS = {
     "llmb_rng_uniform": [c_p, c_ll, c_ull, c_ull, c_ull, c_p],
     "llmb_attention_fwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
     "llmb_attention_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
+    "llmb_attention_bwd_dbias": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
 }
 _RET_LL = {"llmb_encoder_bwd_scratch_bytes", "llmb_dbias_scratch_bytes", "llmb_layernorm_bwd_scratch_bytes",
            "llmb_nvfp4_scale_bytes"}

@@ -88,6 +88,13 @@ def test_layernorm_fwd_bwd(C, dtype):
         close(dres, r_dres, tol[0] * 4, tol[1], f"dres acc={accumulate}")
         close(dw, r_dw, 1e-3 * math.sqrt(rows), 1e-2, "dgamma")
         close(db, r_db, 1e-3 * math.sqrt(rows), 1e-2, "dbeta")
+        # the same pass can also return the column sums of the gradient it wrote (the bias gradient of the layer above)
+        dres2, dw2, db2 = dres0.to(DEV).clone(), torch.zeros(C, device=DEV), torch.zeros(C, device=DEV)
+        cs = torch.full((C,), 0.5, device=DEV)
+        ops.layernorm_bwd(dres2, dw2, db2, dout.to(DEV), xs.to(dtype).to(DEV), w.to(DEV), mean, rstd, accumulate=accumulate,
+                          dres_colsum=cs)
+        assert torch.equal(dres2, dres) and torch.equal(dw2, dw) and torch.equal(db2, db)
+        close(cs, 0.5 + dres.float().sum(0), 2e-3 * math.sqrt(rows), 1e-3, f"colsum of dres acc={accumulate}")
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
@@ -286,11 +293,14 @@ def test_attention_fwd_bwd(B, T, NH):
     r_dqkv = torch.empty(B, T, 3 * C)
     ops.attention_bwd(r_dqkv, dout.float(), qkv.float(), r_out, r_lse, NH)
     dqkv = torch.full((B, T, 3 * C), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.attention_bwd(dqkv, dout.to(DEV), qkv.to(DEV), out, lse, NH)
+    dbias = torch.full((3 * C,), 0.25, device=DEV)
+    ops.attention_bwd(dqkv, dout.to(DEV), qkv.to(DEV), out, lse, NH, dbias=dbias)
     torch.cuda.synchronize()
     status_ok()
     for i, nm in enumerate(("dq", "dk", "dv")):
         close(dqkv[..., i * C:(i + 1) * C], r_dqkv[..., i * C:(i + 1) * C], 2e-2, 3e-2, nm)
+    # the qkv bias gradient from the kernels' epilogues: column sums of dqkv (added to what the buffer held)
+    close(dbias, 0.25 + r_dqkv.view(B * T, 3 * C).sum(0), 2e-2 * math.sqrt(B * T), 2e-2, "qkv dbias", strict=True)
 
 
 def test_unfused_softmax_bwd_and_crossentropy():
