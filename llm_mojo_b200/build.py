@@ -15,6 +15,7 @@ from typing import List
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libllmb200.so")
+CHECK_LIB_PATH = os.path.join(CSRC, "libllmb200_check.so")     # -DLLMB_BOUNDS_CHECK: data-dependent indices tested before use
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 # Every kernel here is free of cluster-multicast TMA loads, so one library serves 1-GPU and multi-GPU runs.
@@ -31,8 +32,9 @@ def sources() -> List[str]:
     return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def _digest(path: str) -> str:
+def _digest(path: str, extra: str = "") -> str:
     h = hashlib.sha256()
+    h.update(extra.encode())
     for name in sorted(os.listdir(CSRC)):
         if name.endswith((".cuh", ".h")) or name == os.path.basename(path):
             with open(os.path.join(CSRC, name), "rb") as f:
@@ -41,14 +43,17 @@ def _digest(path: str) -> str:
     return h.hexdigest()
 
 
-def build(verbose: bool = True, force: bool = False) -> str:
+def build(verbose: bool = True, force: bool = False, check: bool = False) -> str:
+    """Compile and link the library; ``check=True`` builds the bounds-checked variant beside it."""
     nvcc = _nvcc()
     objs, jobs = [], []
+    flags = NVCC_FLAGS + (["-DLLMB_BOUNDS_CHECK"] if check else [])
+    lib_path = CHECK_LIB_PATH if check else LIB_PATH
     for src in sources():
         sp = os.path.join(CSRC, src)
-        obj = sp[:-3] + ".o"
+        obj = sp[:-3] + (".check.o" if check else ".o")
         stamp = obj + ".sha"
-        dig = _digest(sp)
+        dig = _digest(sp, "check" if check else "")
         objs.append(obj)
         if not force and os.path.exists(obj) and os.path.exists(stamp) and open(stamp).read() == dig:
             continue
@@ -56,7 +61,7 @@ def build(verbose: bool = True, force: bool = False) -> str:
 
     def compile_one(job):
         sp, obj, stamp, dig = job
-        cmd = [nvcc, *NVCC_FLAGS, "-c", sp, "-o", obj]
+        cmd = [nvcc, *flags, "-c", sp, "-o", obj]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -68,15 +73,15 @@ def build(verbose: bool = True, force: bool = False) -> str:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
-    if jobs or not os.path.exists(LIB_PATH):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart"]
+    if jobs or not os.path.exists(lib_path):
+        cmd = [nvcc, "-shared", "-o", lib_path, *objs, "-lcudart"]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, check="--check" in sys.argv))

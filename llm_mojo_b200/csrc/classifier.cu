@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(1024) classifier_kernel(T* __restrict__ logits
   const float L2E = 1.4426950408889634f;
   // second pass: e = 2^((x - max)·log2e) once per element; the row buffer is overwritten with e (in the
   // storage dtype) so that the third pass is a multiply, not another exponential
-  const int tgt = targets[row];
+  const int tgt_raw = targets[row];
+  const int tgt = llmb_in_range(tgt_raw, V, LLMB_SITE_CLASSIFIER_TARGET) ? tgt_raw : 0;   // checked build: a bad target is recorded and clamped
   const float x_tgt = to_f<T>(row_s[tgt]);            // read before the buffer is overwritten
   __syncthreads();
   float sum = 0.f;
@@ -137,7 +138,8 @@ __global__ void __launch_bounds__(1024, 1) classifier_stream_kernel(__nv_bfloat1
     if (wid == 0) { float m = lane < nw ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bcast[0] = m; }
     __syncthreads();
     mx = bcast[0];
-    const int tgt = targets[r];
+    const int tgt_raw = targets[r];
+  const int tgt = llmb_in_range(tgt_raw, V, LLMB_SITE_CLASSIFIER_TARGET) ? tgt_raw : 0;   // checked build: a bad target is recorded and clamped
     const float x_tgt = __bfloat162float(row_s[tgt]);     // read before the buffer is overwritten
     __syncthreads();
     // pass 2: e = 2^((x - max) log2 e), once per element, written back over the row
@@ -267,7 +269,8 @@ __global__ void __launch_bounds__(1024, 1) classifier_stream2_kernel(__nv_bfloat
     if (wid == 0) { float m = lane < NCW ? red[lane] : -INFINITY; m = warp_max(m); if (lane == 0) bcast[0] = m; }
     csync();
     mx = bcast[0];
-    const int tgt = targets[r];
+    const int tgt_raw = targets[r];
+  const int tgt = llmb_in_range(tgt_raw, V, LLMB_SITE_CLASSIFIER_TARGET) ? tgt_raw : 0;   // checked build: a bad target is recorded and clamped
     const float x_tgt = __bfloat162float(row_s[tgt]);     // read before the buffer is overwritten
     csync();
     // pass 2: e = 2^((x - max) log2 e), once per element, written back over the row
@@ -383,6 +386,8 @@ LLMB_API int llmb_crossentropy_bwd(float* dprobs, const float* dlosses, const fl
   crossentropy_bwd_kernel<<<ceil_div(rows, 256), 256, 0, st>>>(dprobs, dlosses, probs, targets, rows, ld);
   return (int)cudaGetLastError();
 }
+
+LLMB_BOUNDS_REPORT_FN(llmb_bounds_report_classifier)
 
 // logits [rows, Vp] are overwritten with dlogits when write_dlogits != 0.
 LLMB_API int llmb_fused_classifier(void* logits, float* losses, const int* targets, float dloss, int rows, int V,

@@ -16,6 +16,32 @@ enum { LLMB_F32 = 0, LLMB_BF16 = 1 };
 // status codes written by kernels with bounded waits
 enum { LLMB_OK = 0, LLMB_ERR_TIMEOUT = 1, LLMB_ERR_BAD_ARG = 2 };
 
+// Checked build (-DLLMB_BOUNDS_CHECK, `python -m llm_mojo_b200.build --check` -> libllmb200_check.so): every index that comes
+// out of DATA (token ids, target ids) is tested against its limit before it addresses memory; a bad index is recorded
+// (first offender per translation unit: site, value, limit) and the access is skipped, so a corrupt batch shows up as a
+// report instead of an illegal address.  In the normal build llmb_in_range() is `true` and compiles away.  The records
+// are read with llmb_bounds_report_<file>(); the sites are listed there.
+enum { LLMB_SITE_ENCODER_FWD_TOKEN = 1, LLMB_SITE_ENCODER_BWD_TOKEN = 2, LLMB_SITE_CLASSIFIER_TARGET = 3, LLMB_SITE_CE_TARGET = 4 };
+#ifdef LLMB_BOUNDS_CHECK
+static __device__ int llmb_bounds_rec[4];      // {seen, site, value, limit}
+__device__ __forceinline__ bool llmb_in_range(long long v, long long limit, int site) {
+  if (v >= 0 && v < limit) return true;
+  if (atomicCAS(&llmb_bounds_rec[0], 0, 1) == 0) { llmb_bounds_rec[1] = site; llmb_bounds_rec[2] = (int)v; llmb_bounds_rec[3] = (int)limit; }
+  return false;
+}
+#define LLMB_BOUNDS_REPORT_FN(name)                                                                      \
+  LLMB_API int name(int* out4, int reset) {                                                              \
+    int z[4] = {0, 0, 0, 0};                                                                             \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, llmb_bounds_rec, sizeof(z));                              \
+    if (e == cudaSuccess && reset) e = cudaMemcpyToSymbol(llmb_bounds_rec, z, sizeof(z));                \
+    return (int)e;                                                                                       \
+  }
+#else
+__device__ __forceinline__ bool llmb_in_range(long long, long long, int) { return true; }
+#define LLMB_BOUNDS_REPORT_FN(name)                                                                      \
+  LLMB_API int name(int* out4, int reset) { (void)reset; out4[0] = out4[1] = out4[2] = out4[3] = 0; return 0; }
+#endif
+
 namespace llmb {
 
 constexpr int WARP = 32;

@@ -14,7 +14,7 @@ using namespace llmb;
 // ---------------------------------------------------------------- encoder forward
 template <typename T>
 __global__ void encoder_fwd_kernel(T* __restrict__ out, const int* __restrict__ tok, const T* __restrict__ wte,
-                                   const T* __restrict__ wpe, int BT, int Tlen, int C) {
+                                   const T* __restrict__ wpe, int BT, int Tlen, int C, int V) {
   constexpr int N = Pack<T>::N;
   const int vec_per_row = C / N;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -23,6 +23,7 @@ __global__ void encoder_fwd_kernel(T* __restrict__ out, const int* __restrict__ 
   int row = (int)(idx / vec_per_row), c = (int)(idx % vec_per_row) * N;
   int t = row % Tlen;
   int id = tok[row];
+  if (!llmb_in_range(id, V, LLMB_SITE_ENCODER_FWD_TOKEN)) return;
   Pack<T> a, b;
   a.load(wte + (size_t)id * C + c);
   b.load(wpe + (size_t)t * C + c);
@@ -31,19 +32,22 @@ __global__ void encoder_fwd_kernel(T* __restrict__ out, const int* __restrict__ 
   a.store(out + (size_t)row * C + c);
 }
 
-LLMB_API int llmb_encoder_fwd(void* out, const int* tok, const void* wte, const void* wpe, int B, int T, int C,
+LLMB_BOUNDS_REPORT_FN(llmb_bounds_report_elementwise)
+
+// V: rows of wte (token ids must be below it; tested in the checked build only)
+LLMB_API int llmb_encoder_fwd(void* out, const int* tok, const void* wte, const void* wpe, int B, int T, int C, int V,
                               int dtype, cudaStream_t st) {
   int BT = B * T;
   if (dtype == LLMB_BF16) {
     if (C % 8) return LLMB_ERR_BAD_ARG;
     long long total = (long long)BT * (C / 8);
     encoder_fwd_kernel<__nv_bfloat16><<<(unsigned)ceil_div_ll(total, 256), 256, 0, st>>>(
-        (__nv_bfloat16*)out, tok, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, BT, T, C);
+        (__nv_bfloat16*)out, tok, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, BT, T, C, V);
   } else {
     if (C % 4) return LLMB_ERR_BAD_ARG;
     long long total = (long long)BT * (C / 4);
     encoder_fwd_kernel<float><<<(unsigned)ceil_div_ll(total, 256), 256, 0, st>>>(
-        (float*)out, tok, (const float*)wte, (const float*)wpe, BT, T, C);
+        (float*)out, tok, (const float*)wte, (const float*)wpe, BT, T, C, V);
   }
   return (int)cudaGetLastError();
 }
@@ -59,11 +63,12 @@ __global__ void make_keys_kernel(unsigned long long* keys, const int* tok, int B
 // shared-memory reduction over lanes keeps the sum order independent of scheduling.
 template <typename T, int LANES>
 __global__ void wte_bwd_kernel(float* __restrict__ dwte, const T* __restrict__ dout,
-                               const unsigned long long* __restrict__ keys, int BT, int C) {
+                               const unsigned long long* __restrict__ keys, int BT, int C, int V) {
   constexpr int N = Pack<T>::N;
   int i = blockIdx.x;
   unsigned tokv = (unsigned)(keys[i] >> 32);
   if (i > 0 && (unsigned)(keys[i - 1] >> 32) == tokv) return;
+  if (!llmb_in_range((long long)tokv, V, LLMB_SITE_ENCODER_BWD_TOKEN)) return;
   extern __shared__ float sm[];  // [LANES][C]
   const int vec_per_row = C / N;
   const int nvec_threads = blockDim.x / LANES;
@@ -119,7 +124,7 @@ LLMB_API long long llmb_encoder_bwd_scratch_bytes(int BT) {
 }
 
 LLMB_API int llmb_encoder_bwd(float* dwte, float* dwpe, const void* dout, const int* tok, void* scratch,
-                              long long scratch_bytes, int B, int T, int C, int vocab_bits, int dtype,
+                              long long scratch_bytes, int B, int T, int C, int V, int vocab_bits, int dtype,
                               cudaStream_t st) {
   int BT = B * T;
   if (scratch_bytes < llmb_encoder_bwd_scratch_bytes(BT)) return LLMB_ERR_BAD_ARG;
@@ -136,10 +141,10 @@ LLMB_API int llmb_encoder_bwd(float* dwte, float* dwpe, const void* dout, const 
   constexpr int LANES = 4;
   size_t smem = (size_t)LANES * C * sizeof(float);
   if (dtype == LLMB_BF16) {
-    wte_bwd_kernel<__nv_bfloat16, LANES><<<BT, 256, smem, st>>>(dwte, (const __nv_bfloat16*)dout, kout, BT, C);
+    wte_bwd_kernel<__nv_bfloat16, LANES><<<BT, 256, smem, st>>>(dwte, (const __nv_bfloat16*)dout, kout, BT, C, V);
     wpe_bwd_kernel<__nv_bfloat16><<<ceil_div(T * (C / 8), 256), 256, 0, st>>>(dwpe, (const __nv_bfloat16*)dout, B, T, C);
   } else {
-    wte_bwd_kernel<float, LANES><<<BT, 256, smem, st>>>(dwte, (const float*)dout, kout, BT, C);
+    wte_bwd_kernel<float, LANES><<<BT, 256, smem, st>>>(dwte, (const float*)dout, kout, BT, C, V);
     wpe_bwd_kernel<float><<<ceil_div(T * (C / 4), 256), 256, 0, st>>>(dwpe, (const float*)dout, B, T, C);
   }
   return (int)cudaGetLastError();

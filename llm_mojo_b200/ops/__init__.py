@@ -34,19 +34,43 @@ _SCRATCH = {}
 LAUNCHES = 0     # number of kernel-library launches issued (bench.py reports it)
 
 
+_CANARIES = {}
+
+
 def _count(n: int = 1) -> None:
     global LAUNCHES
     LAUNCHES += n
 
 
+CANARY_BYTES, CANARY_VALUE = 256, 0xA5
+
+
 def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
-    """Persistent per-(name, device) scratch buffer, grown on demand (cf. llmm/memory.mojo:81-123)."""
+    """Persistent per-(name, device) scratch buffer, grown on demand (cf. llmm/memory.mojo:81-123).  Under
+    ``LLMB_BOUNDS_CHECK=1`` every buffer is followed by a 256-byte canary that ``verify_scratch_canaries`` checks:
+    a kernel that writes past the scratch it was given (the reference's ``_check_scratch``, llmm/zero.mojo:555) is
+    caught at the end of the step instead of corrupting a neighbour."""
     key = (name, str(device))
     t = _SCRATCH.get(key)
     if t is None or t.numel() < nbytes:
-        t = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        size = max(nbytes, 256)
+        if _lib.BOUNDS_CHECK:
+            full = torch.empty(size + CANARY_BYTES, dtype=torch.uint8, device=device)
+            full[size:].fill_(CANARY_VALUE)
+            _CANARIES[key] = full
+            t = full[:size]
+        else:
+            t = torch.empty(size, dtype=torch.uint8, device=device)
         _SCRATCH[key] = t
     return t
+
+
+def verify_scratch_canaries() -> None:
+    """Raises if any scratch buffer's canary was overwritten (checked mode only; no-op otherwise)."""
+    for (name, dev), full in _CANARIES.items():
+        tail = full[full.numel() - CANARY_BYTES:]
+        if not bool((tail == CANARY_VALUE).all()):
+            raise _lib.KernelError(f"scratch buffer {name!r} on {dev}: a kernel wrote past its {full.numel() - CANARY_BYTES} bytes")
 
 
 # ----------------------------------------------------------------------------- encoder
@@ -55,7 +79,7 @@ def encoder_fwd(out: torch.Tensor, tokens: torch.Tensor, wte: torch.Tensor, wpe:
     B, T = tokens.shape
     C = wte.shape[1]
     if out.is_cuda:
-        check(lib().llmb_encoder_fwd(ptr(out), ptr(tokens), ptr(wte), ptr(wpe), B, T, C, dtype_code(out), stream()),
+        check(lib().llmb_encoder_fwd(ptr(out), ptr(tokens), ptr(wte), ptr(wpe), B, T, C, wte.shape[0], dtype_code(out), stream()),
               "encoder_fwd")
         _count()
     else:
@@ -71,7 +95,7 @@ def encoder_bwd(dwte: torch.Tensor, dwpe: torch.Tensor, dout: torch.Tensor, toke
         nb = L.llmb_encoder_bwd_scratch_bytes(B * T)
         s = scratch("encoder_bwd", nb, dout.device)
         vocab_bits = max(1, int(dwte.shape[0] - 1).bit_length())
-        check(L.llmb_encoder_bwd(ptr(dwte), ptr(dwpe), ptr(dout), ptr(tokens), ptr(s), s.numel(), B, T, C,
+        check(L.llmb_encoder_bwd(ptr(dwte), ptr(dwpe), ptr(dout), ptr(tokens), ptr(s), s.numel(), B, T, C, dwte.shape[0],
                                  vocab_bits, dtype_code(dout), stream()), "encoder_bwd")
         _count(4)
     else:

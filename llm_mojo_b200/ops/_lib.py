@@ -13,14 +13,19 @@ from typing import Optional
 import torch
 
 _LIB: Optional[ctypes.CDLL] = None
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc", "libllmb200.so")
+# LLMB_BOUNDS_CHECK=1 loads the checked build (data-dependent indices tested before use; see csrc/common.cuh)
+BOUNDS_CHECK = os.environ.get("LLMB_BOUNDS_CHECK", "") not in ("", "0")
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc",
+                         "libllmb200_check.so" if BOUNDS_CHECK else "libllmb200.so")
 
 c_int, c_ll, c_f, c_p, c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_ulonglong
 
 _SIGS = {
-    "llmb_encoder_fwd": [c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_p],
+    "llmb_encoder_fwd": [c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_p],
     "llmb_encoder_bwd_scratch_bytes": [c_int],
-    "llmb_encoder_bwd": [c_p, c_p, c_p, c_p, c_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_p],
+    "llmb_encoder_bwd": [c_p, c_p, c_p, c_p, c_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_p],
+    "llmb_bounds_report_elementwise": [c_p, c_int],
+    "llmb_bounds_report_classifier": [c_p, c_int],
     "llmb_gelu_fwd": [c_p, c_p, c_ll, c_int, c_p],
     "llmb_gelu_bwd": [c_p, c_p, c_p, c_ll, c_int, c_p],
     "llmb_dbias_scratch_bytes": [c_int, c_int],
@@ -135,6 +140,21 @@ def status_word(device: torch.device) -> torch.Tensor:
         t = torch.zeros(1, dtype=torch.int32, device=device)
         _STATUS[key] = t
     return t
+
+
+SITES = {1: "encoder_fwd token id", 2: "encoder_bwd token id", 3: "fused_classifier target id", 4: "chunked CE target id"}
+
+
+def bounds_report(reset: bool = True):
+    """Checked build: the first out-of-range data-dependent index each kernel file saw since the last reset, as
+    (site name, value, limit) tuples; empty when everything was in range (always empty in the normal build)."""
+    out = []
+    for name in ("llmb_bounds_report_elementwise", "llmb_bounds_report_classifier"):
+        rec = (c_int * 4)()
+        check(getattr(lib(), name)(rec, int(reset)), name)
+        if rec[0]:
+            out.append((SITES.get(rec[1], f"site {rec[1]}"), rec[2], rec[3]))
+    return out
 
 
 def read_status(device: Optional[torch.device] = None) -> int:

@@ -241,6 +241,13 @@ class Trainer:
             return
         from .ops import _lib
         status = _lib.read_status(self.device)
+        if _lib.BOUNDS_CHECK:                      # checked build: data-dependent indices and scratch canaries
+            from . import ops
+            bad = _lib.bounds_report()
+            if bad:
+                self.abort(f"out-of-range index in step {self.step}: {bad}")
+                raise _lib.KernelError(f"rank {self.rank}: out-of-range data-dependent index in step {self.step}: {bad}")
+            ops.verify_scratch_canaries()
         if status == 0:
             return
         _lib.status_word(self.device).zero_()
