@@ -7,6 +7,7 @@
 // exit path (TMEM freed, no trap), keeping the context usable.
 #pragma once
 #include <cuda.h>
+#include <unordered_map>
 #include "common.cuh"
 
 namespace tc05 {
@@ -299,11 +300,36 @@ inline EncodeTiledFn encode_fn() {
   }
   return fn;
 }
+// Encoded tensor maps are cached per host thread: the operands of a training step are persistent buffers, so after the
+// first step every launch finds its maps (a 128-byte copy) instead of calling the driver's encoder two to four times.
+struct TmapKey {
+  uint64_t v[12];
+  bool operator==(const TmapKey& o) const { for (int i = 0; i < 12; ++i) if (v[i] != o.v[i]) return false; return true; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    uint64_t h = 0x9e3779b97f4a7c15ull;
+    for (int i = 0; i < 12; ++i) { h ^= k.v[i] + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); }
+    return (size_t)h;
+  }
+};
+inline bool tmap_cache_lookup(const TmapKey& k, CUtensorMap* out, bool store) {
+  static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  if (store) { if (cache.size() > 8192) cache.clear(); cache.emplace(k, *out); return true; }
+  auto it = cache.find(k);
+  if (it == cache.end()) return false;
+  *out = it->second;
+  return true;
+}
+
 // 2-D row-major tensor [rows, cols] with row pitch ld (elements); box = [box_rows, box_cols];
 // 128-byte swizzle (box_cols * elem_bytes must be 128).
 inline int make_tmap_2d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t rows,
                         uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols,
                         CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  const TmapKey key{{2, (uint64_t)reinterpret_cast<uintptr_t>(ptr), (uint64_t)dt, (uint64_t)elem_bytes, rows, cols, ld, box_rows, box_cols,
+                     (uint64_t)swizzle, 0, 0}};
+  if (tmap_cache_lookup(key, m, false)) return 0;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {cols, rows};
@@ -312,12 +338,16 @@ inline int make_tmap_2d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt,
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) tmap_cache_lookup(key, m, true);
   return (int)r;
 }
 // 3-D tensor [d2, d1, d0(inner)] with pitches in elements; box = [1, box1, box0]
 inline int make_tmap_3d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int elem_bytes, uint64_t d0,
                         uint64_t d1, uint64_t d2, uint64_t pitch1, uint64_t pitch2, uint32_t box0, uint32_t box1,
                         uint32_t box2 = 1, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  const TmapKey key{{3, (uint64_t)reinterpret_cast<uintptr_t>(ptr), (uint64_t)dt | ((uint64_t)elem_bytes << 32), d0, d1, d2, pitch1, pitch2,
+                     box0, box1, box2, (uint64_t)swizzle}};
+  if (tmap_cache_lookup(key, m, false)) return 0;
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[3] = {d0, d1, d2};
@@ -326,6 +356,7 @@ inline int make_tmap_3d(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt,
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) tmap_cache_lookup(key, m, true);
   return (int)r;
 }
 

@@ -37,21 +37,48 @@ def classify(kernel_name: str) -> str:
 
 
 def summarize_launch_csv(path: str) -> dict:
-    """Bucket an `ncu --metrics gpu__time_duration.sum --csv` launch list into kernel families (µs)."""
+    """Bucket an ``ncu --csv`` launch list into kernel families.
+
+    With ``--metrics gpu__time_duration.sum`` alone (one pass per launch) the result is {family: microseconds}.  When the
+    capture also holds ``dram__bytes_read.sum``, ``dram__bytes_write.sum`` and / or
+    ``sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed`` (more passes: capture a small case), every
+    family additionally gets its DRAM megabytes and its time-weighted tensor-pipe activity under ``detail``."""
     import csv
-    out = {}
     with open(path) as f:
         rows = [r for r in csv.reader(f) if r and not r[0].startswith("==")]
     hdr = rows[0]
-    ni, vi = hdr.index("Kernel Name"), hdr.index("Metric Value")
-    ui = hdr.index("Metric Unit")
-    for r in rows[1:]:
+    ni, vi, ui = hdr.index("Kernel Name"), hdr.index("Metric Value"), hdr.index("Metric Unit")
+    mi = hdr.index("Metric Name") if "Metric Name" in hdr else None
+    idi = hdr.index("ID") if "ID" in hdr else None
+    launches = {}                                    # launch id -> {"name", metric: value}
+    for n, r in enumerate(rows[1:]):
         if len(r) <= vi:
             continue
-        v = float(r[vi].replace(",", ""))
-        v = v / 1e3 if r[ui] in ("ns", "nsecond") else v
-        fam = classify(r[ni])
-        out[fam] = out.get(fam, 0.0) + v
+        key = r[idi] if idi is not None else str(n)
+        metric = r[mi] if mi is not None else "gpu__time_duration.sum"
+        try:
+            v = float(r[vi].replace(",", ""))
+        except ValueError:
+            continue
+        unit = r[ui]
+        if metric.startswith("gpu__time_duration"):
+            v = v / 1e3 if unit in ("ns", "nsecond") else v * 1e3 if unit in ("ms", "msecond") else v      # microseconds
+        elif metric.startswith("dram__bytes"):
+            v = v * {"byte": 1e-6, "Kbyte": 1e-3, "Mbyte": 1.0, "Gbyte": 1e3}.get(unit, 1e-6)              # megabytes
+        launches.setdefault(key, {"name": r[ni]})[metric] = v
+    out, detail = {}, {}
+    for rec in launches.values():
+        fam = classify(rec["name"])
+        us = rec.get("gpu__time_duration.sum", 0.0)
+        out[fam] = out.get(fam, 0.0) + us
+        d = detail.setdefault(fam, {"dram_mb": 0.0, "tensor_x_us": 0.0, "launches": 0})
+        d["launches"] += 1
+        d["dram_mb"] += rec.get("dram__bytes_read.sum", 0.0) + rec.get("dram__bytes_write.sum", 0.0)
+        d["tensor_x_us"] += rec.get("sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed", 0.0) * us
+    if any(d["dram_mb"] or d["tensor_x_us"] for d in detail.values()):
+        out["detail"] = {fam: {"launches": d["launches"], "dram_mb": d["dram_mb"],
+                               "tensor_pipe_pct": d["tensor_x_us"] / out[fam] if out.get(fam) else 0.0}
+                         for fam, d in detail.items()}
     return out
 
 
@@ -106,7 +133,13 @@ def run_profile() -> dict:
 
 if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[1] == "--families":
-        for fam, us in sorted(summarize_launch_csv(sys.argv[2]).items(), key=lambda kv: -kv[1]):
-            print(f"{fam:12s} {us / 1e3:10.3f} ms")
+        res = summarize_launch_csv(sys.argv[2])
+        detail = res.pop("detail", {})
+        for fam, us in sorted(res.items(), key=lambda kv: -kv[1]):
+            extra = ""
+            if fam in detail:
+                d = detail[fam]
+                extra = f"   {d['launches']:4d} launches   DRAM {d['dram_mb']:10.1f} MB   tensor pipe {d['tensor_pipe_pct']:5.1f} %"
+            print(f"{fam:12s} {us / 1e3:10.3f} ms{extra}")
     else:
         run_profile()

@@ -5,6 +5,7 @@
     python profile_kernels.py gemm        # fc GEMM with the fused bias+GELU epilogue, its dinp (dGELU) and dW GEMMs
     python profile_kernels.py lmhead      # LM-head GEMM on 8192 rows + fused softmax/cross-entropy
     python profile_kernels.py layernorm   # LayerNorm forward + backward on 65536 x 768
+    python profile_kernels.py fusedpull   # a layer GEMM that pulls its own weight (four emulated owners) with its copier warps
     python profile_kernels.py fusedgather # the all-gather-fused GEMM with four "ranks" emulated on ONE GPU: the peers'
                                           # chunks are other local buffers and their flags are preset, so the single
                                           # kernel (copier warps + tile loop) runs exactly as on a rank of a 4-GPU job
@@ -106,6 +107,43 @@ def case_fusedgather(reps):
     print("max abs diff vs fp32 reference", (out.float() - want).abs().max().item())
 
 
+def case_fusedpull(reps):
+    """The ZeRO-3 weight pull inside a layer GEMM, with four "owners" emulated on ONE GPU: the segments of the weight
+    live in four other local buffers, the copier warps of the kernel copy them into the window the GEMM reads as its B
+    operand while the tile loop waits for them only at its start - exactly what a rank of a 4-GPU job runs, minus NVLink."""
+    import ctypes
+    from llm_mojo_b200.ops import _lib
+    rows, C, OC = 32768, 768, 3072
+    L = _lib.lib()
+    P, I, U, LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_longlong
+    L.llmb_gemm_set_pull.argtypes = [ctypes.POINTER(P), ctypes.POINTER(P), ctypes.POINTER(LL), ctypes.POINTER(I), I, P, U, P,
+                                     ctypes.POINTER(P), ctypes.POINTER(LL), I, I]
+    L.llmb_gemm_set_pull.restype = I
+    x = torch.randn(rows, C, device="cuda").bfloat16()
+    w_true = (torch.randn(OC, C, device="cuda") * 0.02).bfloat16()
+    nseg = 4
+    pieces = [w_true.view(-1)[i * (OC * C // nseg):(i + 1) * (OC * C // nseg)].clone() for i in range(nseg)]    # the "owners' shards"
+    window = torch.zeros(OC, C, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(rows, OC, device="cuda", dtype=torch.bfloat16)
+    bias = torch.zeros(OC, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(256, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(16, dtype=torch.int32, device="cuda")
+    seg_bytes = OC * C // nseg * 2
+    for rep in range(reps):
+        window.zero_()
+        counts.zero_()
+        src = (P * 8)(*[t.data_ptr() for t in pieces])
+        dst = (P * 8)(*[window.data_ptr() + i * seg_bytes for i in range(nseg)])
+        nb = (LL * 8)(*([seg_bytes] * nseg))
+        own = (I * 8)(*range(nseg))
+        wc = (P * 8)(*[counts.data_ptr() + 4 * i for i in range(nseg)])
+        assert L.llmb_gemm_set_pull(src, dst, nb, own, nseg, flags.data_ptr(), 0, counts.data_ptr(), wc, nb, nseg, nseg) == 0
+        ops.gemm(out, x, window, epi=ops.EPI_BIAS, bias=bias)
+    torch.cuda.synchronize()
+    want = x.float() @ w_true.float().t()
+    print("max abs diff vs fp32 reference", (out.float() - want).abs().max().item(), "| window == weight:", bool(torch.equal(window, w_true)))
+
+
 def case_nvfp4(reps):
     """NVFP4 linear layer pieces: stochastic-rounding quantise (both orientations), native block-scaled GEMM."""
     from llm_mojo_b200.ops import lowp
@@ -121,7 +159,7 @@ def case_nvfp4(reps):
         lowp.matmul_bwd_fp4(dinp, dw, None, d, x, w, seed=1, step=i)
 
 
-CASES = {"nvfp4": case_nvfp4, "fusedgather": case_fusedgather, "attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
+CASES = {"nvfp4": case_nvfp4, "fusedgather": case_fusedgather, "fusedpull": case_fusedpull, "attn": case_attn, "gemm": case_gemm, "lmhead": case_lmhead, "layernorm": case_layernorm}
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)

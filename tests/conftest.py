@@ -13,6 +13,11 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
+    if not os.environ.get("LLMB_RUN_SLOW"):
+        slow = pytest.mark.skip(reason="slow: set LLMB_RUN_SLOW=1 (minutes on host cores)")
+        for item in items:
+            if "slow" in item.keywords:
+                item.add_marker(slow)
     if torch.cuda.is_available():
         return
     skip = pytest.mark.skip(reason="no CUDA device")

@@ -127,6 +127,29 @@ def test_fused_classifier(dtype):
     assert torch.all(g_logits[:, V:] == 0), "padded vocabulary tail must be zeroed"
 
 
+def test_fused_classifier_every_cta_refills_its_row_buffers():
+    """700 rows of the full GPT-2 vocabulary on at most 148 persistent CTAs: every CTA streams four or five rows, so
+    both row buffers of the streaming kernel are refilled and their barrier phases wrap.  Oracle: the fp32 statement
+    of the op on the GPU (log-softmax minus one-hot, scaled), strict tolerance."""
+    rows, V, Vp = 700, 50257, 50304
+    logits = rnd(rows, Vp, scale=3.0).to(DEV)
+    tgt = torch.randint(0, V, (rows,), dtype=torch.int32, generator=torch.Generator().manual_seed(3)).to(DEV)
+    dloss = 1.0 / rows
+    x = logits[:, :V].float()
+    lse = torch.logsumexp(x, dim=1)
+    r_losses = lse - x.gather(1, tgt.long().view(-1, 1)).squeeze(1)
+    r_d = torch.softmax(x, dim=1)
+    r_d[torch.arange(rows, device=DEV), tgt.long()] -= 1.0
+    r_d *= dloss
+    losses = torch.empty(rows, device=DEV)
+    ops.fused_classifier(logits, losses, tgt, dloss, V)
+    torch.cuda.synchronize()
+    status_ok()
+    close(losses, r_losses, 2e-3, 1e-3, "losses (700 rows)", strict=True)
+    close(logits[:, :V], r_d, 1e-2 * dloss, 2e-2, "dlogits (700 rows)", strict=True)
+    assert torch.all(logits[:, V:] == 0), "padded vocabulary tail must be zeroed"
+
+
 def test_dbias_regression():
     """dbias at 124M / 774M widths with a row count that is not a multiple of the slab size
     (the reference's dbias scratch-overrun regression, tests/test_dbias_regression.mojo)."""

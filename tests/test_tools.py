@@ -150,3 +150,28 @@ def test_gate_lock_serialises_and_reports_holders(tmp_path, monkeypatch):
                             capture_output=True, text=True, timeout=60)
     assert "second ran" in second.stdout and time.time() - t0 > 1.0       # it had to wait for the holder
     holder.wait(timeout=30)
+
+
+def test_launch_list_summary_buckets_time_dram_and_tensor_pipe(tmp_path):
+    """profile_gpt2 --families reads a profiler launch list (csv): per kernel family the time and, when the capture has
+    them, the DRAM bytes and the time-weighted tensor-pipe activity."""
+    import csv
+    import profile_gpt2 as pg
+    hdr = ["ID", "Process ID", "Process Name", "Host Name", "Kernel Name", "Context", "Stream", "Block Size", "Grid Size",
+           "Device", "CC", "Section Name", "Metric Name", "Metric Unit", "Metric Value"]
+    rows = [hdr]
+
+    def add(i, name, metric, unit, value):
+        rows.append([str(i), "1", "py", "h", name, "1", "7", "(1,1,1)", "(1,1,1)", "0", "10.0", "x", metric, unit, value])
+    tp = "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_elapsed"
+    add(0, "gemm_pair_kernel<0,1>", "gpu__time_duration.sum", "us", "100"); add(0, "gemm_pair_kernel<0,1>", "dram__bytes_read.sum", "Mbyte", "50")
+    add(0, "gemm_pair_kernel<0,1>", tp, "%", "80")
+    add(1, "gemm_pair_kernel<0,4>", "gpu__time_duration.sum", "us", "300"); add(1, "gemm_pair_kernel<0,4>", tp, "%", "40")
+    add(2, "attn_fwd3_kernel", "gpu__time_duration.sum", "ns", "200000"); add(2, "attn_fwd3_kernel", "dram__bytes_write.sum", "Kbyte", "1000")
+    path = tmp_path / "launches.csv"
+    with open(path, "w", newline="") as f:
+        csv.writer(f).writerows(rows)
+    res = pg.summarize_launch_csv(str(path))
+    assert res["matmul"] == 400.0 and res["attention"] == 200.0
+    assert res["detail"]["matmul"] == {"launches": 2, "dram_mb": 50.0, "tensor_pipe_pct": 50.0}
+    assert abs(res["detail"]["attention"]["dram_mb"] - 1.0) < 1e-9
