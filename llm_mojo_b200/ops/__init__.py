@@ -29,6 +29,7 @@ GELU_K = math.sqrt(2.0 / math.pi)
 # Library GEMM/attention can be forced for A/B comparisons (never the default on CUDA).
 GEMM_IMPL = os.environ.get("LLMB_GEMM", "tcgen05")        # tcgen05 | cublas
 ATTN_IMPL = os.environ.get("LLMB_ATTN", "tcgen05")        # tcgen05 | sdpa
+ATTN_BWD = os.environ.get("LLMB_ATTN_BWD", "split")       # fused (one kernel, dQ partials reduced in fp32) | split (dK/dV and dQ kernels)
 
 _SCRATCH = {}
 LAUNCHES = 0     # number of kernel-library launches issued (bench.py reports it)
@@ -45,8 +46,9 @@ def _count(n: int = 1) -> None:
 CANARY_BYTES, CANARY_VALUE = 256, 0xA5
 
 
-def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
-    """Persistent per-(name, device) scratch buffer, grown on demand (cf. llmm/memory.mojo:81-123).  Under
+def scratch(name: str, nbytes: int, device: torch.device, zero: bool = False) -> torch.Tensor:
+    """Persistent per-(name, device) scratch buffer, grown on demand (cf. llmm/memory.mojo:81-123).  ``zero``: the buffer
+    is zero-filled when it is (re)allocated - for kernels that leave their accumulation scratch zeroed behind them.  Under
     ``LLMB_BOUNDS_CHECK=1`` every buffer is followed by a 256-byte canary that ``verify_scratch_canaries`` checks:
     a kernel that writes past the scratch it was given (the reference's ``_check_scratch``, llmm/zero.mojo:555) is
     caught at the end of the step instead of corrupting a neighbour."""
@@ -61,6 +63,8 @@ def scratch(name: str, nbytes: int, device: torch.device) -> torch.Tensor:
             t = full[:size]
         else:
             t = torch.empty(size, dtype=torch.uint8, device=device)
+        if zero:
+            t.zero_()
         _SCRATCH[key] = t
     return t
 
@@ -413,6 +417,14 @@ def attention_bwd(dqkv, dout, qkv, out, lse, num_heads: int, dbias=None) -> None
     B, T, C3 = qkv.shape
     C = C3 // 3
     hs = C // num_heads
+    if qkv.is_cuda and ATTN_IMPL == "tcgen05" and hs == 64 and qkv.dtype == torch.bfloat16 and ATTN_BWD == "fused":
+        L = lib()
+        stats = scratch("attn_bwd_stats", L.llmb_attention_bwd_fused_stats_floats(B, T, num_heads) * 4, qkv.device)
+        acc = scratch("attn_bwd_dq_acc", L.llmb_attention_bwd_fused_acc_floats(B, T, num_heads) * 4, qkv.device, zero=True)
+        check(L.llmb_attention_bwd_fused(ptr(dqkv), ptr(dbias), ptr(stats), ptr(acc), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T,
+                                         num_heads, ptr(status_word(qkv.device)), stream()), "attention_bwd_fused")
+        _count(3)
+        return
     if qkv.is_cuda and ATTN_IMPL == "tcgen05" and hs == 64 and qkv.dtype == torch.bfloat16:
         dvec = scratch("attn_dvec", B * num_heads * (T + 128 * ((T + 63) // 64)) * 4 + 16, qkv.device)
         check(lib().llmb_attention_bwd_dbias(ptr(dqkv), ptr(dbias), ptr(dvec), ptr(dout), ptr(qkv), ptr(out), ptr(lse), B, T,

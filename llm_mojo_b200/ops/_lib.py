@@ -73,9 +73,12 @@ _SIGS = {
     "llmb_attention_fwd": [c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
     "llmb_attention_bwd": [c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
     "llmb_attention_bwd_dbias": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
+    "llmb_attention_bwd_fused": [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p],
+    "llmb_attention_bwd_fused_stats_floats": [c_int, c_int, c_int],
+    "llmb_attention_bwd_fused_acc_floats": [c_int, c_int, c_int],
 }
 _RET_LL = {"llmb_encoder_bwd_scratch_bytes", "llmb_dbias_scratch_bytes", "llmb_layernorm_bwd_scratch_bytes",
-           "llmb_nvfp4_scale_bytes"}
+           "llmb_nvfp4_scale_bytes", "llmb_attention_bwd_fused_stats_floats", "llmb_attention_bwd_fused_acc_floats"}
 
 
 def lib_path() -> str:

@@ -299,8 +299,10 @@ def test_gemm_tf32_fp32_storage(gemm_mode):
 
 
 # ------------------------------------------------------------------------------ attention
+@pytest.mark.parametrize("bwd", ["fused", "split"])
 @pytest.mark.parametrize("B,T,NH", [(2, 128, 2), (1, 256, 3), (2, 1024, 2), (2, 64, 2), (1, 200, 1), (3, 640, 5), (2, 384, 2)])
-def test_attention_fwd_bwd(B, T, NH):
+def test_attention_fwd_bwd(B, T, NH, bwd, monkeypatch):
+    monkeypatch.setattr(ops, "ATTN_BWD", bwd)
     C = NH * 64
     qkv = rnd(B, T, 3 * C, scale=1.0)
     dout = rnd(B, T, C, seed=1)
@@ -324,6 +326,16 @@ def test_attention_fwd_bwd(B, T, NH):
         close(dqkv[..., i * C:(i + 1) * C], r_dqkv[..., i * C:(i + 1) * C], 2e-2, 3e-2, nm)
     # the qkv bias gradient from the kernels' epilogues: column sums of dqkv (added to what the buffer held)
     close(dbias, 0.25 + r_dqkv.view(B * T, 3 * C).sum(0), 2e-2 * math.sqrt(B * T), 2e-2, "qkv dbias", strict=True)
+    if bwd == "fused":
+        # the fp32 dQ accumulation scratch is left zeroed, so a second call gives the same result
+        acc = ops.scratch("attn_bwd_dq_acc", 4, torch.device(DEV)).view(torch.float32)
+        assert int(torch.count_nonzero(acc)) == 0
+        again = torch.full_like(dqkv, float("nan"))
+        ops.attention_bwd(again, dout.to(DEV), qkv.to(DEV), out, lse, NH)
+        torch.cuda.synchronize()
+        status_ok()
+        close(again[..., :C], dqkv[..., :C], 1e-6, 2e-2, "dq, second call")     # atomic order differs: last-bit differences only
+        assert torch.equal(again[..., C:], dqkv[..., C:])
 
 
 def test_unfused_softmax_bwd_and_crossentropy():
@@ -343,11 +355,13 @@ def test_unfused_softmax_bwd_and_crossentropy():
     close(ops.softmax_bwd(dprobs, probs, V), ops.softmax_bwd(dprobs_c, probs_c, V), 1e-5, 1e-4, "softmax bwd", strict=True)
 
 
-def test_attention_persistent_loops_large():
+@pytest.mark.parametrize("bwd", ["fused", "split"])
+def test_attention_persistent_loops_large(bwd, monkeypatch):
     """B=16, NH=12, T=1024: 768 work items on at most 148 CTAs, so every persistent CTA walks several items per
     tile stream (barrier phase wrap, TMEM hand-back between items, the heavy/light tile alternation).  Oracle: the
     fp32 statement of the op with autograd, on the GPU because of its [B,NH,T,T] intermediates.  Strict: no element
     may miss the tolerance."""
+    monkeypatch.setattr(ops, "ATTN_BWD", bwd)
     B, T, NH = 16, 1024, 12
     C = NH * 64
     qkv = rnd(B, T, 3 * C, scale=1.0).to(DEV)
