@@ -3,46 +3,41 @@
 // Reference behaviour: llmm/attention.mojo:4692-5030 / :5033-5276 (backward via dP, the row dot D = sum(dO * O), dS,
 // and the dQ / dK / dV products over stored [T,T] probabilities).  Here nothing of size T x T reaches HBM and the
 // scores are recomputed ONCE: a CTA owns a 128-key tile (K and V resident in shared memory, dK and dV accumulating
-// in TMEM) and walks the 128-row query blocks that can see it, each as two chunks of 64 queries.  Per chunk c, with
-// lanes = keys, columns = queries:
-//   S^T  = K Q_c^T          (tensor core, fp32 in TMEM)
-//   dP^T = V dO_c^T         (tensor core, fp32 in TMEM)
-//   P^T  = 2^(S^T * a - lse[q])          compute warps; written back over S^T as packed bf16
-//   dV  += P^T dO_c         (A operand read from TMEM, dO_c as an MN-major shared-memory operand)
-//   dS^T = P^T * (dP^T - D[q])           compute warps; bf16 into a swizzled shared-memory tile [keys, 64 queries]
-//   dK  += dS^T Q_c         (A K-major from that tile)
-// and per block, once both chunks' dS^T tiles are written,
-//   dQ partial = dS K       (A MN-major from the two tiles side by side, B = the resident K tile as an MN-major operand)
-// The two compute warpgroups take alternate chunks and run half a period apart: while one is in its exponentials
-// the other does the multiplies and stores of dS, and every product is issued at least one chunk before its
-// result is needed, so no warp waits for the latency of a tcgen05.commit round trip in steady state.
+// in TMEM) and walks the 128-row query blocks i that can see it.  Per block, with lanes = keys, columns = queries:
+//   S^T  = K Q_i^T          (tensor core, fp32 in TMEM)
+//   dP^T = V dO_i^T         (tensor core, fp32 in TMEM)
+//   P^T  = 2^(S^T * a - lse[q])          compute warps; packed bf16 into its own TMEM columns
+//   dV  += P^T dO_i         (A operand read from TMEM, dO_i as an MN-major shared-memory operand)
+//   dS^T = P^T * (dP^T - D[q])           compute warps; bf16 into a swizzled shared-memory tile [keys, queries]
+//   dK  += dS^T Q_i         (A K-major from that tile)
+//   dQ_i partial = dS K     (A MN-major from the SAME tile, B = the resident K tile as an MN-major operand)
+// Because P^T does not live in the columns of S^T, the issuer can start S^T(n+1) as soon as the compute warps hold
+// S^T(n) in registers (and dP^T(n+1) when they hold dP^T(n)): the scores of a block are in TMEM a whole block
+// before they are used, and no compute warp waits for a tcgen05.commit round trip in steady state.
 // The dQ partials of the key tiles are summed in an fp32 buffer by vector reductions (`red.global.add.v4.f32`, 16
 // per thread and block, laid out so that a warp's 32 lanes hit 512 consecutive bytes); a small second kernel scales
 // and rounds that buffer into the dQ part of dqkv and leaves it zeroed for the next call.  dK and dV are produced
-// by exactly one CTA each in a fixed order.
+// by exactly one CTA each in a fixed order and leave through a staging tile as TMA stores.
 //
 // Roles of the 512 threads:
-//   warps 0..3 / 4..7   compute warpgroup 0 / 1: one thread per key row, the 64 query columns of chunks 2n / 2n+1
+//   warps 0..3 / 4..7   compute warpgroups: one thread per key row, query columns 0..63 / 64..127 of the block
 //   warps 8..11         dQ warpgroup: TMEM -> reductions per block, and the dK / dV epilogue per tile
-//   warp 12             TMA producer: K, V per tile (two buffers), Q_c, dO_c and the row statistics per chunk (ring)
-//   warp 13             MMA issuer
-// TMEM columns (512): S^T / P^T of warpgroup 0, 1: 0..63, 64..127 | dP^T: 128..191, 192..255 | dV 256..319 |
-// dK 320..383 | dQ 384..447, 448..511.  S^T(c+2) is issued behind dV(c) on the (in-order) tensor pipe, so it
-// overwrites P^T(c) only after that product has read it.
+//   warp 12             TMA producer: K, V per tile (two buffers), Q_i, dO_i and the row statistics per block (ring),
+//                       and L2 prefetches of the CTA's next tile
+//   warp 13             MMA issuer (one warp: several issuing warps measured slower)
+// TMEM columns (512): S^T 0..127 | dP^T 128..255 | dV 256..319 | dK 320..383 | dQ 384..447 | P^T 448..511.
+// Every wait is bounded; a wait that runs out sets the status word and the role leaves its loop.
 #include <type_traits>
 #include "attention_common.cuh"
 
 namespace {
-constexpr int B3_NS = 5;                                   // ring depth in chunks: Q_c and dO_c, 8 KB each
-constexpr int B3_DSB = 2;                                  // dS^T buffers (each two chunk tiles of 16 KB)
+constexpr int B3_NS = 3;                                   // ring depth in blocks: Q_i and dO_i, 16 KB each
 constexpr int B3_THREADS = 512;
-constexpr int B3_SMEM = 4 * T128 /*K,V x2*/ + B3_NS * 2 * T64 + B3_DSB * 2 * T128 /*dS^T: buffers x 2 chunks*/ + B3_NS * 512 /*-lse, -D*/ +
+constexpr int B3_SMEM = 4 * T128 /*K,V x2*/ + B3_NS * 2 * T128 + 2 * T128 /*dS^T*/ + T128 /*epilogue staging*/ + B3_NS * 1024 /*-lse, -D*/ +
                         1024 /*alignment*/ + 512 /*barriers*/;
 constexpr uint32_t IDESC_TS_MN = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, 64);     // A K-major (TMEM or smem), B stored [K rows, 64]
 constexpr uint32_t IDESC_MN_MN = make_idesc(FMT_BF16, FMT_BF16, 1, 1, 128, 64);     // A stored [K rows, 128], B stored [K rows, 64]
 
-__device__ long long g_b3_trace[8 * 128 * 4];
-#define B3_TR(role, step, k) do { if ((p.dbg & 16384) && blockIdx.x == 0 && (step) < 128 && lane == 0) g_b3_trace[((role) * 128 + (step)) * 4 + (k)] = clock64(); } while (0)
 #define B3_FAIL() do { atomicExch(p.status, LLMB_ERR_TIMEOUT); failed = true; } while (0)
 
 struct B3Params {
@@ -53,7 +48,6 @@ struct B3Params {
   int B, T, NH, C;
   float scale_log2, scale;
   int* status;
-  int dbg;
 };
 
 // D = rowsum(dO * O) and the packed row statistics of every 128-row tile.  Eight threads per row, 16 bytes of dO and O each,
@@ -127,60 +121,56 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// chunk cursor: block cursor plus which half of the block
-struct Chk3 { Blk3 b; int g; };
-__device__ __forceinline__ void chk3_next(Chk3& c, int n_t, int n_items) {
-  c.g ^= 1;
-  if (c.g == 0) blk3_next(c.b, n_t, n_items);
-}
-
 __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_constant__ CUtensorMap tmQKV,
-                                                                  const __grid_constant__ CUtensorMap tmDO, const B3Params p) {
+                                                                  const __grid_constant__ CUtensorMap tmDO,
+                                                                  const __grid_constant__ CUtensorMap tmOUT, const B3Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sKV = sm;                                  // buffer kb: K at kb*2*T128, V at +T128
-  unsigned char* sST = sKV + 4 * T128;                      // ring: stage s holds Q_c at s*2*T64, dO_c at +T64
-  unsigned char* sDS = sST + B3_NS * 2 * T64;               // dS^T: buffer b at b*2*T128: chunk 0 at +0, chunk 1 at +T128 ([128 keys][64] each)
-  float* sStat = reinterpret_cast<float*>(sDS + B3_DSB * 2 * T128);  // per stage: -lse[64], -D[64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + B3_NS * 128);
+  unsigned char* sST = sKV + 4 * T128;                      // ring: stage s holds Q_i at s*2*T128, dO_i at +T128
+  unsigned char* sDS = sST + B3_NS * 2 * T128;              // dS^T: queries 0..63 at +0, 64..127 at +T128 ([128 keys][64] each)
+  unsigned char* sEP = sDS + 2 * T128;                      // staging tile of the dK / dV epilogue ([128 keys][64] bf16, swizzled)
+  float* sStat = reinterpret_cast<float*>(sEP + T128);      // per stage: -lse[128], -D[128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + B3_NS * 256);
   uint64_t* kv_full = bars;                                 // [2]
-  uint64_t* kv_empty = kv_full + 2;                         // [2] the tile's last product is complete
+  uint64_t* kv_empty = kv_full + 2;                         // [2] the tile's last reads of K and V are complete 
   uint64_t* st_full = kv_empty + 2;                         // [NS]
-  uint64_t* st_empty = st_full + B3_NS;                     // [NS] the chunk's dV and dK products are complete
-  uint64_t* s_full = st_empty + B3_NS;                      // [2] per warpgroup: S^T is in TMEM
-  uint64_t* dp_full = s_full + 2;                           // [2] dP^T is in TMEM
-  uint64_t* p_full = dp_full + 2;                           // [2] P^T is in TMEM (4 warps)
-  uint64_t* p_used = p_full + 2;                            // [2] dV has read P^T
-  uint64_t* dp_free = p_used + 2;                           // [2] the warpgroup holds dP^T in registers (4 warps)
-  uint64_t* ds_full = dp_free + 2;                          // [2] the chunk's dS^T is in shared memory (4 warps)
-  uint64_t* ds_free = ds_full + 2;                          // [2] per dS^T buffer: the block's dK and dQ products are complete
-  uint64_t* dq_full = ds_free + 2;                          // [2]
-  uint64_t* dq_free = dq_full + 2;                          // [2] (4 warps)
-  uint64_t* acc_full = dq_free + 2;                         // dK and dV of a tile are complete
+  uint64_t* st_empty = st_full + B3_NS;                     // [NS] the block's reads of Q and dO are complete 
+  uint64_t* s_full = st_empty + B3_NS;                      // S^T is in TMEM
+  uint64_t* s_free = s_full + 1;                            // the compute warps hold S^T in registers (8 warps)
+  uint64_t* dp_full = s_free + 1;                           // dP^T is in TMEM
+  uint64_t* dp_free = dp_full + 1;                          // the compute warps hold dP^T in registers (8 warps)
+  uint64_t* p_full = dp_free + 1;                           // P^T is in TMEM (8 warps)
+  uint64_t* p_used = p_full + 1;                            // dV has read P^T
+  uint64_t* ds_full = p_used + 1;                           // dS^T is in shared memory (8 warps)
+  uint64_t* ds_free = ds_full + 1;                          // dK and dQ have read dS^T
+  uint64_t* dq_full = ds_free + 1;                          // the block's dQ partial is in TMEM
+  uint64_t* dq_free = dq_full + 1;                          // ... and has left it (4 warps)
+  uint64_t* acc_full = dq_free + 1;                         // dK and dV of a tile are complete 
   uint64_t* acc_free = acc_full + 1;                        // ... and have left TMEM (4 warps)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
+  uint64_t* ep_ready = acc_free + 1;                        // the epilogue's staging tile is written (4 warps)
+  uint64_t* ep_done = ep_ready + 1;                         // ... and its TMA stores have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ep_done + 1);
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
   const int n_t = ceil_div(p.T, TILE);
   const int n_items = ((n_t + 1) / 2) * p.B * p.NH;
 
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 2); mbar_init(&p_used[i], 1); mbar_init(&dp_free[i], 4); mbar_init(&dq_full[i], 1); mbar_init(&dq_free[i], 4);
-      mbar_init(&s_full[i], 1); mbar_init(&dp_full[i], 1); mbar_init(&p_full[i], 4);
-      mbar_init(&ds_full[i], 4); mbar_init(&ds_free[i], 1);
-    }
-    for (int i = 0; i < B3_NS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 3); }
-    mbar_init(acc_full, 2); mbar_init(acc_free, 4);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < B3_NS; ++i) { mbar_init(&st_full[i], 1); mbar_init(&st_empty[i], 1); }
+    mbar_init(s_full, 1); mbar_init(s_free, 8); mbar_init(dp_full, 1); mbar_init(dp_free, 8);
+    mbar_init(p_full, 8); mbar_init(p_used, 1); mbar_init(ds_full, 8); mbar_init(ds_free, 1);
+    mbar_init(dq_full, 1); mbar_init(dq_free, 4); mbar_init(acc_full, 1); mbar_init(acc_free, 4); mbar_init(ep_ready, 4); mbar_init(ep_done, 1);
     fence_barrier_init();
-    prefetch_tmap(&tmQKV); prefetch_tmap(&tmDO);
+    prefetch_tmap(&tmQKV); prefetch_tmap(&tmDO); prefetch_tmap(&tmOUT);
   }
   if (warp == 13) tmem_alloc<512>(tmem_slot);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 320, tDQ = tmem + 384, tP = tmem + 448;
   bool failed = false;
 
   // Registers move from the dQ warpgroup and the producer / issuer warpgroup to the two compute warpgroups:
@@ -193,33 +183,29 @@ __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_c
       for (tile3_seek(c, n_t, n_items); !c.done && !failed;) {
         const int b = c.bh / p.NH, h = c.bh % p.NH, kb = c.t & 1, nbt = n_t - c.tile;
         const int colQ = h * HS, colK = p.C + h * HS, colV = 2 * p.C + h * HS;
-        if (c.t >= 2 && !mbar_wait(&kv_empty[kb], ((c.t >> 1) + 1) & 1)) { B3_FAIL(); break; }
+        if (c.t >= 2 && !mbar_wait_sleep(&kv_empty[kb], ((c.t >> 1) + 1) & 1)) { B3_FAIL(); break; }
         if (elect_one()) {
           mbar_expect_tx(&kv_full[kb], 2 * T128);
           load128(sKV + kb * 2 * T128, &tmQKV, &kv_full[kb], colK, c.tile * TILE, b);
           load128(sKV + kb * 2 * T128 + T128, &tmQKV, &kv_full[kb], colV, c.tile * TILE, b);
         }
         __syncwarp();
-        // While this tile's chunks are loaded, the operands of the CTA's NEXT tile are pulled into L2, two boxes per
-        // chunk, so that its loads find them there.
+        // While this tile's blocks are loaded, the operands of the CTA's NEXT tile are pulled into L2, a few boxes per
+        // block, so that its loads find them there.
         Tile3 nx = c;
         tile3_next(nx, nbt, n_t, n_items);
         const int nxb = nx.bh / p.NH, nxh = nx.bh % p.NH, nx0 = nx.tile * TILE;
-        const bool pf_on = !nx.done && !(p.dbg & 8192);
-        const int pf_per = pf_on ? ceil_div(2 + 2 * (n_t - nx.tile), 2 * nbt) : 0;   // prefetch steps per chunk of this tile
+        const int pf_per = nx.done ? 0 : ceil_div(2 + 2 * (n_t - nx.tile), nbt);     // prefetch steps (64 rows) per block of this tile
         int pf = nx0 - 128;                                                          // next row to prefetch; the first two steps take K and V
-        for (int ic = 0; ic < 2 * nbt; ++ic) {
-          const int cc = 2 * c.g + ic, st = cc % B3_NS, i = c.tile + (ic >> 1), g = ic & 1;
-          if (cc >= B3_NS && !mbar_wait(&st_empty[st], ((cc / B3_NS) + 1) & 1)) { B3_FAIL(); break; }
-          B3_TR(4, cc, 0);
+        for (int ib = 0; ib < nbt; ++ib) {
+          const int n = c.g + ib, st = n % B3_NS, i = c.tile + ib;
+          if (n >= B3_NS && !mbar_wait_sleep(&st_empty[st], ((n / B3_NS) + 1) & 1)) { B3_FAIL(); break; }
           if (elect_one()) {
-            unsigned char* stg = sST + st * 2 * T64;
-            const float* src = p.stats + ((size_t)c.bh * n_t + i) * 256 + g * 64;
-            mbar_expect_tx(&st_full[st], 2 * T64 + 512);
-            tma_load_3d(stg, &tmQKV, &st_full[st], colQ, i * TILE + g * 64, b);
-            tma_load_3d(stg + T64, &tmDO, &st_full[st], colQ, i * TILE + g * 64, b);
-            bulk_load_1d(sStat + st * 128, src, 256, &st_full[st]);
-            bulk_load_1d(sStat + st * 128 + 64, src + 128, 256, &st_full[st]);
+            unsigned char* stg = sST + st * 2 * T128;
+            mbar_expect_tx(&st_full[st], 2 * T128 + 1024);
+            load128(stg, &tmQKV, &st_full[st], colQ, i * TILE, b);
+            load128(stg + T128, &tmDO, &st_full[st], colQ, i * TILE, b);
+            bulk_load_1d(sStat + st * 256, p.stats + ((size_t)c.bh * n_t + i) * 256, 1024, &st_full[st]);
             for (int k = 0; k < pf_per; ++k) {
               const int r = pf + 64 * k;
               if (r < nx0) {
@@ -232,109 +218,82 @@ __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_c
             }
           }
           pf += 64 * pf_per;
-
           __syncwarp();
         }
         if (failed) break;
         tile3_next(c, nbt, n_t, n_items);
       }
     } else if (warp == 13) {
-      // ------------------------------------------------------------ MMA issuer: dV += P^T(c) dO_c
-      const uint64_t q_mn0 = make_smem_desc(smem_u32(sST), 8192, 1024);               // dO_c as an MN-major B operand
-      for (Chk3 iv{blk3_begin(n_t, n_items), 0}; !iv.b.c.done && !failed; chk3_next(iv, n_t, n_items)) {
-        const int cc = 2 * iv.b.n + iv.g, st = cc % B3_NS, g = iv.g;
-        const bool first = iv.b.ib == 0 && g == 0, last = iv.b.ib + 1 == iv.b.nbt && g == 1;
-        if (!mbar_wait(&p_full[g], iv.b.n & 1)) { B3_FAIL(); break; }
-        if (first && iv.b.c.t >= 1 && !mbar_wait(acc_free, (iv.b.c.t - 1) & 1)) { B3_FAIL(); break; }
+      // ------------------------------------------------------------ MMA issuer.  Per block n, in the order in which the compute warps'
+      // signals arrive: S^T(n+1) when they hold S^T(n) in registers, dV(n) when P^T(n) is written, dP^T(n+1) when they hold
+      // dP^T(n), dK(n) and dQ(n) when dS^T(n) is written - so the scores of a block are ready a whole block before their use.
+      const uint64_t k_kk0 = make_smem_desc(smem_u32(sKV), 16, 1024);                 // K / V as K-major A operands
+      const uint64_t k_mn0 = make_smem_desc(smem_u32(sKV), 8192, 1024);               // K as an MN-major B operand
+      const uint64_t q_kk0 = make_smem_desc(smem_u32(sST), 16, 1024);                 // Q_i / dO_i as K-major B operands
+      const uint64_t q_mn0 = make_smem_desc(smem_u32(sST), 8192, 1024);               // Q_i / dO_i as MN-major B operands
+      const uint64_t ds_kk = make_smem_desc(smem_u32(sDS), 16, 1024);                 // dS^T as a K-major A operand (K = queries)
+      const uint64_t ds_mn = make_smem_desc(smem_u32(sDS), T128, 1024);               // dS^T as an MN-major A operand (M = queries)
+      Blk3 nx = blk3_begin(n_t, n_items), it = nx;                                    // block n+1 (scores), block n (accumulating products)
+      auto scores_s = [&]() {                                                         // S^T of block nx
+        const int n = nx.n, st = n % B3_NS, kb = nx.c.t & 1;
+        if (nx.ib == 0 && !mbar_wait(&kv_full[kb], (nx.c.t >> 1) & 1)) { B3_FAIL(); return; }
+        if (!mbar_wait(&st_full[st], (n / B3_NS) & 1)) { B3_FAIL(); return; }
+        if (n >= 1 && !mbar_wait(s_free, (n - 1) & 1)) { B3_FAIL(); return; }
         fence_after_sync();
-        const uint64_t do_mn = q_mn0 + (uint64_t)((st * 2 * T64 + T64) >> 4);
+        const uint64_t kd = k_kk0 + (uint64_t)((kb * 2 * T128) >> 4), qd = q_kk0 + (uint64_t)((st * 2 * T128) >> 4);
         if (elect_one()) {
-          if (!(p.dbg & 128))
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma_ts(tDV, tS + g * 64 + ks * 8, do_mn + 128 * ks, IDESC_TS_MN, (ks > 0 || !first) ? 1u : 0u);
-          umma_commit(&p_used[g]);                                                    // P^T(c) has been read: S^T(c+2) may overwrite it
-          umma_commit(&st_empty[st]);
-          if (last) umma_commit(acc_full);
+          for (int ks = 0; ks < HS / 16; ++ks) umma_ss<KIND_F16>(tS, kd + 2 * ks, qd + 2 * ks, IDESC_S_128x128, ks > 0 ? 1u : 0u);
+          umma_commit(s_full);
         }
         __syncwarp();
-      }
-    } else if (warp == 14) {
-      // ------------------------------------------------------------ MMA issuer: dK += dS^T(c) Q_c, and per block dQ = dS K
-      const uint64_t k_mn0 = make_smem_desc(smem_u32(sKV), 8192, 1024);               // K as an MN-major B operand
-      const uint64_t q_mn0 = make_smem_desc(smem_u32(sST), 8192, 1024);               // Q_c as an MN-major B operand
-      const uint64_t ds_kk0 = make_smem_desc(smem_u32(sDS), 16, 1024);                // a dS^T chunk tile as a K-major A operand (K = queries)
-      const uint64_t ds_mn0 = make_smem_desc(smem_u32(sDS), T128, 1024);              // a dS^T buffer as an MN-major A operand (M = 128 queries)
-      for (Chk3 ik{blk3_begin(n_t, n_items), 0}; !ik.b.c.done && !failed; chk3_next(ik, n_t, n_items)) {
-        const int cc = 2 * ik.b.n + ik.g, st = cc % B3_NS, g = ik.g, n = ik.b.n, bb = n & 1, db = n % B3_DSB, kb = ik.b.c.t & 1;
-        const bool first = ik.b.ib == 0 && g == 0, last = ik.b.ib + 1 == ik.b.nbt && g == 1;
-        if (!mbar_wait(&ds_full[g], n & 1)) { B3_FAIL(); break; }
-        if (first && ik.b.c.t >= 1 && !mbar_wait(acc_free, (ik.b.c.t - 1) & 1)) { B3_FAIL(); break; }
-        if (g == 1 && n >= 2 && !mbar_wait(&dq_free[bb], ((n >> 1) + 1) & 1)) { B3_FAIL(); break; }
+      };
+      auto scores_dp = [&]() {                                                        // dP^T of block nx, then nx moves on
+        const int n = nx.n, st = n % B3_NS, kb = nx.c.t & 1;
+        if (n >= 1 && !mbar_wait(dp_free, (n - 1) & 1)) { B3_FAIL(); return; }
         fence_after_sync();
-        const uint64_t q_mn = q_mn0 + (uint64_t)((st * 2 * T64) >> 4);
-        const uint64_t dsk = ds_kk0 + (uint64_t)((db * 2 * T128 + g * T128) >> 4), dsm = ds_mn0 + (uint64_t)((db * 2 * T128) >> 4);
+        const uint64_t vd = k_kk0 + (uint64_t)((kb * 2 * T128 + T128) >> 4), dod = q_kk0 + (uint64_t)((st * 2 * T128 + T128) >> 4);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < HS / 16; ++ks) umma_ss<KIND_F16>(tDP, vd + 2 * ks, dod + 2 * ks, IDESC_S_128x128, ks > 0 ? 1u : 0u);
+          umma_commit(dp_full);
+        }
+        __syncwarp();
+        blk3_next(nx, n_t, n_items);
+      };
+      if (!nx.c.done) { scores_s(); if (!failed) scores_dp(); }                       // block 0
+      while (!it.c.done && !failed) {
+        const int n = it.n, st = n % B3_NS, kb = it.c.t & 1;
+        const bool first = it.ib == 0, last = it.ib + 1 == it.nbt;
+        if (!nx.c.done) { scores_s(); if (failed) break; }                            // waits for s_free(n)
+        if (!mbar_wait(p_full, n & 1)) { B3_FAIL(); break; }
+        if (first && it.c.t >= 1 && !mbar_wait(acc_free, (it.c.t - 1) & 1)) { B3_FAIL(); break; }
+        fence_after_sync();
+        const uint64_t do_mn = q_mn0 + (uint64_t)((st * 2 * T128 + T128) >> 4), q_mn = q_mn0 + (uint64_t)((st * 2 * T128) >> 4);
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < TILE / 16; ++ks) umma_ts(tDV, tP + ks * 8, do_mn + 128 * ks, IDESC_TS_MN, (ks > 0 || !first) ? 1u : 0u);   // dV += P^T dO
+          umma_commit(p_used);                                                        // the compute warps may write P^T(n+1)
+        }
+        __syncwarp();
+        if (!nx.c.done) { scores_dp(); if (failed) break; }                           // waits for dp_free(n)
+        if (!mbar_wait(ds_full, n & 1)) { B3_FAIL(); break; }
+        if (n >= 1 && !mbar_wait(dq_free, (n - 1) & 1)) { B3_FAIL(); break; }
+        fence_after_sync();
         const uint64_t kmn = k_mn0 + (uint64_t)((kb * 2 * T128) >> 4);
         if (elect_one()) {
-          if (!(p.dbg & 64))
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma_ss<KIND_F16>(tDK, dsk + 2 * ks, q_mn + 128 * ks, IDESC_TS_MN, (ks > 0 || !first) ? 1u : 0u);
+          for (int ks = 0; ks < TILE / 16; ++ks)                                                                                          // dK += dS^T Q
+            umma_ss<KIND_F16>(tDK, ds_kk + (ks < 4 ? 2 * ks : (T128 >> 4) + 2 * (ks - 4)), q_mn + 128 * ks, IDESC_TS_MN, (ks > 0 || !first) ? 1u : 0u);
+#pragma unroll
+          for (int ks = 0; ks < TILE / 16; ++ks) umma_ss<KIND_F16>(tDQ, ds_mn + 128 * ks, kmn + 128 * ks, IDESC_MN_MN, ks > 0 ? 1u : 0u);  // dQ = dS K
+          umma_commit(dq_full);
+          umma_commit(ds_free);
           umma_commit(&st_empty[st]);
-          if (g == 1) {
-            if (!(p.dbg & 1024))
-#pragma unroll
-            for (int ks = 0; ks < TILE / 16; ++ks) umma_ss<KIND_F16>(tDQ + bb * 64, dsm + 128 * ks, kmn + 128 * ks, IDESC_MN_MN, ks > 0 ? 1u : 0u);
-            umma_commit(&dq_full[bb]);
-            umma_commit(&ds_free[db]);
-            if (last) { umma_commit(acc_full); umma_commit(&kv_empty[kb]); }
-          }
+          if (last) { umma_commit(acc_full); umma_commit(&kv_empty[kb]); }
         }
         __syncwarp();
-      }
-    } else {
-      // ------------------------------------------------------------ MMA issuer: S^T(c+2) = K Q^T as soon as dV has read P^T(c), then dP^T(c+1) = V dO^T
-      const uint64_t k_kk0 = make_smem_desc(smem_u32(sKV), 16, 1024);                 // K / V as K-major A operands
-      const uint64_t q_kk0 = make_smem_desc(smem_u32(sST), 16, 1024);                 // Q_c / dO_c as K-major B operands
-      Chk3 is{blk3_begin(n_t, n_items), 0}, ip = is;
-      auto do_s = [&]() {
-        const int cc = 2 * is.b.n + is.g, st = cc % B3_NS, g = is.g, n = is.b.n, kb = is.b.c.t & 1;
-        if (is.b.ib == 0 && g == 0 && !mbar_wait(&kv_full[kb], (is.b.c.t >> 1) & 1)) { B3_FAIL(); return; }
-        if (!mbar_wait(&st_full[st], (cc / B3_NS) & 1)) { B3_FAIL(); return; }
-        if (n >= 1 && !mbar_wait(&p_used[g], (n - 1) & 1)) { B3_FAIL(); return; }     // dV has read the P^T this goes over
-        fence_after_sync();
-        const uint64_t kd = k_kk0 + (uint64_t)((kb * 2 * T128) >> 4), qd = q_kk0 + (uint64_t)((st * 2 * T64) >> 4);
-        if (elect_one()) {
-          if (!(p.dbg & 256))
-#pragma unroll
-          for (int ks = 0; ks < HS / 16; ++ks) umma_ss<KIND_F16>(tS + g * 64, kd + 2 * ks, qd + 2 * ks, IDESC_128x64_KK, ks > 0 ? 1u : 0u);
-          umma_commit(&s_full[g]);
-        }
-        __syncwarp();
-        chk3_next(is, n_t, n_items);
-      };
-      auto do_dp = [&]() {                                                            // st_full / kv_full of this chunk were acquired by do_s
-        const int cc = 2 * ip.b.n + ip.g, st = cc % B3_NS, g = ip.g, n = ip.b.n, kb = ip.b.c.t & 1;
-        const bool last = ip.b.ib + 1 == ip.b.nbt && g == 1;
-        if (n >= 1 && !mbar_wait(&dp_free[g], (n - 1) & 1)) { B3_FAIL(); return; }    // the warpgroup holds dP^T(c-2) in registers
-        fence_after_sync();
-        const uint64_t vd = k_kk0 + (uint64_t)((kb * 2 * T128 + T128) >> 4), dod = q_kk0 + (uint64_t)((st * 2 * T64 + T64) >> 4);
-        if (elect_one()) {
-          if (!(p.dbg & 256))
-#pragma unroll
-          for (int ks = 0; ks < HS / 16; ++ks) umma_ss<KIND_F16>(tDP + g * 64, vd + 2 * ks, dod + 2 * ks, IDESC_128x64_KK, ks > 0 ? 1u : 0u);
-          umma_commit(&dp_full[g]);
-          umma_commit(&st_empty[st]);                                                 // this warp's reads of the stage (S^T, dP^T)
-          if (last) umma_commit(&kv_empty[kb]);
-        }
-        __syncwarp();
-        chk3_next(ip, n_t, n_items);
-      };
-      if (!is.b.c.done) {
-        do_s(); if (!failed) do_s();                                                  // chunks 0 and 1
-        if (!failed) do_dp();                                                         // chunk 0
-        while (!ip.b.c.done && !failed) {                                             // step m: S^T(m+2), dP^T(m+1)
-          if (!is.b.c.done) { do_s(); if (failed) break; }
-          do_dp();
-        }
+        blk3_next(it, n_t, n_items);
       }
     }
   } else if (warp >= 8) {
@@ -342,102 +301,104 @@ __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_c
     asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    int ne = 0;                                             // epilogue rounds so far
     for (Blk3 it = blk3_begin(n_t, n_items); !it.c.done && !failed; blk3_next(it, n_t, n_items)) {
-      const int n = it.n, buf = n & 1, i = it.c.tile + it.ib;
-      if (!mbar_wait(&dq_full[buf], (n >> 1) & 1)) { B3_FAIL(); break; }
-      if (warp == 8) B3_TR(3, n, 0);
+      const int n = it.n, i = it.c.tile + it.ib;
+      if (!mbar_wait_sleep(dq_full, n & 1)) { B3_FAIL(); break; }
       fence_after_sync();
       float* dst = p.dq_acc + ((size_t)it.c.bh * n_t + i) * (TILE * HS) + row * 4;
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
         uint32_t r[32];
-        tmem_ld32(tDQ + buf * 64 + lane_addr + half * 32, r);
+        tmem_ld32(tDQ + lane_addr + half * 32, r);
         tmem_wait_ld();
         if (half == 1) {
           fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&dq_free[buf]);
+          if (lane == 0) mbar_arrive(dq_free);
         }
-        if (!(p.dbg & 1))
 #pragma unroll
         for (int c = 0; c < 8; ++c)
           red_add_v4(dst + (half * 8 + c) * (TILE * 4), __uint_as_float(r[4 * c]), __uint_as_float(r[4 * c + 1]), __uint_as_float(r[4 * c + 2]),
                      __uint_as_float(r[4 * c + 3]));
       }
       if (it.ib + 1 < it.nbt) continue;
-      // the tile's dV and dK
-      if (!mbar_wait(acc_full, it.c.t & 1)) { B3_FAIL(); break; }
+      // The tile's dV and dK: rounded rows go through a swizzled staging tile and leave as TMA stores (whole 128-byte
+      // rows; rows beyond T are clipped by the tensor map).  Per-thread stores of 16 bytes at a row stride of 3C would
+      // keep this warpgroup busy for longer than a whole block takes.
+      if (!mbar_wait_sleep(acc_full, it.c.t & 1)) { B3_FAIL(); break; }
       fence_after_sync();
-      const int b = it.c.bh / p.NH, h = it.c.bh % p.NH, kj = it.c.tile * TILE + row;
-      __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.dqkv) + ((size_t)b * p.T + kj) * (3 * (size_t)p.C) + h * HS;
-      const float sc = p.scale;                             // dS^T was stored without the 1/sqrt(HS) factor
+      const int b = it.c.bh / p.NH, h = it.c.bh % p.NH, k0 = it.c.tile * TILE, kj = k0 + row;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        uint32_t rv[32], rk[32];
-        tmem_ld32(tDV + lane_addr + half * 32, rv);
-        tmem_ld32(tDK + lane_addr + half * 32, rk);
-        tmem_wait_ld();
-        if (half == 1) {
-          fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(acc_free);
-        }
-        if (kj < p.T) {
+      for (int mat = 0; mat < 2; ++mat) {                   // 0: dV, 1: dK
+        const float sc = mat ? p.scale : 1.0f;              // dS^T was stored without the 1/sqrt(HS) factor
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32((mat ? tDK : tDV) + lane_addr + half * 32, r);
+          tmem_wait_ld();
+          if (mat == 1 && half == 1) {
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_free);
+          }
+          float v[32];
 #pragma unroll
-          for (int j8 = 0; j8 < 4; ++j8) {
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(rv[j8 * 8 + 0]), __uint_as_float(rv[j8 * 8 + 1]));
-            u.y = pack_bf16x2(__uint_as_float(rv[j8 * 8 + 2]), __uint_as_float(rv[j8 * 8 + 3]));
-            u.z = pack_bf16x2(__uint_as_float(rv[j8 * 8 + 4]), __uint_as_float(rv[j8 * 8 + 5]));
-            u.w = pack_bf16x2(__uint_as_float(rv[j8 * 8 + 6]), __uint_as_float(rv[j8 * 8 + 7]));
-            *reinterpret_cast<uint4*>(base + 2 * p.C + half * 32 + j8 * 8) = u;
-            u.x = pack_bf16x2(__uint_as_float(rk[j8 * 8 + 0]) * sc, __uint_as_float(rk[j8 * 8 + 1]) * sc);
-            u.y = pack_bf16x2(__uint_as_float(rk[j8 * 8 + 2]) * sc, __uint_as_float(rk[j8 * 8 + 3]) * sc);
-            u.z = pack_bf16x2(__uint_as_float(rk[j8 * 8 + 4]) * sc, __uint_as_float(rk[j8 * 8 + 5]) * sc);
-            u.w = pack_bf16x2(__uint_as_float(rk[j8 * 8 + 6]) * sc, __uint_as_float(rk[j8 * 8 + 7]) * sc);
-            *reinterpret_cast<uint4*>(base + p.C + half * 32 + j8 * 8) = u;
+          for (int x = 0; x < 32; ++x) v[x] = kj < p.T ? __uint_as_float(r[x]) * sc : 0.f;
+          store_row32(sEP, row, half * 32, v);
+          if (p.dbias) {                                    // qkv bias gradient, dK and dV parts: column sums of this warp's 32 rows
+            const float cs = warp_colsum32(v, lane);
+            atomicAdd(p.dbias + (mat ? 1 : 2) * p.C + h * HS + half * 32 + lane, cs);
           }
         }
-        if (p.dbias) {                                      // qkv bias gradient, dK and dV parts: column sums of this warp's 32 rows
-          float cv[32];
-#pragma unroll
-          for (int x = 0; x < 32; ++x) cv[x] = kj < p.T ? __uint_as_float(rk[x]) * sc : 0.f;
-          const float ck = warp_colsum32(cv, lane);
-#pragma unroll
-          for (int x = 0; x < 32; ++x) cv[x] = kj < p.T ? __uint_as_float(rv[x]) : 0.f;
-          const float cvv = warp_colsum32(cv, lane);
-          atomicAdd(p.dbias + p.C + h * HS + half * 32 + lane, ck);
-          atomicAdd(p.dbias + 2 * p.C + h * HS + half * 32 + lane, cvv);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ep_ready);
+        if (warp == 8) {
+          if (!mbar_wait_sleep(ep_ready, ne & 1)) { B3_FAIL(); break; }
+          if (elect_one()) {
+            const int col = (mat ? 1 : 2) * p.C + h * HS;
+            tma_store_3d(&tmOUT, sEP, col, k0, b);
+            tma_store_3d(&tmOUT, sEP + T64, col, k0 + 64, b);
+            bulk_commit();
+            bulk_wait_read<0>();
+            mbar_arrive(ep_done);
+          }
+          __syncwarp();
         }
+        if (!mbar_wait_sleep(ep_done, ne & 1)) { B3_FAIL(); break; }      // the staging tile may be rewritten
+        ++ne;
       }
     }
   } else {
-    // ------------------------------------------------------------------ compute warpgroup g: one thread per key row, chunk 2n + g of every block
+    // ------------------------------------------------------------------ compute warpgroup hq: one thread per key row, query columns hq*64 .. +63
     asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
-    const int g = warp >> 2;
+    const int hq = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tSg = tS + lane_addr + g * 64, tDPg = tDP + lane_addr + g * 64;
+    const uint32_t tSh = tS + lane_addr + hq * 64, tDPh = tDP + lane_addr + hq * 64, tPh = tP + lane_addr + hq * 32;
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     for (Blk3 it = blk3_begin(n_t, n_items); !it.c.done && !failed; blk3_next(it, n_t, n_items)) {
-      const int n = it.n, cc = 2 * n + g, st = cc % B3_NS, bb = n & 1;
-      const float* stat = sStat + st * 128;
-      if (!mbar_wait(&st_full[st], (cc / B3_NS) & 1)) { B3_FAIL(); break; }      // acquire the chunk's row statistics
-      if (!mbar_wait(&s_full[g], n & 1)) { B3_FAIL(); break; }
-      if ((warp & 3) == 0) B3_TR(1 + g, n, 0);
+      const int n = it.n, st = n % B3_NS;
+      const float* stat = sStat + st * 256 + hq * 64;
+      if (!mbar_wait_sleep(&st_full[st], (n / B3_NS) & 1)) { B3_FAIL(); break; }      // acquire the block's row statistics
+      if (!mbar_wait_sleep(s_full, n & 1)) { B3_FAIL(); break; }
       fence_after_sync();
       uint32_t s[64];
       {
         uint32_t (&q0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[0]);
         uint32_t (&q1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[32]);
-        tmem_ld32(tSg, q0); tmem_ld32(tSg + 32, q1);
+        tmem_ld32(tSh, q0); tmem_ld32(tSh + 32, q1);
       }
       tmem_wait_ld();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);                   // S^T(n+1) may be issued now
       {
         uint32_t pk[32];
         const float4* nl4 = reinterpret_cast<const float4*>(stat);
         auto p_phase = [&](auto diag) {
-          const int lim = row - g * 64;                     // diagonal block: local query columns x < lim see nothing of this key
+          const int lim = row - hq * 64;                    // diagonal block: local query columns x < lim see nothing of this key
 #pragma unroll
           for (int x = 0; x < 16; ++x) {
             const float4 l = nl4[x];
@@ -453,30 +414,29 @@ __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_c
             pk[2 * x] = pack_bf16x2(e0, e1); pk[2 * x + 1] = pack_bf16x2(e2, e3);
           }
         };
-        if (p.dbg & 16) { for (int x = 0; x < 32; ++x) pk[x] = s[x]; }
-        else if (it.ib == 0) p_phase(std::true_type{}); else p_phase(std::false_type{});
-        tmem_st32(tSg, pk);                                 // P^T over the first half of the chunk's score columns
+        if (it.ib == 0) p_phase(std::true_type{}); else p_phase(std::false_type{});
+        if (n >= 1 && !mbar_wait_sleep(p_used, (n - 1) & 1)) { B3_FAIL(); break; }   // dV has read P^T(n-1)
+        fence_after_sync();
+        tmem_st32(tPh, pk);
       }
       tmem_wait_st();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[g]);
-      if ((warp & 3) == 0) B3_TR(1 + g, n, 1);
-      if (!mbar_wait(&dp_full[g], n & 1)) { B3_FAIL(); break; }
-      if ((warp & 3) == 0) B3_TR(1 + g, n, 2);
+      if (lane == 0) mbar_arrive(p_full);
+      if (!mbar_wait_sleep(dp_full, n & 1)) { B3_FAIL(); break; }
       fence_after_sync();
       uint32_t d[64];
       {
         uint32_t (&q0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[0]);
         uint32_t (&q1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&d[32]);
-        tmem_ld32(tDPg, q0); tmem_ld32(tDPg + 32, q1);
+        tmem_ld32(tDPh, q0); tmem_ld32(tDPh + 32, q1);
       }
       tmem_wait_ld();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&dp_free[g]);
-      if (!(p.dbg & 32)) {
-        const float4* nd4 = reinterpret_cast<const float4*>(stat + 64);
+      if (lane == 0) mbar_arrive(dp_free);                  // dP^T(n+1) may be issued now
+      {
+        const float4* nd4 = reinterpret_cast<const float4*>(stat + 128);
 #pragma unroll
         for (int x = 0; x < 16; ++x) {
           const float4 nd = nd4[x];
@@ -488,18 +448,17 @@ __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_c
           s[4 * x + 2] = __float_as_uint(r23.x); s[4 * x + 3] = __float_as_uint(r23.y);
         }
       }
-      if (n >= B3_DSB && !mbar_wait(&ds_free[n % B3_DSB], ((n / B3_DSB) + 1) & 1)) { B3_FAIL(); break; }   // the products of the buffer's previous block have read it
-      if (!(p.dbg & 512)) {
+      if (n >= 1 && !mbar_wait_sleep(ds_free, (n - 1) & 1)) { B3_FAIL(); break; }   // dK and dQ of block n-1 have read the tile
+      {
         const float (&v0)[32] = *reinterpret_cast<const float (*)[32]>(&s[0]);
         const float (&v1)[32] = *reinterpret_cast<const float (*)[32]>(&s[32]);
-        store_row32(sDS + (n % B3_DSB) * 2 * T128 + g * T128, row, 0, v0);
-        store_row32(sDS + (n % B3_DSB) * 2 * T128 + g * T128, row, 32, v1);
+        store_row32(sDS + hq * T128, row, 0, v0);
+        store_row32(sDS + hq * T128, row, 32, v1);
       }
       fence_proxy_async();
-      fence_before_sync();                                  // also orders this warp's read of dP^T before the product that overwrites it
+      fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_full[g]);
-      if ((warp & 3) == 0) B3_TR(1 + g, n, 3);
+      if (lane == 0) mbar_arrive(ds_full);
     }
   }
   fence_before_sync();
@@ -511,7 +470,7 @@ __global__ void __launch_bounds__(B3_THREADS, 1) attn_bwd3_kernel(const __grid_c
 // One block of 128 threads per (batch, head, tile): thread r reads row r (a warp reads 512 consecutive bytes per load), the
 // rounded rows cross a swizzled shared-memory tile, and every warp then writes four whole 128-byte rows per instruction.
 __global__ void __launch_bounds__(128) attn_bwd3_dq_kernel(__nv_bfloat16* __restrict__ dqkv, float* __restrict__ dbias, float* __restrict__ dq_acc,
-                                                           int T, int NH, int C, float scale, int dbg) {
+                                                           int T, int NH, int C, float scale) {
   __shared__ float part[4][HS];
   __shared__ __align__(16) unsigned char tile_s[TILE * ROWB];
   const int n_t = ceil_div(T, TILE);
@@ -543,20 +502,17 @@ __global__ void __launch_bounds__(128) attn_bwd3_dq_kernel(__nv_bfloat16* __rest
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const int row = k * 16 + (r >> 3), qi = tile * TILE + row;
-    if (qi < T && !(dbg & 4096))
+    if (qi < T)
       *reinterpret_cast<uint4*>(dqkv + ((size_t)b * T + qi) * (3 * (size_t)C) + h * HS + chunk * 8) =
           *reinterpret_cast<const uint4*>(tile_s + sw128(row, chunk));
   }
   // Zeroed only now, when every load above has returned its data: a store to an address whose load is still in flight
   // waits for it, and the kernel then runs at a quarter of the memory bandwidth.
-  if (!(dbg & 2048))
 #pragma unroll
   for (int c = 0; c < 16; ++c) *reinterpret_cast<float4*>(src + c * (TILE * 4)) = make_float4(0.f, 0.f, 0.f, 0.f);
   if (dbias && r < HS) atomicAdd(dbias + h * HS + r, part[0][r] + part[1][r] + part[2][r] + part[3][r]);
 }
 }  // namespace
-
-LLMB_API int llmb_b3_trace_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_b3_trace, sizeof(long long) * 8 * 128 * 4); }
 
 // Sizes (in floats) of the two scratch buffers of llmb_attention_bwd_fused.
 LLMB_API long long llmb_attention_bwd_fused_stats_floats(int B, int T, int NH) { return (long long)B * NH * ceil_div(T, TILE) * 256; }
@@ -572,6 +528,8 @@ LLMB_API int llmb_attention_bwd_fused(void* dqkv, float* dbias, float* stats, fl
   CUtensorMap tq, td;
   int rc = make_qkv_map(&tq, qkv, B, T, 3 * C); if (rc) return 1000 + rc;
   rc = make_qkv_map(&td, dout, B, T, C); if (rc) return 1000 + rc;
+  CUtensorMap to;
+  rc = make_qkv_map(&to, dqkv, B, T, 3 * C); if (rc) return 1000 + rc;
   B3Params p{}; p.dqkv = dqkv; p.stats = stats; p.dq_acc = dq_acc; p.dbias = dbias;
   p.B = B; p.T = T; p.NH = NH; p.C = C; p.scale = 0.125f; p.scale_log2 = 0.125f * 1.4426950408889634f; p.status = status;
   static bool attr = false;
@@ -581,14 +539,10 @@ LLMB_API int llmb_attention_bwd_fused(void* dqkv, float* dbias, float* stats, fl
   }
   const int n_t = ceil_div(T, TILE);
   const long long rows = (long long)B * NH * n_t * TILE;
-  { const char* e = getenv("LLMB_B3_DBG"); p.dbg = e ? atoi(e) : 0; }
-  if (!(p.dbg & 4))
   attn_bwd3_prep_kernel<<<(unsigned)ceil_div_ll(rows * 8, 256), 256, 0, st>>>(stats, lse, (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, B, T, NH, C);
   const long long n_items = (long long)((n_t + 1) / 2) * B * NH;
   const int grid = (int)(n_items < sm_count() ? n_items : sm_count());          // persistent: one CTA per SM
-  if (!(p.dbg & 8))
-  attn_bwd3_kernel<<<grid, B3_THREADS, B3_SMEM, st>>>(tq, td, p);
-  if (!(p.dbg & 2))
-  attn_bwd3_dq_kernel<<<(unsigned)(B * NH * n_t), 128, 0, st>>>((__nv_bfloat16*)dqkv, dbias, dq_acc, T, NH, C, p.scale, p.dbg);
+  attn_bwd3_kernel<<<grid, B3_THREADS, B3_SMEM, st>>>(tq, td, to, p);
+  attn_bwd3_dq_kernel<<<(unsigned)(B * NH * n_t), 128, 0, st>>>((__nv_bfloat16*)dqkv, dbias, dq_acc, T, NH, C, p.scale);
   return (int)cudaGetLastError();
 }

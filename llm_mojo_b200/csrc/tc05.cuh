@@ -53,6 +53,33 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// As mbar_wait, but every poll carries a suspend-time hint: the hardware may keep the thread suspended until the phase
+// completes (or the hint runs out) instead of returning after its short default time slice, so that a warp waiting for a
+// far-away event does not compete with the working warps for issue slots and the shared-memory pipe.  Bounded: 2^17
+// polls of at most ~10 us.
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 17); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(10000u) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+// Bounded wait for a role that has slack: non-blocking probes with a sleep between them, so that the waiting warp stays
+// off the barrier unit and the issue slots while the warps on the critical path use them (~1 s at most).
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, unsigned ns = 256) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (mbar_test(bar, parity)) return true;
+    __nanosleep(ns);
+  }
+  return false;
+}
+
 // ------------------------------------------------------------------ TMA (tile mode, no multicast)
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* t) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(t)) : "memory");
@@ -81,6 +108,10 @@ __device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* t, int c0,
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* t, const void* src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(t)), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* t, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(t)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all but the newest N groups of this thread have finished READING their shared-memory source

@@ -29,7 +29,7 @@ GELU_K = math.sqrt(2.0 / math.pi)
 # Library GEMM/attention can be forced for A/B comparisons (never the default on CUDA).
 GEMM_IMPL = os.environ.get("LLMB_GEMM", "tcgen05")        # tcgen05 | cublas
 ATTN_IMPL = os.environ.get("LLMB_ATTN", "tcgen05")        # tcgen05 | sdpa
-ATTN_BWD = os.environ.get("LLMB_ATTN_BWD", "split")       # fused (one kernel, dQ partials reduced in fp32) | split (dK/dV and dQ kernels)
+ATTN_BWD = os.environ.get("LLMB_ATTN_BWD", "fused")       # fused (one kernel, dQ partials reduced in fp32) | split (dK/dV and dQ kernels)
 
 _SCRATCH = {}
 LAUNCHES = 0     # number of kernel-library launches issued (bench.py reports it)

@@ -328,7 +328,7 @@ def test_attention_fwd_bwd(B, T, NH, bwd, monkeypatch):
     close(dbias, 0.25 + r_dqkv.view(B * T, 3 * C).sum(0), 2e-2 * math.sqrt(B * T), 2e-2, "qkv dbias", strict=True)
     if bwd == "fused":
         # the fp32 dQ accumulation scratch is left zeroed, so a second call gives the same result
-        acc = ops.scratch("attn_bwd_dq_acc", 4, torch.device(DEV)).view(torch.float32)
+        acc = ops.scratch("attn_bwd_dq_acc", 4, dqkv.device).view(torch.float32)
         assert int(torch.count_nonzero(acc)) == 0
         again = torch.full_like(dqkv, float("nan"))
         ops.attention_bwd(again, dout.to(DEV), qkv.to(DEV), out, lse, NH)
