@@ -408,21 +408,25 @@ __device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_
   const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(c < 4 ? r0[(c & 3) * 8 + j] : r1[(c & 3) * 8 + j]) * alpha;
+    float v[8], b[8];
     const int col = col0 + c * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b[j] = 0.f;
     if (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID) {
       if (bias && col < p.N) {
-        float b[8];
         if (p.bias_vec) unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
         else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) b[j] = __bfloat162float(bias[col + j]);
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] += b[j];
       }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const uint32_t (&r)[32] = c < 4 ? r0 : r1;
+      const float2 y = __ffma2_rn(make_float2(__uint_as_float(r[(c & 3) * 8 + j]), __uint_as_float(r[(c & 3) * 8 + j + 1])),
+                                  make_float2(alpha, alpha), make_float2(b[j], b[j + 1]));
+      v[j] = y.x; v[j + 1] = y.y;
     }
     unsigned char* slot = myrow + ((c ^ (lane & 7)) << 4);
     if (EPI == EPI_BIAS_GELU) {
@@ -430,13 +434,20 @@ __device__ __forceinline__ void epi_slab_bf16(const GemmParams& p, const uint32_
       *reinterpret_cast<uint4*>(slot) = pre;
       float x[8]; unpack8(pre, x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = (p.dbg & 8) ? x[j] : gelu_fast_f(x[j]);
+      for (int j = 0; j < 8; j += 2) {
+        const float2 y = (p.dbg & 8) ? make_float2(x[j], x[j + 1]) : gelu_fast2(make_float2(x[j], x[j + 1]));
+        v[j] = y.x; v[j + 1] = y.y;
+      }
       *reinterpret_cast<uint4*>(slot + SLAB_BYTES) = pack8(v);
     } else {
       if (EPI == EPI_DGELU || EPI == EPI_BIAS_RESID) {
         float x[8]; unpack8(*reinterpret_cast<const uint4*>(slot), x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (EPI == EPI_DGELU) ? v[j] * gelu_grad_fast_f(x[j]) : v[j] + x[j];
+        for (int j = 0; j < 8; j += 2) {
+          const float2 xx = make_float2(x[j], x[j + 1]), vv = make_float2(v[j], v[j + 1]);
+          const float2 y = (EPI == EPI_DGELU) ? __fmul2_rn(vv, gelu_grad_fast2(xx)) : __fadd2_rn(vv, xx);
+          v[j] = y.x; v[j + 1] = y.y;
+        }
       }
       *reinterpret_cast<uint4*>(slot) = pack8(v);
     }
@@ -451,19 +462,23 @@ __device__ __forceinline__ void epi_slab_pre(const GemmParams& p, const uint32_t
   const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(c < 4 ? r0[(c & 3) * 8 + j] : r1[(c & 3) * 8 + j]) * alpha;
+    float v[8], b[8];
     const int col = col0 + c * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b[j] = 0.f;
     if (bias && col < p.N) {
-      float b[8];
       if (p.bias_vec) unpack8(__ldg(reinterpret_cast<const uint4*>(bias + col)), b);
       else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) b[j] = __bfloat162float(bias[col + j]);
       }
+    }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] += b[j];
+    for (int j = 0; j < 8; j += 2) {
+      const uint32_t (&r)[32] = c < 4 ? r0 : r1;
+      const float2 y = __ffma2_rn(make_float2(__uint_as_float(r[(c & 3) * 8 + j]), __uint_as_float(r[(c & 3) * 8 + j + 1])),
+                                  make_float2(alpha, alpha), make_float2(b[j], b[j + 1]));
+      v[j] = y.x; v[j + 1] = y.y;
     }
     pre[c] = pack8(v);
     *reinterpret_cast<uint4*>(myrow + ((c ^ (lane & 7)) << 4)) = pre[c];
@@ -476,7 +491,10 @@ __device__ __forceinline__ void epi_slab_gelu(const GemmParams& p, const uint4 (
   for (int c = 0; c < 8; ++c) {
     float x[8]; unpack8(pre[c], x);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] = (p.dbg & 8) ? x[j] : gelu_fast_f(x[j]);
+    for (int j = 0; j < 8; j += 2) {
+      const float2 y = (p.dbg & 8) ? make_float2(x[j], x[j + 1]) : gelu_fast2(make_float2(x[j], x[j + 1]));
+      x[j] = y.x; x[j + 1] = y.y;
+    }
     *reinterpret_cast<uint4*>(myrow + ((c ^ (lane & 7)) << 4)) = pack8(x);
   }
 }
