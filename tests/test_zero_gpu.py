@@ -167,8 +167,10 @@ def test_zero3_weight_pull_inside_gemm_matches_gather_kernel(tmp_path):
     """ZeRO-3 on the peer-memory backend: the layer weights pulled by the copier warps of the layer's own GEMM kernels
     (default) against the stand-alone gather kernel prefetched one layer ahead.  The same bytes land in the same
     windows, so losses and parameters must agree to the last bit."""
-    fused = _run(3, "p2p", 2, str(tmp_path), LLMM_FUSED_Z3="1")
-    plain = _run(3, "p2p", 2, str(tmp_path), LLMM_FUSED_Z3="0")
+    # bitwise comparison: the two bias-gradient fusions that sum by atomics (arbitrary order) are switched off in both runs
+    det = dict(LLMM_FUSED_QKV_DBIAS="0", LLMM_FUSED_LN_DBIAS="0", LLMB_ATTN_BWD="split")
+    fused = _run(3, "p2p", 2, str(tmp_path), LLMM_FUSED_Z3="1", **det)
+    plain = _run(3, "p2p", 2, str(tmp_path), LLMM_FUSED_Z3="0", **det)
     assert fused["status"] == 0 and plain["status"] == 0
     assert fused["fused_z3"] and not plain["fused_z3"]
     assert fused["losses"] == plain["losses"], (fused["losses"], plain["losses"])
