@@ -58,41 +58,86 @@ __global__ void make_keys_kernel(unsigned long long* keys, const int* tok, int B
   if (i < BT) keys[i] = ((unsigned long long)(unsigned)tok[i] << 32) | (unsigned)i;
 }
 
-// One block per sorted index; only the block sitting on the first key of a token run works.
-// Threads are (position lane, channel vector); lanes stride the run, then a fixed-order
-// shared-memory reduction over lanes keeps the sum order independent of scheduling.
-template <typename T, int LANES>
-__global__ void wte_bwd_kernel(float* __restrict__ dwte, const T* __restrict__ dout,
-                               const unsigned long long* __restrict__ keys, int BT, int C, int V) {
+// dwte[token] += sum of the dout rows of that token's positions, deterministic and independent of how skewed the token
+// distribution is (on real text a handful of tokens own several per cent of the positions; a loop over one token's run
+// would take milliseconds).  The sorted keys are cut into segments of 16; one warp sums the runs inside its segment.  A run
+// that lies inside one segment is added to dwte at once (nothing else touches that row); the piece of a run that crosses a
+// segment border goes to a per-segment partial row (slot 0: the run began in an earlier segment, slot 1: it goes on in the
+// next one), and wte_bwd_combine_kernel adds up the pieces of each such run in segment order.
+constexpr int WTE_SEG = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) wte_bwd_kernel(float* __restrict__ dwte, float* __restrict__ partial, const T* __restrict__ dout,
+                                                      const unsigned long long* __restrict__ keys, int BT, int C, int V) {
   constexpr int N = Pack<T>::N;
-  int i = blockIdx.x;
-  unsigned tokv = (unsigned)(keys[i] >> 32);
-  if (i > 0 && (unsigned)(keys[i - 1] >> 32) == tokv) return;
-  if (!llmb_in_range((long long)tokv, V, LLMB_SITE_ENCODER_BWD_TOKEN)) return;
-  extern __shared__ float sm[];  // [LANES][C]
+  const int lane = threadIdx.x % 32, seg = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  const int j0 = seg * WTE_SEG;
+  if (j0 >= BT) return;
+  const int cnt = min(WTE_SEG, BT - j0);
+  unsigned long long mykey = lane < cnt ? keys[j0 + lane] : 0ull;
+  const unsigned prev_tok = j0 > 0 ? (unsigned)(keys[j0 - 1] >> 32) : 0xffffffffu;
+  const unsigned next_tok = j0 + cnt < BT ? (unsigned)(keys[j0 + cnt] >> 32) : 0xffffffffu;
   const int vec_per_row = C / N;
-  const int nvec_threads = blockDim.x / LANES;
-  int lane = threadIdx.x / nvec_threads, vt = threadIdx.x % nvec_threads;
-  for (int vc = vt; vc < vec_per_row; vc += nvec_threads) {
+  for (int vc = lane; vc < vec_per_row; vc += 32) {       // this lane's channel vectors, one after the other
     float acc[N];
 #pragma unroll
     for (int k = 0; k < N; ++k) acc[k] = 0.f;
-    for (int j = i + lane; j < BT; j += LANES) {
-      unsigned long long key = keys[j];
-      if ((unsigned)(key >> 32) != tokv) break;
-      int pos = (int)(key & 0xffffffffu);
-      Pack<T> p; p.load(dout + (size_t)pos * C + vc * N);
+    int a = 0;                                              // first position of the current run inside the segment
+    for (int j = 0; j < cnt; ++j) {
+      const unsigned long long key = __shfl_sync(0xffffffffu, mykey, j);
+      const unsigned tokv = (unsigned)(key >> 32);
+      const bool ok = llmb_in_range((long long)tokv, V, LLMB_SITE_ENCODER_BWD_TOKEN);
+      if (ok) {
+        Pack<T> p; p.load(dout + (size_t)(unsigned)(key & 0xffffffffu) * C + vc * N);
 #pragma unroll
-      for (int k = 0; k < N; ++k) acc[k] += p.v[k];
+        for (int k = 0; k < N; ++k) acc[k] += p.v[k];
+      }
+      const unsigned nxt = j + 1 < cnt ? (unsigned)(__shfl_sync(0xffffffffu, mykey, j + 1) >> 32) : next_tok;
+      if (j + 1 == cnt || nxt != tokv) {                    // the run (or its piece in this segment) ends here
+        const bool from_before = a == 0 && prev_tok == tokv, goes_on = j + 1 == cnt && next_tok == tokv;
+        if (ok) {
+          float* dst = (from_before || goes_on) ? partial + ((size_t)seg * 2 + (from_before ? 0 : 1)) * C + vc * N
+                                                : dwte + (size_t)tokv * C + vc * N;
+          if (from_before || goes_on) {
+#pragma unroll
+            for (int k = 0; k < N; ++k) dst[k] = acc[k];
+          } else {
+#pragma unroll
+            for (int k = 0; k < N; ++k) dst[k] += acc[k];
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] = 0.f;
+        a = j + 1;
+      }
     }
-#pragma unroll
-    for (int k = 0; k < N; ++k) sm[lane * C + vc * N + k] = acc[k];
+  }
+}
+// One block per segment: if a run leaves this segment through its end (and did not enter through its start, i.e. this
+// is where the run's first piece lives), its pieces are summed in segment order and added to dwte.
+__global__ void __launch_bounds__(256) wte_bwd_combine_kernel(float* __restrict__ dwte, const float* __restrict__ partial,
+                                                              const unsigned long long* __restrict__ keys, int BT, int C, int V) {
+  const int seg = blockIdx.x, j0 = seg * WTE_SEG, cnt = min(WTE_SEG, BT - j0);
+  const unsigned tokv = (unsigned)(keys[j0 + cnt - 1] >> 32);
+  if (j0 + cnt >= BT || (unsigned)(keys[j0 + cnt] >> 32) != tokv) return;            // nothing leaves through the end
+  const bool whole = (unsigned)(keys[j0] >> 32) == tokv;                              // the segment holds this token only
+  if (whole && j0 > 0 && (unsigned)(keys[j0 - 1] >> 32) == tokv) return;              // a middle piece: the run's first segment does the sum
+  if (!llmb_in_range((long long)tokv, V, LLMB_SITE_ENCODER_BWD_TOKEN)) return;
+  // the run's end by bisection over the sorted keys (the loop below then has no load in its condition)
+  __shared__ int last_seg_s;
+  if (threadIdx.x == 0) {
+    int lo = j0 + cnt, hi = BT;                            // keys[lo] is this token; first index beyond the run in (lo, hi]
+    while (lo + 1 < hi) {
+      const int mid = lo + (hi - lo) / 2;
+      if ((unsigned)(keys[mid] >> 32) == tokv) lo = mid; else hi = mid;
+    }
+    last_seg_s = lo / WTE_SEG;
   }
   __syncthreads();
+  const int last_seg = last_seg_s;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float s = 0.f;
-#pragma unroll
-    for (int l = 0; l < LANES; ++l) s += sm[l * C + c];
+    float s = partial[((size_t)seg * 2 + 1) * C + c];
+#pragma unroll 8
+    for (int t = seg + 1; t <= last_seg; ++t) s += partial[((size_t)t * 2) * C + c];
     dwte[(size_t)tokv * C + c] += s;
   }
 }
@@ -116,35 +161,41 @@ __global__ void wpe_bwd_kernel(float* __restrict__ dwpe, const T* __restrict__ d
   for (int k = 0; k < N; ++k) dwpe[(size_t)t * C + c + k] += acc[k];
 }
 
-// Scratch layout: keys_in[BT] u64 | keys_out[BT] u64 | cub temp. Query the size first.
-LLMB_API long long llmb_encoder_bwd_scratch_bytes(int BT) {
+// Scratch layout: keys_in[BT] u64 | keys_out[BT] u64 | cub temp | partial rows [segments][2][C] fp32.  Query the size first.
+static size_t encoder_bwd_sort_bytes(int BT) {
   size_t temp = 0;
   cub::DeviceRadixSort::SortKeys(nullptr, temp, (unsigned long long*)nullptr, (unsigned long long*)nullptr, BT);
-  return (long long)(2 * (size_t)BT * sizeof(unsigned long long) + ((temp + 255) / 256) * 256 + 256);
+  return 2 * (size_t)BT * sizeof(unsigned long long) + ((temp + 255) / 256) * 256 + 256;
+}
+LLMB_API long long llmb_encoder_bwd_scratch_bytes(int BT, int C) {
+  return (long long)(encoder_bwd_sort_bytes(BT) + (size_t)ceil_div(BT, WTE_SEG) * 2 * C * sizeof(float));
 }
 
 LLMB_API int llmb_encoder_bwd(float* dwte, float* dwpe, const void* dout, const int* tok, void* scratch,
                               long long scratch_bytes, int B, int T, int C, int V, int vocab_bits, int dtype,
                               cudaStream_t st) {
   int BT = B * T;
-  if (scratch_bytes < llmb_encoder_bwd_scratch_bytes(BT)) return LLMB_ERR_BAD_ARG;
+  if (scratch_bytes < llmb_encoder_bwd_scratch_bytes(BT, C)) return LLMB_ERR_BAD_ARG;
   unsigned long long* kin = (unsigned long long*)scratch;
   unsigned long long* kout = kin + BT;
   void* temp = (void*)(kout + BT);
-  size_t temp_bytes = (size_t)scratch_bytes - 2 * (size_t)BT * sizeof(unsigned long long);
+  const size_t sort_bytes = encoder_bwd_sort_bytes(BT);
+  size_t temp_bytes = sort_bytes - 2 * (size_t)BT * sizeof(unsigned long long);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(scratch) + sort_bytes);
   make_keys_kernel<<<ceil_div(BT, 256), 256, 0, st>>>(kin, tok, BT);
-  int pos_bits = 1; while ((1ll << pos_bits) < BT) ++pos_bits;
   // position bits live in [0, 32); token bits in [32, 32 + vocab_bits). Sort only the used bits.
   cudaError_t e = cub::DeviceRadixSort::SortKeys(temp, temp_bytes, kin, kout, BT, 0, 32 + vocab_bits, st);
   if (e != cudaSuccess) return (int)e;
-  (void)pos_bits;
-  constexpr int LANES = 4;
-  size_t smem = (size_t)LANES * C * sizeof(float);
+  const int nseg = ceil_div(BT, WTE_SEG);
   if (dtype == LLMB_BF16) {
-    wte_bwd_kernel<__nv_bfloat16, LANES><<<BT, 256, smem, st>>>(dwte, (const __nv_bfloat16*)dout, kout, BT, C, V);
+    if (C % 8) return LLMB_ERR_BAD_ARG;
+    wte_bwd_kernel<__nv_bfloat16><<<ceil_div(nseg, 8), 256, 0, st>>>(dwte, partial, (const __nv_bfloat16*)dout, kout, BT, C, V);
+    wte_bwd_combine_kernel<<<nseg, 256, 0, st>>>(dwte, partial, kout, BT, C, V);
     wpe_bwd_kernel<__nv_bfloat16><<<ceil_div(T * (C / 8), 256), 256, 0, st>>>(dwpe, (const __nv_bfloat16*)dout, B, T, C);
   } else {
-    wte_bwd_kernel<float, LANES><<<BT, 256, smem, st>>>(dwte, (const float*)dout, kout, BT, C, V);
+    if (C % 4) return LLMB_ERR_BAD_ARG;
+    wte_bwd_kernel<float><<<ceil_div(nseg, 8), 256, 0, st>>>(dwte, partial, (const float*)dout, kout, BT, C, V);
+    wte_bwd_combine_kernel<<<nseg, 256, 0, st>>>(dwte, partial, kout, BT, C, V);
     wpe_bwd_kernel<float><<<ceil_div(T * (C / 4), 256), 256, 0, st>>>(dwpe, (const float*)dout, B, T, C);
   }
   return (int)cudaGetLastError();

@@ -376,12 +376,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 //     global access of the epilogue is a full 128-byte row segment; out-of-range rows and columns are
 //     clipped by the tensor maps.
 // Epilogues with an auxiliary input or a second output (BIAS_GELU stores the pre-activation too) get
-// two 4 KB buffers per warp and a 5-deep operand ring; the others one buffer and a 6-deep ring.
+// two 4 KB buffers per warp and a 5-deep operand ring, and so do the fp32 outputs (two 32-column boxes of a 64-column slab,
+// added into or stored to global memory by TMA); the others one buffer and a 6-deep ring.
 template <int EPI> struct EpiCfg {
   static constexpr bool AUX_IN = EPI == EPI_DGELU || EPI == EPI_BIAS_RESID;
   static constexpr bool TWO_OUT = EPI == EPI_BIAS_GELU;
   static constexpr bool F32_OUT = EPI == EPI_ACC_F32 || EPI == EPI_STORE_F32;
-  static constexpr int STAGES = (!F32_OUT && (AUX_IN || TWO_OUT)) ? 5 : 6;
+  static constexpr int STAGES = (F32_OUT || AUX_IN || TWO_OUT) ? 5 : 6;
   static constexpr int WARP_STAGE = STAGES == 5 ? 16384 : 8192;     // staging bytes per warp of the 4-warp register epilogue (half that per warp of the 8-warp TMA epilogue)
 };
 constexpr int SLAB_BYTES = 32 * 128;
@@ -770,7 +771,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // 128-column half of the tile, i.e. two 64-column slabs per warp and tile.  The register epilogue (fp32
     // outputs, layouts without a tensor map) keeps four working warps with all four slabs of a band each.
     const int q = warp & 3, e = warp - 2, hcol = e >> 2;
-    const bool tma_epi = !Cfg::F32_OUT && p.tma_epi;      // warp-uniform
+    const bool tma_epi = p.tma_epi;                       // warp-uniform
     unsigned char* wstage = epi_stage + e * (tma_epi ? WSB / 2 : WSB);
     uint64_t* abar = aux_bar + e * 2;
     const int band_off = (int)cta * BM + q * 32;
@@ -817,6 +818,36 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld32(tacc + (hcol * 2 + ls) * 64 + 32, r1);
           tmem_wait_ld();
           unsigned char* buf;
+          if (Cfg::F32_OUT) {
+            // fp32 accumulate / store: the slab leaves as two boxes of 32 rows x 32 fp32 columns (128-byte rows, swizzled), which
+            // the TMA engine adds into (split-K partial sums, gradient accumulation) or writes to the output; the warp goes on
+            // to its next slab at once instead of waiting on 64 vector reductions per lane.
+            buf = wstage;
+            if (lane == 0) bulk_wait_read<0>();           // the previous slab's boxes have been read
+            __syncwarp();
+            unsigned char* myrow = buf + lane * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const int sw = (c ^ (lane & 7)) << 4;
+              *reinterpret_cast<float4*>(myrow + sw) = make_float4(__uint_as_float(r0[4 * c]) * alpha, __uint_as_float(r0[4 * c + 1]) * alpha,
+                                                                   __uint_as_float(r0[4 * c + 2]) * alpha, __uint_as_float(r0[4 * c + 3]) * alpha);
+              *reinterpret_cast<float4*>(myrow + SLAB_BYTES + sw) = make_float4(__uint_as_float(r1[4 * c]) * alpha, __uint_as_float(r1[4 * c + 1]) * alpha,
+                                                                                __uint_as_float(r1[4 * c + 2]) * alpha, __uint_as_float(r1[4 * c + 3]) * alpha);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && !(p.dbg & 1)) {
+              if (EPI == EPI_ACC_F32) {
+                tma_reduce_add_2d(&tmD, buf, col0, row0);
+                if (col0 + 32 < p.N) tma_reduce_add_2d(&tmD, buf + SLAB_BYTES, col0 + 32, row0);
+              } else {
+                tma_store_2d(&tmD, buf, col0, row0);
+                if (col0 + 32 < p.N) tma_store_2d(&tmD, buf + SLAB_BYTES, col0 + 32, row0);
+              }
+              bulk_commit();
+            }
+            continue;
+          }
           if (Cfg::AUX_IN) {
             buf = wstage + ls * SLAB_BYTES;
             if (!mbar_wait(&abar[ls], (aux_phase >> ls) & 1)) { ok = false; break; }
@@ -1032,6 +1063,9 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
         ok = make_tmap_2d(&taux, aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)N, (uint64_t)ldaux, 32, 64) == 0;
       p.tma_epi = ok;
     }
+    if (tma_epi_on && !p.io_f32 && (epi == EPI_ACC_F32 || epi == EPI_STORE_F32) && (ldd * 4) % 16 == 0 &&
+        (reinterpret_cast<uintptr_t>(D) & 15) == 0)
+      p.tma_epi = make_tmap_2d(&td, D, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)M, (uint64_t)N, (uint64_t)ldd, 32, 32) == 0;
     if (p.colsum && !p.tma_epi) return LLMB_ERR_BAD_ARG;   // the column sums are taken in the TMA epilogue only
     switch (epi) {
       case EPI_NONE: return launch_pair<KIND, EPI_NONE>(ta, tb, td, taux, p, grid2, st);

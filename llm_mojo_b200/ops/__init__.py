@@ -96,7 +96,7 @@ def encoder_bwd(dwte: torch.Tensor, dwpe: torch.Tensor, dout: torch.Tensor, toke
     C = dwte.shape[1]
     if dout.is_cuda:
         L = lib()
-        nb = L.llmb_encoder_bwd_scratch_bytes(B * T)
+        nb = L.llmb_encoder_bwd_scratch_bytes(B * T, C)
         s = scratch("encoder_bwd", nb, dout.device)
         vocab_bits = max(1, int(dwte.shape[0] - 1).bit_length())
         check(L.llmb_encoder_bwd(ptr(dwte), ptr(dwpe), ptr(dout), ptr(tokens), ptr(s), s.numel(), B, T, C, dwte.shape[0],

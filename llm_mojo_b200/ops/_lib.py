@@ -22,7 +22,7 @@ c_int, c_ll, c_f, c_p, c_ull = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, 
 
 _SIGS = {
     "llmb_encoder_fwd": [c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_int, c_int, c_p],
-    "llmb_encoder_bwd_scratch_bytes": [c_int],
+    "llmb_encoder_bwd_scratch_bytes": [c_int, c_int],
     "llmb_encoder_bwd": [c_p, c_p, c_p, c_p, c_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_p],
     "llmb_bounds_report_elementwise": [c_p, c_int],
     "llmb_bounds_report_classifier": [c_p, c_int],

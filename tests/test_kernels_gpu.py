@@ -56,6 +56,34 @@ def test_encoder_fwd_bwd(dtype):
     assert torch.equal(gw, gw2) and torch.equal(gp, gp2), "encoder backward must be bitwise repeatable"
 
 
+@pytest.mark.parametrize("kind", ["zipf", "one_token", "aligned_runs"])
+def test_encoder_bwd_skewed_tokens(kind):
+    """Token distributions of real text: a few tokens own thousands of positions.  The kernel cuts the sorted positions
+    into segments of 16 and sums the pieces of a run that crosses segment borders in a second pass; here runs span hundreds
+    of segments, start and end exactly on segment borders, and the last segment is partial."""
+    B, T, C, V = 5, 1000, 256, 50304
+    g = torch.Generator().manual_seed(3)
+    if kind == "zipf":
+        w = 1.0 / torch.arange(1, 50258, dtype=torch.float64) ** 1.2
+        tok = torch.multinomial(w, B * T, replacement=True, generator=g).view(B, T).int()
+    elif kind == "one_token":
+        tok = torch.full((B, T), 4321, dtype=torch.int32)
+    else:       # runs of exactly 16, 32, 48 positions so that runs begin and end on segment borders, then singles
+        ids = torch.cat([torch.full((16,), 5), torch.full((32,), 9), torch.full((48,), 11), torch.full((15,), 12), torch.full((17,), 13),
+                         torch.arange(100, 100 + B * T - 128)])
+        tok = ids[torch.randperm(B * T, generator=g)].view(B, T).int()
+    dout = rnd(B, T, C, dtype=torch.bfloat16, seed=4)
+    dwte, dwpe = torch.zeros(V, C), torch.zeros(T, C)
+    ops.encoder_bwd(dwte, dwpe, dout.float(), tok)
+    gw, gp = torch.full((V, C), 0.5, device=DEV), torch.zeros(T, C, device=DEV)
+    ops.encoder_bwd(gw, gp, dout.to(DEV), tok.to(DEV))
+    torch.cuda.synchronize()
+    close(gw, dwte + 0.5, 2e-3, 1e-4, "dwte (skewed)", strict=True)      # sums of up to 5000 bf16 rows in fp32
+    gw2, gp2 = torch.full((V, C), 0.5, device=DEV), torch.zeros(T, C, device=DEV)
+    ops.encoder_bwd(gw2, gp2, dout.to(DEV), tok.to(DEV))
+    assert torch.equal(gw, gw2), "encoder backward must be bitwise repeatable"
+
+
 @pytest.mark.parametrize("C", [768, 1024, 1280, 1600])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_layernorm_fwd_bwd(C, dtype):
