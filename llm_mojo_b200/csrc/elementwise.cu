@@ -77,7 +77,9 @@ __global__ void __launch_bounds__(256) wte_bwd_kernel(float* __restrict__ dwte, 
   const unsigned prev_tok = j0 > 0 ? (unsigned)(keys[j0 - 1] >> 32) : 0xffffffffu;
   const unsigned next_tok = j0 + cnt < BT ? (unsigned)(keys[j0 + cnt] >> 32) : 0xffffffffu;
   const int vec_per_row = C / N;
-  for (int vc = lane; vc < vec_per_row; vc += 32) {       // this lane's channel vectors, one after the other
+  for (int vc0 = 0; vc0 < vec_per_row; vc0 += 32) {       // this lane's channel vectors, one after the other; every lane walks the
+    const int vc = vc0 + lane;                             // loop (the shuffles below need the whole warp), idle ones past the row end
+    const bool live = vc < vec_per_row;
     float acc[N];
 #pragma unroll
     for (int k = 0; k < N; ++k) acc[k] = 0.f;
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(256) wte_bwd_kernel(float* __restrict__ dwte, 
       const unsigned long long key = __shfl_sync(0xffffffffu, mykey, j);
       const unsigned tokv = (unsigned)(key >> 32);
       const bool ok = llmb_in_range((long long)tokv, V, LLMB_SITE_ENCODER_BWD_TOKEN);
-      if (ok) {
+      if (ok && live) {
         Pack<T> p; p.load(dout + (size_t)(unsigned)(key & 0xffffffffu) * C + vc * N);
 #pragma unroll
         for (int k = 0; k < N; ++k) acc[k] += p.v[k];
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(256) wte_bwd_kernel(float* __restrict__ dwte, 
       const unsigned nxt = j + 1 < cnt ? (unsigned)(__shfl_sync(0xffffffffu, mykey, j + 1) >> 32) : next_tok;
       if (j + 1 == cnt || nxt != tokv) {                    // the run (or its piece in this segment) ends here
         const bool from_before = a == 0 && prev_tok == tokv, goes_on = j + 1 == cnt && next_tok == tokv;
-        if (ok) {
+        if (ok && live) {
           float* dst = (from_before || goes_on) ? partial + ((size_t)seg * 2 + (from_before ? 0 : 1)) * C + vc * N
                                                 : dwte + (size_t)tokv * C + vc * N;
           if (from_before || goes_on) {
