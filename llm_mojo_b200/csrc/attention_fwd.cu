@@ -31,8 +31,8 @@
 namespace {
 constexpr int F3_NS = 3;                                  // K/V ring depth (32 KB per stage)
 constexpr int F3_THREADS = 512;                           // 2 softmax warpgroups | output warpgroup | producer, two issuers, one idle warp
-constexpr int F3_SMEM = 4 * T128 /*Q: 2 buffers x 2 tiles*/ + F3_NS * 2 * T128 /*K,V ring*/ + 1024 /*alignment*/ + 512 /*barriers*/ +
-                        4096 /*row statistics*/;
+constexpr int F3_SMEM = 4 * T128 /*Q: 2 buffers x 2 tiles*/ + F3_NS * 2 * T128 /*K,V ring*/ + 2 * T128 /*output staging, one tile per lane*/ +
+                        1024 /*alignment*/ + 512 /*barriers*/ + 4096 /*row statistics*/;
 constexpr int F3_POLY = 0;                                // of every 8 score pairs, how many take their exponential on the FMA pipe
 constexpr uint32_t IDESC_PV = make_idesc(FMT_BF16, FMT_BF16, 0, 1, 128, 64);   // A (P) K-major from TMEM, B (V) stored [keys, HS]
 
@@ -62,12 +62,14 @@ __device__ __forceinline__ F3Item f3_item(int k, int n_t, int n_pairs, int gpw, 
   return it;
 }
 
-__global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p) {
+__global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmO,
+                                                                   const AttnParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = sm;                                 // buffer qb: tile 2i at qb*2*T128, tile 2i+1 at +T128
   unsigned char* sKV = sQ + 4 * T128;                     // stage s: K block at s*2*T128, V block at +T128
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + F3_NS * 2 * T128);
+  unsigned char* sOut = sKV + F3_NS * 2 * T128;           // lane r: the tile's rounded output rows, swizzled, source of its TMA stores
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + 2 * T128);
   uint64_t* q_full = bars;                                // [2]
   uint64_t* q_empty = q_full + 2;                         // [lane][2] the lane's last score product of the item is complete
   uint64_t* kv_full = q_empty + 4;                        // [NS]
@@ -78,7 +80,9 @@ __global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_c
   uint64_t* pv_done = p_full + 2;                         // [2] per lane: O += P V complete (P may be overwritten)
   uint64_t* o_free = pv_done + 2;                         // [2] per lane: the item's output has left TMEM
   uint64_t* fin = o_free + 2;                             // [2] per lane: the item's row statistics are in shared memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fin + 2);
+  uint64_t* out_ready = fin + 2;                          // [2] per lane: the staging tile is written (4 warps)
+  uint64_t* out_done = out_ready + 2;                     // [2] per lane: its TMA stores have read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(out_done + 2);
   float* stats = reinterpret_cast<float*>(bars + 64);     // [lane][item parity][m | l][128 rows]
 
   const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -92,10 +96,11 @@ __global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_c
       mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); mbar_init(&q_empty[2 + i], 1);
       mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4); mbar_init(&p_full[i], 4);
       mbar_init(&pv_done[i], 1); mbar_init(&o_free[i], 4); mbar_init(&fin[i], 4);
+      mbar_init(&out_ready[i], 4); mbar_init(&out_done[i], 1);
     }
     for (int i = 0; i < F3_NS; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&kv_empty[F3_NS + i], 1); }
     fence_barrier_init();
-    prefetch_tmap(&tm);
+    prefetch_tmap(&tm); prefetch_tmap(&tmO);
   }
   if (warp == 13) tmem_alloc<512>(tmem_slot);
   fence_before_sync();
@@ -212,7 +217,7 @@ __global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_c
     asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    int cp[2] = {0, 0}, ni[2] = {0, 0};                   // per lane: products / items so far
+    int cp[2] = {0, 0}, ni[2] = {0, 0}, no[2] = {0, 0};   // per lane: products / items / output tiles so far
     for (int k = 0; !failed; ++k) {
       const F3Item it = f3_item(k, n_t, n_pairs, gpw, BH);
       if (!it.valid) break;
@@ -232,7 +237,11 @@ __global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_c
           fence_after_sync();
           const uint32_t tO = tmem + 256 + r * 64 + lane_addr;
           const float inv = 1.0f / l_run;
-          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + ((size_t)b * p.T + qi) * p.C + h * HS;
+          // The rounded rows go through a swizzled staging tile and leave as two TMA stores (whole 128-byte rows, rows beyond
+          // T clipped by the tensor map): 16-byte stores per thread at a row stride of C keep a warp on 32 sectors per
+          // instruction and this warpgroup busy for longer than a short item takes.
+          unsigned char* stg = sOut + r * T128;
+          if (no[r] >= 1 && !mbar_wait(&out_done[r], (no[r] - 1) & 1)) { F3_FAIL(); break; }   // the previous tile's stores have read it
 #pragma unroll 1
           for (int half = 0; half < 2; ++half) {
             uint32_t o[32];
@@ -243,18 +252,26 @@ __global__ void __launch_bounds__(F3_THREADS, 1) attn_fwd3_kernel(const __grid_c
               __syncwarp();
               if (lane == 0) mbar_arrive(&o_free[r]);
             }
-            if (qi < p.T) {
+            float v[32];
 #pragma unroll
-              for (int j8 = 0; j8 < 4; ++j8) {
-                uint4 u;
-                u.x = pack_bf16x2(__uint_as_float(o[j8 * 8 + 0]) * inv, __uint_as_float(o[j8 * 8 + 1]) * inv);
-                u.y = pack_bf16x2(__uint_as_float(o[j8 * 8 + 2]) * inv, __uint_as_float(o[j8 * 8 + 3]) * inv);
-                u.z = pack_bf16x2(__uint_as_float(o[j8 * 8 + 4]) * inv, __uint_as_float(o[j8 * 8 + 5]) * inv);
-                u.w = pack_bf16x2(__uint_as_float(o[j8 * 8 + 6]) * inv, __uint_as_float(o[j8 * 8 + 7]) * inv);
-                *reinterpret_cast<uint4*>(op + half * 32 + j8 * 8) = u;
-              }
-            }
+            for (int x = 0; x < 32; ++x) v[x] = __uint_as_float(o[x]) * inv;
+            store_row32(stg, row, half * 32, v);
           }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&out_ready[r]);
+          if (warp == 8) {
+            if (!mbar_wait(&out_ready[r], no[r] & 1)) { F3_FAIL(); break; }
+            if (elect_one()) {
+              tma_store_3d(&tmO, stg, h * HS, (it.t0 + tt) * TILE, b);
+              tma_store_3d(&tmO, stg + T64, h * HS, (it.t0 + tt) * TILE + 64, b);
+              bulk_commit();
+              bulk_wait_read<0>();
+              mbar_arrive(&out_done[r]);
+            }
+            __syncwarp();
+          }
+          ++no[r];
           if (qi < p.T) p.lse[(size_t)it.bh * p.T + qi] = m_run + log2f(l_run);
         }
       }
@@ -387,6 +404,9 @@ LLMB_API int llmb_attention_fwd_pair(void* out, float* lse, const void* qkv, int
   CUtensorMap tm;
   int rc = make_qkv_map(&tm, qkv, B, T, 3 * C);
   if (rc) return 1000 + rc;
+  CUtensorMap tmo;
+  rc = make_qkv_map(&tmo, out, B, T, C);
+  if (rc) return 1000 + rc;
   AttnParams p{}; p.out = out; p.lse = lse; p.B = B; p.T = T; p.NH = NH; p.C = C;
   p.scale = 0.125f; p.scale_log2 = 0.125f * 1.4426950408889634f; p.status = status;
   static bool attr = false;
@@ -396,6 +416,6 @@ LLMB_API int llmb_attention_fwd_pair(void* out, float* lse, const void* qkv, int
   int grid = sm_count();
   if (n_items < grid) grid = (int)n_items;
   if (grid < n_pairs) grid = n_pairs;                     // one (batch, head) needs n_pairs CTAs side by side
-  attn_fwd3_kernel<<<grid, F3_THREADS, F3_SMEM, st>>>(tm, p);
+  attn_fwd3_kernel<<<grid, F3_THREADS, F3_SMEM, st>>>(tm, tmo, p);
   return (int)cudaGetLastError();
 }
