@@ -329,7 +329,8 @@ def test_gemm_tf32_fp32_storage(gemm_mode):
 
 # ------------------------------------------------------------------------------ attention
 @pytest.mark.parametrize("bwd", ["fused", "split"])
-@pytest.mark.parametrize("B,T,NH", [(2, 128, 2), (1, 256, 3), (2, 1024, 2), (2, 64, 2), (1, 200, 1), (3, 640, 5), (2, 384, 2)])
+@pytest.mark.parametrize("B,T,NH", [(2, 128, 2), (1, 256, 3), (2, 1024, 2), (2, 64, 2), (1, 200, 1), (3, 640, 5), (2, 384, 2), (1, 2048, 2),
+                                    (1, 1100, 3)])
 def test_attention_fwd_bwd(B, T, NH, bwd, monkeypatch):
     monkeypatch.setattr(ops, "ATTN_BWD", bwd)
     C = NH * 64
