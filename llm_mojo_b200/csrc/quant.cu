@@ -402,7 +402,78 @@ __global__ void rng_uniform_kernel(float* out, long long n, unsigned long long s
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = rng_uniform01(seed, base + i, stream);
 }
+
+// Delayed scaling after the warm-up: the scale of this step comes from the history BEFORE this step's amax is pushed, so the
+// tensor needs to be read only once - quantise with the scale that `amax_scale_from_history_kernel` has just derived, take max|x|
+// on the way (same NaN-infectious integer max as amax_kernel), and let `amax_push_kernel` append it to the history afterwards.
+__global__ void amax_scale_from_history_kernel(float* state, unsigned* amax_bits, float fmt_max, float margin_mult) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const float* hist = state + 4;
+  float m = 0.f; bool bad = false;
+  for (int i = 0; i < AMAX_HISTORY; ++i) { float h = hist[i]; if (isnan(h) || isinf(h)) bad = true; else m = fmaxf(m, h); }
+  const float a = bad ? NAN : m;
+  const float scale = (a <= 0.f || isnan(a) || isinf(a)) ? 1.0f : (fmt_max * margin_mult) / a;
+  state[0] = scale; state[1] = 1.0f / scale;
+  *amax_bits = 0u;
+}
+__global__ void amax_push_kernel(float* state, const float* amax_cur) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int step = __float_as_int(state[2]);
+  state[4 + step % AMAX_HISTORY] = *amax_cur;
+  state[2] = __int_as_float(step + 1);
+}
+template <typename T, int FMT>
+__global__ void __launch_bounds__(512) quantize_fp8_amax_kernel(uint8_t* __restrict__ out, unsigned* __restrict__ amax_bits, const T* __restrict__ x,
+                                                               const float* __restrict__ scale_ptr, long long n) {
+  constexpr int N = Pack<T>::N;
+  const float s = *scale_ptr;
+  unsigned m = 0;
+  const long long nvec = n / N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    Pack<T> p; p.load(x + i * N);
+    uint8_t q[N];
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      m = max(m, __float_as_uint(p.v[k]) & 0x7fffffffu);
+      q[k] = (uint8_t)__nv_cvt_float_to_fp8(p.v[k] * s, __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+    }
+    if (N == 8) *reinterpret_cast<uint2*>(out + i * N) = *reinterpret_cast<uint2*>(q);
+    else *reinterpret_cast<uint32_t*>(out + i * N) = *reinterpret_cast<uint32_t*>(q);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ unsigned red[32];
+  const int lane = threadIdx.x % 32, wid = threadIdx.x / 32;
+  if (lane == 0) red[wid] = m;
+  __syncthreads();
+  if (wid == 0) {
+    m = lane < (int)(blockDim.x / 32) ? red[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) atomicMax(amax_bits, m);
+  }
+}
 }  // namespace
+
+// One pass over x for a delayed-scaling operand whose history is full (the caller checks that: state[2] >= the history
+// length): state[0..1] = scale / 1/scale from the history, out = fp8(x * scale) saturated, amax[0] = max|x| (NaN-infectious),
+// then the amax is appended to the history.  n must be a multiple of the vector width (8 for bf16, 4 for fp32).
+LLMB_API int llmb_quantize_fp8_delayed(void* out, const void* x, float* state, float* amax, long long n, int fmt, float fmt_max,
+                                       float margin_mult, int dtype, cudaStream_t st) {
+  if (n % (dtype == LLMB_BF16 ? 8 : 4)) return LLMB_ERR_BAD_ARG;
+  amax_scale_from_history_kernel<<<1, 32, 0, st>>>(state, (unsigned*)amax, fmt_max, margin_mult);
+  long long blocks = ceil_div_ll(n, 512 * 8);
+  int grid = (int)(blocks < (long long)sm_count() * 4 ? (blocks < 1 ? 1 : blocks) : (long long)sm_count() * 4);
+  if (dtype == LLMB_BF16) {
+    if (fmt == 0) quantize_fp8_amax_kernel<__nv_bfloat16, 0><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const __nv_bfloat16*)x, state, n);
+    else quantize_fp8_amax_kernel<__nv_bfloat16, 1><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const __nv_bfloat16*)x, state, n);
+  } else {
+    if (fmt == 0) quantize_fp8_amax_kernel<float, 0><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const float*)x, state, n);
+    else quantize_fp8_amax_kernel<float, 1><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const float*)x, state, n);
+  }
+  amax_push_kernel<<<1, 32, 0, st>>>(state, amax);
+  return (int)cudaGetLastError();
+}
 
 // out (1 float, device) = max |x|, NaN if any element is NaN
 LLMB_API int llmb_amax(float* out, const void* x, long long n, int dtype, cudaStream_t st) {

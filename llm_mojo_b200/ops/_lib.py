@@ -62,6 +62,7 @@ _SIGS = {
     "llmb_amax_state_floats": [],
     "llmb_amax_update": [c_p, c_p, c_f, c_f, c_p],
     "llmb_quantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_int, c_p],
+    "llmb_quantize_fp8_delayed": [c_p, c_p, c_p, c_p, c_ll, c_int, c_f, c_f, c_int, c_p],
     "llmb_dequantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_p],
     "llmb_nvfp4_tensor_scale": [c_p, c_p, c_p],
     "llmb_nvfp4_scale_bytes": [c_ll, c_ll, c_int],

@@ -123,6 +123,12 @@ class LinearSite:
         self.weight = AmaxState(device, E4M3)
         self.dout = AmaxState(device, E5M2)
         self.alpha = torch.ones(1, dtype=torch.float32, device=device)
+        # fp8 copies of the forward operands, kept for the backward pass of the same micro-step (1 byte per element of the
+        # layer input and of the weight) so that it does not quantise them a second time; `LLMM_FP8_KEEP_OPERANDS=0` drops
+        # them and re-quantises, as the reference does
+        self.qx: Optional[torch.Tensor] = None
+        self.qw: Optional[torch.Tensor] = None
+        self.kept = None          # (data_ptr, version) of the input and the weight the kept bytes were made from
 
 
 class LowpState:
@@ -177,10 +183,30 @@ class LowpState:
         return out
 
 
-def _q(name: str, x: torch.Tensor, state: AmaxState) -> torch.Tensor:
-    """Update the site's scale from ``x`` and return its fp8 quantisation (uint8 storage, same shape)."""
+FUSED_DELAYED = os.environ.get("LLMM_FP8_FUSED_QUANT", "1") != "0"     # one pass (quantise + amax) once the amax history is full
+
+
+KEEP_OPERANDS = os.environ.get("LLMM_FP8_KEEP_OPERANDS", "1") != "0"
+
+
+def _q(name: str, x: torch.Tensor, state: AmaxState, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Update the site's scale from ``x`` and return its fp8 quantisation (uint8 storage, same shape).
+
+    While the amax history is filling up the scale of a step depends on the step's own amax: two passes (amax, then
+    quantise).  Afterwards it depends on the history before this step only, and one kernel reads ``x`` once: it quantises
+    with the scale just derived from the history and takes max|x| on the way, which is then pushed (same numbers as the
+    two-pass order of ``llmm/amax.mojo:425-565``)."""
+    if buf is None:
+        buf = scratch("fp8_" + name, x.numel(), x.device)[:x.numel()].view(x.shape)
+    vec = 8 if x.dtype == torch.bfloat16 else 4
+    if (FUSED_DELAYED and x.is_cuda and not state.static and state.host_step >= AMAX_HISTORY and x.is_contiguous()
+            and x.numel() % vec == 0 and x.dtype in (torch.bfloat16, torch.float32)):
+        check(lib().llmb_quantize_fp8_delayed(ptr(buf), ptr(x), ptr(state.state), ptr(state.amax), x.numel(), state.fmt,
+                                              FMT_MAX[state.fmt], state.margin_mult, dtype_code(x), stream()), "quantize_fp8_delayed")
+        _count(3)
+        state.host_step += 1
+        return buf
     state.update_scale(x)
-    buf = scratch("fp8_" + name, x.numel(), x.device)[:x.numel()].view(x.shape)
     quantize_fp8(buf, x, state.scale, state.fmt)
     return buf
 
@@ -190,8 +216,18 @@ def matmul_fwd_fp8(out, inp, weight, bias, site: LinearSite, *, pre_gelu=None, r
     OC, C = weight.shape
     rows = inp.numel() // C
     x = inp.reshape(rows, C)
-    qx = _q("x", x, site.inp)
-    qw = _q("w", weight, site.weight)
+    site.kept = None
+    if KEEP_OPERANDS and out.is_cuda:
+        if site.qx is None or site.qx.shape != x.shape:
+            site.qx = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+        if site.qw is None or site.qw.shape != weight.shape:
+            site.qw = torch.empty(weight.shape, dtype=torch.uint8, device=x.device)
+        qx = _q("x", x, site.inp, site.qx)
+        qw = _q("w", weight, site.weight, site.qw)
+        site.kept = (x.data_ptr(), x._version, weight.data_ptr(), weight._version)
+    else:
+        qx = _q("x", x, site.inp)
+        qw = _q("w", weight, site.weight)
     torch.mul(site.inp.scale_inv, site.weight.scale_inv, out=site.alpha)
     o = out.view(rows, OC)
     if out.is_cuda:
@@ -224,8 +260,11 @@ def matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, site: LinearSite, *,
     d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
     qd = _q("d", d, site.dout)
     if dinp is not None:
-        qw = scratch("fp8_w", weight.numel(), weight.device)[:weight.numel()].view(weight.shape)
-        quantize_fp8(qw, weight, site.weight.scale, E4M3)           # same scale as the forward pass of this step
+        if site.kept is not None and site.kept[2:] == (weight.data_ptr(), weight._version) and site.qw.shape == weight.shape:
+            qw = site.qw                                                # the forward pass's bytes (same scale, same weight)
+        else:
+            qw = scratch("fp8_w", weight.numel(), weight.device)[:weight.numel()].view(weight.shape)
+            quantize_fp8(qw, weight, site.weight.scale, E4M3)           # same scale as the forward pass of this step
         torch.mul(site.dout.scale_inv, site.weight.scale_inv, out=site.alpha)
         di = dinp.view(rows, C)
         if dout.is_cuda:
@@ -236,8 +275,11 @@ def matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, site: LinearSite, *,
             if gelu_pre is not None:
                 g = g * _gelu_grad_t(gelu_pre.view(rows, C).float())
             di.copy_(g)
-    qx = scratch("fp8_x", x.numel(), x.device)[:x.numel()].view(x.shape)
-    quantize_fp8(qx, x, site.inp.scale, E4M3)
+    if site.kept is not None and site.kept[:2] == (x.data_ptr(), x._version) and site.qx.shape == x.shape:
+        qx = site.qx
+    else:
+        qx = scratch("fp8_x", x.numel(), x.device)[:x.numel()].view(x.shape)
+        quantize_fp8(qx, x, site.inp.scale, E4M3)
     alpha2 = site.dout.scale_inv * site.inp.scale_inv
     if dout.is_cuda:
         gemm(dweight.view(OC, C), qd, qx, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), alpha=alpha2,

@@ -201,6 +201,29 @@ def test_delayed_scaling_state_on_device_matches_host():
 
 
 @gpu
+@pytest.mark.parametrize("fmt", [lowp.E4M3, lowp.E5M2])
+def test_single_pass_delayed_quantisation_matches_two_passes(fmt, monkeypatch):
+    """Once the amax history is full, `_q` reads the tensor once (quantise with the scale from the history, amax on the way,
+    push).  Scales, history and fp8 bytes must equal the two-pass order at every step, across the warm-up boundary, with a NaN
+    in one step (its amax is NaN: the scale falls back to 1 while it is in the history) and with values that saturate."""
+    one, two = lowp.AmaxState("cuda", fmt), lowp.AmaxState("cuda", fmt)
+    g = torch.Generator().manual_seed(5)
+    for step in range(lowp.AMAX_HISTORY + 24):
+        x = (torch.randn(64, 1024, generator=g) * float(torch.rand(1, generator=g) * 20 + 0.05)).bfloat16().cuda()
+        if step == lowp.AMAX_HISTORY + 3:
+            x[5, 7] = float("nan")
+        monkeypatch.setattr(lowp, "FUSED_DELAYED", True)
+        q1 = lowp._q("t1", x, one).clone()
+        monkeypatch.setattr(lowp, "FUSED_DELAYED", False)
+        q2 = lowp._q("t2", x, two).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(one.state.cpu().nan_to_num(-1.0), two.state.cpu().nan_to_num(-1.0)), step
+        keep = ~torch.isnan(x)                      # what a NaN input encodes to is not part of the contract
+        assert torch.equal(q1[keep], q2[keep]), step
+    assert one.host_step == two.host_step == lowp.AMAX_HISTORY + 24
+
+
+@gpu
 @pytest.mark.parametrize("axis,block_rows,rht", [(1, 1, False), (1, 16, False), (0, 1, False), (0, 1, True), (0, 16, False)])
 def test_nvfp4_kernel_matches_emulation(axis, block_rows, rht):
     x = torch.randn(256, 384).bfloat16()
