@@ -1017,7 +1017,7 @@ int gemm_dispatch(void* D, const void* A, const void* B, const void* bias, void*
   if ((p.pull.nseg > 0 || p.pull.nwait > 0) && (!pair || p.g.W > 1)) return LLMB_ERR_BAD_ARG;   // copier warps exist in the pair kernel only
   p.colsum = g_pending_colsum;
   g_pending_colsum = nullptr;
-  if (p.colsum && !(pair && epi == EPI_DGELU && KIND == KIND_F16)) return LLMB_ERR_BAD_ARG;
+  if (p.colsum && !(pair && epi == EPI_DGELU && (KIND == KIND_F16 || KIND == KIND_F8F6F4))) return LLMB_ERR_BAD_ARG;   // bf16 output, TMA epilogue
   if (p.g.W > 1) {
     // gathered A: K-major bf16 rows, CTA-pair kernel, whole 256-row tiles per chunk, no split-K
     if (!pair || a_mn || KIND != KIND_F16 || p.g.tiles_per_chunk <= 0 || M != p.g.W * p.g.tiles_per_chunk * 2 * BM || epi == EPI_ACC_F32)

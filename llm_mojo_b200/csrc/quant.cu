@@ -455,6 +455,59 @@ __global__ void __launch_bounds__(512) quantize_fp8_amax_kernel(uint8_t* __restr
 }
 }  // namespace
 
+// The same three steps for the operands of one linear layer with two tiny launches instead of two per operand plus the
+// host-side products of the inverse scales: `llmb_fp8_prepare` derives the scales of up to two states from their histories,
+// clears their amax words and writes up to two GEMM scale factors (products of inverse scales of states that are final by
+// then); `llmb_quantize_fp8_amax` is the pass over a tensor; `llmb_fp8_push` appends the amax words to the histories.
+namespace {
+__device__ void derive_scale(float* state, unsigned* amax_bits, float fmt_max, float margin_mult) {
+  const float* hist = state + 4;
+  float m = 0.f; bool bad = false;
+  for (int i = 0; i < AMAX_HISTORY; ++i) { float h = hist[i]; if (isnan(h) || isinf(h)) bad = true; else m = fmaxf(m, h); }
+  const float a = bad ? NAN : m;
+  const float scale = (a <= 0.f || isnan(a) || isinf(a)) ? 1.0f : (fmt_max * margin_mult) / a;
+  state[0] = scale; state[1] = 1.0f / scale;
+  *amax_bits = 0u;
+}
+__global__ void fp8_prepare_kernel(float* sa, unsigned* aa, float fa, float ma, float* sb, unsigned* ab, float fb, float mb,
+                                   float* alpha1, const float* p1, const float* q1, float* alpha2, const float* p2, const float* q2) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (sa) derive_scale(sa, aa, fa, ma);
+  if (sb) derive_scale(sb, ab, fb, mb);
+  if (alpha1) *alpha1 = p1[1] * q1[1];
+  if (alpha2) *alpha2 = p2[1] * q2[1];
+}
+__global__ void fp8_push_kernel(float* sa, const float* aa, float* sb, const float* ab) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (sa) { const int step = __float_as_int(sa[2]); sa[4 + step % AMAX_HISTORY] = *aa; sa[2] = __int_as_float(step + 1); }
+  if (sb) { const int step = __float_as_int(sb[2]); sb[4 + step % AMAX_HISTORY] = *ab; sb[2] = __int_as_float(step + 1); }
+}
+}  // namespace
+LLMB_API int llmb_fp8_prepare(float* sa, float* aa, float fa, float ma, float* sb, float* ab, float fb, float mb, float* alpha1,
+                              const float* p1, const float* q1, float* alpha2, const float* p2, const float* q2, cudaStream_t st) {
+  fp8_prepare_kernel<<<1, 32, 0, st>>>(sa, (unsigned*)aa, fa, ma, sb, (unsigned*)ab, fb, mb, alpha1, p1, q1, alpha2, p2, q2);
+  return (int)cudaGetLastError();
+}
+LLMB_API int llmb_fp8_push(float* sa, const float* aa, float* sb, const float* ab, cudaStream_t st) {
+  fp8_push_kernel<<<1, 32, 0, st>>>(sa, aa, sb, ab);
+  return (int)cudaGetLastError();
+}
+// out = fp8(x * state[0]) saturated and amax[0] = max(amax[0], max|x|) as raw bits (clear it first); n a multiple of the vector width
+LLMB_API int llmb_quantize_fp8_amax(void* out, const void* x, const float* state, float* amax, long long n, int fmt, int dtype,
+                                    cudaStream_t st) {
+  if (n % (dtype == LLMB_BF16 ? 8 : 4)) return LLMB_ERR_BAD_ARG;
+  long long blocks = ceil_div_ll(n, 512 * 8);
+  int grid = (int)(blocks < (long long)sm_count() * 4 ? (blocks < 1 ? 1 : blocks) : (long long)sm_count() * 4);
+  if (dtype == LLMB_BF16) {
+    if (fmt == 0) quantize_fp8_amax_kernel<__nv_bfloat16, 0><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const __nv_bfloat16*)x, state, n);
+    else quantize_fp8_amax_kernel<__nv_bfloat16, 1><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const __nv_bfloat16*)x, state, n);
+  } else {
+    if (fmt == 0) quantize_fp8_amax_kernel<float, 0><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const float*)x, state, n);
+    else quantize_fp8_amax_kernel<float, 1><<<grid, 512, 0, st>>>((uint8_t*)out, (unsigned*)amax, (const float*)x, state, n);
+  }
+  return (int)cudaGetLastError();
+}
+
 // One pass over x for a delayed-scaling operand whose history is full (the caller checks that: state[2] >= the history
 // length): state[0..1] = scale / 1/scale from the history, out = fp8(x * scale) saturated, amax[0] = max|x| (NaN-infectious),
 // then the amax is appended to the history.  n must be a multiple of the vector width (8 for bf16, 4 for fp32).

@@ -467,7 +467,7 @@ class GPT2:
             else:
                 gelu_out = a["fch_gelu"][l]
             # bf16 MLP: the fc bias gradient (column sums of dl4) is taken in the epilogue of the GEMM that writes dl4
-            fc_dbias_upstream = self._site_mode("fcproj", l) == "bf16" and self._site_mode("fc", l) == "bf16"
+            fc_dbias_upstream = self._site_mode("fcproj", l) == self._site_mode("fc", l) and self._site_mode("fc", l) in ("bf16", "fp8")
             kw = {"dinp_colsum": g["fcb"][l]} if fc_dbias_upstream else {}
             self._linear_bwd("fcproj", l, dl4, g["fcprojw"][l], None if ln_dbias_prev else g["fcprojb"][l], dres, gelu_out,
                              p["fcprojw"][l], gelu_pre=a["fch"][l], **kw)

@@ -123,6 +123,7 @@ class LinearSite:
         self.weight = AmaxState(device, E4M3)
         self.dout = AmaxState(device, E5M2)
         self.alpha = torch.ones(1, dtype=torch.float32, device=device)
+        self.alpha2 = torch.ones(1, dtype=torch.float32, device=device)
         # fp8 copies of the forward operands, kept for the backward pass of the same micro-step (1 byte per element of the
         # layer input and of the weight) so that it does not quantise them a second time; `LLMM_FP8_KEEP_OPERANDS=0` drops
         # them and re-quantises, as the reference does
@@ -211,6 +212,19 @@ def _q(name: str, x: torch.Tensor, state: AmaxState, buf: Optional[torch.Tensor]
     return buf
 
 
+def _delayed_ready(state: AmaxState, x: torch.Tensor) -> bool:
+    """True when ``x`` can be quantised for ``state`` by the single-pass kernel: history full, scale not frozen."""
+    vec = 8 if x.dtype == torch.bfloat16 else 4
+    return (FUSED_DELAYED and x.is_cuda and not state.static and state.host_step >= AMAX_HISTORY and x.is_contiguous()
+            and x.numel() % vec == 0 and x.dtype in (torch.bfloat16, torch.float32))
+
+
+def _quant_amax(buf: torch.Tensor, x: torch.Tensor, state: AmaxState) -> None:
+    check(lib().llmb_quantize_fp8_amax(ptr(buf), ptr(x), ptr(state.state), ptr(state.amax), x.numel(), state.fmt, dtype_code(x),
+                                       stream()), "quantize_fp8_amax")
+    _count()
+
+
 def matmul_fwd_fp8(out, inp, weight, bias, site: LinearSite, *, pre_gelu=None, residual=None) -> None:
     """out = deq(q(inp)·q(W)ᵀ) (+bias)(+GELU / +residual); ``llmm/matmul.mojo:1851-2035``."""
     OC, C = weight.shape
@@ -222,13 +236,28 @@ def matmul_fwd_fp8(out, inp, weight, bias, site: LinearSite, *, pre_gelu=None, r
             site.qx = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
         if site.qw is None or site.qw.shape != weight.shape:
             site.qw = torch.empty(weight.shape, dtype=torch.uint8, device=x.device)
-        qx = _q("x", x, site.inp, site.qx)
-        qw = _q("w", weight, site.weight, site.qw)
+        if _delayed_ready(site.inp, x) and _delayed_ready(site.weight, weight):
+            # both histories are full: one launch derives both scales and the GEMM's scale factor, one appends both amax values
+            si, sw = site.inp, site.weight
+            check(lib().llmb_fp8_prepare(ptr(si.state), ptr(si.amax), FMT_MAX[si.fmt], si.margin_mult, ptr(sw.state), ptr(sw.amax),
+                                         FMT_MAX[sw.fmt], sw.margin_mult, ptr(site.alpha), ptr(si.state), ptr(sw.state), None, None, None,
+                                         stream()), "fp8_prepare")
+            qx, qw = site.qx, site.qw
+            _quant_amax(qx, x, si)
+            _quant_amax(qw, weight, sw)
+            check(lib().llmb_fp8_push(ptr(si.state), ptr(si.amax), ptr(sw.state), ptr(sw.amax), stream()), "fp8_push")
+            _count(2)
+            si.host_step += 1
+            sw.host_step += 1
+        else:
+            qx = _q("x", x, site.inp, site.qx)
+            qw = _q("w", weight, site.weight, site.qw)
+            torch.mul(site.inp.scale_inv, site.weight.scale_inv, out=site.alpha)
         site.kept = (x.data_ptr(), x._version, weight.data_ptr(), weight._version)
     else:
         qx = _q("x", x, site.inp)
         qw = _q("w", weight, site.weight)
-    torch.mul(site.inp.scale_inv, site.weight.scale_inv, out=site.alpha)
+        torch.mul(site.inp.scale_inv, site.weight.scale_inv, out=site.alpha)
     o = out.view(rows, OC)
     if out.is_cuda:
         if pre_gelu is not None:
@@ -253,34 +282,59 @@ def _finish_fwd(o, y, bias, pre_gelu, residual, rows, OC):
     o.copy_(y)
 
 
-def matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, site: LinearSite, *, gelu_pre=None) -> None:
-    """dinp = deq(q5(dout)·q4(W)), dW += deq(q5(dout)ᵀ·q4(inp)); ``llmm/matmul.mojo:4146-4310``."""
+def matmul_bwd_fp8(dinp, dweight, dbias, dout, inp, weight, site: LinearSite, *, gelu_pre=None, dinp_colsum=None) -> None:
+    """dinp = deq(q5(dout)·q4(W)), dW += deq(q5(dout)ᵀ·q4(inp)); ``llmm/matmul.mojo:4146-4310``.  ``dinp_colsum`` (fp32 [C]) +=
+    column sums of dinp, i.e. the bias gradient of the layer below, taken in the dGELU epilogue where that kernel runs."""
     OC, C = weight.shape
     rows = inp.numel() // C
     d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
-    qd = _q("d", d, site.dout)
+    site_fused = _delayed_ready(site.dout, d)
+    if site_fused:
+        # the d_output scale from its history and both GEMM scale factors (the input / weight scales of this step are final)
+        sd = site.dout
+        check(lib().llmb_fp8_prepare(ptr(sd.state), ptr(sd.amax), FMT_MAX[sd.fmt], sd.margin_mult, None, None, 0.0, 0.0, ptr(site.alpha),
+                                     ptr(sd.state), ptr(site.weight.state), ptr(site.alpha2), ptr(sd.state), ptr(site.inp.state), stream()),
+              "fp8_prepare")
+        qd = scratch("fp8_d", d.numel(), d.device)[:d.numel()].view(d.shape)
+        _quant_amax(qd, d, sd)
+        check(lib().llmb_fp8_push(ptr(sd.state), ptr(sd.amax), None, None, stream()), "fp8_push")
+        _count(2)
+        sd.host_step += 1
+    else:
+        qd = _q("d", d, site.dout)
     if dinp is not None:
         if site.kept is not None and site.kept[2:] == (weight.data_ptr(), weight._version) and site.qw.shape == weight.shape:
             qw = site.qw                                                # the forward pass's bytes (same scale, same weight)
         else:
             qw = scratch("fp8_w", weight.numel(), weight.device)[:weight.numel()].view(weight.shape)
             quantize_fp8(qw, weight, site.weight.scale, E4M3)           # same scale as the forward pass of this step
-        torch.mul(site.dout.scale_inv, site.weight.scale_inv, out=site.alpha)
+        if not site_fused:
+            torch.mul(site.dout.scale_inv, site.weight.scale_inv, out=site.alpha)
         di = dinp.view(rows, C)
         if dout.is_cuda:
-            gemm(di, qd, qw, b_mn=True, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE,
-                 aux=gelu_pre.view(rows, C) if gelu_pre is not None else None, alpha=site.alpha, kind=2, a_fmt=E5M2, b_fmt=E4M3)
+            from . import colsum_usable, dbias_reduce as _dbias_reduce
+            aux = gelu_pre.view(rows, C) if gelu_pre is not None else None
+            fused = dinp_colsum is not None and aux is not None and colsum_usable(di, aux)
+            gemm(di, qd, qw, b_mn=True, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE, aux=aux, alpha=site.alpha, kind=2,
+                 a_fmt=E5M2, b_fmt=E4M3, colsum=dinp_colsum if fused else None)
+            if dinp_colsum is not None and not fused:
+                _dbias_reduce(dinp_colsum, di)
         else:
             g = dequantize_fp8(qd, site.dout.scale_inv, E5M2) @ dequantize_fp8(qw, site.weight.scale_inv, E4M3)
             if gelu_pre is not None:
                 g = g * _gelu_grad_t(gelu_pre.view(rows, C).float())
             di.copy_(g)
+            if dinp_colsum is not None:
+                dinp_colsum += di.float().sum(0)
     if site.kept is not None and site.kept[:2] == (x.data_ptr(), x._version) and site.qx.shape == x.shape:
         qx = site.qx
     else:
         qx = scratch("fp8_x", x.numel(), x.device)[:x.numel()].view(x.shape)
         quantize_fp8(qx, x, site.inp.scale, E4M3)
-    alpha2 = site.dout.scale_inv * site.inp.scale_inv
+    if site_fused:
+        alpha2 = site.alpha2
+    else:
+        alpha2 = site.dout.scale_inv * site.inp.scale_inv
     if dout.is_cuda:
         gemm(dweight.view(OC, C), qd, qx, a_mn=True, b_mn=True, epi=EPI_ACC_F32, splits=_splits_for(OC, C, rows), alpha=alpha2,
              kind=2, a_fmt=E5M2, b_fmt=E4M3)

@@ -224,6 +224,35 @@ def test_single_pass_delayed_quantisation_matches_two_passes(fmt, monkeypatch):
 
 
 @gpu
+def test_fp8_linear_site_fast_path_matches_reference_order(monkeypatch):
+    """A linear layer in fp8 for more steps than the amax history holds: the fast path (scales of input and weight derived in one
+    launch, single-pass quantisation, forward bytes kept for the backward GEMMs, fc bias gradient in the dGELU epilogue) against the
+    plain order (amax pass, scale update, quantise pass per operand and per use).  Outputs, input gradients, weight gradients and
+    the scaling states must be equal at every step."""
+    rows, C, OC = 512, 256, 1024
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(OC, C, generator=g) * 0.05).bfloat16().cuda()
+    b = torch.randn(OC, generator=g).bfloat16().cuda()
+    fast, ref = lowp.LinearSite("cuda"), lowp.LinearSite("cuda")
+    for step in range(lowp.AMAX_HISTORY + 6):
+        x = (torch.randn(rows, C, generator=g) * (0.5 + step % 5)).bfloat16().cuda()
+        dy = (torch.randn(rows, OC, generator=g) * 10.0 ** (step % 3 - 2)).bfloat16().cuda()
+        res = {}
+        for name, site, on in (("fast", fast, True), ("ref", ref, False)):
+            monkeypatch.setattr(lowp, "FUSED_DELAYED", on)
+            monkeypatch.setattr(lowp, "KEEP_OPERANDS", on)
+            out, pre = torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda"), torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda")
+            lowp.matmul_fwd_fp8(out, x, w, b, site, pre_gelu=pre)
+            dx, dw, db = torch.empty_like(x), torch.zeros(OC, C, device="cuda"), torch.zeros(OC, device="cuda")
+            lowp.matmul_bwd_fp8(dx, dw, db, dy, x, w, site)
+            torch.cuda.synchronize()
+            res[name] = (out, pre, dx, dw, db, site.inp.state.clone(), site.weight.state.clone(), site.dout.state.clone())
+        for a, r in zip(res["fast"], res["ref"]):
+            assert torch.equal(a, r), step
+    assert fast.inp.host_step == ref.inp.host_step == lowp.AMAX_HISTORY + 6
+
+
+@gpu
 @pytest.mark.parametrize("axis,block_rows,rht", [(1, 1, False), (1, 16, False), (0, 1, False), (0, 1, True), (0, 16, False)])
 def test_nvfp4_kernel_matches_emulation(axis, block_rows, rht):
     x = torch.randn(256, 384).bfloat16()
