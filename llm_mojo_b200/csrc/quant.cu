@@ -806,6 +806,80 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(uint8_t* __restric
     *reinterpret_cast<uint32_t*>(sf + atom * 512 + (t & 31) * 16 + (t >> 5) * 4) = e * 0x01010101u;
   }
 }
+// Both orientations of one operand from ONE read of the tile: q0 / sf0 as <FMT, 0, 0> writes them (1 x 128 blocks, bytes
+// [rows, cols]: the operand of a product contracted over the columns) and q1 / sf1 as <FMT, 1, 1> does (128 x 1 blocks, bytes
+// transposed [cols, rows]: the operand of a product contracted over the rows).  A layer input needs the first in the forward
+// pass and the second for its weight gradient, an output gradient needs the first for dinp and the second for dW.
+template <int FMT>
+__global__ void __launch_bounds__(256) fp8_block_quant_dual_kernel(uint8_t* __restrict__ q0, uint8_t* __restrict__ sf0, uint8_t* __restrict__ q1,
+                                                                   uint8_t* __restrict__ sf1, const __nv_bfloat16* __restrict__ x, int rows, int cols) {
+  __shared__ float red[16][128];                          // partial column maxima
+  __shared__ float row_scale[128], col_scale[128];
+  __shared__ __align__(16) uint8_t tile[128 * 128];       // transposed bytes, 8-byte chunks XOR-swizzled by line / 8
+  const int tiles_c = cols / 128;
+  const int tr = blockIdx.x / tiles_c, tc = blockIdx.x % tiles_c;
+  const int t = threadIdx.x, g = t >> 4, l = t & 15;      // g: row group (rows 8 g + i), l: 8-column slot
+  const __nv_bfloat16* src = x + (long long)tr * 128 * cols + tc * 128;
+  const float fmax = FMT == 0 ? 448.0f : 57344.0f;
+  Pack<__nv_bfloat16> p[8];
+  float rmax[8];
+  float cmax[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    p[i].load(src + (long long)(8 * g + i) * cols + l * 8);
+    rmax[i] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { const float a = fabsf(p[i].v[k]); rmax[i] = fmaxf(rmax[i], a); cmax[k] = fmaxf(cmax[k], a); }
+  }
+  float s_row[8], s_col[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) rmax[i] = fmaxf(rmax[i], __shfl_xor_sync(0xffffffffu, rmax[i], o, 16));
+    s_row[i] = pow2_scale(rmax[i], fmax);
+    if (l == 0) row_scale[8 * g + i] = s_row[i];
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[g][l * 8 + k] = cmax[k];
+  __syncthreads();
+  if (t < 128) {
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) m = fmaxf(m, red[j][t]);
+    col_scale[t] = pow2_scale(m, fmax);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s_col[k] = col_scale[l * 8 + k];
+  uint8_t bt[8][8];                                      // [column slot k][row i]: the transposed 8 x 8 block of this thread
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint8_t b[8];
+    const float inv_r = 1.0f / s_row[i];                  // powers of two: exact
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      b[k] = (uint8_t)__nv_cvt_float_to_fp8(p[i].v[k] * inv_r, __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+      bt[k][i] = (uint8_t)__nv_cvt_float_to_fp8(p[i].v[k] * (1.0f / s_col[k]), __NV_SATFINITE, FMT == 0 ? __NV_E4M3 : __NV_E5M2);
+    }
+    *reinterpret_cast<uint2*>(q0 + (long long)(tr * 128 + 8 * g + i) * cols + tc * 128 + l * 8) = *reinterpret_cast<uint2*>(b);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    *reinterpret_cast<uint2*>(&tile[(l * 8 + k) * 128 + ((g ^ l) << 3)]) = *reinterpret_cast<uint2*>(bt[k]);
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {                           // 128 lines of 128 bytes = 1024 pieces of 16 bytes
+    const int ch = t + j * 256, c = ch >> 3, part = ch & 7, ls = c >> 3;
+    uint4 v = *reinterpret_cast<const uint4*>(&tile[c * 128 + ((part ^ (ls >> 1)) << 4)]);
+    if (ls & 1) v = make_uint4(v.z, v.w, v.x, v.y);       // odd swizzle: the two chunks of the pair are exchanged
+    *reinterpret_cast<uint4*>(q1 + (long long)(tc * 128 + c) * rows + tr * 128 + part * 16) = v;
+  }
+  if (t < 128) {
+    const uint32_t er = (__float_as_uint(row_scale[t]) >> 23) & 0xffu, ec = (__float_as_uint(col_scale[t]) >> 23) & 0xffu;
+    *reinterpret_cast<uint32_t*>(sf0 + ((long long)tr * tiles_c + tc) * 512 + (t & 31) * 16 + (t >> 5) * 4) = er * 0x01010101u;
+    *reinterpret_cast<uint32_t*>(sf1 + ((long long)tc * (rows / 128) + tr) * 512 + (t & 31) * 16 + (t >> 5) * 4) = ec * 0x01010101u;
+  }
+}
 }  // namespace
 // mode 0: 1 x 128 blocks along axis 1 (cols % 128 == 0); mode 1: 128 x 1 blocks along axis 0 (rows % 128 == 0, cols % 8 == 0);
 // mode 2: 128 x 128 blocks (both % 128 == 0).  fmt 0 = e4m3, 1 = e5m2.  x and out are contiguous [rows, cols] bf16.
@@ -843,6 +917,15 @@ LLMB_API int llmb_fp8_block_quant(void* q, void* sf, const void* x, int rows, in
   else if (gran == 2 && transpose) { if (fmt == 0) FP8Q(0, 2, 1); else FP8Q(1, 2, 1); }
   else return LLMB_ERR_BAD_ARG;
 #undef FP8Q
+  return (int)cudaGetLastError();
+}
+
+// Both at once from one read of x: (q0, sf0) = llmb_fp8_block_quant(gran 0) and (q1, sf1) = llmb_fp8_block_quant(gran 1, transpose).
+LLMB_API int llmb_fp8_block_quant_dual(void* q0, void* sf0, void* q1, void* sf1, const void* x, int rows, int cols, int fmt, cudaStream_t st) {
+  if (rows % 128 || cols % 128 || fmt < 0 || fmt > 1) return LLMB_ERR_BAD_ARG;
+  const unsigned grid = (unsigned)((rows / 128) * (cols / 128));
+  if (fmt == 0) fp8_block_quant_dual_kernel<0><<<grid, 256, 0, st>>>((uint8_t*)q0, (uint8_t*)sf0, (uint8_t*)q1, (uint8_t*)sf1, (const __nv_bfloat16*)x, rows, cols);
+  else fp8_block_quant_dual_kernel<1><<<grid, 256, 0, st>>>((uint8_t*)q0, (uint8_t*)sf0, (uint8_t*)q1, (uint8_t*)sf1, (const __nv_bfloat16*)x, rows, cols);
   return (int)cudaGetLastError();
 }
 

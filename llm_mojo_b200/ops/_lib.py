@@ -63,6 +63,7 @@ _SIGS = {
     "llmb_amax_update": [c_p, c_p, c_f, c_f, c_p],
     "llmb_quantize_fp8": [c_p, c_p, c_p, c_ll, c_int, c_int, c_p],
     "llmb_quantize_fp8_delayed": [c_p, c_p, c_p, c_p, c_ll, c_int, c_f, c_f, c_int, c_p],
+    "llmb_fp8_block_quant_dual": [c_p, c_p, c_p, c_p, c_p, c_int, c_int, c_int, c_p],
     "llmb_fp8_prepare": [c_p, c_p, c_f, c_f, c_p, c_p, c_f, c_f, c_p, c_p, c_p, c_p, c_p, c_p, c_p],
     "llmb_fp8_push": [c_p, c_p, c_p, c_p, c_p],
     "llmb_quantize_fp8_amax": [c_p, c_p, c_p, c_p, c_ll, c_int, c_int, c_p],

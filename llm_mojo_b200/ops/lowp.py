@@ -594,6 +594,25 @@ def fp8_block_quant(x: torch.Tensor, gran: int, fmt: int = E4M3, transpose: bool
     return q, sf
 
 
+def fp8_block_quant_dual(x: torch.Tensor, fmt: int = E4M3) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """GPU only: both orientations from one read of ``x`` [rows, cols]: ``(q0, s0)`` = ``fp8_block_quant(x, 0)`` (1×128 blocks,
+    for a product contracted over the columns) and ``(q1, s1)`` = ``fp8_block_quant(x, 1, transpose=True)`` (128×1 blocks,
+    bytes [cols, rows], for a product contracted over the rows)."""
+    rows, cols = x.shape
+    q0 = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    q1 = torch.empty((cols, rows), dtype=torch.uint8, device=x.device)
+    nsf = (rows // 128) * (cols // 128) * 512
+    s0, s1 = (torch.empty(nsf, dtype=torch.uint8, device=x.device) for _ in range(2))
+    check(lib().llmb_fp8_block_quant_dual(ptr(q0), ptr(s0), ptr(q1), ptr(s1), ptr(x.contiguous()), rows, cols, fmt, stream()),
+          "fp8_block_quant_dual")
+    _count()
+    return q0, s0, q1, s1
+
+
+FP8B_DUAL = os.environ.get("LLMM_FP8B_DUAL_QUANT", "1") != "0"
+_FP8B_KEPT: Dict[Tuple[int, Tuple[int, ...]], Tuple[torch.Tensor, torch.Tensor]] = {}   # (input pointer, shape) -> its 128×1 bytes and scales
+
+
 def fp8_block_native() -> bool:
     """Block-scaled FP8 products on the MXFP8 tensor path (default on a GPU); ``LLMM_FP8B_NATIVE=0`` runs them on the
     bf16 path over fake-quantised operands (same numerics, the path the tests compare against)."""
@@ -609,7 +628,13 @@ def matmul_fwd_fp8_block(out, inp, weight, bias, *, pre_gelu=None, residual=None
     if not fp8_block_usable(rows, C, OC):
         return ops_matmul_fwd(out, inp, weight, bias, pre_gelu=pre_gelu, residual=residual)
     if out.is_cuda and inp.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and fp8_block_native():
-        qx, sx = fp8_block_quant(inp.reshape(rows, C), 0, E4M3)
+        x2 = inp.reshape(rows, C)
+        if FP8B_DUAL:
+            # the 128×1 orientation the weight gradient will need comes out of the same read and is kept until the backward pass
+            qx, sx, qxt, sxt = fp8_block_quant_dual(x2, E4M3)
+            _FP8B_KEPT[(x2.data_ptr(), tuple(x2.shape))] = (qxt, sxt)
+        else:
+            qx, sx = fp8_block_quant(x2, 0, E4M3)
         qw, sw = fp8_block_quant(weight, 2, E4M3)
         o = out.view(rows, OC)
         if pre_gelu is not None:
@@ -634,13 +659,24 @@ def matmul_bwd_fp8_block(dinp, dweight, dbias, dout, inp, weight, *, gelu_pre=No
     d, x = dout.reshape(rows, OC), inp.reshape(rows, C)
     if dout.is_cuda and dout.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and inp.dtype == torch.bfloat16 and fp8_block_native():
         # operands of a product contracted over the rows (or over OC for the weight) are written transposed: all K-major
+        qdt = None
         if dinp is not None:
-            qd, sd = fp8_block_quant(d, 0, E5M2)
+            if FP8B_DUAL:
+                qd, sd, qdt, sdt = fp8_block_quant_dual(d, E5M2)      # both orientations of the output gradient from one read
+            else:
+                qd, sd = fp8_block_quant(d, 0, E5M2)
             qw, sw = fp8_block_quant(weight, 2, E4M3, transpose=True)
             gemm_mxfp8(dinp.view(rows, C), qd, sd, qw, sw, a_fmt=E5M2, b_fmt=E4M3, epi=EPI_DGELU if gelu_pre is not None else EPI_NONE,
                        aux=gelu_pre.view(rows, C) if gelu_pre is not None else None)
-        qd, sd = fp8_block_quant(d, 1, E5M2, transpose=True)
-        qx, sx = fp8_block_quant(x, 1, E4M3, transpose=True)
+        if qdt is not None:
+            qd, sd = qdt, sdt
+        else:
+            qd, sd = fp8_block_quant(d, 1, E5M2, transpose=True)
+        kept = _FP8B_KEPT.pop((x.data_ptr(), tuple(x.shape)), None) if FP8B_DUAL else None
+        if kept is not None:
+            qx, sx = kept                                           # made in the forward pass of this micro-step from the same tensor
+        else:
+            qx, sx = fp8_block_quant(x, 1, E4M3, transpose=True)
         gemm_mxfp8(dweight.view(OC, C), qd, sd, qx, sx, a_fmt=E5M2, b_fmt=E4M3, epi=EPI_ACC_F32,
                    splits=_splits_for(OC, C, rows, tile=128, tile_n=256, bk=128, units=148))
         if dbias is not None:

@@ -4,7 +4,7 @@
 Parity: ``profile_gpt2.mojo:61-181`` (synthetic tokens ``i % V``, phase wall times, optional
 Chrome/Perfetto trace) and ``profile_gpt2.py:42-70`` (kernel-family buckets for an ``ncu`` run).
 Environment: LLMM_PROFILE_B, LLMM_PROFILE_T, LLMM_PROFILE_LAYERS, LLMM_PROFILE_STEPS,
-LLMM_PROFILE_TRACE (file), LLMM_PROFILE_MODEL (descriptor, default d12).
+LLMM_PROFILE_TRACE (file), LLMM_PROFILE_MODEL (descriptor, default d12), LLMM_PROFILE_PRECISION (bf16 | fp8 | fp8b | fp4).
 
 Phases are timed with CUDA events on the launching stream (wall clock on CPU).  The printed
 `forward / backward / update` seconds line is the one benchmark scripts parse.
@@ -91,7 +91,7 @@ def run_profile() -> dict:
         cfg.num_layer = int(os.environ["LLMM_PROFILE_LAYERS"])
     dev = torch.device("cuda" if torch.cuda.is_available() and not os.environ.get("LLMM_USE_CPU") else "cpu")
     T = min(T, cfg.max_seq_len)
-    model = GPT2(cfg, "bf16" if dev.type == "cuda" else "fp32", dev)
+    model = GPT2(cfg, os.environ.get("LLMM_PROFILE_PRECISION", "bf16") if dev.type == "cuda" else "fp32", dev)
     toks = (torch.arange(B * T + 1) % cfg.vocab_size).to(torch.int32)
     x, y = toks[:-1].view(B, T).contiguous(), toks[1:].view(B, T).contiguous()
     tracer = TraceProfiler(os.environ.get("LLMM_PROFILE_TRACE", ""))

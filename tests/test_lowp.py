@@ -224,6 +224,39 @@ def test_single_pass_delayed_quantisation_matches_two_passes(fmt, monkeypatch):
 
 
 @gpu
+@pytest.mark.parametrize("fmt", [lowp.E4M3, lowp.E5M2])
+def test_fp8_block_dual_quantisation_equals_the_two_single_kernels(fmt):
+    rows, cols = 384, 640
+    x = (torch.randn(rows, cols) * torch.logspace(-3, 3, cols)).bfloat16().cuda()
+    q0, s0, q1, s1 = lowp.fp8_block_quant_dual(x, fmt)
+    r0, t0 = lowp.fp8_block_quant(x, 0, fmt)
+    r1, t1 = lowp.fp8_block_quant(x, 1, fmt, transpose=True)
+    torch.cuda.synchronize()
+    assert torch.equal(q0, r0) and torch.equal(s0, t0) and torch.equal(q1, r1) and torch.equal(s1, t1)
+
+
+@gpu
+def test_fp8_block_linear_dual_path_is_bit_identical(monkeypatch):
+    rows, C, OC = 256, 384, 512
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(rows, C, generator=g).bfloat16().cuda()
+    w = (torch.randn(OC, C, generator=g) * 0.05).bfloat16().cuda()
+    b = torch.randn(OC, generator=g).bfloat16().cuda()
+    dy = torch.randn(rows, OC, generator=g).bfloat16().cuda()
+    res = {}
+    for on in (True, False):
+        monkeypatch.setattr(lowp, "FP8B_DUAL", on)
+        out = torch.empty(rows, OC, dtype=torch.bfloat16, device="cuda")
+        lowp.matmul_fwd_fp8_block(out, x, w, b)
+        dx, dw, db = torch.empty_like(x), torch.zeros(OC, C, device="cuda"), torch.zeros(OC, device="cuda")
+        lowp.matmul_bwd_fp8_block(dx, dw, db, dy, x, w)
+        torch.cuda.synchronize()
+        res[on] = (out, dx, dw, db)
+    for a, r in zip(res[True], res[False]):
+        assert torch.equal(a, r)
+
+
+@gpu
 def test_fp8_linear_site_fast_path_matches_reference_order(monkeypatch):
     """A linear layer in fp8 for more steps than the amax history holds: the fast path (scales of input and weight derived in one
     launch, single-pass quantisation, forward bytes kept for the backward GEMMs, fc bias gradient in the dGELU epilogue) against the
